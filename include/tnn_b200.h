@@ -1,0 +1,206 @@
+/*
+ * tnn_b200 — C ABI of the B200 (sm_100a) kernels behind TNN's transformer-encoder attention path.
+ *
+ * Who calls this: the DEVICE_CUDA layer accs of the TNN plug-in (tnn_b200/tnn_plugin), one launcher per fused layer,
+ * from `Init/Reshape/Forward`; and the Python/ctypes host mirror used by the tests and the benchmark.  Nothing here
+ * takes a framework type: plain pointers, sizes and POD descriptor structs only.
+ *
+ * Conventions
+ *   - every launcher enqueues on the given stream and returns immediately: no allocation, no synchronisation, no exit();
+ *   - return value 0 = B200_OK, negative = error (b200_status_string() names it); the accs map it to a TNN `Status`
+ *     (TNNERR_PARAM_ERR / TNNERR_CUDA_KERNEL_LAUNCH_ERROR, include/tnn/core/status.h:29-144) instead of the
+ *     reference's abort-on-error CUDA_CHECK (source/tnn/device/cuda/cuda_macro.h:24-40);
+ *   - device pointers are `(char*)BlobHandle.base + BlobHandle.bytes_offset` (include/tnn/core/blob.h:32-50);
+ *   - activations are row-major `[tokens, features]` (a TNN blob `[B,S,H]` flattened over B and S);
+ *   - kernels never spin unboundedly: a wait that runs out sets a bit in a per-device status word, the CTA tears
+ *     down cleanly and b200_device_status() reports it after the stream is synchronised.
+ */
+#ifndef TNN_B200_H_
+#define TNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200_API
+#else
+#define B200_API __attribute__((visibility("default")))
+#endif
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer so that this header needs no CUDA header. */
+typedef void* b200_stream_t;
+
+enum {
+    B200_OK                   = 0,
+    B200_ERR_PARAM            = -1, /* null pointer, bad dtype, misaligned pointer or leading dimension            */
+    B200_ERR_UNSUPPORTED      = -2, /* shape outside what the kernel handles (stated per entry point)              */
+    B200_ERR_LAUNCH           = -3, /* cudaLaunch / cudaGetLastError reported an error                            */
+    B200_ERR_DRIVER           = -4, /* tensor-map encode entry point missing or it refused the descriptor          */
+    B200_ERR_DEVICE_TIMEOUT   = -5, /* reported by b200_device_status(): a bounded device-side wait ran out        */
+    B200_ERR_NOT_SM100        = -6  /* the current device is not compute capability 10.x                           */
+};
+
+enum { B200_F16 = 0, B200_BF16 = 1, B200_F32 = 2 };
+
+/* Epilogue of the projection GEMM; replaces the Add / GELU / Add layers that follow MatMul in the unfused graph. */
+enum {
+    B200_EPI_BIAS          = 0, /* y = x.W + b                       MatMul -> Add(bias)                              */
+    B200_EPI_BIAS_GELU     = 1, /* y = gelu_erf(x.W + b)             MatMul -> Add(bias) -> GELU                      */
+    B200_EPI_BIAS_RESIDUAL = 2  /* y = x.W + b + r                   MatMul -> Add(bias) -> Add(residual)             */
+};
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * Weight pre-pack.  Replaces nothing in the reference's hot loop: TNN keeps MatMul weights as an fp32 `[K,N]`
+ * RawBuffer (source/tnn/interpreter/layer_resource.h:165-169, y = x.W) and the x86 acc re-packs them on every call
+ * (source/tnn/device/x86/acc/compute/jit/conv_sgemm_driver.cc:128-133); here it is done once at Init.
+ * Reads fp32 `w_kn[K, N]` (row stride ld_src elements) and writes `dtype` `w_nk[N, K]` (row stride ld_dst elements),
+ * i.e. transposed so that K is contiguous, rounding to nearest even.  Both pointers are device pointers.
+ * To concatenate Q/K/V weights into one `[3H, K]` operand, call three times with dst offset by rows.
+ */
+B200_API int b200_pack_weight(const float* w_kn, int64_t K, int64_t N, int64_t ld_src, void* w_nk, int64_t ld_dst,
+                              int dtype, b200_stream_t stream);
+
+/* Element-wise dtype conversion of `n` contiguous elements (the fp32 <-> fp16/bf16 boundary of the fused region:
+ * DefaultNetwork keeps every CUDA blob fp32, source/tnn/core/blob_manager.cc:101-117).  n*sizeof must keep both
+ * pointers 16-byte aligned at their start. */
+B200_API int b200_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * Projection / FFN GEMM with fused epilogue:  y[M,N] = epilogue(x[M,K] . w_nk[N,K]^T + bias[N] (+ residual[M,N])).
+ * Replaces MatMulLayer (+ X86MatMulLayerAcc::DoForward, source/tnn/device/x86/acc/x86_mat_mul_layer_acc.cc:49-114;
+ * the reference's CUDA MatMul acc is a batched GEMV only, source/tnn/device/cuda/acc/cuda_mat_mul_layer_acc.cu:181-249)
+ * followed by the bias Add (source/tnn/device/x86/acc/x86_add_layer_acc.cc:66-92), and optionally GELU
+ * (source/tnn/device/x86/acc/x86_gelu_layer_acc.cc:22-62, erf form) or the residual Add.
+ * tcgen05 UMMA 128 x BN x 16 (fp32 accumulation in TMEM), operands by TMA into 128-byte-swizzled shared memory.
+ *   x, w_nk, residual : `dtype` (B200_F16 or B200_BF16); y : `out_dtype` (F16, BF16 or F32); bias : fp32 or NULL.
+ *   Requirements: K % 8 == 0, ldx % 8 == 0, ldw % 8 == 0, x and w_nk 16-byte aligned; y/residual rows 16-byte aligned
+ *   (N % 8 == 0, ldy % 8 == 0, ldr % 8 == 0).  M, N, K > 0 otherwise arbitrary (edge tiles are zero-filled/guarded).
+ *   block_n: 0 = choose, else 64, 128 or 256.
+ */
+typedef struct B200LinearDesc {
+    const void*  x;
+    const void*  w_nk;
+    const float* bias;
+    const void*  residual;
+    void*        y;
+    int64_t      M, N, K;
+    int64_t      ldx, ldw, ldr, ldy;
+    int32_t      dtype;
+    int32_t      out_dtype;
+    int32_t      epilogue;
+    int32_t      block_n;
+} B200LinearDesc;
+B200_API int b200_linear_fwd(const B200LinearDesc* desc, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * Fused multi-head attention:  out[b, q, h*D:(h+1)*D] = softmax_k(scale * Q_bh[q].K_bh[k] + mask_add[b,k]) . V_bh.
+ * Replaces the unfused chain Reshape -> Permute -> MatMul(QK^T) -> Mul(scale) -> Add(mask) -> Softmax(axis 3) ->
+ * MatMul(PV) -> Permute -> Reshape (source/tnn/layer/reshape_layer.cc:40-91, source/tnn/layer/permute_layer.cc:28-63,
+ * source/tnn/device/x86/acc/x86_softmax_layer_acc.cc:28-83, source/tnn/device/x86/acc/x86_binary_op_layer_acc.cc:536-805).
+ * The head split/merge is done by TMA coordinates; no [B,h,S,S] tensor ever reaches HBM.
+ *   q, k, v : `dtype` (F16/BF16), token-major `[B, S, ld*]` with head h at columns h*64 .. h*64+63 (so a packed QKV
+ *             activation `[B,S,3H]` is passed as q = base, k = base + H, v = base + 2H, ldq = ldk = ldv = 3H);
+ *   mask_add: fp32 `[B, S]` additive key mask (0 valid, -10000 padded — TNN feeds it as a `[B,1,1,S]` blob) or NULL.
+ *             A key whose mask value is <= mask_exclude_below gets weight exactly 0 (it is dropped, not merely
+ *             down-weighted); other values are added to the scaled score.  A sequence with no key above the
+ *             threshold is computed with purely additive semantics (what the reference's softmax yields then).
+ *   kv_len  : int32 `[B]` = 1 + index of the last non-excluded key (from b200_mask_to_kv_len) or NULL (= S): whole
+ *             key tiles at or beyond it are skipped.  Keys below kv_len are still tested one by one, so a mask with
+ *             holes is exact.  When mask_add is given without kv_len, a sequence whose keys are all excluded yields
+ *             zero rows (the additive fallback above needs kv_len to know about it).
+ *   out     : `dtype` `[B, S, ldo]`.  Rows of padded queries are computed like any other row (as the reference does).
+ *   Requirements: head_dim == 64; ld* % 8 == 0; pointers 16-byte aligned; S >= 1.
+ */
+typedef struct B200AttentionDesc {
+    const void*    q;
+    const void*    k;
+    const void*    v;
+    const float*   mask_add;
+    const int32_t* kv_len;
+    void*          out;
+    int64_t        B, S;
+    int64_t        ldq, ldk, ldv, ldo;
+    int32_t        heads;
+    int32_t        head_dim;
+    int32_t        dtype;
+    float          scale;
+    float          mask_exclude_below;
+} B200AttentionDesc;
+B200_API int b200_attention_fwd(const B200AttentionDesc* desc, b200_stream_t stream);
+
+/* kv_len[b] = 1 + max{k : mask_add[b,k] > exclude_below}, 0 if there is none.  The mask is a run-time input of the
+ * graph, so this runs on the device once per Forward. */
+B200_API int b200_mask_to_kv_len(const float* mask_add, int64_t B, int64_t S, float exclude_below, int32_t* kv_len,
+                                 b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * (residual +) LayerNorm over the last dimension:  y = (x (+ r) - mean) * rsqrt(var + eps) * gamma + beta.
+ * Replaces Add(residual) + LayerNorm (source/tnn/device/x86/acc/x86_layer_norm_layer_acc.cc:26-86; gamma and beta are
+ * the layer's input blobs 1 and 2, source/tnn/layer/layer_norm_layer.cc:28-30).  One warp per row, fp32 statistics,
+ * variance as the mean of squared deviations (the reference's one-pass E[x^2]-mean^2 agrees to fp32 rounding).
+ *   x, residual : in_dtype (F16/BF16/F32), residual may be NULL;  y : out_dtype;  gamma, beta : fp32 [H].
+ *   Requirements: H % 8 == 0, H <= 4096, leading dimensions % 8 == 0, 16-byte aligned pointers.
+ */
+typedef struct B200LayerNormDesc {
+    const void*  x;
+    const void*  residual;
+    const float* gamma;
+    const float* beta;
+    void*        y;
+    int64_t      rows, H;
+    int64_t      ldx, ldr, ldy;
+    int32_t      in_dtype;
+    int32_t      out_dtype;
+    float        eps;
+} B200LayerNormDesc;
+B200_API int b200_add_layernorm_fwd(const B200LayerNormDesc* desc, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * One post-LN transformer-encoder layer (the fused form of the ~30 TNN layers of one BERT layer) and a whole encoder
+ * stack, as a fixed sequence of the launchers above.  All buffers are the caller's.
+ *   hidden  : `dtype` [tokens, H]   in/out (layer input, overwritten with the layer output)
+ *   w_qkv   : [3H, H] packed, b_qkv fp32 [3H];  w_o : [H, H];  w_ffn1 : [F, H];  w_ffn2 : [H, F]  (all `[N,K]` packed)
+ *   workspace: b200_encoder_workspace_bytes(tokens, H, F, dtype) bytes, 256-byte aligned.
+ */
+typedef struct B200EncoderLayerWeights {
+    const void*  w_qkv;  const float* b_qkv;
+    const void*  w_o;    const float* b_o;
+    const float* ln1_gamma; const float* ln1_beta;
+    const void*  w_ffn1; const float* b_ffn1;
+    const void*  w_ffn2; const float* b_ffn2;
+    const float* ln2_gamma; const float* ln2_beta;
+} B200EncoderLayerWeights;
+
+typedef struct B200EncoderDesc {
+    void*                          hidden;
+    const float*                   mask_add;   /* [B,S] or NULL */
+    const int32_t*                 kv_len;     /* [B] or NULL   */
+    const B200EncoderLayerWeights* layers;     /* host array of num_layers entries */
+    void*                          workspace;
+    int64_t                        B, S, H, F;
+    int32_t                        heads;
+    int32_t                        num_layers;
+    int32_t                        dtype;
+    float                          ln_eps;
+    float                          mask_exclude_below;
+} B200EncoderDesc;
+B200_API size_t b200_encoder_workspace_bytes(int64_t tokens, int64_t H, int64_t F, int dtype);
+B200_API int    b200_encoder_fwd(const B200EncoderDesc* desc, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
+ * Housekeeping. */
+B200_API const char* b200_status_string(int status);
+/* Reads and clears the current device's status word (synchronous, small).  0 or B200_ERR_DEVICE_TIMEOUT. */
+B200_API int         b200_device_status(void);
+/* Number of kernel launches issued by this library in this process (all devices, all threads). */
+B200_API uint64_t    b200_launch_count(void);
+B200_API const char* b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TNN_B200_H_ */

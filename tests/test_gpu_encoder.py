@@ -1,0 +1,74 @@
+"""GPU: the fused encoder through the C ABI against (a) outputs of the reference's DEVICE_X86 committed under
+tests/golden and (b) the CPU oracle, at the benchmark's tolerances."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bert_oracle
+from oracle.make_golden import CASES, GOLDEN, golden_workload
+from tnn_b200 import capi, model_synth
+from tnn_b200.encoder import Encoder
+from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(wl, dtype, single_call=True):
+    enc = Encoder.from_workload(wl, dtype)
+    x = torch.from_numpy(wl.x).cuda()
+    m = torch.from_numpy(wl.mask_add).cuda()
+    y = enc.forward(x, m) if single_call else enc.forward_ops(x, m)
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.OK
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_against_reference_x86_fixture(cuda_device, name, dtype):
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    wl = golden_workload(**CASES[name])
+    y = _run(wl, dtype)
+    ref = g["x86"]
+    # full tensor: padded query rows are computed like any other row, as the reference does
+    tol = MAX_ABS_TOL if dtype == torch.float16 else 4 * MAX_ABS_TOL   # bf16 carries 3 fewer mantissa bits
+    assert max_abs(y, ref) <= tol
+    assert cosine(y, ref) >= (COS_TOL if dtype == torch.float16 else 0.999)
+    assert max_abs(valid_rows(y, wl.lengths), valid_rows(ref, wl.lengths)) <= tol
+
+
+def test_single_call_equals_layer_by_layer(cuda_device):
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    a = _run(wl, torch.float16, single_call=True)
+    b = _run(wl, torch.float16, single_call=False)
+    assert np.array_equal(a, b)
+
+
+def test_config2_shape_subset_against_oracle(cuda_device):
+    """Config 2 geometry (12 layers, S=128, full length) on the first 4 sequences of the seeded batch."""
+    wl = model_synth.config_workload(2, batch=4)
+    y = _run(wl, torch.float16)
+    want = bert_oracle.encoder_forward(wl)
+    assert max_abs(y, want) <= MAX_ABS_TOL
+    assert cosine(y, want) >= COS_TOL
+
+
+def test_config3_ragged_against_oracle(cuda_device):
+    """Config 3 geometry: S=256, lengths ~ U[16,256], 12 layers, first 4 sequences."""
+    wl = model_synth.config_workload(3, batch=4)
+    y = _run(wl, torch.float16)
+    want = bert_oracle.encoder_forward(wl)
+    assert max_abs(valid_rows(y, wl.lengths), valid_rows(want, wl.lengths)) <= MAX_ABS_TOL
+    assert cosine(valid_rows(y, wl.lengths), valid_rows(want, wl.lengths)) >= COS_TOL
+
+
+def test_sequences_are_independent_at_full_batch(cuda_device):
+    """Size-independent property at config 2's full batch: a sequence's output does not depend on its batch-mates
+    (run B=64, then the first 4 alone: bit-identical)."""
+    wl = model_synth.config_workload(2, batch=64, num_layers=2)
+    y = _run(wl, torch.float16)
+    sub = model_synth.Workload(wl.cfg, wl.weights, wl.x[:4], wl.lengths[:4], wl.mask_add[:4], wl.meta)
+    y4 = _run(sub, torch.float16)
+    assert np.array_equal(y[:4], y4)

@@ -1,0 +1,197 @@
+"""GPU: each kernel of the path through the C ABI against the CPU oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bert_oracle
+from tnn_b200 import capi, ops
+from util import cosine, max_abs
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f16": torch.float16, "bf16": torch.bfloat16}
+# one half-precision rounding of an O(1) value: 2^-11 (fp16) / 2^-8 (bf16); sums of K products stay fp32
+ATOL = {"f16": 4e-3, "bf16": 3e-2}
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _rounded(a, dt):
+    """numpy fp32 -> rounded through the half dtype (what the kernel's operands hold) -> fp32."""
+    return torch.from_numpy(a).to(dt).float().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(cuda_device):
+    yield
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.OK
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 128, 64, 128), (128, 256, 128, 256), (256, 64, 64, 64),
+    (512, 768, 768, 0), (300, 2304, 768, 0), (1, 8, 8, 0), (129, 136, 72, 128),
+    (1024, 3072, 768, 256), (640, 768, 3072, 128),
+])
+def test_linear_bias(cuda_device, dt, M, N, K, bn):
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    x = rng.normal(0, 1, (M, K)).astype(np.float32)
+    w = rng.normal(0, 0.05, (K, N)).astype(np.float32)
+    b = rng.normal(0, 0.5, (N,)).astype(np.float32)
+    xd = torch.from_numpy(x).to(cuda_device).to(DT[dt])
+    wd = ops.pack_weight(torch.from_numpy(w).to(cuda_device), DT[dt])
+    assert np.array_equal(_np(wd), _rounded(w, DT[dt]).T)          # the pre-pack is exact rounding + transpose
+    y = ops.linear(xd, wd, torch.from_numpy(b).to(cuda_device), out_dtype=torch.float32, block_n=bn)
+    want = bert_oracle.linear(_rounded(x, DT[dt]), _rounded(w, DT[dt]), b)
+    assert max_abs(_np(y), want) < 2e-3 * max(1.0, np.sqrt(K / 64))
+    y16 = ops.linear(xd, wd, torch.from_numpy(b).to(cuda_device), block_n=bn)
+    assert max_abs(_np(y16), want) < ATOL[dt] * max(1.0, float(np.abs(want).max()))
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("epi", ["gelu", "residual"])
+def test_linear_epilogues(cuda_device, dt, epi):
+    M, N, K = 384, 1024, 256
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 1, (M, K)).astype(np.float32)
+    w = rng.normal(0, 0.08, (K, N)).astype(np.float32)
+    b = rng.normal(0, 0.5, (N,)).astype(np.float32)
+    r = rng.normal(0, 1, (M, N)).astype(np.float32)
+    xd = torch.from_numpy(x).to(cuda_device).to(DT[dt])
+    wd = ops.pack_weight(torch.from_numpy(w).to(cuda_device), DT[dt])
+    bd = torch.from_numpy(b).to(cuda_device)
+    xr, wr = _rounded(x, DT[dt]), _rounded(w, DT[dt])
+    if epi == "gelu":
+        y = ops.linear(xd, wd, bd, epilogue=ops.EPI_BIAS_GELU, out_dtype=torch.float32)
+        want = bert_oracle.linear(xr, wr, b, act="gelu")
+    else:
+        rd = torch.from_numpy(r).to(cuda_device).to(DT[dt])
+        y = ops.linear(xd, wd, bd, residual=rd, epilogue=ops.EPI_BIAS_RESIDUAL, out_dtype=torch.float32)
+        want = bert_oracle.linear(xr, wr, b, residual=_rounded(r, DT[dt]))
+    assert max_abs(_np(y), want) < 4e-3
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("H,rows", [(768, 1000), (1024, 77), (8, 3), (4096, 9), (1536, 64)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_add_layernorm(cuda_device, dt, H, rows, with_res):
+    rng = np.random.default_rng(H + rows)
+    x = rng.normal(0.3, 2.0, (rows, H)).astype(np.float32)
+    r = rng.normal(0, 1.0, (rows, H)).astype(np.float32)
+    g = (1 + rng.normal(0, 0.2, (H,))).astype(np.float32)
+    be = rng.normal(0, 0.2, (H,)).astype(np.float32)
+    xd = torch.from_numpy(x).to(cuda_device).to(DT[dt])
+    rd = torch.from_numpy(r).to(cuda_device).to(DT[dt]) if with_res else None
+    y = ops.add_layernorm(xd, torch.from_numpy(g).to(cuda_device), torch.from_numpy(be).to(cuda_device), 1e-12,
+                          residual=rd, out_dtype=torch.float32)
+    xin = _rounded(x, DT[dt]) + (_rounded(r, DT[dt]) if with_res else 0)
+    want = bert_oracle.layer_norm(xin.astype(np.float32), g, be, 1e-12)
+    assert max_abs(_np(y), want) < 2e-4
+    # fp32 in / fp32 out: the un-fused LayerNorm layer of the graph
+    y32 = ops.add_layernorm(torch.from_numpy(x).to(cuda_device), torch.from_numpy(g).to(cuda_device),
+                            torch.from_numpy(be).to(cuda_device), 1e-12)
+    assert max_abs(_np(y32), bert_oracle.layer_norm(x, g, be, 1e-12)) < 2e-4
+
+
+def test_convert_roundtrip_and_tail(cuda_device):
+    for n in (1, 7, 8, 1000, 4099):
+        a = torch.randn(n, device=cuda_device)
+        h = ops.convert(a, torch.float16)
+        assert torch.equal(h, a.to(torch.float16))
+        assert torch.equal(ops.convert(h, torch.float32), h.float())
+        b = ops.convert(a, torch.bfloat16)
+        assert torch.equal(b, a.to(torch.bfloat16))
+
+
+def test_mask_to_kv_len(cuda_device):
+    B, S = 7, 300
+    m = np.full((B, S), -10000.0, np.float32)
+    lens = [0, 1, 128, 129, 300, 17, 256]
+    for b, n in enumerate(lens):
+        m[b, :n] = 0
+    m[5, 40] = 0          # a hole beyond the prefix: kv_len follows the last valid key
+    out = ops.mask_to_kv_len(torch.from_numpy(m).to(cuda_device)).cpu().numpy()
+    want = np.array(lens)
+    want[5] = 41
+    assert np.array_equal(out, want)
+
+
+def _attention_case(cuda_device, dt, B, S, heads, lengths, seed=0, holes=False):
+    H = heads * 64
+    rng = np.random.default_rng(seed)
+    qkv = rng.normal(0, 1, (B, S, 3 * H)).astype(np.float32)
+    mask = np.zeros((B, S), np.float32)
+    for b, n in enumerate(lengths):
+        mask[b, n:] = -10000.0
+    if holes:
+        mask[:, 1::5] = -10000.0
+    qd = torch.from_numpy(qkv).to(cuda_device).to(DT[dt])
+    md = torch.from_numpy(mask).to(cuda_device)
+    kv = ops.mask_to_kv_len(md)
+    out = ops.attention(qd, heads, md, kv)
+    r = _rounded(qkv, DT[dt]).reshape(B, S, 3, heads, 64)
+    q, k, v = (r[:, :, i].transpose(0, 2, 1, 3) for i in range(3))
+    want = bert_oracle.attention_core(q, k, v, mask, 0.125).transpose(0, 2, 1, 3).reshape(B, S, H)
+    return _np(out), want, qd, md, kv
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("B,S,heads,lengths", [
+    (2, 128, 12, [128, 128]), (3, 128, 2, [1, 17, 100]), (2, 96, 4, [96, 5]), (2, 200, 3, [200, 131]),
+    (2, 256, 2, [16, 256]), (1, 384, 16, [300]), (1, 1, 1, [1]), (2, 512, 2, [512, 129]), (1, 130, 1, [130]),
+])
+def test_attention(cuda_device, dt, B, S, heads, lengths):
+    got, want, *_ = _attention_case(cuda_device, dt, B, S, heads, lengths, seed=S + B)
+    tol = 6e-3 if dt == "f16" else 3e-2
+    for b, n in enumerate(lengths):
+        # every query row, padded ones included, is computed like the reference computes it
+        assert max_abs(got[b], want[b]) < tol
+    assert cosine(got, want) > 0.9995
+
+
+def test_attention_mask_with_holes_and_no_mask(cuda_device):
+    got, want, *_ = _attention_case(cuda_device, "f16", 2, 256, 2, [256, 200], seed=3, holes=True)
+    assert max_abs(got, want) < 6e-3
+    # no mask at all
+    rng = np.random.default_rng(9)
+    qkv = rng.normal(0, 1, (1, 128, 3 * 128)).astype(np.float32)
+    qd = torch.from_numpy(qkv).cuda().half()
+    out = ops.attention(qd, 2)
+    r = _rounded(qkv, torch.float16).reshape(1, 128, 3, 2, 64)
+    q, k, v = (r[:, :, i].transpose(0, 2, 1, 3) for i in range(3))
+    want = bert_oracle.attention_core(q, k, v, None, 0.125).transpose(0, 2, 1, 3).reshape(1, 128, 128)
+    assert max_abs(_np(out), want) < 6e-3
+
+
+def test_attention_padded_keys_have_exactly_zero_weight(cuda_device):
+    """Perturbing K/V rows of padded keys must leave every output bit-identical."""
+    B, S, heads = 2, 256, 4
+    H = heads * 64
+    lengths = [77, 200]
+    got, _, qd, md, kv = _attention_case(cuda_device, "f16", B, S, heads, lengths, seed=11)
+    q2 = qd.clone()
+    for b, n in enumerate(lengths):
+        q2[b, n:, H:] = torch.randn_like(q2[b, n:, H:]) * 50.0      # K and V of padded keys
+    out2 = ops.attention(q2, heads, md, kv)
+    out1 = ops.attention(qd, heads, md, kv)
+    for b, n in enumerate(lengths):
+        assert torch.equal(out1[b, :n], out2[b, :n])
+
+
+def test_attention_all_keys_masked_follows_reference(cuda_device):
+    """A sequence with no valid key: the reference's softmax sees a constant shift and weighs all keys uniformly."""
+    got, want, *_ = _attention_case(cuda_device, "f16", 2, 128, 2, [0, 64], seed=5)
+    assert max_abs(got, want) < 6e-3
+
+
+def test_bad_arguments_on_gpu(cuda_device):
+    x = torch.zeros(16, 24, dtype=torch.float16, device=cuda_device)
+    w = torch.zeros(8, 24, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(capi.B200Error) as e:
+        ops.linear(x[:, :20], w[:, :20])       # K = 20 is not a multiple of 8
+    assert e.value.code == capi.ERR_PARAM
+    with pytest.raises(capi.B200Error):
+        ops.linear(x, w, block_n=96)

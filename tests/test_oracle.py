@@ -1,0 +1,62 @@
+"""CPU: the numpy restatement against outputs of the reference itself (tests/golden, made by oracle/make_golden.py)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from util import cosine, max_abs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+
+from oracle import bert_oracle  # noqa: E402
+from oracle.make_golden import CASES, GOLDEN, golden_workload  # noqa: E402
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_restatement_matches_reference_x86(name):
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    wl = golden_workload(**CASES[name])
+    assert np.array_equal(g["lengths"], wl.lengths)
+    y = bert_oracle.encoder_forward(wl)
+    ref = g["x86"]
+    assert y.shape == ref.shape
+    # fp32 against fp32: only summation order differs (the x86 acc blocks K by 256 and uses FMA)
+    assert max_abs(y, ref) < 5e-5
+    assert cosine(y, ref) > 1 - 1e-9
+    # the reference's two CPU devices agreed with each other when the fixture was made
+    assert float(g["x86_vs_naive_max_abs"]) < 5e-5
+
+
+def test_softmax_masked_keys_underflow_to_zero():
+    # -10000 on a key underflows exp() to exactly 0 in fp32: the reference's padded keys carry no weight.
+    x = np.zeros((1, 1, 2, 8), np.float32)
+    x[..., 5:] = -10000.0
+    p = bert_oracle.softmax_last(x)
+    assert np.all(p[..., 5:] == 0.0)
+    assert np.allclose(p[..., :5], 0.2)
+
+
+def test_layer_norm_constant_row_is_finite():
+    x = np.full((2, 16), 3.0, np.float32)
+    y = bert_oracle.layer_norm(x, np.ones(16, np.float32), np.zeros(16, np.float32), 1e-12)
+    assert np.all(np.isfinite(y))
+
+
+def test_gelu_erf_form():
+    x = np.array([-3.0, -1.0, 0.0, 0.5, 2.0], np.float32)
+    import math
+    want = np.array([0.5 * v * (1 + math.erf(v / math.sqrt(2))) for v in x], np.float32)
+    assert np.allclose(bert_oracle.gelu(x), want, atol=1e-6)
+
+
+def test_reference_build_matches_fixture_when_present():
+    """Where the compiled reference is present, re-run config 1 and compare with the committed fixture."""
+    from oracle import tnn_ref
+    if not tnn_ref.available():
+        pytest.skip("oracle/_ref not built here")
+    wl = golden_workload(**CASES["c1_attention_block"])
+    out, _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_X86)
+    g = np.load(os.path.join(GOLDEN, "c1_attention_block.npz"))
+    assert max_abs(out, g["x86"]) < 1e-5

@@ -1,0 +1,327 @@
+// Fused multi-head attention for sm_100a, head_dim 64:  out = softmax(scale * Q K^T + mask) V, one CTA per
+// (128-query tile, head, sequence), flash-style loop over 128-key tiles with online softmax.
+//
+//   TMA   : Q, K, V tiles [128 x 64] straight out of the token-major QKV activation (the head split of the unfused
+//           graph's Reshape+Permute is just the TMA column coordinate h*64) into 128-byte-swizzled shared memory.
+//   UMMA  : S = Q K^T (128 x 128 x 64, both operands K-major) into TMEM columns [0,128);
+//           O_j = P V (128 x 64 x 128, P K-major from shared memory, V MN-major exactly as TMA delivered it) into
+//           TMEM columns [128,192).
+//   softmax: thread t owns query row t (TMEM lane t), so row max / row sum are in-thread; scores are scaled, the
+//           additive key mask is applied in registers, excluded keys get weight exactly 0 (exp2(-inf)), P is written
+//           to shared memory as half precision in the swizzled K-major layout the second UMMA reads.
+//   The running output is kept in registers and rescaled per key tile; K_{j+1} is fetched while tile j is in softmax
+//   and PV, V_{j+1} while tile j+1 is in QK^T and softmax.  Two CTAs fit per SM (81 KB shared memory, 256 TMEM
+//   columns each), which overlaps one CTA's softmax with the other's UMMAs.
+// Algorithmic work per launch: 4 * S^2 * 64 * heads * B flop (QK^T and PV); HBM bytes: Q, K, V read once per CTA, O written.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int TQ = 128;   // queries per CTA
+constexpr int TK = 128;   // keys per tile
+constexpr int HD = 64;    // head dim
+constexpr int kAttnThreads = 128;
+constexpr int TILE_BYTES = 128 * HD * 2;  // 16 KB
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + TILE_BYTES;
+constexpr int OFF_V = OFF_K + TILE_BYTES;
+constexpr int OFF_P = OFF_V + TILE_BYTES;       // 2 x 16 KB (keys 0..63, 64..127)
+constexpr int OFF_MASK = OFF_P + 2 * TILE_BYTES;  // 2 x 128 floats
+constexpr int OFF_BAR = OFF_MASK + 2 * TK * 4;
+constexpr int ATTN_SMEM = OFF_BAR + 128;
+constexpr int ATTN_TMEM_COLS = 256;
+constexpr int TMEM_S = 0;
+constexpr int TMEM_O = 128;
+
+struct AttnParams {
+    const float* mask_add;
+    const int* kv_len;
+    void* out;
+    int S, heads;
+    long long ldo;
+    int dtype;
+    float scale_log2;   // scale * log2(e)
+    float mask_below;
+    uint32_t idesc_qk, idesc_pv;
+    unsigned int* status;
+};
+
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* bar_q = bars + 0;
+    uint64_t* bar_k = bars + 1;
+    uint64_t* bar_v = bars + 2;
+    uint64_t* bar_s = bars + 3;
+    uint64_t* bar_o = bars + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* mask_s = reinterpret_cast<float*>(smem + OFF_MASK);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int q0 = blockIdx.x * TQ;
+    const int head = blockIdx.y;
+    const int b = blockIdx.z;
+
+    // The swizzled tiles need 1024-byte alignment; refuse to run rather than compute garbage if it is ever violated.
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0 && p.status) atomicOr(p.status, 4u);
+        return;
+    }
+
+    int kv_eff = p.S;
+    bool additive_only = (p.mask_add == nullptr);
+    if (p.kv_len != nullptr) {
+        const int kl = p.kv_len[b];
+        if (kl <= 0) additive_only = true;          // no key above the threshold: the reference's behaviour
+        else kv_eff = kl < p.S ? kl : p.S;
+    }
+    const int n_tiles = (kv_eff + TK - 1) / TK;
+
+    if (tid == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tm_q);
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, ATTN_TMEM_COLS);
+        tmem_relinquish();
+    }
+
+    // Key mask of a tile, in log2 units: -inf drops the key exactly.
+    auto write_mask = [&](int j) {
+        const int key = j * TK + tid;
+        float m = -INFINITY;
+        if (key < p.S) {
+            const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + key] : 0.f;
+            if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+        }
+        mask_s[(j & 1) * TK + tid] = m;
+    };
+    write_mask(0);
+
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (tid == 0) {
+        mbar_expect_tx(bar_q, TILE_BYTES);
+        tma_load_3d(smem + OFF_Q, &tm_q, bar_q, head * HD, q0, b);
+        mbar_expect_tx(bar_k, TILE_BYTES);
+        tma_load_3d(smem + OFF_K, &tm_k, bar_k, head * HD, 0, b);
+        mbar_expect_tx(bar_v, TILE_BYTES);
+        tma_load_3d(smem + OFF_V, &tm_v, bar_v, head * HD, 0, b);
+    }
+
+    const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t ph = static_cast<uint32_t>(j) & 1u;
+        // ---- S = Q K^T
+        if (tid == 0) {
+            bool w = true;
+            if (j == 0) w = mbar_wait(bar_q, 0, abort_flag);
+            w = w && mbar_wait(bar_k, ph, abort_flag);
+            if (w) {
+                tcgen05_fence_after();
+                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + OFF_Q));
+                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_K));
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)
+                    umma_f16_ss(tmem_base + TMEM_S, a_desc + 2u * k, b_desc + 2u * k, p.idesc_qk, k != 0 ? 1u : 0u);
+                umma_commit(bar_s);
+            }
+        }
+        if (j + 1 < n_tiles) write_mask(j + 1);
+        if (!mbar_wait(bar_s, ph, abort_flag)) { ok = false; break; }
+        __syncwarp();  // tcgen05.ld is warp-collective: lane 0 took a longer path through the issue block
+        tcgen05_fence_after();
+        if (tid == 0 && j + 1 < n_tiles) {  // K tile is free again: fetch the next one under the softmax
+            mbar_expect_tx(bar_k, TILE_BYTES);
+            tma_load_3d(smem + OFF_K, &tm_k, bar_k, head * HD, (j + 1) * TK, b);
+        }
+
+        // ---- online softmax on row `tid`
+        const float* mrow = mask_s + (j & 1) * TK;
+        float tmax = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < TK / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_S + c * 32, r);
+            tmem_ld_wait(r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                tmax = fmaxf(tmax, fmaf(__uint_as_float(r[i]), p.scale_log2, mrow[c * 32 + i]));
+        }
+        const float m_new = fmaxf(m_run, tmax);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_run - m_use);
+        float psum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < TK / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_S + c * 32, r);
+            tmem_ld_wait(r);
+            float pv[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                pv[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mrow[c * 32 + i]) - m_use);
+                psum += pv[i];
+            }
+            // P[row tid][keys c*32 .. c*32+31] -> swizzled K-major tile: 16-byte chunk index ^= (row & 7)
+            uint8_t* prow = smem + OFF_P + (c >> 1) * TILE_BYTES + tid * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint4 qv;
+                qv.x = pack2(pv[g * 8 + 0], pv[g * 8 + 1], p.dtype);
+                qv.y = pack2(pv[g * 8 + 2], pv[g * 8 + 3], p.dtype);
+                qv.z = pack2(pv[g * 8 + 4], pv[g * 8 + 5], p.dtype);
+                qv.w = pack2(pv[g * 8 + 6], pv[g * 8 + 7], p.dtype);
+                const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
+                *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
+            }
+        }
+        l_run = l_run * alpha + psum;
+        m_run = m_new;
+
+        fence_async_proxy_shared();   // P (generic-proxy stores) must be visible to the UMMA (async proxy)
+        tcgen05_fence_before();
+        __syncthreads();
+
+        // ---- O_j = P V
+        if (tid == 0) {
+            tcgen05_fence_after();
+            if (mbar_wait(bar_v, ph, abort_flag)) {
+                tcgen05_fence_after();
+#pragma unroll
+                for (int k = 0; k < TK / 16; ++k) {
+                    const uint64_t a_desc =
+                        make_smem_desc_sw128(smem_u32(smem + OFF_P + (k >> 2) * TILE_BYTES)) + 2u * (k & 3);
+                    // V rows are keys: 16 keys = 2 groups of 8 rows = 2048 bytes per UMMA step
+                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_V + k * 2048));
+                    umma_f16_ss(tmem_base + TMEM_O, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);
+                }
+                umma_commit(bar_o);
+            }
+        }
+        if (!mbar_wait(bar_o, ph, abort_flag)) { ok = false; break; }
+        __syncwarp();
+        tcgen05_fence_after();
+        if (tid == 0 && j + 1 < n_tiles) {  // V tile is free again
+            mbar_expect_tx(bar_v, TILE_BYTES);
+            tma_load_3d(smem + OFF_V, &tm_v, bar_v, head * HD, (j + 1) * TK, b);
+        }
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_O + c * 32, r);
+            tmem_ld_wait(r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
+        }
+        // The next iteration's UMMAs overwrite S (after the next bar_k wait, issued by tid 0 only after it has itself
+        // passed this point) and O/P (after the next __syncthreads), so TMEM reads above are ordered before them.
+        tcgen05_fence_before();
+    }
+
+    if (ok) {
+        const int q = q0 + tid;
+        if (q < p.S) {
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;  // every key excluded and no kv_len given: zeros
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + q) * p.ldo + head * HD;
+#pragma unroll
+            for (int g = 0; g < HD / 8; ++g) {
+                uint4 qv;
+                qv.x = pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv, p.dtype);
+                qv.y = pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv, p.dtype);
+                qv.z = pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv, p.dtype);
+                qv.w = pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv, p.dtype);
+                *reinterpret_cast<uint4*>(dst + g * 8) = qv;
+            }
+        }
+    } else if (tid == 0) {
+        for (int i = 0; i < 64; ++i) nanosleep(10000);  // let copies in flight land before shared memory is released
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, ATTN_TMEM_COLS);
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stream_) {
+    using namespace b200;
+    if (!d || !d->q || !d->k || !d->v || !d->out) return B200_ERR_PARAM;
+    if (d->B <= 0 || d->S <= 0 || d->heads <= 0) return B200_ERR_PARAM;
+    if (d->head_dim != HD) return B200_ERR_UNSUPPORTED;
+    if (!is_half_dtype(d->dtype)) return B200_ERR_PARAM;
+    const int64_t width = static_cast<int64_t>(d->heads) * HD;
+    if ((d->ldq % 8) || (d->ldk % 8) || (d->ldv % 8) || (d->ldo % 8)) return B200_ERR_PARAM;
+    if (d->ldq < width || d->ldk < width || d->ldv < width || d->ldo < width) return B200_ERR_PARAM;
+    if (!aligned16(d->q) || !aligned16(d->k) || !aligned16(d->v) || !aligned16(d->out)) return B200_ERR_PARAM;
+    if (d->B > 65535 || d->heads > 65535 || d->S > (1 << 24)) return B200_ERR_UNSUPPORTED;
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B200_ERR_LAUNCH;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) return B200_ERR_NOT_SM100;
+
+    const uint64_t dims[3] = {static_cast<uint64_t>(width), static_cast<uint64_t>(d->S), static_cast<uint64_t>(d->B)};
+    const uint32_t box[3] = {HD, 128, 1};
+    const uint64_t sq[2] = {static_cast<uint64_t>(d->ldq) * 2, static_cast<uint64_t>(d->ldq) * 2 * d->S};
+    const uint64_t sk[2] = {static_cast<uint64_t>(d->ldk) * 2, static_cast<uint64_t>(d->ldk) * 2 * d->S};
+    const uint64_t sv[2] = {static_cast<uint64_t>(d->ldv) * 2, static_cast<uint64_t>(d->ldv) * 2 * d->S};
+    const CUtensorMap* tq = get_tensor_map(d->q, 3, dims, sq, box);
+    const CUtensorMap* tk = get_tensor_map(d->k, 3, dims, sk, box);
+    const CUtensorMap* tv = get_tensor_map(d->v, 3, dims, sv, box);
+    if (!tq || !tk || !tv) return B200_ERR_DRIVER;
+
+    AttnParams p;
+    p.mask_add = d->mask_add;
+    p.kv_len = d->kv_len;
+    p.out = d->out;
+    p.S = static_cast<int>(d->S);
+    p.heads = d->heads;
+    p.ldo = d->ldo;
+    p.dtype = d->dtype;
+    p.scale_log2 = d->scale * 1.4426950408889634f;
+    p.mask_below = d->mask_exclude_below;
+    const int fmt = d->dtype == B200_BF16 ? 1 : 0;
+    p.idesc_qk = make_idesc_f16(128, TK, fmt, 0, 0);
+    p.idesc_pv = make_idesc_f16(128, HD, fmt, 0, 1);  // B (= V) is MN-major
+    p.status = device_status_ptr();
+
+    static bool attr_set[64] = {false};
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    dim3 grid(static_cast<unsigned>((d->S + TQ - 1) / TQ), static_cast<unsigned>(d->heads), static_cast<unsigned>(d->B));
+    attention_kernel<<<grid, kAttnThreads, ATTN_SMEM, static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, p);
+    count_launch();
+    return check_launch();
+}

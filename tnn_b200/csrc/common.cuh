@@ -1,0 +1,57 @@
+// Shared host/device helpers of the tnn_b200 kernel library: dtype tags, packed conversions, the per-device status
+// word that bounded waits report through, the launch counter and the tensor-map (TMA descriptor) cache.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tnn_b200.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- device status word
+// Bit 0: a bounded wait ran out in a GEMM CTA; bit 1: in an attention CTA.  The word itself is a __device__ variable
+// of runtime.cu; kernels receive its address as a parameter (no relocatable device code needed).
+unsigned int* device_status_ptr();  // address of the word on the current device (looked up once per device)
+
+void count_launch(int n = 1);
+
+// ---------------------------------------------------------------- dtype helpers (device)
+template <int DT> struct Elem;
+template <> struct Elem<B200_F16> { using type = __half; using type2 = __half2; };
+template <> struct Elem<B200_BF16> { using type = __nv_bfloat16; using type2 = __nv_bfloat162; };
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int dtype) {
+    if (dtype == B200_F16) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+__device__ __forceinline__ float2 unpack2(uint32_t u, int dtype) {
+    if (dtype == B200_F16) {
+        return __half22float2(*reinterpret_cast<__half2*>(&u));
+    } else {
+        return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+    }
+}
+
+inline size_t dtype_size(int dt) { return dt == B200_F32 ? 4 : 2; }
+inline bool is_half_dtype(int dt) { return dt == B200_F16 || dt == B200_BF16; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------- tensor maps
+// 2-D or 3-D tiled map over a 2-byte-element tensor whose innermost dimension is contiguous, 128-byte swizzle,
+// inner box = 64 elements (128 bytes).  dims/strides are innermost first; strides[i] is the byte stride of dim i+1.
+// Maps are cached per device by their full key; encoding takes about a microsecond and the same activations and
+// weights come back every Forward.  Returns nullptr if the driver entry point is missing or refuses the descriptor.
+const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                                  const uint32_t* box);
+
+inline int check_launch() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH; }
+
+}  // namespace b200

@@ -1,0 +1,357 @@
+// Projection / FFN GEMM with fused epilogue for sm_100a:  y = epilogue(x . w^T + bias (+ residual)).
+//
+// Persistent, warp-specialised CTA (one per SM):
+//   warp 0      : TMA producer   — x tile [128 x 64] and w tile [BN x 64] per k-block into a STAGES-deep ring of
+//                                   128-byte-swizzled shared memory; completion on the stage's `full` mbarrier.
+//   warp 1      : UMMA issuer    — owns the TMEM allocation (2 accumulators of BN fp32 columns); one elected lane
+//                                   issues 4 x tcgen05.mma (128 x BN x 16) per k-block, commits the stage's `empty`
+//                                   barrier, and commits `acc_full` after the last k-block of a tile.
+//   warps 2..9  : epilogue       — tcgen05.ld of the accumulator (a thread owns one row: lane = row), bias / GELU /
+//                                   residual in registers, 16-byte stores.  Two warps share a 32-row quarter and
+//                                   split the columns.  While they drain accumulator b, the issuer fills b^1.
+// Algorithmic work per launch: 2*M*N*K flop; HBM traffic at least (M*K + N*K + M*N (+ M*N residual)) elements.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + kEpiWarps * 32;
+
+struct LinearParams {
+    const float* bias;
+    const void* residual;
+    void* y;
+    int M, N, K;
+    long long ldr, ldy;
+    int dtype, out_dtype, epilogue;
+    int num_n_tiles, num_tiles, num_k_blocks;
+    uint32_t idesc;
+    unsigned int* status;
+};
+
+template <int BN, int STAGES>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+    static constexpr int TMEM_COLS = 2 * BN;                    // 128, 256 or 512: powers of two
+};
+
+// erf-form GELU, 0.5 x (1 + erf(x / sqrt 2)), as the reference's CPU accs compute it.
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const LinearParams p) {
+    using C = Cfg<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], kEpiWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tm_x);
+        prefetch_tmap(&tm_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                const int m_blk = tile / p.num_n_tiles;
+                const int n_blk = tile % p.num_n_tiles;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* a = smem + s * C::STAGE_BYTES;
+                    uint8_t* b = a + C::A_BYTES;
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_2d(a, &tm_x, &full[s], kb * BK, m_blk * BM);
+                    tma_load_2d(b, &tm_w, &full[s], kb * BK, n_blk * BN);
+                }
+            }
+            if (!ok) {
+                // Give copies already in flight time to land before the CTA's shared memory is released.
+                for (int i = 0; i < 64; ++i) nanosleep(10000);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (elect_one()) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+                const uint32_t buf = tcount & 1u;
+                const uint32_t aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 elements along K = 32 bytes inside the 128-byte swizzled row: +2 in (address >> 4) units
+                        umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int ew = warp - 2;
+        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. 32*quarter+31 are the ones this warp may read
+        const int half = ew >> 2;      // which half of the BN columns
+        constexpr int COLS = BN / 2;
+        constexpr int CHUNKS = COLS / 32;
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+            const int m_blk = tile / p.num_n_tiles;
+            const int n_blk = tile % p.num_n_tiles;
+            const uint32_t buf = tcount & 1u;
+            const uint32_t aph = (tcount >> 1) & 1u;
+            if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
+            __syncwarp();  // tcgen05.ld is warp-collective
+            tcgen05_fence_after();
+            const int row = m_blk * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+#pragma unroll 1
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int col0 = half * COLS + c * 32;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + col0;
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr, r);
+                tmem_ld_wait(r);
+                const int n0 = n_blk * BN + col0;
+                if (n0 >= p.N) continue;  // uniform across the warp
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        if (n0 + g * 4 < p.N) {
+                            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + n0 + g * 4));
+                            v[g * 4 + 0] += b.x;
+                            v[g * 4 + 1] += b.y;
+                            v[g * 4 + 2] += b.z;
+                            v[g * 4 + 3] += b.w;
+                        }
+                    }
+                }
+                if (p.epilogue == B200_EPI_BIAS_GELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                }
+                if (!row_ok) continue;
+                if (p.epilogue == B200_EPI_BIAS_RESIDUAL) {
+                    const uint16_t* rp = reinterpret_cast<const uint16_t*>(p.residual) + row * p.ldr + n0;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (n0 + g * 8 < p.N) {
+                            const uint4 q = __ldg(reinterpret_cast<const uint4*>(rp + g * 8));
+                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = unpack2(w[e], p.dtype);
+                                v[g * 8 + e * 2 + 0] += f.x;
+                                v[g * 8 + e * 2 + 1] += f.y;
+                            }
+                        }
+                    }
+                }
+                if (p.out_dtype == B200_F32) {
+                    float* yp = reinterpret_cast<float*>(p.y) + row * p.ldy + n0;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        if (n0 + g * 4 < p.N) {
+                            *reinterpret_cast<float4*>(yp + g * 4) =
+                                make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                        }
+                    }
+                } else {
+                    uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + row * p.ldy + n0;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (n0 + g * 8 < p.N) {
+                            uint4 q;
+                            q.x = pack2(v[g * 8 + 0], v[g * 8 + 1], p.out_dtype);
+                            q.y = pack2(v[g * 8 + 2], v[g * 8 + 3], p.out_dtype);
+                            q.z = pack2(v[g * 8 + 4], v[g * 8 + 5], p.out_dtype);
+                            q.w = pack2(v[g * 8 + 6], v[g * 8 + 7], p.out_dtype);
+                            *reinterpret_cast<uint4*>(yp + g * 8) = q;
+                        }
+                    }
+                }
+            }
+            // This warp has read everything it needs from accumulator `buf`.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown (also the exit of an aborted CTA)
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 1u);
+}
+
+int device_sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int n = 0, major = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        sms[dev] = (major == 10) ? n : -1;
+    }
+    return sms[dev];
+}
+
+template <int BN, int STAGES>
+int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
+    using C = Cfg<BN, STAGES>;
+    const uint64_t xd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.M)};
+    const uint64_t xs[1] = {static_cast<uint64_t>(d.ldx) * 2};
+    const uint32_t xb[2] = {BK, BM};
+    const uint64_t wd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.N)};
+    const uint64_t ws[1] = {static_cast<uint64_t>(d.ldw) * 2};
+    const uint32_t wb[2] = {BK, BN};
+    const CUtensorMap* tx = get_tensor_map(d.x, 2, xd, xs, xb);
+    const CUtensorMap* tw = get_tensor_map(d.w_nk, 2, wd, ws, wb);
+    if (!tx || !tw) return B200_ERR_DRIVER;
+
+    LinearParams p;
+    p.bias = d.bias;
+    p.residual = d.residual;
+    p.y = d.y;
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.K = static_cast<int>(d.K);
+    p.ldr = d.ldr;
+    p.ldy = d.ldy;
+    p.dtype = d.dtype;
+    p.out_dtype = d.out_dtype;
+    p.epilogue = d.epilogue;
+    p.num_n_tiles = (p.N + BN - 1) / BN;
+    p.num_tiles = ((p.M + BM - 1) / BM) * p.num_n_tiles;
+    p.num_k_blocks = (p.K + BK - 1) / BK;
+    p.idesc = make_idesc_f16(BM, BN, d.dtype == B200_BF16 ? 1 : 0, 0, 0);
+    p.status = device_status_ptr();
+
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(linear_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+    linear_kernel<BN, STAGES><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, p);
+    count_launch();
+    return check_launch();
+}
+
+int choose_block_n(int64_t M, int64_t N, int sm_count) {
+    // Estimated time ~ waves * BN * (per-column cost): narrow tiles read proportionally more shared memory per flop.
+    const int cand[3] = {256, 128, 64};
+    const double cost[3] = {1.0, 1.12, 1.5};
+    const int64_t mt = (M + BM - 1) / BM;
+    double best = 1e300;
+    int best_bn = 128;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = mt * ((N + cand[i] - 1) / cand[i]);
+        const int64_t waves = (tiles + sm_count - 1) / sm_count;
+        const double t = static_cast<double>(waves) * cand[i] * cost[i];
+        if (t < best) {
+            best = t;
+            best_bn = cand[i];
+        }
+    }
+    return best_bn;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
+    using namespace b200;
+    if (!d || !d->x || !d->w_nk || !d->y) return B200_ERR_PARAM;
+    if (d->M <= 0 || d->N <= 0 || d->K <= 0) return B200_ERR_PARAM;
+    if (d->M > (1ll << 30) || d->N > (1ll << 30) || d->K > (1ll << 30)) return B200_ERR_UNSUPPORTED;
+    if (!is_half_dtype(d->dtype)) return B200_ERR_PARAM;
+    if (d->out_dtype != B200_F16 && d->out_dtype != B200_BF16 && d->out_dtype != B200_F32) return B200_ERR_PARAM;
+    if (d->epilogue < B200_EPI_BIAS || d->epilogue > B200_EPI_BIAS_RESIDUAL) return B200_ERR_PARAM;
+    if (d->epilogue == B200_EPI_BIAS_RESIDUAL && !d->residual) return B200_ERR_PARAM;
+    if ((d->K % 8) || (d->N % 8) || (d->ldx % 8) || (d->ldw % 8) || (d->ldy % 8)) return B200_ERR_PARAM;
+    if (d->ldx < d->K || d->ldw < d->K || d->ldy < d->N) return B200_ERR_PARAM;
+    if (!aligned16(d->x) || !aligned16(d->w_nk) || !aligned16(d->y)) return B200_ERR_PARAM;
+    if (d->bias && !aligned16(d->bias)) return B200_ERR_PARAM;
+    if (d->epilogue == B200_EPI_BIAS_RESIDUAL && ((d->ldr % 8) || d->ldr < d->N || !aligned16(d->residual)))
+        return B200_ERR_PARAM;
+    const int sms = device_sm_count();
+    if (sms <= 0) return B200_ERR_NOT_SM100;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int bn = d->block_n;
+    if (bn == 0) bn = choose_block_n(d->M, d->N, sms);
+    switch (bn) {
+        case 256: return launch_linear<256, 4>(*d, stream, sms);
+        case 128: return launch_linear<128, 6>(*d, stream, sms);
+        case 64: return launch_linear<64, 8>(*d, stream, sms);
+        default: return B200_ERR_PARAM;
+    }
+}

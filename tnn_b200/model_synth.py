@@ -1,0 +1,235 @@
+"""Synthetic BERT-style encoder models in TNN's own formats, and the seeded weights/inputs of the benchmark configs.
+
+The reference's BERT model files are download-only, so every workload here is synthetic: weights ~ N(0, 0.02),
+biases 0, LayerNorm gamma 1 / beta 0 / eps 1e-12, activations ~ N(0, 1), drawn from numpy `default_rng(seed)` in a
+fixed order (per layer Wq, Wk, Wv, Wo, W1, W2; then activations; then lengths).  `randomize_affine=True` additionally
+draws non-trivial biases / gamma / beta so that tests exercise those terms.
+
+`write_tnn_model` emits the UNFUSED graph exactly as a converter would (MatMul, Add, Reshape, Permute, Mul, Softmax,
+LayerNorm, GELU layers) as `.tnnproto` text + `.tnnmodel` binary:
+  * proto grammar: source/tnn/interpreter/tnn/model_interpreter.cc:174-398 (header line, inputs, blobs, outputs, layers)
+  * model binary : source/tnn/interpreter/tnn/model_interpreter.cc:400-476, source/tnn/interpreter/tnn/objseri.h:57-167
+    (magic, layer count, per-layer {type enum, type string, name, RawBuffer}, then the constant map)
+so that the very same files run on the reference's DEVICE_X86 and on DEVICE_CUDA through the fusion pass.
+"""
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+MAGIC = 0x0FABC0002   # untyped-input proto / model magic (source/tnn/interpreter/tnn/objseri.h:29-30)
+MAGIC_RAW = 0x0FABC0004
+# LayerType enum values used in the binary (source/tnn/core/layer_type.h); the parser keys on the type string.
+_TYPE_ID = {"MatMul": 105, "Add": 38, "Mul": 42}
+
+
+@dataclass
+class EncoderConfig:
+    layers: int = 12
+    hidden: int = 768
+    heads: int = 12
+    ffn: int = 3072
+    ln_eps: float = 1e-12
+    with_ffn: bool = True      # False: attention block + residual + LayerNorm only (config 1)
+
+    @property
+    def head_dim(self):
+        return self.hidden // self.heads
+
+
+BERT_BASE = EncoderConfig(12, 768, 12, 3072)
+BERT_LARGE = EncoderConfig(24, 1024, 16, 4096)
+
+
+@dataclass
+class LayerWeights:
+    wq: np.ndarray
+    wk: np.ndarray
+    wv: np.ndarray
+    wo: np.ndarray
+    bq: np.ndarray
+    bk: np.ndarray
+    bv: np.ndarray
+    bo: np.ndarray
+    ln1_g: np.ndarray
+    ln1_b: np.ndarray
+    w1: np.ndarray = None
+    b1: np.ndarray = None
+    w2: np.ndarray = None
+    b2: np.ndarray = None
+    ln2_g: np.ndarray = None
+    ln2_b: np.ndarray = None
+
+
+@dataclass
+class Workload:
+    cfg: EncoderConfig
+    weights: list
+    x: np.ndarray            # [B, S, H] fp32
+    lengths: np.ndarray      # [B] int
+    mask_add: np.ndarray     # [B, 1, 1, S] fp32: 0 valid, -10000 padded
+    meta: dict = field(default_factory=dict)
+
+
+def make_workload(cfg, batch, seq, seed=0, length_range=None, randomize_affine=False, num_layers=None):
+    """Seeded weights + inputs.  `length_range=(lo, hi)` draws integer lengths ~ Uniform[lo, hi]; None = all full."""
+    rng = np.random.default_rng(seed)
+    H, F = cfg.hidden, cfg.ffn
+    L = cfg.layers if num_layers is None else num_layers
+    ws = []
+    for _ in range(L):
+        def w(k, n):
+            return rng.normal(0.0, 0.02, (k, n)).astype(np.float32)
+        wq, wk, wv, wo = w(H, H), w(H, H), w(H, H), w(H, H)
+        w1 = w(H, F) if cfg.with_ffn else None
+        w2 = w(F, H) if cfg.with_ffn else None
+        z = lambda n: np.zeros((n,), np.float32)  # noqa: E731
+        o = lambda n: np.ones((n,), np.float32)   # noqa: E731
+        lw = LayerWeights(wq, wk, wv, wo, z(H), z(H), z(H), z(H), o(H), z(H))
+        if cfg.with_ffn:
+            lw.w1, lw.b1, lw.w2, lw.b2, lw.ln2_g, lw.ln2_b = w1, z(F), w2, z(H), o(H), z(H)
+        ws.append(lw)
+    x = rng.normal(0.0, 1.0, (batch, seq, H)).astype(np.float32)
+    if length_range is None:
+        lengths = np.full((batch,), seq, np.int64)
+    else:
+        lengths = rng.integers(length_range[0], length_range[1] + 1, size=(batch,))
+    if randomize_affine:
+        r2 = np.random.default_rng(seed + 7919)
+        for lw in ws:
+            for name in ("bq", "bk", "bv", "bo", "b1", "b2"):
+                a = getattr(lw, name)
+                if a is not None:
+                    setattr(lw, name, r2.normal(0, 0.1, a.shape).astype(np.float32))
+            for name in ("ln1_g", "ln2_g"):
+                a = getattr(lw, name)
+                if a is not None:
+                    setattr(lw, name, (1.0 + r2.normal(0, 0.1, a.shape)).astype(np.float32))
+            for name in ("ln1_b", "ln2_b"):
+                a = getattr(lw, name)
+                if a is not None:
+                    setattr(lw, name, r2.normal(0, 0.1, a.shape).astype(np.float32))
+    mask = np.zeros((batch, 1, 1, seq), np.float32)
+    for b in range(batch):
+        mask[b, 0, 0, int(lengths[b]):] = -10000.0
+    return Workload(cfg, ws, x, np.asarray(lengths, np.int64), mask,
+                    {"batch": batch, "seq": seq, "seed": seed, "layers": L})
+
+
+# The five benchmark configurations (sizes only; `scale` shrinks batch for tests that must finish in seconds).
+def config_workload(index, batch=None, num_layers=None, dtype_note=None):
+    if index == 1:
+        cfg = EncoderConfig(1, 768, 12, 3072, with_ffn=False)
+        return make_workload(cfg, batch or 1, 128, seed=0)
+    if index == 2:
+        return make_workload(BERT_BASE, batch or 64, 128, seed=0, num_layers=num_layers)
+    if index == 3:
+        return make_workload(BERT_BASE, batch or 32, 256, seed=0, length_range=(16, 256), num_layers=num_layers)
+    if index == 4:
+        return make_workload(BERT_LARGE, batch or 64, 384, seed=0, length_range=(128, 384), num_layers=num_layers)
+    if index == 5:
+        return make_workload(BERT_BASE, batch or 1024, 128, seed=0, num_layers=num_layers)
+    raise ValueError("config index 1..5")
+
+
+# --------------------------------------------------------------------------------------------- TNN file writers
+def _pstr(s):
+    b = s.encode()
+    return struct.pack("<i", len(b)) + b
+
+
+def _raw(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    dims = a.shape
+    return (struct.pack("<Iii", MAGIC_RAW, 0, a.nbytes) + struct.pack("<i", len(dims)) +
+            b"".join(struct.pack("<i", d) for d in dims) + a.tobytes())
+
+
+def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"):
+    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name."""
+    cfg = wl.cfg
+    B, S, H = wl.x.shape
+    NH, D, F = cfg.heads, cfg.head_dim, cfg.ffn
+    layers, res, consts = [], [], {}
+
+    def layer(t, name, ins, outs, params=""):
+        layers.append('"%s %s %d %d %s %s %s,"' % (t, name, len(ins), len(outs), " ".join(ins), " ".join(outs), params))
+
+    def resource(t, name, arr):
+        res.append(struct.pack("<i", _TYPE_ID[t]) + _pstr(t) + _pstr(name) + _raw(arr))
+
+    def linear(name, x, w, b):
+        layer("MatMul", name + "_mm", [x], [name + "_mm"], "1")
+        resource("MatMul", name + "_mm", w)
+        layer("Add", name + "_b", [name + "_mm"], [name + "_b"], "1")
+        resource("Add", name + "_b", b.reshape(-1))   # explicit [N] dims: see MultidirBroadcastLayer's guess rule
+        return name + "_b"
+
+    def lnorm(name, x, g, be):
+        consts[name + "_g"] = g
+        consts[name + "_be"] = be
+        layer("LayerNorm", name, [x, name + "_g", name + "_be"], [name], "1 %.1e" % cfg.ln_eps)
+        return name
+
+    x = input_name
+    for li, lw in enumerate(wl.weights):
+        p = "l%d_" % li
+        for n, w, b, perm in (("q", lw.wq, lw.bq, "0 2 1 3"), ("k", lw.wk, lw.bk, "0 2 3 1"),
+                              ("v", lw.wv, lw.bv, "0 2 1 3")):
+            o = linear(p + n, x, w, b)
+            layer("Reshape", p + n + "_r", [o], [p + n + "_r"], "0 4 4 0 0 %d %d 0" % (NH, D))
+            layer("Permute", p + n + "_p", [p + n + "_r"], [p + n + "_p"], "4 " + perm)
+        layer("MatMul", p + "qk", [p + "q_p", p + "k_p"], [p + "qk"], "-1")
+        layer("Mul", p + "qk_s", [p + "qk"], [p + "qk_s"], "1")
+        resource("Mul", p + "qk_s", np.array([1.0 / np.sqrt(D)], np.float32))
+        layer("Add", p + "qk_m", [p + "qk_s", mask_name], [p + "qk_m"], "-1")
+        layer("Softmax", p + "sm", [p + "qk_m"], [p + "sm"], "3")
+        layer("MatMul", p + "ctx", [p + "sm", p + "v_p"], [p + "ctx"], "-1")
+        layer("Permute", p + "ctx_p", [p + "ctx"], [p + "ctx_p"], "4 0 2 1 3")
+        layer("Reshape", p + "ctx_r", [p + "ctx_p"], [p + "ctx_r"], "0 3 3 0 0 %d 0" % H)
+        o = linear(p + "o", p + "ctx_r", lw.wo, lw.bo)
+        layer("Add", p + "res1", [o, x], [p + "res1"], "-1")
+        a = lnorm(p + "ln1", p + "res1", lw.ln1_g, lw.ln1_b)
+        if cfg.with_ffn:
+            f1 = linear(p + "f1", a, lw.w1, lw.b1)
+            layer("GELU", p + "gelu", [f1], [p + "gelu"])
+            f2 = linear(p + "f2", p + "gelu", lw.w2, lw.b2)
+            layer("Add", p + "res2", [f2, a], [p + "res2"], "-1")
+            x = lnorm(p + "ln2", p + "res2", lw.ln2_g, lw.ln2_b)
+        else:
+            x = a
+    blobs = set()
+    for ln in layers:
+        t = ln.strip('",').split()
+        ni, no = int(t[2]), int(t[3])
+        blobs.update(t[4:4 + ni + no])
+    proto = ['"1 %d 1 %d ,"' % (len(blobs), MAGIC),
+             '"%s %d 1 1 %d : %s %d %d %d ,"' % (mask_name, B, S, input_name, B, S, H),
+             '" ' + " ".join(sorted(blobs)) + ' ,"',
+             '"%s ,"' % x,
+             '" %d ,"' % len(layers)] + layers
+    with open(proto_path, "w") as fh:
+        fh.write("\n".join(proto) + "\n")
+    m = struct.pack("<I", MAGIC) + struct.pack("<i", len(res)) + b"".join(res)
+    m += struct.pack("<Ii", MAGIC, len(consts)) + b"".join(_pstr(k) + _raw(v) for k, v in consts.items())
+    with open(model_path, "wb") as fh:
+        fh.write(m)
+    return x
+
+
+# --------------------------------------------------------------------------------------------- FLOP accounting
+def layer_flops(seq_len, hidden, ffn=None, with_ffn=True):
+    """Algorithmic FLOPs of one encoder layer for one sequence of `seq_len` tokens (2 per MAC; GEMMs + QK^T + PV)."""
+    ffn = 4 * hidden if ffn is None else ffn
+    f = 8 * seq_len * hidden * hidden + 4 * seq_len * seq_len * hidden
+    if with_ffn:
+        f += 4 * seq_len * hidden * ffn
+    return f
+
+
+def workload_flops(wl, effective=True):
+    cfg = wl.cfg
+    S = wl.x.shape[1]
+    L = len(wl.weights)
+    lens = wl.lengths if effective else np.full_like(wl.lengths, S)
+    return int(sum(L * layer_flops(int(n), cfg.hidden, cfg.ffn, cfg.with_ffn) for n in lens))

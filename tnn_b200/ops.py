@@ -1,0 +1,135 @@
+"""Host-side operator wrappers over the C ABI: one function per fused layer of the path.
+
+Names and argument meaning follow the fused TNN layers (FusedLinear, FusedAttention, LayerNorm) that the graph pass
+emits; tensors are torch CUDA tensors used as device buffers.  Every function launches through `extern "C"` entry
+points of libtnn_b200.so on the current torch stream; nothing here computes with torch.
+"""
+import ctypes
+
+import torch
+
+from . import capi
+from .capi import EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL  # noqa: F401
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("tnn_b200 operators take CUDA tensors only (there is no CPU path)")
+
+
+def pack_weight(w_kn, dtype=torch.float16, out=None):
+    """fp32 `[K, N]` (TNN MatMul weight layout, y = x.W) -> `dtype` `[N, K]` on the device."""
+    _require_cuda(w_kn)
+    assert w_kn.dtype == torch.float32 and w_kn.dim() == 2 and w_kn.stride(1) == 1
+    K, N = w_kn.shape
+    if out is None:
+        out = torch.empty((N, K), dtype=dtype, device=w_kn.device)
+    assert out.shape[0] == N and out.shape[1] == K and out.stride(1) == 1
+    rc = capi.lib().b200_pack_weight(w_kn.data_ptr(), K, N, w_kn.stride(0), out.data_ptr(), out.stride(0),
+                                     capi.dtype_code(out.dtype), capi.stream_ptr())
+    capi.check(rc, "b200_pack_weight")
+    return out
+
+
+def convert(src, dtype, out=None):
+    _require_cuda(src)
+    assert src.is_contiguous()
+    if out is None:
+        out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    assert out.is_contiguous() and out.numel() == src.numel()
+    rc = capi.lib().b200_convert(src.data_ptr(), capi.dtype_code(src.dtype), out.data_ptr(),
+                                 capi.dtype_code(out.dtype), src.numel(), capi.stream_ptr())
+    capi.check(rc, "b200_convert")
+    return out
+
+
+def linear(x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out_dtype=None, out=None, block_n=0):
+    """y[M,N] = epilogue(x[M,K] . w_nk[N,K]^T + bias (+ residual)); x may be `[..., K]`."""
+    _require_cuda(x, w_nk, bias, residual, out)
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    M = x2.shape[0]
+    N = w_nk.shape[0]
+    assert w_nk.shape[1] == K and x2.stride(1) == 1 and w_nk.stride(1) == 1
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (N,), dtype=out_dtype, device=x.device)
+    y2 = out.reshape(-1, N)
+    d = capi.LinearDesc()
+    d.x, d.w_nk, d.bias, d.y = x2.data_ptr(), w_nk.data_ptr(), capi.ptr(bias), y2.data_ptr()
+    d.M, d.N, d.K = M, N, K
+    d.ldx, d.ldw, d.ldy = x2.stride(0), w_nk.stride(0), y2.stride(0)
+    if residual is not None:
+        r2 = residual.reshape(-1, N)
+        assert r2.dtype == x.dtype and r2.stride(1) == 1
+        d.residual, d.ldr = r2.data_ptr(), r2.stride(0)
+    d.dtype, d.out_dtype = capi.dtype_code(x.dtype), capi.dtype_code(out.dtype)
+    d.epilogue, d.block_n = epilogue, block_n
+    rc = capi.lib().b200_linear_fwd(ctypes.byref(d), capi.stream_ptr())
+    capi.check(rc, "b200_linear_fwd")
+    return out
+
+
+def mask_to_kv_len(mask_add, exclude_below=-5000.0, out=None):
+    """mask_add fp32 `[B, S]` (or `[B,1,1,S]`) -> int32 `[B]`."""
+    _require_cuda(mask_add)
+    S = mask_add.shape[-1]
+    m2 = mask_add.reshape(-1, S)
+    assert m2.is_contiguous() and m2.dtype == torch.float32
+    if out is None:
+        out = torch.empty((m2.shape[0],), dtype=torch.int32, device=mask_add.device)
+    rc = capi.lib().b200_mask_to_kv_len(m2.data_ptr(), m2.shape[0], S, exclude_below, out.data_ptr(),
+                                        capi.stream_ptr())
+    capi.check(rc, "b200_mask_to_kv_len")
+    return out
+
+
+def attention(qkv, heads, mask_add=None, kv_len=None, scale=None, exclude_below=-5000.0, out=None):
+    """qkv `[B, S, 3*heads*64]` packed (Q | K | V along the last axis) -> context `[B, S, heads*64]`."""
+    _require_cuda(qkv, mask_add, kv_len, out)
+    B, S, W = qkv.shape
+    H = heads * 64
+    assert W == 3 * H and qkv.stride(2) == 1 and qkv.stride(0) == S * qkv.stride(1)
+    if out is None:
+        out = torch.empty((B, S, H), dtype=qkv.dtype, device=qkv.device)
+    es = qkv.element_size()
+    d = capi.AttentionDesc()
+    d.q, d.k, d.v = qkv.data_ptr(), qkv.data_ptr() + H * es, qkv.data_ptr() + 2 * H * es
+    d.ldq = d.ldk = d.ldv = qkv.stride(1)
+    d.out, d.ldo = out.data_ptr(), out.stride(1)
+    if mask_add is not None:
+        m2 = mask_add.reshape(B, S)
+        assert m2.is_contiguous() and m2.dtype == torch.float32
+        d.mask_add = m2.data_ptr()
+    if kv_len is not None:
+        assert kv_len.dtype == torch.int32 and kv_len.numel() == B
+        d.kv_len = kv_len.data_ptr()
+    d.B, d.S, d.heads, d.head_dim = B, S, heads, 64
+    d.dtype = capi.dtype_code(qkv.dtype)
+    d.scale = float(scale if scale is not None else 0.125)
+    d.mask_exclude_below = float(exclude_below)
+    rc = capi.lib().b200_attention_fwd(ctypes.byref(d), capi.stream_ptr())
+    capi.check(rc, "b200_attention_fwd")
+    return out
+
+
+def add_layernorm(x, gamma, beta, eps, residual=None, out_dtype=None, out=None):
+    _require_cuda(x, gamma, beta, residual, out)
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    assert x2.stride(1) == 1 and gamma.dtype == torch.float32 and beta.dtype == torch.float32
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    y2 = out.reshape(-1, H)
+    d = capi.LayerNormDesc()
+    d.x, d.gamma, d.beta, d.y = x2.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y2.data_ptr()
+    d.rows, d.H, d.ldx, d.ldy = x2.shape[0], H, x2.stride(0), y2.stride(0)
+    if residual is not None:
+        r2 = residual.reshape(-1, H)
+        assert r2.dtype == x.dtype
+        d.residual, d.ldr = r2.data_ptr(), r2.stride(0)
+    d.in_dtype, d.out_dtype, d.eps = capi.dtype_code(x.dtype), capi.dtype_code(out.dtype), float(eps)
+    rc = capi.lib().b200_add_layernorm_fwd(ctypes.byref(d), capi.stream_ptr())
+    capi.check(rc, "b200_add_layernorm_fwd")
+    return out

@@ -1,0 +1,170 @@
+// C ABI over TNN's public C++ API (TNN::Init / CreateInst / Instance::Forward, include/tnn/core/tnn.h:34-67,
+// include/tnn/core/instance.h:42-144) so that a host without C++ bindings — the Python tests and the benchmark — can
+// drive a TNN instance on any registered device: DEVICE_NAIVE / DEVICE_X86 (the reference's CPU implementations) or
+// DEVICE_CUDA (served by the tnn_b200 plug-in once it has been loaded into the process).
+// Only public TNN headers are used.  Nothing here computes.
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "tnn/core/common.h"
+#include "tnn/core/instance.h"
+#include "tnn/core/mat.h"
+#include "tnn/core/tnn.h"
+#include "tnn/utils/blob_converter.h"
+#include "tnn/utils/dims_vector_utils.h"
+
+using namespace TNN_NS;
+
+namespace {
+
+struct Handle {
+    TNN net;
+    std::shared_ptr<Instance> inst;
+    DeviceType device;
+    std::string last_error;
+};
+
+bool read_file(const char* path, std::string* out) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f) return false;
+    std::stringstream ss;
+    ss << f.rdbuf();
+    *out = ss.str();
+    return true;
+}
+
+void set_err(char* err, int errlen, const std::string& msg) {
+    if (err && errlen > 0) {
+        std::snprintf(err, static_cast<size_t>(errlen), "%s", msg.c_str());
+    }
+}
+
+int64_t count(const DimsVector& d) {
+    int64_t n = 1;
+    for (int x : d) n *= x;
+    return n;
+}
+
+}  // namespace
+
+extern "C" {
+
+#define TNNC_API __attribute__((visibility("default")))
+
+// device: 0 = DEVICE_NAIVE, 1 = DEVICE_X86, 2 = DEVICE_CUDA.  precision: -1 auto, 0 normal, 1 high, 2 low.
+// Returns an opaque handle or NULL (message in err).
+TNNC_API void* tnnc_create(const char* proto_path, const char* model_path, int device, int device_id, int precision,
+                           int cpu_threads, char* err, int errlen) {
+    std::unique_ptr<Handle> h(new Handle);
+    ModelConfig mc;
+    mc.model_type = MODEL_TYPE_TNN;
+    std::string proto, model;
+    if (!read_file(proto_path, &proto) || !read_file(model_path, &model)) {
+        set_err(err, errlen, "cannot read proto/model file");
+        return nullptr;
+    }
+    mc.params = {proto, model};
+    Status st = h->net.Init(mc);
+    if (st != TNN_OK) {
+        set_err(err, errlen, "TNN::Init: " + st.description());
+        return nullptr;
+    }
+    NetworkConfig nc;
+    nc.device_type = device == 0 ? DEVICE_NAIVE : (device == 1 ? DEVICE_X86 : DEVICE_CUDA);
+    nc.device_id = device_id;
+    nc.network_type = NETWORK_TYPE_DEFAULT;
+    nc.precision = static_cast<Precision>(precision);
+    h->device = nc.device_type;
+    h->inst = h->net.CreateInst(nc, st);
+    if (st != TNN_OK || !h->inst) {
+        set_err(err, errlen, "CreateInst: " + st.description());
+        return nullptr;
+    }
+    if (cpu_threads > 0) h->inst->SetCpuNumThreads(cpu_threads);
+    return h.release();
+}
+
+TNNC_API void tnnc_destroy(void* handle) { delete static_cast<Handle*>(handle); }
+
+TNNC_API const char* tnnc_last_error(void* handle) { return static_cast<Handle*>(handle)->last_error.c_str(); }
+
+// Copies `n` floats into the named input blob (host blobs: plain copy; CUDA blobs: through the blob converter, as
+// TNNTest does, test/test.cc:125-152).  Returns 0 or a TNN status code.
+TNNC_API int tnnc_set_input(void* handle, const char* name, const float* data, int64_t n) {
+    Handle* h = static_cast<Handle*>(handle);
+    BlobMap blobs;
+    Status st = h->inst->GetAllInputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    auto it = blobs.find(name);
+    if (it == blobs.end()) { h->last_error = std::string("no input named ") + name; return -1; }
+    Blob* blob = it->second;
+    const DimsVector dims = blob->GetBlobDesc().dims;
+    if (count(dims) != n) { h->last_error = "input element count mismatch"; return -2; }
+    if (h->device == DEVICE_CUDA) {
+        auto mat = std::make_shared<Mat>(DEVICE_NAIVE, NCHW_FLOAT, dims, const_cast<float*>(data));
+        MatConvertParam param;
+        st = h->inst->SetInputMat(mat, param, name);
+        if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    } else {
+        BlobHandle bh = blob->GetHandle();
+        std::memcpy(static_cast<char*>(bh.base) + bh.bytes_offset, data, static_cast<size_t>(n) * sizeof(float));
+    }
+    return 0;
+}
+
+TNNC_API int tnnc_forward(void* handle) {
+    Handle* h = static_cast<Handle*>(handle);
+    Status st = h->inst->Forward();
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    return 0;
+}
+
+// Runs Forward `iters` times and returns the mean wall time per call in milliseconds (negative on error).
+TNNC_API double tnnc_time_forward(void* handle, int warmup, int iters) {
+    Handle* h = static_cast<Handle*>(handle);
+    for (int i = 0; i < warmup; ++i)
+        if (h->inst->Forward() != TNN_OK) return -1.0;
+    auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < iters; ++i)
+        if (h->inst->Forward() != TNN_OK) return -1.0;
+    auto t1 = std::chrono::steady_clock::now();
+    return std::chrono::duration<double, std::milli>(t1 - t0).count() / (iters > 0 ? iters : 1);
+}
+
+// Output blob -> host floats.  dims_out receives up to 8 dims; returns the element count, or a negative error.
+TNNC_API int64_t tnnc_get_output(void* handle, const char* name, float* dst, int64_t capacity, int* dims_out,
+                                 int* ndims_out) {
+    Handle* h = static_cast<Handle*>(handle);
+    BlobMap blobs;
+    Status st = h->inst->GetAllOutputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return -1; }
+    auto it = (name && name[0]) ? blobs.find(name) : blobs.begin();
+    if (it == blobs.end()) { h->last_error = "no such output"; return -1; }
+    Blob* blob = it->second;
+    const DimsVector dims = blob->GetBlobDesc().dims;
+    const int64_t n = count(dims);
+    if (ndims_out) *ndims_out = static_cast<int>(dims.size());
+    if (dims_out)
+        for (size_t i = 0; i < dims.size() && i < 8; ++i) dims_out[i] = dims[i];
+    if (!dst) return n;
+    if (capacity < n) { h->last_error = "output buffer too small"; return -2; }
+    if (h->device == DEVICE_CUDA) {
+        std::shared_ptr<Mat> mat;
+        MatConvertParam param;
+        st = h->inst->GetOutputMat(mat, param, it->first, DEVICE_NAIVE, NCHW_FLOAT);
+        if (st != TNN_OK || !mat) { h->last_error = st.description(); return -3; }
+        std::memcpy(dst, mat->GetData(), static_cast<size_t>(n) * sizeof(float));
+    } else {
+        BlobHandle bh = blob->GetHandle();
+        std::memcpy(dst, static_cast<char*>(bh.base) + bh.bytes_offset, static_cast<size_t>(n) * sizeof(float));
+    }
+    return n;
+}
+
+}  // extern "C"
