@@ -1,0 +1,392 @@
+#!/usr/bin/env python3
+"""Benchmark of the transformer-encoder attention path: BERT-base, sequence length 128, sequences/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one Forward of the fused 12-layer encoder over one batch (fp32 activations in, fp16 fused region, fp32 out).
+Per GPU the batch is the benchmark's config 2 (64 sequences x 128 tokens); with N GPUs every rank runs its own batch
+(independent replicas, no collective on the data path), so `value` = N * 64 * K / max-over-ranks(device time).
+
+Keys of the JSON line beyond the base contract:
+  roofline     the projection/FFN GEMM kernel (dominant): algorithmic FLOPs of its launches / their CUDA-event time
+  cpu_baseline the reference's own DEVICE_X86 implementation timed on this host on a bounded sample (rank 0, N = 1)
+  e2e          the same metric with HOST buffers: pinned fp32 input -> H2D -> Forward -> D2H of the fp32 output per step
+`--impl reference` times the reference's CPU implementation of the same path with all host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "bert_base_seq128_sequences_per_s"
+UNIT = "sequences/s"
+BATCH_PER_GPU = 64
+SEQ = 128
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"tflops": float(p["bf16_tflops"]), "tflops_sustained": float(p.get("bf16_tflops_sustained", 0.0)),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------ clocks sampler
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return {"sm_mhz": (statistics.median(self.samples) if self.samples else None),
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU reference
+def cpu_reference_seq_per_s(sequences_per_instance, instances, layers=12, warmup=1, iters=1):
+    """Times the reference's DEVICE_X86 encoder (oracle/_ref/libTNN.so) on `instances` host threads, each running its
+    own TNN instance over `sequences_per_instance` sequences.  Returns (seq/s, kind, description)."""
+    from tnn_b200 import model_synth
+    from oracle import tnn_ref
+    wl = model_synth.make_workload(model_synth.BERT_BASE, sequences_per_instance, SEQ, seed=0, num_layers=layers)
+    if not tnn_ref.available():
+        # the numpy restatement of the same arithmetic (single process; numpy's BLAS threads)
+        from oracle import bert_oracle
+        bert_oracle.encoder_forward(wl)
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            bert_oracle.encoder_forward(wl)
+        dt = (time.perf_counter() - t0) / iters
+        return sequences_per_instance / dt, "port", "numpy restatement, %d sequences x %d layers" % (
+            sequences_per_instance, layers)
+    import tempfile
+    d = tempfile.mkdtemp(prefix="tnnref_bench_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    model_synth.write_tnn_model(wl, proto, model)
+    insts = []
+    for _ in range(instances):
+        inst = tnn_ref.TnnInstance(proto, model, device=tnn_ref.DEVICE_X86, threads=1)
+        inst.set_input("x", wl.x)
+        inst.set_input("mask", wl.mask_add)
+        insts.append(inst)
+    results = [None] * instances
+
+    def run(i):
+        results[i] = insts[i].time_forward(warmup, iters)   # ctypes releases the GIL inside the call
+
+    t0 = time.perf_counter()
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(instances)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    wall = time.perf_counter() - t0
+    ms = max(results)
+    for inst in insts:
+        inst.close()
+    seq_per_s = instances * sequences_per_instance / (ms / 1e3)
+    desc = ("reference DEVICE_X86 fp32, %d instance(s) x %d sequences x %d layers, S=%d, %d warm-up + %d timed "
+            "Forward (%.1f s wall)" % (instances, sequences_per_instance, layers, SEQ, warmup, iters, wall))
+    return seq_per_s, "reference", desc
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cores = host_cores()
+    instances = max(1, min(cores, 32))
+    t0 = time.perf_counter()
+    steps = max(1, min(args.steps, 3))
+    value, kind, desc = cpu_reference_seq_per_s(2, instances, layers=12, warmup=1, iters=steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": 1, "ms_per_step": 1e3 * instances * 2 / value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BERT-base 12-layer encoder, S=128, fp32, reference DEVICE_X86 on host cores; "
+                               "each step = %d instances x 2 sequences" % instances},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": instances, "kind": kind, "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from tnn_b200 import capi, model_synth, ops
+    from tnn_b200.encoder import Encoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    capi.lib()  # fail loudly here if the CUDA library is missing
+
+    B = args.batch
+    wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
+    cfg = wl.cfg
+    enc = Encoder.from_workload(wl, torch.float16, dev)
+    x_dev = torch.from_numpy(wl.x).to(dev)
+    mask_dev = torch.from_numpy(wl.mask_add.reshape(B, SEQ)).to(dev).contiguous()
+    kv_len = ops.mask_to_kv_len(mask_dev)
+    hidden = torch.empty((B, SEQ, cfg.hidden), dtype=torch.float16, device=dev)
+    out_dev = torch.empty((B, SEQ, cfg.hidden), dtype=torch.float32, device=dev)
+
+    def step_resident():
+        ops.convert(x_dev, torch.float16, out=hidden)
+        enc.forward_hidden(hidden, mask_dev, kv_len)
+        ops.convert(hidden, torch.float32, out=out_dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step_resident()
+    barrier()
+
+    # ---- timed region: device-resident inputs
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = capi.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = capi.launch_count() - launches0
+    clocks = sampler.stop()
+    if capi.device_status() != capi.OK:
+        raise SystemExit("device status word set: a bounded wait ran out")
+
+    # ---- e2e: host buffers, copies inside the timed region (double-buffered so copies overlap the previous step)
+    x_host = torch.from_numpy(wl.x).pin_memory()
+    out_host = [torch.empty((B, SEQ, cfg.hidden), dtype=torch.float32).pin_memory() for _ in range(2)]
+    x_in = [torch.empty_like(x_dev) for _ in range(2)]
+    o_out = [torch.empty_like(out_dev) for _ in range(2)]
+    hid = [torch.empty_like(hidden) for _ in range(2)]
+    s_copy_in, s_copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_main = torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_loop(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_copy_in):
+                s_copy_in.wait_event(ev_free[b])           # the compute that last read x_in[b] is done
+                x_in[b].copy_(x_host, non_blocking=True)
+                ev_in[b].record(s_copy_in)
+            s_main.wait_event(ev_in[b])
+            s_main.wait_event(ev_out[b])                    # o_out[b] has been drained to the host
+            ops.convert(x_in[b], torch.float16, out=hid[b])
+            ev_free[b].record(s_main)
+            enc.forward_hidden(hid[b], mask_dev, kv_len)
+            ops.convert(hid[b], torch.float32, out=o_out[b])
+            ev_done[b].record(s_main)
+            with torch.cuda.stream(s_copy_out):
+                s_copy_out.wait_event(ev_done[b])
+                out_host[b].copy_(o_out[b], non_blocking=True)
+                ev_out[b].record(s_copy_out)
+
+    e2e_loop(4)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_loop(args.steps)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    h2d = x_host.numel() * 4
+    d2h = out_host[0].numel() * 4
+
+    # ---- roofline of the dominant kernel (the GEMM): an instrumented pass with an event pair around every launch
+    tokens = B * SEQ
+    H, F = cfg.hidden, cfg.ffn
+    shapes = {"qkv": (tokens, 3 * H, H), "out_proj": (tokens, H, H), "ffn1": (tokens, F, H), "ffn2": (tokens, H, F)}
+    ev_pairs = {k: [] for k in list(shapes) + ["attention", "layernorm"]}
+
+    def timed(name, fn):
+        a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b2.record()
+        ev_pairs[name].append((a, b2))
+        return r
+
+    def instrumented_step():
+        h = ops.convert(x_dev, torch.float16, out=hidden)
+        for L in enc.layers:
+            qkv = timed("qkv", lambda: ops.linear(h, L["w_qkv"], L["b_qkv"]))
+            ctx = timed("attention", lambda: ops.attention(qkv, cfg.heads, mask_dev, kv_len))
+            t = timed("out_proj", lambda: ops.linear(ctx, L["w_o"], L["b_o"], residual=h,
+                                                     epilogue=ops.EPI_BIAS_RESIDUAL))
+            a = timed("layernorm", lambda: ops.add_layernorm(t, L["ln1_g"], L["ln1_b"], cfg.ln_eps))
+            f1 = timed("ffn1", lambda: ops.linear(a, L["w_ffn1"], L["b_ffn1"], epilogue=ops.EPI_BIAS_GELU))
+            t2 = timed("ffn2", lambda: ops.linear(f1, L["w_ffn2"], L["b_ffn2"], residual=a,
+                                                  epilogue=ops.EPI_BIAS_RESIDUAL))
+            h = timed("layernorm", lambda: ops.add_layernorm(t2, L["ln2_g"], L["ln2_b"], cfg.ln_eps))
+
+    for _ in range(2):
+        instrumented_step()
+    torch.cuda.synchronize()
+    for k in ev_pairs:
+        ev_pairs[k].clear()
+    for _ in range(min(args.steps, 20)):
+        instrumented_step()
+    torch.cuda.synchronize()
+    kernel_ms = {k: [a.elapsed_time(b2) for a, b2 in v] for k, v in ev_pairs.items()}
+    gemm_flops = gemm_ms = 0.0
+    per_shape = {}
+    for k, (m, n, kk) in shapes.items():
+        fl = 2.0 * m * n * kk
+        tms = statistics.mean(kernel_ms[k])
+        per_shape[k] = {"M": m, "N": n, "K": kk, "ms": round(tms, 4), "tflops": round(fl / tms / 1e9, 1)}
+        gemm_flops += fl * len(kernel_ms[k])
+        gemm_ms += sum(kernel_ms[k])
+    peaks = measured_peaks()
+    achieved = gemm_flops / gemm_ms / 1e9
+    n_gemm = sum(len(kernel_ms[k]) for k in shapes)
+    attn_ms = statistics.mean(kernel_ms["attention"])
+    attn_flops = 4.0 * SEQ * SEQ * 64 * cfg.heads * B
+
+    # ---- reduce over ranks
+    ms_t = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_total_max, e2e_ms_max = float(ms_t[0]), float(ms_t[1])
+    seqs = world * B * args.steps
+    value = seqs / (ms_total_max / 1e3)
+    e2e_value = seqs / (e2e_ms_max / 1e3)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, kind, desc = cpu_reference_seq_per_s(8, 1, layers=12, warmup=1, iters=2)
+        cpu_baseline = {"value": v, "unit": UNIT, "cores": 1, "kind": kind, "sample": desc}
+
+    if rank == 0:
+        flops_per_seq = model_synth.layer_flops(SEQ, H, F) * len(enc.layers)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_total_max / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "config 2: BERT-base 12-layer encoder, batch %d x seq %d per GPU, fp16 weights, "
+                                   "all sequences full length, fp32 activations in/out" % (B, SEQ),
+                       "batch_per_gpu": B, "seq_len": SEQ, "layers": len(enc.layers),
+                       "parallelism": "independent replicas, batch-sharded, no collective",
+                       "l2": "per-step working set (170 MB fp16 weights + activations) exceeds the 126 MB L2; "
+                             "no explicit flush"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "pinned fp32 host buffers, copies double-buffered on side streams, wall clock"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "kernel": "linear_kernel (projection/FFN GEMM, tcgen05)",
+                         "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"], "peak_source": "of " + peaks["source"] + " (burst)",
+                         "peak_sustained": peaks["tflops_sustained"],
+                         "flops_per_launch_avg": gemm_flops / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm,
+                         "launches_timed": n_gemm, "per_shape": per_shape, "traffic": None},
+            "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
+                                 "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
+            "layernorm_kernel": {"ms": statistics.mean(kernel_ms["layernorm"]),
+                                 "gbs": tokens * H * 2 * 2 / statistics.mean(kernel_ms["layernorm"]) / 1e6},
+            "model_tflops": value * flops_per_seq / 1e12,
+            "model_frac_of_tensor_peak": value * flops_per_seq / 1e12 / peaks["tflops"] / world,
+            "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="sequences per GPU per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,95 @@
+"""Run one kernel of the path a few times in isolation (for `ncu` captures and quick timing).
+
+    python -m tnn_b200.profile_case linear --M 8192 --N 2304 --K 768 [--epilogue gelu] [--block-n 256] [--iters 5]
+    python -m tnn_b200.profile_case attention --B 64 --S 128 --heads 12
+    python -m tnn_b200.profile_case layernorm --rows 8192 --H 768
+    python -m tnn_b200.profile_case encoder --B 64 --S 128 --layers 2
+
+Prints the mean CUDA-event time per launch.  Operands are seeded random device tensors; sizes default to the
+benchmark's config 2 shapes.
+"""
+import argparse
+
+import torch
+
+from . import capi, ops
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["linear", "attention", "layernorm", "encoder"])
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--N", type=int, default=2304)
+    ap.add_argument("--K", type=int, default=768)
+    ap.add_argument("--epilogue", default="bias", choices=["bias", "gelu", "residual"])
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--B", type=int, default=64)
+    ap.add_argument("--S", type=int, default=128)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--H", type=int, default=768)
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    a = ap.parse_args()
+    dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    capi.lib()
+
+    if a.kernel == "linear":
+        x = torch.randn(a.M, a.K, device=dev).to(dt)
+        w = (torch.randn(a.N, a.K, device=dev) * 0.02).to(dt)
+        b = torch.randn(a.N, device=dev)
+        r = torch.randn(a.M, a.N, device=dev).to(dt) if a.epilogue == "residual" else None
+        y = torch.empty(a.M, a.N, device=dev, dtype=dt)
+        epi = {"bias": ops.EPI_BIAS, "gelu": ops.EPI_BIAS_GELU, "residual": ops.EPI_BIAS_RESIDUAL}[a.epilogue]
+        fn = lambda: ops.linear(x, w, b, residual=r, epilogue=epi, out=y, block_n=a.block_n)  # noqa: E731
+        work = 2.0 * a.M * a.N * a.K
+        unit = "TFLOP/s"
+    elif a.kernel == "attention":
+        H = a.heads * 64
+        qkv = torch.randn(a.B, a.S, 3 * H, device=dev).to(dt)
+        mask = torch.zeros(a.B, a.S, device=dev)
+        kv = ops.mask_to_kv_len(mask)
+        out = torch.empty(a.B, a.S, H, device=dev, dtype=dt)
+        fn = lambda: ops.attention(qkv, a.heads, mask, kv, out=out)  # noqa: E731
+        work = 4.0 * a.S * a.S * 64 * a.heads * a.B
+        unit = "TFLOP/s"
+    elif a.kernel == "layernorm":
+        x = torch.randn(a.rows, a.H, device=dev).to(dt)
+        g = torch.ones(a.H, device=dev)
+        be = torch.zeros(a.H, device=dev)
+        y = torch.empty_like(x)
+        fn = lambda: ops.add_layernorm(x, g, be, 1e-12, out=y)  # noqa: E731
+        work = 2.0 * a.rows * a.H * 2 * 1e3   # bytes, scaled so that the print below reads GB/s
+        unit = "GB/s"
+    else:
+        from . import model_synth
+        from .encoder import Encoder
+        wl = model_synth.make_workload(model_synth.BERT_BASE, a.B, a.S, seed=0, num_layers=a.layers)
+        enc = Encoder.from_workload(wl, dt, dev)
+        hidden = torch.from_numpy(wl.x).to(dev).to(dt)
+        mask = torch.from_numpy(wl.mask_add.reshape(a.B, a.S)).to(dev)
+        kv = ops.mask_to_kv_len(mask)
+        fn = lambda: enc.forward_hidden(hidden, mask, kv)  # noqa: E731
+        work = float(model_synth.workload_flops(wl))
+        unit = "TFLOP/s"
+
+    for _ in range(a.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.iters
+    print("%s: %.4f ms per call, %.1f %s, device status %d" % (a.kernel, ms, work / ms / 1e9, unit,
+                                                              capi.device_status()))
+
+
+if __name__ == "__main__":
+    main()
