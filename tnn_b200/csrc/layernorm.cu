@@ -103,6 +103,117 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(B200LayerNormDesc d)
     }
 }
 
+// Persistent variant for H <= 1024 (NV <= 4): a warp walks rows with a grid stride, keeps its gamma/beta slice in
+// registers for all of them (the generic kernel re-reads 4x more gamma/beta bytes than activation bytes per row) and
+// has the next row's loads in flight while it reduces the current one.
+template <int NV>
+__global__ void __launch_bounds__(128) add_layernorm_rows_kernel(B200LayerNormDesc d) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const long long nwarps = static_cast<long long>(gridDim.x) * 4;
+    const int groups = static_cast<int>(d.H >> 3);
+    const bool f32_in = d.in_dtype == B200_F32;
+    float gm[NV][8], bt[NV][8];
+#pragma unroll
+    for (int g = 0; g < NV; ++g) {
+        const int gi = g * 32 + lane;
+        if (gi < groups) {
+            load8(d.gamma, gi * 8, B200_F32, gm[g]);
+            load8(d.beta, gi * 8, B200_F32, bt[g]);
+        }
+    }
+    uint4 raw[NV][2], rres[NV][2];
+    auto fetch = [&](long long row) {
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const int gi = g * 32 + lane;
+            if (gi < groups) {
+                if (f32_in) {
+                    const uint4* px = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.x) + row * d.ldx + gi * 8);
+                    raw[g][0] = __ldg(px);
+                    raw[g][1] = __ldg(px + 1);
+                    if (d.residual) {
+                        const uint4* pr = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.residual) + row * d.ldr + gi * 8);
+                        rres[g][0] = __ldg(pr);
+                        rres[g][1] = __ldg(pr + 1);
+                    }
+                } else {
+                    raw[g][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d.x) + row * d.ldx + gi * 8));
+                    if (d.residual)
+                        rres[g][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d.residual) + row * d.ldr + gi * 8));
+                }
+            }
+        }
+    };
+    auto decode = [&](const uint4 (&q)[2], float (&v)[8]) {
+        if (f32_in) {
+            v[0] = __uint_as_float(q[0].x); v[1] = __uint_as_float(q[0].y);
+            v[2] = __uint_as_float(q[0].z); v[3] = __uint_as_float(q[0].w);
+            v[4] = __uint_as_float(q[1].x); v[5] = __uint_as_float(q[1].y);
+            v[6] = __uint_as_float(q[1].z); v[7] = __uint_as_float(q[1].w);
+        } else {
+            const uint32_t w[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack2(w[e], d.in_dtype);
+                v[2 * e] = f.x;
+                v[2 * e + 1] = f.y;
+            }
+        }
+    };
+    const float inv_h = 1.0f / static_cast<float>(d.H);
+    long long row = warp0;
+    if (row < d.rows) fetch(row);
+    for (; row < d.rows; row += nwarps) {
+        float v[NV][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const int gi = g * 32 + lane;
+            if (gi < groups) {
+                decode(raw[g], v[g]);
+                if (d.residual) {
+                    float r[8];
+                    decode(rres[g], r);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[g][e] += r[e];
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum += v[g][e];
+            }
+        }
+        if (row + nwarps < d.rows) fetch(row + nwarps);   // next row's loads fly during the reductions below
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum * inv_h;
+        float sq = 0.f;
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const int gi = g * 32 + lane;
+            if (gi < groups) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float c = v[g][e] - mean;
+                    sq += c * c;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float rstd = 1.0f / sqrtf(sq * inv_h + d.eps);
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const int gi = g * 32 + lane;
+            if (gi < groups) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[g][e] + bt[g][e];
+                store8(d.y, row * d.ldy + gi * 8, d.out_dtype, o);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- conversion
 __global__ void __launch_bounds__(256) convert_kernel(const void* src, int sdt, void* dst, int ddt, long long n8,
                                                       long long n) {
@@ -192,9 +303,17 @@ int b200_add_layernorm_fwd(const B200LayerNormDesc* d, b200_stream_t stream_) {
     const int warps_per_block = 8;
     const unsigned grid = static_cast<unsigned>((d->rows + warps_per_block - 1) / warps_per_block);
     const int nv = static_cast<int>((d->H / 8 + 31) / 32);
-    if (nv <= 3) add_layernorm_kernel<3><<<grid, 256, 0, stream>>>(*d);
-    else if (nv <= 4) add_layernorm_kernel<4><<<grid, 256, 0, stream>>>(*d);
-    else if (nv <= 8) add_layernorm_kernel<8><<<grid, 256, 0, stream>>>(*d);
+    if (nv <= 4) {
+        // One resident wave: the register footprint (gamma/beta slices + a prefetched row) allows 4 / 3 / 2 blocks
+        // of 4 warps per SM; every warp then walks rows with a grid stride.
+        const int per_sm = nv <= 1 ? 4 : (nv <= 3 ? 3 : 2);
+        long long blocks = (d->rows + 3) / 4;
+        if (blocks > 148ll * per_sm) blocks = 148ll * per_sm;
+        const unsigned g2 = static_cast<unsigned>(blocks);
+        if (nv <= 1) add_layernorm_rows_kernel<1><<<g2, 128, 0, stream>>>(*d);
+        else if (nv <= 3) add_layernorm_rows_kernel<3><<<g2, 128, 0, stream>>>(*d);
+        else add_layernorm_rows_kernel<4><<<g2, 128, 0, stream>>>(*d);
+    } else if (nv <= 8) add_layernorm_kernel<8><<<grid, 256, 0, stream>>>(*d);
     else add_layernorm_kernel<16><<<grid, 256, 0, stream>>>(*d);
     count_launch();
     return check_launch();
