@@ -1,0 +1,49 @@
+"""CPU: the graph pass of the TNN plug-in (no GPU needed: the pass only rewrites the interpreted model)."""
+import os
+import tempfile
+
+import pytest
+
+from tnn_b200 import model_synth as ms
+from tnn_b200 import tnn_runtime as rt
+
+pytestmark = pytest.mark.skipif(not rt.available(), reason="TNN host framework / plug-in not built here")
+
+
+def _fuse(wl, precision=rt.PRECISION_AUTO):
+    d = tempfile.mkdtemp(prefix="fuse_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model)
+    n_before = sum(1 for ln in open(proto).read().split("\n")[5:] if ln.strip())
+    return n_before, rt.fuse_report(proto, model, precision)
+
+
+def test_encoder_layers_collapse_to_seven_fused_layers():
+    wl = ms.make_workload(ms.BERT_BASE, 2, 128, seed=1, num_layers=3)
+    n_before, lines = _fuse(wl)
+    assert n_before == 3 * 30
+    types = [ln.split()[0] for ln in lines]
+    assert types == ["FusedLinear", "FusedAttention", "FusedLinear", "LayerNorm",
+                     "FusedLinear", "FusedLinear", "LayerNorm"] * 3
+    # the attention layer consumes the packed QKV projection and the graph's mask input
+    attn = [ln for ln in lines if ln.startswith("FusedAttention")][0].split()
+    assert attn[3] == "mask"
+    # layer names stay unique across encoder layers
+    names = [ln.split()[1] for ln in lines]
+    assert len(set(names)) == len(names)
+    # the graph output keeps its name
+    assert lines[-1].split()[-1] == "l2_ln2"
+
+
+def test_attention_block_only_and_large_geometry():
+    n_before, lines = _fuse(ms.config_workload(1))
+    assert n_before == 23
+    assert [ln.split()[0] for ln in lines] == ["FusedLinear", "FusedAttention", "FusedLinear", "LayerNorm"]
+    wl = ms.make_workload(ms.BERT_LARGE, 1, 64, seed=2, num_layers=1)
+    _, lines = _fuse(wl, rt.PRECISION_LOW)
+    assert [ln.split()[0] for ln in lines].count("FusedLinear") == 4
+
+
+def test_precision_high_is_refused():
+    with pytest.raises(RuntimeError):
+        _fuse(ms.config_workload(1), rt.PRECISION_HIGH)

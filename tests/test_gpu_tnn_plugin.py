@@ -1,0 +1,93 @@
+"""GPU: the drop-in path — TNN's own Instance::Forward on DEVICE_CUDA (served by the plug-in: fusion pass + fused
+accs) against TNN's DEVICE_X86 on the same model files and inputs, in the same process.  This is the reference's
+differential test idea (test/unit_test/layer_test/layer_test.cc) one level up."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from oracle.make_golden import CASES, GOLDEN, golden_workload
+from tnn_b200 import model_synth as ms
+from tnn_b200 import tnn_runtime as rt
+from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not rt.available(), reason="TNN host framework / plug-in missing")]
+
+
+def _files(wl):
+    d = tempfile.mkdtemp(prefix="plug_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model)
+    return proto, model
+
+
+def _run(proto, model, wl, device, precision=rt.PRECISION_AUTO):
+    inst = rt.Instance(proto, model, device=device, precision=precision)
+    inst.set_input("x", wl.x)
+    inst.set_input("mask", wl.mask_add)
+    inst.forward()
+    out = inst.get_output()
+    inst.close()
+    return out
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_cuda_instance_matches_x86_instance(cuda_device, name):
+    wl = golden_workload(**CASES[name])
+    proto, model = _files(wl)
+    y = _run(proto, model, wl, rt.DEVICE_CUDA)
+    ref = _run(proto, model, wl, rt.DEVICE_X86, rt.PRECISION_HIGH)
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    assert max_abs(ref, g["x86"]) < 1e-5            # the x86 instance in this process is the committed fixture
+    assert y.shape == ref.shape
+    assert max_abs(y, ref) <= MAX_ABS_TOL
+    assert cosine(y, ref) >= COS_TOL
+    assert max_abs(valid_rows(y, wl.lengths), valid_rows(ref, wl.lengths)) <= MAX_ABS_TOL
+
+
+def test_bf16_precision_low(cuda_device):
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    proto, model = _files(wl)
+    y = _run(proto, model, wl, rt.DEVICE_CUDA, rt.PRECISION_LOW)
+    ref = np.load(os.path.join(GOLDEN, "base_2layer_ragged.npz"))["x86"]
+    assert max_abs(y, ref) <= 4 * MAX_ABS_TOL
+    assert cosine(y, ref) >= 0.999
+
+
+def test_plugin_path_equals_c_abi_path(cuda_device):
+    """The accs launch the same kernels as the host mirror: bit-identical outputs."""
+    import torch
+    from tnn_b200.encoder import Encoder
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    proto, model = _files(wl)
+    y = _run(proto, model, wl, rt.DEVICE_CUDA)
+    enc = Encoder.from_workload(wl, torch.float16)
+    z = enc.forward(torch.from_numpy(wl.x).cuda(), torch.from_numpy(wl.mask_add).cuda()).cpu().numpy()
+    assert np.array_equal(y, z)
+
+
+def test_two_instances_share_weights_and_repeat(cuda_device):
+    """Two instances from the same files (shared host weights, private packed copies), forward twice each."""
+    wl = golden_workload(**CASES["c1_attention_block"])
+    proto, model = _files(wl)
+    a = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    b = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    outs = []
+    for inst in (a, b, a, b):
+        inst.set_input("x", wl.x)
+        inst.set_input("mask", wl.mask_add)
+        inst.forward()
+        outs.append(inst.get_output())
+    for o in outs[1:]:
+        assert np.array_equal(outs[0], o)
+    ref = np.load(os.path.join(GOLDEN, "c1_attention_block.npz"))["x86"]
+    assert max_abs(outs[0], ref) <= MAX_ABS_TOL
+
+
+def test_unfusable_graph_fails_loudly(cuda_device):
+    """PRECISION_HIGH has no CUDA path here: instance creation must fail, not fall back to a CPU device."""
+    wl = golden_workload(**CASES["c1_attention_block"])
+    proto, model = _files(wl)
+    with pytest.raises(RuntimeError):
+        rt.Instance(proto, model, device=rt.DEVICE_CUDA, precision=rt.PRECISION_HIGH)

@@ -1,0 +1,226 @@
+// DEVICE_CUDA layer accs of the fused encoder graph: FusedLinear, FusedAttention and LayerNorm.  Each Forward is one
+// launch through the kernel library's C ABI on the context's stream (plus a conversion launch where an fp32 blob
+// enters the half-precision region).  Registered in the device's acc registry like the reference's accs
+// (REGISTER_CUDA_ACC, source/tnn/device/cuda/acc/cuda_layer_acc.h:105-107).
+#include <cstring>
+
+#include "b200_cuda_layer_acc.h"
+#include "tnn/utils/dims_utils.h"
+
+namespace TNN_NS {
+
+namespace {
+
+int64_t Rows(const DimsVector& dims) {
+    int64_t n = 1;
+    for (size_t i = 0; i + 1 < dims.size(); ++i) n *= dims[i];
+    return n;
+}
+
+}  // namespace
+
+// ================================================================= FusedLinear
+B200_DECLARE_CUDA_ACC(FusedLinear)
+    // `src` as a half-precision [rows, cols] device pointer: the blob itself when it already has the compute dtype,
+    // otherwise a conversion into the acc's staging buffer.
+    Status AsCompute(Blob* src, void* staging, int64_t count, const void** out);
+
+    void* w_packed_   = nullptr;   // [N, K] compute dtype
+    float* bias_      = nullptr;   // [N] fp32
+    void* x_staging_  = nullptr;   // conversion buffers for fp32 inputs (first layer of the graph)
+    size_t x_cap_     = 0;
+    void* r_staging_  = nullptr;
+    size_t r_cap_     = 0;
+    int64_t K_ = 0, N_ = 0;
+};
+
+Status B200CudaFusedLinearLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                         const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param);
+    auto* r = dynamic_cast<FusedLinearLayerResource*>(resource);
+    if (!p || !r || r->weights.empty() || r->weights.size() != r->biases.size())
+        return Status(TNNERR_PARAM_ERR, "FusedLinear: param/resource missing");
+    K_ = p->in_features;
+    N_ = p->out_features;
+    cudaStream_t stream = context_->GetStream();
+    const size_t es = 2;
+    size_t cap = 0;
+    RETURN_ON_NEQ(EnsureBuffer(&w_packed_, &cap, static_cast<size_t>(N_) * K_ * es), TNN_OK);
+    cap = 0;
+    void* bias = nullptr;
+    RETURN_ON_NEQ(EnsureBuffer(&bias, &cap, static_cast<size_t>(N_) * sizeof(float)), TNN_OK);
+    bias_ = static_cast<float*>(bias);
+
+    // Upload each fp32 [K, N_i] weight and pack it to [N_i, K] half precision at row offset n0 of the merged operand.
+    // The host RawBuffers are only read: they are shared with every other instance of the model.
+    int64_t n0 = 0;
+    for (size_t i = 0; i < r->weights.size(); ++i) {
+        RawBuffer& w = r->weights[i];
+        RawBuffer& b = r->biases[i];
+        const DimsVector wd = w.GetBufferDims();
+        if (w.GetDataType() != DATA_TYPE_FLOAT || wd.size() != 2 || wd[0] != K_)
+            return Status(TNNERR_PARAM_ERR, "FusedLinear: weight must be fp32 [K, N]");
+        const int64_t Ni = wd[1];
+        if (b.GetDataType() != DATA_TYPE_FLOAT || b.GetDataCount() != Ni)
+            return Status(TNNERR_PARAM_ERR, "FusedLinear: bias must be fp32 [N]");
+        void* tmp = nullptr;
+        RETURN_ON_NEQ(device_->Allocate(&tmp, static_cast<size_t>(K_) * Ni * sizeof(float)), TNN_OK);
+        Status st = TNN_OK;
+        if (cudaMemcpyAsync(tmp, w.force_to<float*>(), static_cast<size_t>(K_) * Ni * sizeof(float),
+                            cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+            cudaMemcpyAsync(bias_ + n0, b.force_to<float*>(), static_cast<size_t>(Ni) * sizeof(float),
+                            cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+            cudaGetLastError();
+            st = Status(TNNERR_CUDA_MEMCPY_ERROR, "FusedLinear: weight upload failed");
+        }
+        if (st == TNN_OK)
+            st = B200ToStatus(b200_pack_weight(static_cast<const float*>(tmp), K_, Ni, Ni,
+                                               static_cast<char*>(w_packed_) + n0 * K_ * es, K_, p->compute_dtype, stream),
+                              "b200_pack_weight");
+        cudaStreamSynchronize(stream);   // Init time: the staging copy is released right away
+        device_->Free(tmp);
+        RETURN_ON_NEQ(st, TNN_OK);
+        n0 += Ni;
+    }
+    if (n0 != N_) return Status(TNNERR_PARAM_ERR, "FusedLinear: merged weight widths do not add up to out_features");
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaFusedLinearLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
+    const int64_t rows = Rows(inputs[0]->GetBlobDesc().dims);
+    // Staging for inputs that are not in the compute dtype yet (sized here, never in Forward).
+    if (B200DataType(inputs[0]->GetBlobDesc().data_type) != p->compute_dtype)
+        RETURN_ON_NEQ(EnsureBuffer(&x_staging_, &x_cap_, static_cast<size_t>(rows) * K_ * 2), TNN_OK);
+    if (inputs.size() > 1 && B200DataType(inputs[1]->GetBlobDesc().data_type) != p->compute_dtype)
+        RETURN_ON_NEQ(EnsureBuffer(&r_staging_, &r_cap_, static_cast<size_t>(rows) * N_ * 2), TNN_OK);
+    return TNN_OK;
+}
+
+Status B200CudaFusedLinearLayerAcc::AsCompute(Blob* src, void* staging, int64_t count, const void** out) {
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
+    const int sdt = B200DataType(src->GetBlobDesc().data_type);
+    if (sdt == p->compute_dtype) {
+        *out = DevicePtr(src);
+        return TNN_OK;
+    }
+    if (sdt < 0 || !staging) return Status(TNNERR_PARAM_ERR, "FusedLinear: unsupported input data type");
+    *out = staging;
+    return B200ToStatus(b200_convert(DevicePtr(src), sdt, staging, p->compute_dtype, count, context_->GetStream()),
+                        "b200_convert");
+}
+
+Status B200CudaFusedLinearLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
+    const int64_t rows = Rows(inputs[0]->GetBlobDesc().dims);
+    B200LinearDesc d;
+    std::memset(&d, 0, sizeof(d));
+    RETURN_ON_NEQ(AsCompute(inputs[0], x_staging_, rows * K_, &d.x), TNN_OK);
+    if (p->epilogue == B200_EPI_BIAS_RESIDUAL)
+        RETURN_ON_NEQ(AsCompute(inputs[1], r_staging_, rows * N_, &d.residual), TNN_OK);
+    d.w_nk = w_packed_;
+    d.bias = bias_;
+    d.y    = DevicePtr(outputs[0]);
+    d.M = rows; d.N = N_; d.K = K_;
+    d.ldx = K_; d.ldw = K_; d.ldr = N_; d.ldy = N_;
+    d.dtype     = p->compute_dtype;
+    d.out_dtype = B200DataType(outputs[0]->GetBlobDesc().data_type);
+    d.epilogue  = p->epilogue;
+    d.block_n   = 0;
+    return B200ToStatus(b200_linear_fwd(&d, context_->GetStream()), "b200_linear_fwd");
+}
+B200_REGISTER_CUDA_ACC(FusedLinear, LAYER_B200_FUSED_LINEAR)
+
+// ================================================================= FusedAttention
+B200_DECLARE_CUDA_ACC(FusedAttention)
+};
+
+Status B200CudaFusedAttentionLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                            const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    auto* p = dynamic_cast<FusedAttentionLayerParam*>(param);
+    if (!p) return Status(TNNERR_PARAM_ERR, "FusedAttention: param missing");
+    if (p->head_dim != 64) return Status(TNNERR_PARAM_ERR, "FusedAttention: only head_dim 64 is implemented");
+    if (B200DataType(inputs[0]->GetBlobDesc().data_type) != p->compute_dtype)
+        return Status(TNNERR_PARAM_ERR, "FusedAttention: qkv input must already be in the compute dtype");
+    if (inputs.size() > 1 && inputs[1]->GetBlobDesc().data_type != DATA_TYPE_FLOAT)
+        return Status(TNNERR_PARAM_ERR, "FusedAttention: mask must be fp32");
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaFusedAttentionLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return TNN_OK;
+}
+
+Status B200CudaFusedAttentionLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedAttentionLayerParam*>(param_);
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    const int64_t B = dims[0], S = dims[1];
+    const int64_t H = static_cast<int64_t>(p->heads) * p->head_dim;
+    B200AttentionDesc d;
+    std::memset(&d, 0, sizeof(d));
+    char* qkv = static_cast<char*>(DevicePtr(inputs[0]));
+    d.q = qkv; d.k = qkv + H * 2; d.v = qkv + 2 * H * 2;
+    d.ldq = d.ldk = d.ldv = 3 * H;
+    d.out = DevicePtr(outputs[0]);
+    d.ldo = H;
+    if (inputs.size() > 1) {
+        d.mask_add = static_cast<const float*>(DevicePtr(inputs[1]));
+        Status st = TNN_OK;
+        d.kv_len = context_->GetKvLen(d.mask_add, static_cast<int>(B), static_cast<int>(S), p->mask_exclude_below, &st);
+        RETURN_ON_NEQ(st, TNN_OK);
+    }
+    d.B = B; d.S = S;
+    d.heads = p->heads; d.head_dim = p->head_dim;
+    d.dtype = p->compute_dtype;
+    d.scale = p->scale;
+    d.mask_exclude_below = p->mask_exclude_below;
+    return B200ToStatus(b200_attention_fwd(&d, context_->GetStream()), "b200_attention_fwd");
+}
+B200_REGISTER_CUDA_ACC(FusedAttention, LAYER_B200_FUSED_ATTENTION)
+
+// ================================================================= LayerNorm
+// The graph's own LayerNorm layer (gamma, beta = input blobs 1 and 2, uploaded by ReloadConstantBlobs).  The reference's
+// CUDA acc (source/tnn/device/cuda/acc/cuda_layer_norm_layer_acc.cu:28-146) reads gamma/beta in the activation's
+// type; here they stay fp32 whatever the activation type is.
+B200_DECLARE_CUDA_ACC(LayerNorm)
+};
+
+Status B200CudaLayerNormLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                       const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    auto* p = dynamic_cast<LayerNormLayerParam*>(param);
+    if (!p || inputs.size() < 3) return Status(TNNERR_PARAM_ERR, "LayerNorm: needs x, scale and bias inputs");
+    if (p->reduce_dims_size != 1)
+        return Status(TNNERR_PARAM_ERR, "LayerNorm: only normalisation over the last dimension is implemented");
+    if (inputs[1]->GetBlobDesc().data_type != DATA_TYPE_FLOAT || inputs[2]->GetBlobDesc().data_type != DATA_TYPE_FLOAT)
+        return Status(TNNERR_PARAM_ERR, "LayerNorm: scale and bias must be fp32");
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaLayerNormLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return TNN_OK;
+}
+
+Status B200CudaLayerNormLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<LayerNormLayerParam*>(param_);
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    B200LayerNormDesc d;
+    std::memset(&d, 0, sizeof(d));
+    d.x = DevicePtr(inputs[0]);
+    d.gamma = static_cast<const float*>(DevicePtr(inputs[1]));
+    d.beta  = static_cast<const float*>(DevicePtr(inputs[2]));
+    d.y = DevicePtr(outputs[0]);
+    d.rows = Rows(dims);
+    d.H = dims.back();
+    d.ldx = d.ldy = d.H;
+    d.in_dtype  = B200DataType(inputs[0]->GetBlobDesc().data_type);
+    d.out_dtype = B200DataType(outputs[0]->GetBlobDesc().data_type);
+    d.eps = p->eps;
+    if (d.in_dtype < 0 || d.out_dtype < 0) return Status(TNNERR_PARAM_ERR, "LayerNorm: unsupported data type");
+    return B200ToStatus(b200_add_layernorm_fwd(&d, context_->GetStream()), "b200_add_layernorm_fwd");
+}
+B200_REGISTER_CUDA_ACC(LayerNorm, LAYER_LAYER_NORM)
+
+}  // namespace TNN_NS

@@ -1,0 +1,114 @@
+// Mat <-> Blob conversion for DEVICE_CUDA blobs (the I/O edge of the encoder).  Replaces the reference's
+// CudaBlobConverterAcc (source/tnn/device/cuda/cuda_blob_converter.cc:36-194) for the Mat types this path uses:
+// NCHW_FLOAT and NC_INT32, host or device Mats.  Differences: BlobHandle.bytes_offset is honoured (the reference
+// ignores it, :133), half / bfloat16 blobs convert through the library's conversion kernel (the fused region's
+// outputs are half precision), and non-identity scale/bias (image preprocessing) is refused rather than mis-applied
+// to a [B,S,H] activation.
+#include <cuda_runtime.h>
+
+#include "b200_plugin_common.h"
+#include "tnn/core/blob.h"
+#include "tnn/core/mat.h"
+#include "tnn/utils/blob_converter_internal.h"
+#include "tnn/utils/dims_utils.h"
+
+namespace TNN_NS {
+
+class B200CudaBlobConverterAcc : public BlobConverterAcc {
+public:
+    explicit B200CudaBlobConverterAcc(Blob* blob) : BlobConverterAcc(blob) {}
+    virtual ~B200CudaBlobConverterAcc() {
+        if (staging_) cudaFree(staging_);
+    }
+
+    virtual Status ConvertToMat(Mat& image, MatConvertParam param, void* command_queue = NULL) {
+        Status st = ConvertToMatAsync(image, param, command_queue);
+        if (st != TNN_OK) return st;
+        if (cudaStreamSynchronize(static_cast<cudaStream_t>(command_queue)) != cudaSuccess)
+            return Status(TNNERR_CUDA_SYNC_ERROR, "stream sync failed");
+        return TNN_OK;
+    }
+    virtual Status ConvertFromMat(Mat& image, MatConvertParam param, void* command_queue = NULL) {
+        Status st = ConvertFromMatAsync(image, param, command_queue);
+        if (st != TNN_OK) return st;
+        if (cudaStreamSynchronize(static_cast<cudaStream_t>(command_queue)) != cudaSuccess)
+            return Status(TNNERR_CUDA_SYNC_ERROR, "stream sync failed");
+        return TNN_OK;
+    }
+
+    virtual Status ConvertToMatAsync(Mat& image, MatConvertParam param, void* command_queue = NULL) {
+        return Convert(image, param, command_queue, /*to_mat=*/true);
+    }
+    virtual Status ConvertFromMatAsync(Mat& image, MatConvertParam param, void* command_queue = NULL) {
+        return Convert(image, param, command_queue, /*to_mat=*/false);
+    }
+
+private:
+    Status Convert(Mat& image, const MatConvertParam& param, void* command_queue, bool to_mat) {
+        cudaStream_t stream = static_cast<cudaStream_t>(command_queue);
+        if (!blob_) return Status(TNNERR_NULL_PARAM, "blob is null");
+        if (NeedDoScaleBias(param) || param.reverse_channel)
+            return Status(TNNERR_PARAM_ERR, "tnn_b200 blob converter: scale/bias/reverse_channel are not supported");
+        const BlobDesc& desc = blob_->GetBlobDesc();
+        const int64_t count  = DimsVectorUtils::Count(desc.dims);
+        if (count != DimsVectorUtils::Count(image.GetDims()))
+            return Status(TNNERR_PARAM_ERR, "Mat and Blob element counts differ");
+        BlobHandle h   = blob_->GetHandle();
+        char* blob_ptr = static_cast<char*>(h.base) + h.bytes_offset;
+        const MatType mt = image.GetMatType();
+        const bool mat_on_device = image.GetDeviceType() == DEVICE_CUDA;
+        const cudaMemcpyKind kind = to_mat ? (mat_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost)
+                                           : (mat_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+
+        if (mt == NC_INT32) {
+            if (desc.data_type != DATA_TYPE_INT32) return Status(TNNERR_PARAM_ERR, "NC_INT32 Mat needs an int32 blob");
+            return Copy(to_mat ? image.GetData() : blob_ptr, to_mat ? blob_ptr : image.GetData(), count * 4, kind, stream);
+        }
+        if (mt != NCHW_FLOAT) return Status(TNNERR_PARAM_ERR, "tnn_b200 blob converter: Mat type not supported");
+
+        if (desc.data_type == DATA_TYPE_FLOAT)
+            return Copy(to_mat ? image.GetData() : blob_ptr, to_mat ? blob_ptr : image.GetData(), count * 4, kind, stream);
+
+        const int bdt = B200DataType(desc.data_type);
+        if (bdt != B200_F16 && bdt != B200_BF16) return Status(TNNERR_PARAM_ERR, "blob data type not supported");
+        // half/bf16 blob <-> fp32 Mat through a device-side fp32 staging buffer (grown on first use)
+        void* f32 = image.GetData();
+        if (!mat_on_device) {
+            const size_t need = static_cast<size_t>(count) * 4;
+            if (need > staging_bytes_) {
+                if (staging_) cudaFree(staging_);
+                staging_ = nullptr;
+                if (cudaMalloc(&staging_, (need + 255) & ~size_t(255)) != cudaSuccess) {
+                    cudaGetLastError();
+                    staging_bytes_ = 0;
+                    return Status(TNNERR_OUTOFMEMORY, "staging alloc failed");
+                }
+                staging_bytes_ = need;
+            }
+            f32 = staging_;
+        }
+        if (to_mat) {
+            RETURN_ON_NEQ(B200ToStatus(b200_convert(blob_ptr, bdt, f32, B200_F32, count, stream), "b200_convert"), TNN_OK);
+            if (!mat_on_device) return Copy(image.GetData(), f32, count * 4, cudaMemcpyDeviceToHost, stream);
+            return TNN_OK;
+        }
+        if (!mat_on_device) RETURN_ON_NEQ(Copy(f32, image.GetData(), count * 4, cudaMemcpyHostToDevice, stream), TNN_OK);
+        return B200ToStatus(b200_convert(f32, B200_F32, blob_ptr, bdt, count, stream), "b200_convert");
+    }
+
+    static Status Copy(void* dst, const void* src, int64_t bytes, cudaMemcpyKind kind, cudaStream_t stream) {
+        if (cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), kind, stream) != cudaSuccess) {
+            cudaGetLastError();
+            return Status(TNNERR_CUDA_MEMCPY_ERROR, "cudaMemcpyAsync failed");
+        }
+        return TNN_OK;
+    }
+
+    void* staging_        = nullptr;
+    size_t staging_bytes_ = 0;
+};
+
+DECLARE_BLOB_CONVERTER_CREATER(B200Cuda);
+REGISTER_BLOB_CONVERTER(B200Cuda, DEVICE_CUDA);
+
+}  // namespace TNN_NS

@@ -1,0 +1,408 @@
+// Graph-optimizer pass "net_optimizer_b200_fuse_attention": collapses the unfused transformer-encoder subgraphs of a
+// TNN model into the fused layers the B200 accs implement.  Written against the reference's pass registry
+// (NetOptimizerRegister, source/tnn/optimizer/net_optimizer_manager.h:46-66) and its graph matcher
+// (Graph::fromInterpreted / GraphParser / Graph::rewrite, source/tnn/optimizer/graph_matcher/), with
+// source/tnn/optimizer/net_optimizer_convert_matmul_to_conv.cc as the model for how a pass uses them.
+//
+//   1. attention block (with or without the additive mask):
+//        MatMul+Add x3 (Q, K, V on the same input) -> Reshape -> Permute -> MatMul(QK^T) -> Mul(scale) [-> Add(mask)]
+//        -> Softmax(axis 3) -> MatMul(PV) -> Permute -> Reshape
+//      becomes  FusedLinear(x; Wq|Wk|Wv) -> FusedAttention(qkv [, mask])
+//   2. MatMul -> Add(bias) -> GELU            becomes FusedLinear(epilogue GELU)
+//   3. MatMul -> Add(bias) -> Add(residual)   becomes FusedLinear(epilogue residual), either operand order of the Add
+//   4. MatMul -> Add(bias)                    becomes FusedLinear
+// LayerNorm layers stay as they are (the device has an acc for them).
+//
+// The matcher compares layer types, input/output counts and topology only, so everything else — permute orders,
+// reshape targets, softmax axis, weight positions, bias shapes — is validated in the generator, which declines
+// (returns nullptr) when a subgraph is not the attention computation it looks like.  Matched weight buffers are
+// never modified: every instance created from one TNN object shares them.
+#include <cmath>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "b200_plugin_common.h"
+#include "tnn/interpreter/layer_param.h"
+#include "tnn/interpreter/layer_resource.h"
+#include "tnn/optimizer/graph_matcher/graph_matcher.h"
+#include "tnn/optimizer/graph_matcher/graph_parser.h"
+#include "tnn/optimizer/graph_matcher/ir.h"
+#include "tnn/optimizer/graph_matcher/logger.h"
+#include "tnn/optimizer/net_optimizer.h"
+#include "tnn/optimizer/net_optimizer_manager.h"
+
+namespace TNN_NS {
+namespace optimizer {
+
+class NetOptimizerB200FuseAttention : public NetOptimizer {
+public:
+    virtual std::string Strategy() { return "net_optimizer_b200_fuse_attention"; }
+    virtual bool IsSupported(const NetworkConfig& net_config);
+    virtual Status Optimize(NetStructure* structure, NetResource* resource);
+
+private:
+    Precision precision_ = PRECISION_AUTO;
+};
+
+NetOptimizerRegister<NetOptimizerB200FuseAttention> g_net_optimizer_b200_fuse_attention(OptPriority::P1);
+
+bool NetOptimizerB200FuseAttention::IsSupported(const NetworkConfig& net_config) {
+    // DefaultNetwork driving DEVICE_CUDA accs directly; called by the manager right before Optimize under the
+    // optimizer mutex (source/tnn/core/default_network.cc:109-114), so the precision can be handed over in a member.
+    precision_ = net_config.precision;
+    return net_config.device_type == DEVICE_CUDA &&
+           (net_config.network_type == NETWORK_TYPE_DEFAULT || net_config.network_type == NETWORK_TYPE_AUTO);
+}
+
+namespace {
+
+struct LinearParts {
+    RawBuffer weight;   // fp32 [K, N]; shares storage with the matched layer's resource
+    RawBuffer bias;     // fp32 [N]
+    int K = 0, N = 0;
+};
+
+// MatMul(weight as layer resource, [K,N]) followed by Add(bias as layer resource, [N]).
+bool ExtractLinear(const std::shared_ptr<Node>& mm, const std::shared_ptr<Node>& add, NetResource* resource,
+                   LinearParts* out) {
+    if (!mm || !add) return false;
+    auto mm_param = std::dynamic_pointer_cast<MatMulLayerParam>(mm->info->param);
+    if (!mm_param || mm_param->weight_position != 1 || mm->info->inputs.size() != 1) return false;
+    auto it = resource->resource_map.find(mm->info->name);
+    if (it == resource->resource_map.end()) return false;
+    auto mm_res = std::dynamic_pointer_cast<MatMulLayerResource>(it->second);
+    if (!mm_res) return false;
+    const DimsVector wd = mm_res->weight.GetBufferDims();
+    if (wd.size() != 2 || mm_res->weight.GetDataType() != DATA_TYPE_FLOAT) return false;
+
+    auto add_param = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(add->info->param);
+    if (!add_param || add->info->inputs.size() != 1 || add_param->weight_input_index != 1) return false;
+    auto jt = resource->resource_map.find(add->info->name);
+    if (jt == resource->resource_map.end()) return false;
+    auto add_res = std::dynamic_pointer_cast<EltwiseLayerResource>(jt->second);
+    if (!add_res || add_res->element_handle.GetDataType() != DATA_TYPE_FLOAT) return false;
+    if (add_res->element_handle.GetDataCount() != wd[1]) return false;
+
+    out->weight = mm_res->weight;           // RawBuffer copy = shared storage, no data copy
+    out->bias   = add_res->element_handle;
+    out->K      = wd[0];
+    out->N      = wd[1];
+    return true;
+}
+
+bool PermuteIs(const std::shared_ptr<Node>& n, const std::vector<int>& want) {
+    if (!n) return false;
+    auto p = std::dynamic_pointer_cast<PermuteLayerParam>(n->info->param);
+    return p && p->orders == want;
+}
+
+// Reshape [B,S,H] -> [B,S,heads,head_dim]: shape {0,0,heads,head_dim}
+bool SplitHeads(const std::shared_ptr<Node>& n, int* heads, int* head_dim) {
+    if (!n || n->info->inputs.size() != 1) return false;
+    auto p = std::dynamic_pointer_cast<ReshapeLayerParam>(n->info->param);
+    if (!p || p->shape.size() != 4 || p->shape[2] <= 0 || p->shape[3] <= 0) return false;
+    *heads    = p->shape[2];
+    *head_dim = p->shape[3];
+    return true;
+}
+
+std::shared_ptr<Graph> ParsePattern(const std::string& text) {
+    GraphRegistry registry;
+    GraphParser parser(&registry);
+    if (!parser.parseFromString(text)) return nullptr;
+    return parser.getGraph();
+}
+
+Status AddFusedLinear(const std::shared_ptr<Graph>& g, const std::vector<std::string>& ins, const std::string& out,
+                      const std::vector<LinearParts>& parts, int epilogue, int dtype) {
+    RETURN_ON_NEQ(g->createNode(LAYER_B200_FUSED_LINEAR, ins, {out}), TNN_OK);
+    auto node = g->getNodeByTensorName(out);
+    if (!node) return Status(TNNERR_NET_ERR, "fused node not created");
+    RETURN_ON_NEQ(node->createParam<FusedLinearLayerParam>(), TNN_OK);
+    auto p           = node->param<FusedLinearLayerParam>();
+    p->type          = kFusedLinearTypeName;
+    p->name          = out;
+    p->epilogue      = epilogue;
+    p->compute_dtype = dtype;
+    p->in_features   = parts[0].K;
+    p->out_features  = 0;
+    RETURN_ON_NEQ(node->createResource<FusedLinearLayerResource>(), TNN_OK);
+    auto r  = node->resource<FusedLinearLayerResource>();
+    r->name = out;
+    for (const auto& lp : parts) {
+        r->weights.push_back(lp.weight);
+        r->biases.push_back(lp.bias);
+        p->out_features += lp.N;
+    }
+    return TNN_OK;
+}
+
+const char* kAttentionMasked = R"(
+    graph(%x, %mask):
+        %q_mm = MatMul(%x)
+        %q_b  = Add(%q_mm)
+        %q_r  = Reshape(%q_b)
+        %q_p  = Permute(%q_r)
+        %k_mm = MatMul(%x)
+        %k_b  = Add(%k_mm)
+        %k_r  = Reshape(%k_b)
+        %k_p  = Permute(%k_r)
+        %v_mm = MatMul(%x)
+        %v_b  = Add(%v_mm)
+        %v_r  = Reshape(%v_b)
+        %v_p  = Permute(%v_r)
+        %qk   = MatMul(%q_p, %k_p)
+        %qk_s = Mul(%qk)
+        %qk_m = Add(%qk_s, %mask)
+        %sm   = Softmax(%qk_m)
+        %ctx  = MatMul(%sm, %v_p)
+        %ctx_p = Permute(%ctx)
+        %ctx_r = Reshape(%ctx_p)
+        return (%ctx_r)
+)";
+
+const char* kAttentionUnmasked = R"(
+    graph(%x):
+        %q_mm = MatMul(%x)
+        %q_b  = Add(%q_mm)
+        %q_r  = Reshape(%q_b)
+        %q_p  = Permute(%q_r)
+        %k_mm = MatMul(%x)
+        %k_b  = Add(%k_mm)
+        %k_r  = Reshape(%k_b)
+        %k_p  = Permute(%k_r)
+        %v_mm = MatMul(%x)
+        %v_b  = Add(%v_mm)
+        %v_r  = Reshape(%v_b)
+        %v_p  = Permute(%v_r)
+        %qk   = MatMul(%q_p, %k_p)
+        %qk_s = Mul(%qk)
+        %sm   = Softmax(%qk_s)
+        %ctx  = MatMul(%sm, %v_p)
+        %ctx_p = Permute(%ctx)
+        %ctx_r = Reshape(%ctx_p)
+        return (%ctx_r)
+)";
+
+}  // namespace
+
+Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResource* resource) {
+    if (!structure || !resource) return Status(TNNERR_NET_ERR, "Error: empty NetStructure or NetResource");
+    if (precision_ == PRECISION_HIGH)
+        return Status(TNNERR_PARAM_ERR,
+                      "tnn_b200: PRECISION_HIGH (fp32) is not offered on DEVICE_CUDA; use AUTO/NORMAL (fp16) or LOW (bf16)");
+    const int dtype = precision_ == PRECISION_LOW ? B200_BF16 : B200_F16;
+
+    // Already fused (the pass must be idempotent: Instance::Init may run the optimizers twice on one structure).
+    for (auto& l : structure->layers)
+        if (l->type == LAYER_B200_FUSED_LINEAR || l->type == LAYER_B200_FUSED_ATTENTION) return TNN_OK;
+
+    std::shared_ptr<Graph> graph = std::make_shared<Graph>();
+    Status status = graph->fromInterpreted(structure, resource);
+    if (status != TNN_OK) {
+        LOGE("%s", status.description().c_str());
+        return TNN_OK;   // leave the graph alone, as the reference's passes do
+    }
+
+    // ---------------------------------------------------------------- 1. attention
+    for (int masked = 1; masked >= 0; --masked) {
+        std::shared_ptr<Graph> pattern = ParsePattern(masked ? kAttentionMasked : kAttentionUnmasked);
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid attention pattern syntax");
+
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != static_cast<size_t>(masked ? 2 : 1) || in->outputs().size() != 1) return nullptr;
+            auto node = [&](const char* n) { return in->getNodeByTensorName(std::string("@") + n); };
+            LinearParts q, k, v;
+            if (!ExtractLinear(node("q_mm"), node("q_b"), resource, &q) ||
+                !ExtractLinear(node("k_mm"), node("k_b"), resource, &k) ||
+                !ExtractLinear(node("v_mm"), node("v_b"), resource, &v))
+                return nullptr;
+            if (q.K != k.K || q.K != v.K || q.N != k.N || q.N != v.N) return nullptr;
+            int heads = 0, head_dim = 0, h2 = 0, d2 = 0, h3 = 0, d3 = 0;
+            if (!SplitHeads(node("q_r"), &heads, &head_dim) || !SplitHeads(node("k_r"), &h2, &d2) ||
+                !SplitHeads(node("v_r"), &h3, &d3))
+                return nullptr;
+            if (heads != h2 || heads != h3 || head_dim != d2 || head_dim != d3 || heads * head_dim != q.N) return nullptr;
+            if (!PermuteIs(node("q_p"), {0, 2, 1, 3}) || !PermuteIs(node("k_p"), {0, 2, 3, 1}) ||
+                !PermuteIs(node("v_p"), {0, 2, 1, 3}) || !PermuteIs(node("ctx_p"), {0, 2, 1, 3}))
+                return nullptr;
+            for (const char* n : {"qk", "ctx"}) {
+                auto p = std::dynamic_pointer_cast<MatMulLayerParam>(node(n)->info->param);
+                if (!p || p->weight_position != -1) return nullptr;
+            }
+            auto sm = std::dynamic_pointer_cast<SoftmaxLayerParam>(node("sm")->info->param);
+            if (!sm || (sm->axis != 3 && sm->axis != -1)) return nullptr;
+            // merged heads: Reshape back to [B, S, H]
+            auto ctx_r = std::dynamic_pointer_cast<ReshapeLayerParam>(node("ctx_r")->info->param);
+            if (!ctx_r || ctx_r->shape.size() != 3 || ctx_r->shape[2] != q.N) return nullptr;
+            // scale: Mul by a one-element constant held as the layer's resource
+            auto mul = node("qk_s");
+            auto mul_param = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(mul->info->param);
+            if (!mul_param || mul->info->inputs.size() != 1) return nullptr;
+            auto mr = resource->resource_map.find(mul->info->name);
+            if (mr == resource->resource_map.end()) return nullptr;
+            auto mul_res = std::dynamic_pointer_cast<EltwiseLayerResource>(mr->second);
+            if (!mul_res || mul_res->element_handle.GetDataCount() != 1 ||
+                mul_res->element_handle.GetDataType() != DATA_TYPE_FLOAT)
+                return nullptr;
+            const float scale = mul_res->element_handle.force_to<float*>()[0];
+            if (masked) {
+                auto add = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(node("qk_m")->info->param);
+                if (!add || add->weight_input_index != -1 || node("qk_m")->info->inputs.size() != 2) return nullptr;
+            }
+
+            const std::string prefix = node("q_mm")->info->name + "_b200_";
+            auto g = std::make_shared<Graph>();
+            const std::string in_x = "in_0", in_mask = "in_1";
+            g->getNodeOrCreatePlaceHolder(in_x);
+            if (masked) g->getNodeOrCreatePlaceHolder(in_mask);
+            const std::string qkv_name = prefix + "qkv", ctx_name = prefix + "ctx";
+            if (AddFusedLinear(g, {in_x}, qkv_name, {q, k, v}, B200_EPI_BIAS, dtype) != TNN_OK) return nullptr;
+            std::vector<std::string> attn_in = {qkv_name};
+            if (masked) attn_in.push_back(in_mask);
+            if (g->createNode(LAYER_B200_FUSED_ATTENTION, attn_in, {ctx_name}) != TNN_OK) return nullptr;
+            auto attn = g->getNodeByTensorName(ctx_name);
+            if (!attn || attn->createParam<FusedAttentionLayerParam>() != TNN_OK) return nullptr;
+            auto ap           = attn->param<FusedAttentionLayerParam>();
+            ap->type          = kFusedAttentionTypeName;
+            ap->name          = ctx_name;
+            ap->heads         = heads;
+            ap->head_dim      = head_dim;
+            ap->scale         = scale;
+            ap->compute_dtype = dtype;
+            if (masked && g->setInputsOrder({in_x, in_mask}) != TNN_OK) return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 2. MatMul -> Add -> GELU
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%x):
+                %mm  = MatMul(%x)
+                %b   = Add(%mm)
+                %act = GELU(%b)
+                return (%act)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 1 || in->outputs().size() != 1) return nullptr;
+            LinearParts lp;
+            auto mm = in->getNodeByTensorName(std::string("@mm"));
+            if (!ExtractLinear(mm, in->getNodeByTensorName(std::string("@b")), resource, &lp)) return nullptr;
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            if (AddFusedLinear(g, {"in_0"}, mm->info->name + "_b200_gelu", {lp}, B200_EPI_BIAS_GELU, dtype) != TNN_OK)
+                return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 3. MatMul -> Add -> Add(residual)
+    for (int order = 0; order < 2; ++order) {
+        std::shared_ptr<Graph> pattern = ParsePattern(order == 0 ? R"(
+            graph(%x, %r):
+                %mm = MatMul(%x)
+                %b  = Add(%mm)
+                %o  = Add(%b, %r)
+                return (%o)
+        )" : R"(
+            graph(%x, %r):
+                %mm = MatMul(%x)
+                %b  = Add(%mm)
+                %o  = Add(%r, %b)
+                return (%o)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 2 || in->outputs().size() != 1) return nullptr;
+            LinearParts lp;
+            auto mm = in->getNodeByTensorName(std::string("@mm"));
+            if (!ExtractLinear(mm, in->getNodeByTensorName(std::string("@b")), resource, &lp)) return nullptr;
+            auto res_add = in->getNodeByTensorName(std::string("@o"));
+            auto rp = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(res_add->info->param);
+            if (!rp || rp->weight_input_index != -1 || res_add->info->inputs.size() != 2) return nullptr;
+            // the residual must be an activation, not a constant of the model
+            const std::string r_name = res_add->info->inputs[order == 0 ? 1 : 0];
+            if (resource->constant_map.count(r_name) > 0) return nullptr;
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            g->getNodeOrCreatePlaceHolder("in_1");
+            if (AddFusedLinear(g, {"in_0", "in_1"}, mm->info->name + "_b200_res", {lp}, B200_EPI_BIAS_RESIDUAL, dtype) !=
+                TNN_OK)
+                return nullptr;
+            if (g->setInputsOrder({"in_0", "in_1"}) != TNN_OK) return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 4. MatMul -> Add
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%x):
+                %mm = MatMul(%x)
+                %b  = Add(%mm)
+                return (%b)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 1 || in->outputs().size() != 1) return nullptr;
+            LinearParts lp;
+            auto mm = in->getNodeByTensorName(std::string("@mm"));
+            if (!ExtractLinear(mm, in->getNodeByTensorName(std::string("@b")), resource, &lp)) return nullptr;
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            if (AddFusedLinear(g, {"in_0"}, mm->info->name + "_b200_lin", {lp}, B200_EPI_BIAS, dtype) != TNN_OK)
+                return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+    return TNN_OK;
+}
+
+}  // namespace optimizer
+}  // namespace TNN_NS
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host-only hook for tests: run the pass on a model and describe the resulting layer list
+// ("<type> <name> <inputs> -> <outputs>" per line).  Needs no GPU.
+#include "tnn/interpreter/abstract_model_interpreter.h"
+#include "tnn/interpreter/default_model_interpreter.h"
+
+extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const char* proto, size_t proto_len,
+                                                                         const char* model, size_t model_len,
+                                                                         int precision, char* out, size_t out_cap) {
+    using namespace TNN_NS;
+    auto* interp = dynamic_cast<DefaultModelInterpreter*>(CreateModelInterpreter(MODEL_TYPE_TNN));
+    if (!interp) return -1;
+    std::unique_ptr<DefaultModelInterpreter> guard(interp);
+    std::vector<std::string> params = {std::string(proto, proto_len), std::string(model, model_len)};
+    if (interp->Interpret(params) != TNN_OK) return -2;
+    optimizer::NetOptimizerB200FuseAttention pass;
+    NetworkConfig cfg;
+    cfg.device_type  = DEVICE_CUDA;
+    cfg.network_type = NETWORK_TYPE_DEFAULT;
+    cfg.precision    = static_cast<Precision>(precision);
+    if (!pass.IsSupported(cfg)) return -3;
+    Status st = pass.Optimize(interp->GetNetStructure(), interp->GetNetResource());
+    if (st != TNN_OK) return -4;
+    // run it again: must be a no-op
+    if (pass.Optimize(interp->GetNetStructure(), interp->GetNetResource()) != TNN_OK) return -5;
+    std::string text;
+    for (auto& l : interp->GetNetStructure()->layers) {
+        text += l->type_str + " " + l->name;
+        for (auto& i : l->inputs) text += " " + i;
+        text += " ->";
+        for (auto& o : l->outputs) text += " " + o;
+        text += "\n";
+    }
+    if (text.size() + 1 > out_cap) return -6;
+    std::memcpy(out, text.c_str(), text.size() + 1);
+    return static_cast<int>(interp->GetNetStructure()->layers.size());
+}

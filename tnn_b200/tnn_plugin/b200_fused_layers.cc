@@ -1,0 +1,93 @@
+// Shape / data-type inference of the two fused layer types, and their registration (layer factory + type names).
+// Modelled on how the reference adds a CUDA-only fused layer (source/tnn/layer/cbam_fused_reduce_layer.cc).
+#include <map>
+#include <string>
+
+#include "b200_plugin_common.h"
+#include "tnn/layer/base_layer.h"
+
+namespace TNN_NS {
+
+// ---------------------------------------------------------------- type names
+// global_layer_type_map is a file-static of layer_type.cc that is only reachable through a const accessor
+// (source/tnn/core/layer_type.cc:261-263); a build inside the TNN tree would add the two strings there instead.
+struct B200LayerTypeNames {
+    B200LayerTypeNames() {
+        auto& m = const_cast<std::map<std::string, LayerType>&>(GetGlobalLayerTypeMap());
+        m[kFusedLinearTypeName]    = LAYER_B200_FUSED_LINEAR;
+        m[kFusedAttentionTypeName] = LAYER_B200_FUSED_ATTENTION;
+    }
+};
+static B200LayerTypeNames g_b200_layer_type_names;
+
+// ---------------------------------------------------------------- FusedLinear
+DECLARE_LAYER(B200FusedLinear, LAYER_B200_FUSED_LINEAR);
+
+Status B200FusedLinearLayer::InferOutputDataType() {
+    BaseLayer::InferOutputDataType();
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    for (auto* b : output_blobs_) b->GetBlobDesc().data_type = TnnDataType(p->compute_dtype);
+    return TNN_OK;
+}
+
+// Output dims = input dims with the last one replaced by N (the MatMul rule for a 2-D weight,
+// source/tnn/layer/mat_mul_layer.cc:42-148).
+Status B200FusedLinearLayer::InferOutputShape(bool ignore_error) {
+    BaseLayer::InferOutputShape(ignore_error);
+    auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    DimsVector dims = input_blobs_[0]->GetBlobDesc().dims;
+    if (dims.size() < 2 || dims.back() != p->in_features) {
+        LOGE_IF(!ignore_error, "FusedLinear: input feature dim does not match the weight\n");
+        return Status(TNNERR_PARAM_ERR, "FusedLinear: input feature dim does not match the weight");
+    }
+    if (p->epilogue == B200_EPI_BIAS_RESIDUAL) {
+        if (input_blobs_.size() < 2) return Status(TNNERR_PARAM_ERR, "FusedLinear: residual input missing");
+        DimsVector r = input_blobs_[1]->GetBlobDesc().dims;
+        DimsVector want = dims;
+        want.back() = p->out_features;
+        if (r != want) return Status(TNNERR_PARAM_ERR, "FusedLinear: residual dims differ from the output dims");
+    }
+    dims.back() = p->out_features;
+    output_blobs_[0]->GetBlobDesc().dims = dims;
+    return TNN_OK;
+}
+REGISTER_LAYER(B200FusedLinear, LAYER_B200_FUSED_LINEAR);
+
+// ---------------------------------------------------------------- FusedAttention
+DECLARE_LAYER(B200FusedAttention, LAYER_B200_FUSED_ATTENTION);
+
+Status B200FusedAttentionLayer::InferOutputDataType() {
+    BaseLayer::InferOutputDataType();
+    auto* p = dynamic_cast<FusedAttentionLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    for (auto* b : output_blobs_) b->GetBlobDesc().data_type = TnnDataType(p->compute_dtype);
+    return TNN_OK;
+}
+
+// qkv [B, S, 3*heads*head_dim] -> context [B, S, heads*head_dim]
+Status B200FusedAttentionLayer::InferOutputShape(bool ignore_error) {
+    BaseLayer::InferOutputShape(ignore_error);
+    auto* p = dynamic_cast<FusedAttentionLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    DimsVector dims = input_blobs_[0]->GetBlobDesc().dims;
+    const int hidden = p->heads * p->head_dim;
+    if (dims.size() != 3 || dims[2] != 3 * hidden) {
+        LOGE_IF(!ignore_error, "FusedAttention: qkv input must be [B, S, 3*heads*head_dim]\n");
+        return Status(TNNERR_PARAM_ERR, "FusedAttention: qkv input must be [B, S, 3*heads*head_dim]");
+    }
+    if (input_blobs_.size() > 1) {
+        const DimsVector m = input_blobs_[1]->GetBlobDesc().dims;
+        int64_t n = 1;
+        for (int d : m) n *= d;
+        if (m.empty() || m[0] != dims[0] || m.back() != dims[1] || n != static_cast<int64_t>(dims[0]) * dims[1])
+            return Status(TNNERR_PARAM_ERR, "FusedAttention: mask must be [B,1,1,S]");
+    }
+    dims[2] = hidden;
+    output_blobs_[0]->GetBlobDesc().dims = dims;
+    return TNN_OK;
+}
+REGISTER_LAYER(B200FusedAttention, LAYER_B200_FUSED_ATTENTION);
+
+}  // namespace TNN_NS

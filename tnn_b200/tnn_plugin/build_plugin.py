@@ -28,6 +28,18 @@ def main():
     link = ["-L" + REF_OUT, "-lTNN", "-Wl,-rpath,$ORIGIN"]
     subprocess.check_call(common + [os.path.join(HERE, "tnn_capi.cc"), "-o", os.path.join(REF_OUT, "libtnn_capi.so")]
                           + link)
+
+    # The DEVICE_CUDA plug-in: device, context, blob converter, fused layers, accs and the graph pass.  Loaded into
+    # a process next to libTNN.so (dlopen / LD_PRELOAD / link), its static constructors register everything.
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    libdir = os.path.join(ROOT, "tnn_b200", "lib")
+    srcs = sorted(glob.glob(os.path.join(HERE, "b200_*.cc")))
+    out = os.path.join(libdir, "libtnn_b200_plugin.so")
+    cmd = (common + ["-I%s/include" % cuda, "-I%s/include" % ROOT, "-I%s/third_party/xbyak" % ref] + srcs +
+           ["-o", out, "-L" + libdir, "-ltnn_b200", "-L" + REF_OUT, "-lTNN",
+            "-L%s/lib64" % cuda, "-lcudart_static", "-ldl", "-lrt", "-lpthread",
+            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../oracle/_ref"])
+    subprocess.check_call(cmd)
     return 0
 
 
