@@ -172,6 +172,14 @@ def run_reference_arm(args):
     return 0
 
 
+def reduce_max_over_ranks(t, world):
+    """MAX-reduce a tensor of timings over all ranks (the step time of the job is the slowest rank's)."""
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t
+
+
 # ------------------------------------------------------------------------------------------------ our arm
 def run_ours(args):
     import numpy as np
@@ -326,8 +334,7 @@ def run_ours(args):
 
     # ---- reduce over ranks
     ms_t = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_t = reduce_max_over_ranks(ms_t, world)
     ms_total_max, e2e_ms_max = float(ms_t[0]), float(ms_t[1])
     seqs = world * B * args.steps
     value = seqs / (ms_total_max / 1e3)
