@@ -75,11 +75,13 @@ B200_API int b200_convert(const void* src, int src_dtype, void* dst, int dst_dty
  * the reference's CUDA MatMul acc is a batched GEMV only, source/tnn/device/cuda/acc/cuda_mat_mul_layer_acc.cu:181-249)
  * followed by the bias Add (source/tnn/device/x86/acc/x86_add_layer_acc.cc:66-92), and optionally GELU
  * (source/tnn/device/x86/acc/x86_gelu_layer_acc.cc:22-62, erf form) or the residual Add.
- * tcgen05 UMMA 128 x BN x 16 (fp32 accumulation in TMEM), operands by TMA into 128-byte-swizzled shared memory.
+ * tcgen05 UMMA (fp32 accumulation in TMEM), operands by TMA into 128-byte-swizzled shared memory; tiles of 256 x BN
+ * on pairs of SMs (cta_group::2) or 128 x BN on one SM.
  *   x, w_nk, residual : `dtype` (B200_F16 or B200_BF16); y : `out_dtype` (F16, BF16 or F32); bias : fp32 or NULL.
  *   Requirements: K % 8 == 0, ldx % 8 == 0, ldw % 8 == 0, x and w_nk 16-byte aligned; y/residual rows 16-byte aligned
  *   (N % 8 == 0, ldy % 8 == 0, ldr % 8 == 0).  M, N, K > 0 otherwise arbitrary (edge tiles are zero-filled/guarded).
- *   block_n: 0 = choose, else 64, 128 or 256.
+ *   block_n: 0 = choose the tile; > 0 = tile width 64, 128, 192 (CTA-pair tiles only) or 256, on CTA-pair tiles
+ *            (256 x block_n, two SMs per tile) when M > 128; < 0 = single-CTA tiles (128 x -block_n), for testing.
  */
 typedef struct B200LinearDesc {
     const void*  x;

@@ -31,10 +31,13 @@ def _status_clean(cuda_device):
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
+# bn > 0: tile width on CTA-pair tiles (256 x bn) when M > 128; bn < 0: single-CTA tiles (128 x -bn); 0: auto
 @pytest.mark.parametrize("M,N,K,bn", [
     (128, 128, 64, 128), (128, 256, 128, 256), (256, 64, 64, 64),
     (512, 768, 768, 0), (300, 2304, 768, 0), (1, 8, 8, 0), (129, 136, 72, 128),
     (1024, 3072, 768, 256), (640, 768, 3072, 128),
+    (256, 256, 64, 256), (257, 392, 200, 192), (1000, 768, 768, 192), (8192, 768, 768, 0),
+    (900, 2304, 768, -256), (384, 200, 136, -128), (512, 72, 64, -64), (700, 1024, 1024, 64),
 ])
 def test_linear_bias(cuda_device, dt, M, N, K, bn):
     rng = np.random.default_rng(M * 7 + N * 3 + K)
@@ -166,11 +169,11 @@ def test_attention_mask_with_holes_and_no_mask(cuda_device):
     assert max_abs(_np(out), want) < 6e-3
 
 
-def test_attention_padded_keys_have_exactly_zero_weight(cuda_device):
+@pytest.mark.parametrize("S,lengths", [(256, [77, 200]), (128, [5, 100]), (96, [33, 96])])
+def test_attention_padded_keys_have_exactly_zero_weight(cuda_device, S, lengths):
     """Perturbing K/V rows of padded keys must leave every output bit-identical."""
-    B, S, heads = 2, 256, 4
+    B, heads = 2, 4
     H = heads * 64
-    lengths = [77, 200]
     got, _, qd, md, kv = _attention_case(cuda_device, "f16", B, S, heads, lengths, seed=11)
     q2 = qd.clone()
     for b, n in enumerate(lengths):

@@ -10,7 +10,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libtnn_b200.so")
+LIB_PATH = os.environ.get("TNN_B200_LIB", os.path.join(_HERE, "lib", "libtnn_b200.so"))
 
 F16, BF16, F32 = 0, 1, 2
 EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL = 0, 1, 2

@@ -45,12 +45,13 @@ inline bool is_half_dtype(int dt) { return dt == B200_F16 || dt == B200_BF16; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------- tensor maps
-// 2-D or 3-D tiled map over a 2-byte-element tensor whose innermost dimension is contiguous, 128-byte swizzle,
-// inner box = 64 elements (128 bytes).  dims/strides are innermost first; strides[i] is the byte stride of dim i+1.
+// 2-D or 3-D tiled map over a 2-byte-element tensor whose innermost dimension is contiguous, 128- or 64-byte
+// swizzle, inner box = 64 or 32 elements.  dims/strides are innermost first; strides[i] is the byte stride of dim i+1.
 // Maps are cached per device by their full key; encoding takes about a microsecond and the same activations and
 // weights come back every Forward.  Returns nullptr if the driver entry point is missing or refuses the descriptor.
+// swizzle_bytes: 128 (box inner extent 64 elements) or 64 (inner extent 32 elements).
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box);
+                                  const uint32_t* box, int swizzle_bytes = 128);
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH; }
 

@@ -103,26 +103,26 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(B200LayerNormDesc d)
     }
 }
 
-// Persistent variant for H <= 1024 (NV <= 4): a warp walks rows with a grid stride, keeps its gamma/beta slice in
-// registers for all of them (the generic kernel re-reads 4x more gamma/beta bytes than activation bytes per row) and
-// has the next row's loads in flight while it reduces the current one.
-template <int NV>
-__global__ void __launch_bounds__(128) add_layernorm_rows_kernel(B200LayerNormDesc d) {
+// Persistent variant for H <= 1024 (NV <= 4): 8 warps per block walk rows with a grid stride; gamma/beta sit in
+// shared memory (the generic kernel re-reads 4x more gamma/beta bytes than activation bytes per row), and every warp
+// has the next row's loads in flight while it reduces the current one, so that with 4 blocks per SM about 64 rows
+// (100 KB) per SM are in flight — enough to cover HBM latency at full bandwidth.
+template <int NV, bool F32IN>
+__global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm_rows_kernel(B200LayerNormDesc d) {
+    extern __shared__ float gb[];   // gamma[H] | beta[H]
     const int lane = threadIdx.x & 31;
-    const long long warp0 = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-    const long long nwarps = static_cast<long long>(gridDim.x) * 4;
-    const int groups = static_cast<int>(d.H >> 3);
-    const bool f32_in = d.in_dtype == B200_F32;
-    float gm[NV][8], bt[NV][8];
-#pragma unroll
-    for (int g = 0; g < NV; ++g) {
-        const int gi = g * 32 + lane;
-        if (gi < groups) {
-            load8(d.gamma, gi * 8, B200_F32, gm[g]);
-            load8(d.beta, gi * 8, B200_F32, bt[g]);
-        }
+    const int H = static_cast<int>(d.H);
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        *reinterpret_cast<float4*>(gb + i) = __ldg(reinterpret_cast<const float4*>(d.gamma + i));
+        *reinterpret_cast<float4*>(gb + H + i) = __ldg(reinterpret_cast<const float4*>(d.beta + i));
     }
-    uint4 raw[NV][2], rres[NV][2];
+    __syncthreads();
+    const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const long long nwarps = static_cast<long long>(gridDim.x) * 8;
+    const int groups = H >> 3;
+    constexpr bool f32_in = F32IN;
+    constexpr int Q = F32IN ? 2 : 1;   // 16-byte pieces per group of 8 elements
+    uint4 raw[NV][Q], rres[NV][Q];
     auto fetch = [&](long long row) {
 #pragma unroll
         for (int g = 0; g < NV; ++g) {
@@ -131,11 +131,11 @@ __global__ void __launch_bounds__(128) add_layernorm_rows_kernel(B200LayerNormDe
                 if (f32_in) {
                     const uint4* px = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.x) + row * d.ldx + gi * 8);
                     raw[g][0] = __ldg(px);
-                    raw[g][1] = __ldg(px + 1);
+                    raw[g][Q - 1] = __ldg(px + 1);
                     if (d.residual) {
                         const uint4* pr = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.residual) + row * d.ldr + gi * 8);
                         rres[g][0] = __ldg(pr);
-                        rres[g][1] = __ldg(pr + 1);
+                        rres[g][Q - 1] = __ldg(pr + 1);
                     }
                 } else {
                     raw[g][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d.x) + row * d.ldx + gi * 8));
@@ -145,12 +145,12 @@ __global__ void __launch_bounds__(128) add_layernorm_rows_kernel(B200LayerNormDe
             }
         }
     };
-    auto decode = [&](const uint4 (&q)[2], float (&v)[8]) {
+    auto decode = [&](const uint4 (&q)[Q], float (&v)[8]) {
         if (f32_in) {
             v[0] = __uint_as_float(q[0].x); v[1] = __uint_as_float(q[0].y);
             v[2] = __uint_as_float(q[0].z); v[3] = __uint_as_float(q[0].w);
-            v[4] = __uint_as_float(q[1].x); v[5] = __uint_as_float(q[1].y);
-            v[6] = __uint_as_float(q[1].z); v[7] = __uint_as_float(q[1].w);
+            v[4] = __uint_as_float(q[Q - 1].x); v[5] = __uint_as_float(q[Q - 1].y);
+            v[6] = __uint_as_float(q[Q - 1].z); v[7] = __uint_as_float(q[Q - 1].w);
         } else {
             const uint32_t w[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
 #pragma unroll
@@ -205,9 +205,15 @@ __global__ void __launch_bounds__(128) add_layernorm_rows_kernel(B200LayerNormDe
         for (int g = 0; g < NV; ++g) {
             const int gi = g * 32 + lane;
             if (gi < groups) {
+                const float4 g0 = *reinterpret_cast<const float4*>(gb + gi * 8);
+                const float4 g1 = *reinterpret_cast<const float4*>(gb + gi * 8 + 4);
+                const float4 b0 = *reinterpret_cast<const float4*>(gb + H + gi * 8);
+                const float4 b1 = *reinterpret_cast<const float4*>(gb + H + gi * 8 + 4);
+                const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                 float o[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[g][e] + bt[g][e];
+                for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[e] + bt[e];
                 store8(d.y, row * d.ldy + gi * 8, d.out_dtype, o);
             }
         }
@@ -304,15 +310,24 @@ int b200_add_layernorm_fwd(const B200LayerNormDesc* d, b200_stream_t stream_) {
     const unsigned grid = static_cast<unsigned>((d->rows + warps_per_block - 1) / warps_per_block);
     const int nv = static_cast<int>((d->H / 8 + 31) / 32);
     if (nv <= 4) {
-        // One resident wave: the register footprint (gamma/beta slices + a prefetched row) allows 4 / 3 / 2 blocks
-        // of 4 warps per SM; every warp then walks rows with a grid stride.
-        const int per_sm = nv <= 1 ? 4 : (nv <= 3 ? 3 : 2);
-        long long blocks = (d->rows + 3) / 4;
+        // One resident wave of 3 (2 for the wider variants) blocks x 8 warps per SM; every warp then walks rows with a
+        // grid stride.
+        const bool f32 = d->in_dtype == B200_F32;
+        const long long per_sm = (nv >= 4 || f32) ? 2 : 3;
+        long long blocks = (d->rows + 7) / 8;
         if (blocks > 148ll * per_sm) blocks = 148ll * per_sm;
         const unsigned g2 = static_cast<unsigned>(blocks);
-        if (nv <= 1) add_layernorm_rows_kernel<1><<<g2, 128, 0, stream>>>(*d);
-        else if (nv <= 3) add_layernorm_rows_kernel<3><<<g2, 128, 0, stream>>>(*d);
-        else add_layernorm_rows_kernel<4><<<g2, 128, 0, stream>>>(*d);
+        const size_t sm = static_cast<size_t>(d->H) * 2 * sizeof(float);
+        if (nv <= 1) {
+            if (f32) add_layernorm_rows_kernel<1, true><<<g2, 256, sm, stream>>>(*d);
+            else add_layernorm_rows_kernel<1, false><<<g2, 256, sm, stream>>>(*d);
+        } else if (nv <= 3) {
+            if (f32) add_layernorm_rows_kernel<3, true><<<g2, 256, sm, stream>>>(*d);
+            else add_layernorm_rows_kernel<3, false><<<g2, 256, sm, stream>>>(*d);
+        } else {
+            if (f32) add_layernorm_rows_kernel<4, true><<<g2, 256, sm, stream>>>(*d);
+            else add_layernorm_rows_kernel<4, false><<<g2, 256, sm, stream>>>(*d);
+        }
     } else if (nv <= 8) add_layernorm_kernel<8><<<grid, 256, 0, stream>>>(*d);
     else add_layernorm_kernel<16><<<grid, 256, 0, stream>>>(*d);
     count_launch();

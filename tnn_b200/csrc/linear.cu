@@ -10,57 +10,27 @@
 //                                   residual in registers, 16-byte stores.  Two warps share a 32-row quarter and
 //                                   split the columns.  While they drain accumulator b, the issuer fills b^1.
 // Algorithmic work per launch: 2*M*N*K flop; HBM traffic at least (M*K + N*K + M*N (+ M*N residual)) elements.
-#include "common.cuh"
-#include "ptx.cuh"
+#include "linear_common.cuh"
 
 namespace b200 {
-
-namespace {
-
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + kEpiWarps * 32;
-
-struct LinearParams {
-    const float* bias;
-    const void* residual;
-    void* y;
-    int M, N, K;
-    long long ldr, ldy;
-    int dtype, out_dtype, epilogue;
-    int num_n_tiles, num_tiles, num_k_blocks;
-    uint32_t idesc;
-    unsigned int* status;
-};
+namespace lin {
 
 template <int BN, int STAGES>
 struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;               // output staging strips (TMA store)
+    static constexpr int BAR_OFFSET = OUT_OFFSET + kEpiWarps * kStageBytesPerWarp;
     static constexpr int BIAS_OFFSET = BAR_OFFSET + 256;         // per-epilogue-warp bias slice: 8 x (BN/2) floats
     static constexpr int SMEM_BYTES = BIAS_OFFSET + kEpiWarps * (BN / 2) * 4 + 1024;  // + slack for 1024-byte alignment
     static constexpr int TMEM_COLS = 2 * BN;                    // 128, 256 or 512: powers of two
 };
 
-// erf-form GELU, 0.5 x (1 + erf(x / sqrt 2)) = x * Phi(x), as the reference's CPU accs compute it, evaluated as
-// x * sigmoid(2 x (a + b x^2 + c x^4)) with a, b, c fitted to the erf form (max abs deviation 2.5e-5 over all x, i.e.
-// a tenth of a half-precision ulp at |y| ~ 0.5; the reference's own vector path deviates from erf by ~1e-7).  x^2 is
-// clamped at 36, where the sigmoid has saturated, so the negative x^4 term cannot turn the argument around.
-// Cost: 2 MUFU (ex2, rcp) + 7 FMA-pipe instructions instead of erff's ~30.
-__device__ __forceinline__ float gelu_erf(float x) {
-    const float x2 = fminf(x * x, 36.0f);
-    // -2 * log2(e) * (a + b x^2 + c x^4)
-    const float poly = fmaf(x2, fmaf(x2, 1.0142631e-3f, -1.0677572e-1f), -2.3011213f);
-    const float e = exp2f(x * poly);           // exp(-2u)
-    return __fdividef(x, 1.0f + e);
-}
-
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
-linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const LinearParams p) {
+linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+              const __grid_constant__ CUtensorMap tm_y, const LinearParams p) {
     using C = Cfg<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -160,6 +130,8 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         constexpr int COLS = BN / 2;
         constexpr int CHUNKS = COLS / 32;
         float* bias_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * COLS;  // private to this warp
+        WarpEpilogue<CHUNKS, false> epi{p, &tm_y, nullptr, smem + C::OUT_OFFSET + ew * kStageBytesPerWarp, nullptr,
+                                        abort_flag, lane, 0u};
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
@@ -168,87 +140,20 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const uint32_t buf = tcount & 1u;
             const uint32_t aph = (tcount >> 1) & 1u;
             // Stage this tile's bias slice while the accumulator is still being produced.
-            __syncwarp();
-            for (int i = lane; i < COLS; i += 32) {
-                const int n = n_blk * BN + half * COLS + i;
-                bias_w[i] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.f;
-            }
-            __syncwarp();
+            stage_bias(p, bias_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();  // tcgen05.ld is warp-collective
             tcgen05_fence_after();
-            const int row = m_blk * BM + quarter * 32 + lane;
-            const bool row_ok = row < p.M;
-#pragma unroll 1
-            for (int c = 0; c < CHUNKS; ++c) {
-                const int col0 = half * COLS + c * 32;
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + col0;
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr, r);
-                tmem_ld_wait(r);
-                const int n0 = n_blk * BN + col0;
-                if (n0 >= p.N) continue;  // uniform across the warp
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 b = *reinterpret_cast<const float4*>(bias_w + c * 32 + g * 4);
-                    v[g * 4 + 0] += b.x;
-                    v[g * 4 + 1] += b.y;
-                    v[g * 4 + 2] += b.z;
-                    v[g * 4 + 3] += b.w;
-                }
-                if (p.epilogue == B200_EPI_BIAS_GELU) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-                }
-                if (!row_ok) continue;
-                if (p.epilogue == B200_EPI_BIAS_RESIDUAL) {
-                    const uint16_t* rp = reinterpret_cast<const uint16_t*>(p.residual) + row * p.ldr + n0;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        if (n0 + g * 8 < p.N) {
-                            const uint4 q = __ldg(reinterpret_cast<const uint4*>(rp + g * 8));
-                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 f = unpack2(w[e], p.dtype);
-                                v[g * 8 + e * 2 + 0] += f.x;
-                                v[g * 8 + e * 2 + 1] += f.y;
-                            }
-                        }
-                    }
-                }
-                if (p.out_dtype == B200_F32) {
-                    float* yp = reinterpret_cast<float*>(p.y) + row * p.ldy + n0;
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        if (n0 + g * 4 < p.N) {
-                            *reinterpret_cast<float4*>(yp + g * 4) =
-                                make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                        }
-                    }
-                } else {
-                    uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + row * p.ldy + n0;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        if (n0 + g * 8 < p.N) {
-                            uint4 q;
-                            q.x = pack2(v[g * 8 + 0], v[g * 8 + 1], p.out_dtype);
-                            q.y = pack2(v[g * 8 + 2], v[g * 8 + 3], p.out_dtype);
-                            q.z = pack2(v[g * 8 + 4], v[g * 8 + 5], p.out_dtype);
-                            q.w = pack2(v[g * 8 + 6], v[g * 8 + 7], p.out_dtype);
-                            *reinterpret_cast<uint4*>(yp + g * 8) = q;
-                        }
-                    }
-                }
-            }
+            const long long row = static_cast<long long>(m_blk) * BM + quarter * 32 + lane;
+            const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            epi.run(bias_w, tacc, row, n_blk * BN, half * COLS);
             // This warp has read everything it needs from accumulator `buf`.
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
+        if (lane == 0) tma_store_wait_all<0>();   // this warp's tile stores have left shared memory and landed
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- teardown (also the exit of an aborted CTA)
@@ -287,6 +192,14 @@ int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     const CUtensorMap* tx = get_tensor_map(d.x, 2, xd, xs, xb);
     const CUtensorMap* tw = get_tensor_map(d.w_nk, 2, wd, ws, wb);
     if (!tx || !tw) return B200_ERR_DRIVER;
+    const CUtensorMap* ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
+    if (d.out_dtype != B200_F32) {
+        const uint64_t yd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
+        const uint64_t ys[1] = {static_cast<uint64_t>(d.ldy) * 2};
+        const uint32_t yb[2] = {32, 32};
+        ty = get_tensor_map(d.y, 2, yd, ys, yb, 64);
+        if (!ty) return B200_ERR_DRIVER;
+    }
 
     LinearParams p;
     p.bias = d.bias;
@@ -316,35 +229,56 @@ int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
         attr_set[dev] = true;
     }
     const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-    linear_kernel<BN, STAGES><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, p);
+    linear_kernel<BN, STAGES><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, p);
     count_launch();
     return check_launch();
 }
 
-int choose_block_n(int64_t M, int64_t N, int sm_count) {
-    // Estimated time ~ waves * BN * (per-column cost): narrow tiles read proportionally more shared memory per flop.
-    const int cand[3] = {256, 128, 64};
-    const double cost[3] = {1.0, 1.12, 1.5};
-    const int64_t mt = (M + BM - 1) / BM;
-    double best = 1e300;
-    int best_bn = 128;
-    for (int i = 0; i < 3; ++i) {
-        const int64_t tiles = mt * ((N + cand[i] - 1) / cand[i]);
-        const int64_t waves = (tiles + sm_count - 1) / sm_count;
-        const double t = static_cast<double>(waves) * cand[i] * cost[i];
-        if (t < best) {
-            best = t;
-            best_bn = cand[i];
+// Tile choice.  Estimated time ~ waves * (columns per tile * cost per column + fixed per-tile cost), in units of
+// "accumulator columns per SM".  Pair tiles (256 x BN on two SMs) keep the tensor pipe busier than single-CTA tiles
+// (128 x BN) because they need half the w traffic per SM; narrow tiles pay more shared-memory reads per flop.
+struct TileChoice {
+    bool pair;
+    int bn;
+};
+TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
+    TileChoice best = {false, 128};
+    double best_t = 1e300;
+    if (M > 128) {
+        const int bns[4] = {256, 192, 128, 64};
+        const double cost[4] = {1.0, 1.03, 1.10, 1.40};
+        for (int i = 0; i < 4; ++i) {
+            int pairs = max_active_pairs(bns[i]);
+            if (pairs <= 0) continue;
+            const int64_t tiles = ((M + 255) / 256) * ((N + bns[i] - 1) / bns[i]);
+            const int64_t waves = (tiles + pairs - 1) / pairs;
+            const double t = static_cast<double>(waves) * (bns[i] * cost[i] + 16.0);
+            if (t < best_t) {
+                best_t = t;
+                best = {true, bns[i]};
+            }
         }
     }
-    return best_bn;
+    const int bns1[3] = {256, 128, 64};
+    const double cost1[3] = {1.35, 1.50, 1.90};
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = ((M + BM - 1) / BM) * ((N + bns1[i] - 1) / bns1[i]);
+        const int64_t waves = (tiles + sm_count - 1) / sm_count;
+        const double t = static_cast<double>(waves) * (bns1[i] * cost1[i] + 16.0);
+        if (t < best_t) {
+            best_t = t;
+            best = {false, bns1[i]};
+        }
+    }
+    return best;
 }
 
-}  // namespace
+}  // namespace lin
 }  // namespace b200
 
 extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
     using namespace b200;
+    using namespace b200::lin;
     if (!d || !d->x || !d->w_nk || !d->y) return B200_ERR_PARAM;
     if (d->M <= 0 || d->N <= 0 || d->K <= 0) return B200_ERR_PARAM;
     if (d->M > (1ll << 30) || d->N > (1ll << 30) || d->K > (1ll << 30)) return B200_ERR_UNSUPPORTED;
@@ -361,9 +295,24 @@ extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
     const int sms = device_sm_count();
     if (sms <= 0) return B200_ERR_NOT_SM100;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    int bn = d->block_n;
-    if (bn == 0) bn = choose_block_n(d->M, d->N, sms);
-    switch (bn) {
+    TileChoice tc;
+    if (d->block_n == 0) {
+        tc = choose_tile(d->M, d->N, sms);
+    } else if (d->block_n > 0) {
+        tc = {d->M > 128, d->block_n};
+    } else {
+        tc = {false, -d->block_n};
+    }
+    if (tc.pair) {
+        switch (tc.bn) {
+            case 256: return launch_linear_pair<256>(*d, stream, sms);
+            case 192: return launch_linear_pair<192>(*d, stream, sms);
+            case 128: return launch_linear_pair<128>(*d, stream, sms);
+            case 64: return launch_linear_pair<64>(*d, stream, sms);
+            default: return B200_ERR_PARAM;
+        }
+    }
+    switch (tc.bn) {
         case 256: return launch_linear<256, 4>(*d, stream, sms);
         case 128: return launch_linear<128, 6>(*d, stream, sms);
         case 64: return launch_linear<64, 8>(*d, stream, sms);

@@ -1,0 +1,374 @@
+// Projection / FFN GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs on neighbouring SMs computes one
+// 256 x BN output tile.  Each CTA loads its own 128 rows of x and its own BN/2 rows of w per k-block (plain TMA, no
+// multicast: the two CTAs load different data) and the UMMA of the pair reads both CTAs' shared memory, so per SM the
+// w traffic from L2 and the shared-memory bandwidth spent on w are half of what a single-CTA 128 x BN tile needs, and
+// the same 192 KB of pipeline stages covers 1.5x more tensor-core time.
+//
+// Roles per CTA (320 threads, 1 CTA per SM):
+//   warp 0      : TMA producer for this CTA's halves; completion bytes of BOTH CTAs land on the leader's `full`
+//                 barrier (cp.async.bulk.tensor ... .cta_group::2 with the barrier address of CTA rank 0).
+//   warp 1      : TMEM allocation (cta_group::2, both CTAs); in the leader CTA one lane issues
+//                 tcgen05.mma.cta_group::2 (256 x BN x 16) and commits, multicast to both CTAs' `empty` / `acc_full`.
+//   warps 2..9  : epilogue of this CTA's 128 rows (its own TMEM), then arrive on the leader's `acc_empty`.
+// Every wait is bounded; the two CTAs meet at a cluster barrier before either releases TMEM or exits.
+#include "linear_common.cuh"
+
+namespace b200 {
+namespace lin {
+
+namespace {
+
+template <int BN, bool RES>
+struct PairCfg {
+    static constexpr int A_BYTES = 128 * BK * 2;          // this CTA's 128 rows of x
+    static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this CTA's BN/2 rows of w
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    // output staging strips (TMA store); with RES two per warp, which also receive the residual tile (TMA load)
+    static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * (RES ? 2 : 1);
+    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * (BN / 2) * 4;   // + barriers + bias strips
+    static constexpr int STAGES = (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES > 8
+                                      ? 8 : (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES;
+    static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFFSET = OUT_OFFSET + OUT_BYTES;
+    static constexpr int BIAS_OFFSET = BAR_OFFSET + 512;
+    static constexpr int SMEM_BYTES = OUT_OFFSET + TAIL_BYTES + 1024;
+    static constexpr int TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512);   // two accumulators of BN columns
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in the pair's leader CTA (cluster rank 0): the shared::cta address of a
+// CTA in a cluster carries its rank in bit 24.
+__device__ __forceinline__ uint32_t leader_addr(const void* p) { return smem_u32(p) & 0xFEFFFFFFu; }
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int32_t c0,
+                                                 int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in both CTAs of the pair once all UMMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(mask)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, 0;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}\n"
+        ::"r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+template <int BN, bool RES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                   const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_r,
+                   const LinearParams p) {
+    using C = PairCfg<BN, RES>;
+    constexpr int STAGES = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // Both CTAs of a pair must lay their buffers out at identical offsets: the dynamic shared-memory window starts at
+    // the same offset in every CTA of a kernel, so rounding it up gives the same result in both.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint64_t* res_bars = acc_empty + 2;                       // 2 per epilogue warp (RES only)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + 2 * kEpiWarps);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);    // leader's copy is the one in use: its own expect_tx arrival
+            mbar_init(&empty[s], 1);   // one multicast commit per use
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 2 * kEpiWarps);   // leader's copy: epilogue warps of both CTAs
+        }
+        for (int b = 0; b < 2 * kEpiWarps; ++b) mbar_init(&res_bars[b], 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tm_x);
+        prefetch_tmap(&tm_w);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers are initialised and its TMEM allocated before anything is signalled
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+                const int m_blk = tile / p.num_n_tiles;
+                const int n_blk = tile % p.num_n_tiles;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* a = smem + s * C::STAGE_BYTES;
+                    uint8_t* b = a + C::A_BYTES;
+                    if (leader) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
+                    const uint32_t bar = leader_addr(&full[s]);
+                    tma_load_2d_pair(a, &tm_x, bar, kb * BK, m_blk * 256 + static_cast<int>(rank) * 128);
+                    tma_load_2d_pair(b, &tm_w, bar, kb * BK, n_blk * BN + static_cast<int>(rank) * (BN / 2));
+                }
+            }
+            if (!ok) {
+                for (int i = 0; i < 64; ++i) nanosleep(10000);   // let copies in flight land
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer (leader CTA only)
+        if (leader && elect_one()) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tcount) {
+                const uint32_t buf = tcount & 1u;
+                const uint32_t aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16_ss_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const int ew = warp - 2;
+        const int quarter = warp & 3;
+        const int half = ew >> 2;
+        constexpr int COLS = BN / 2;
+        constexpr int CHUNKS = COLS / 32;
+        float* bias_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * COLS;
+        WarpEpilogue<CHUNKS, RES> epi{p, &tm_y, &tm_r,
+                                      smem + C::OUT_OFFSET + ew * kStageBytesPerWarp * (RES ? 2 : 1),
+                                      res_bars + 2 * ew, abort_flag, lane, 0u};
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tcount) {
+            const int m_blk = tile / p.num_n_tiles;
+            const int n_blk = tile % p.num_n_tiles;
+            const uint32_t buf = tcount & 1u;
+            const uint32_t aph = (tcount >> 1) & 1u;
+            const long long row = static_cast<long long>(m_blk) * 256 + rank * 128 + quarter * 32 + lane;
+            epi.begin_tile(n_blk * BN + half * COLS, static_cast<int>(row) - lane);
+            stage_bias(p, bias_w, n_blk * BN + half * COLS, COLS, lane);
+            if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
+            __syncwarp();
+            tcgen05_fence_after();
+            const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (!epi.run(bias_w, tacc, row, n_blk * BN, half * COLS)) { ok = false; break; }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(&acc_empty[buf]);
+                else mbar_arrive_leader(&acc_empty[buf]);
+            }
+        }
+        if (lane == 0) tma_store_wait_all<0>();   // this warp's tile stores have left shared memory and landed
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA frees TMEM or leaves while the other may still signal or read it
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 1u);
+}
+
+}  // namespace
+
+template <int BN, bool RES>
+int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
+    using C = PairCfg<BN, RES>;
+    static_assert(C::STAGES >= 3, "pipeline too shallow");
+    const uint64_t xd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.M)};
+    const uint64_t xs[1] = {static_cast<uint64_t>(d.ldx) * 2};
+    const uint32_t xb[2] = {BK, 128};
+    const uint64_t wd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.N)};
+    const uint64_t ws[1] = {static_cast<uint64_t>(d.ldw) * 2};
+    const uint32_t wb[2] = {BK, BN / 2};
+    const CUtensorMap* tx = get_tensor_map(d.x, 2, xd, xs, xb);
+    const CUtensorMap* tw = get_tensor_map(d.w_nk, 2, wd, ws, wb);
+    if (!tx || !tw) return B200_ERR_DRIVER;
+    const CUtensorMap* ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
+    if (d.out_dtype != B200_F32) {
+        const uint64_t yd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
+        const uint64_t ys[1] = {static_cast<uint64_t>(d.ldy) * 2};
+        const uint32_t yb[2] = {32, 32};
+        ty = get_tensor_map(d.y, 2, yd, ys, yb, 64);
+        if (!ty) return B200_ERR_DRIVER;
+    }
+    const CUtensorMap* tr = tx;   // placeholder without a residual
+    if (RES) {
+        const uint64_t rd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
+        const uint64_t rs[1] = {static_cast<uint64_t>(d.ldr) * 2};
+        const uint32_t rb[2] = {32, 32};
+        tr = get_tensor_map(d.residual, 2, rd, rs, rb, 64);
+        if (!tr) return B200_ERR_DRIVER;
+    }
+
+    LinearParams p;
+    p.bias = d.bias;
+    p.residual = d.residual;
+    p.y = d.y;
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.K = static_cast<int>(d.K);
+    p.ldr = d.ldr;
+    p.ldy = d.ldy;
+    p.dtype = d.dtype;
+    p.out_dtype = d.out_dtype;
+    p.epilogue = d.epilogue;
+    p.num_n_tiles = (p.N + BN - 1) / BN;
+    p.num_tiles = ((p.M + 255) / 256) * p.num_n_tiles;
+    p.num_k_blocks = (p.K + BK - 1) / BK;
+    p.idesc = make_idesc_f16(256, BN, d.dtype == B200_BF16 ? 1 : 0, 0, 0);
+    p.status = device_status_ptr();
+
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES) != cudaSuccess)
+            return B200_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    int pairs = max_active_pairs(BN);   // (the RES variant uses no more shared memory per CTA than its stage count allows)
+    if (pairs <= 0) pairs = sm_count / 2;
+    if (p.num_tiles < pairs) pairs = p.num_tiles;
+    linear_pair_kernel<BN, RES><<<2 * pairs, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, *tr, p);
+    count_launch();
+    return check_launch();
+}
+
+namespace {
+template <int BN>
+int query_pairs(int sm_count) {
+    // A persistent grid must not exceed what is co-resident: a pair that cannot be placed (GPCs with an odd number
+    // of free SMs) would otherwise run as a second wave after the first has finished all the work.
+    using C = PairCfg<BN, false>;
+    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+}  // namespace
+
+int max_active_pairs(int bn) {
+    static int cache[64][4] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 0;
+    const int idx = bn == 256 ? 0 : (bn == 192 ? 1 : (bn == 128 ? 2 : 3));
+    if (cache[dev][idx] == 0) {
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int n = bn == 256 ? query_pairs<256>(sms) : (bn == 192 ? query_pairs<192>(sms)
+                                                  : (bn == 128 ? query_pairs<128>(sms) : query_pairs<64>(sms)));
+        if (n > sms / 2) n = sms / 2;
+        cache[dev][idx] = n > 0 ? n : -1;
+    }
+    return cache[dev][idx] > 0 ? cache[dev][idx] : 0;
+}
+
+template <int BN>
+int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
+    // The TMA residual path needs 16-byte aligned residual rows (checked by the caller) and a half-precision residual.
+    if (d.epilogue == B200_EPI_BIAS_RESIDUAL) return launch_pair<BN, true>(d, stream, sm_count);
+    return launch_pair<BN, false>(d, stream, sm_count);
+}
+
+template int launch_linear_pair<256>(const B200LinearDesc&, cudaStream_t, int);
+template int launch_linear_pair<192>(const B200LinearDesc&, cudaStream_t, int);
+template int launch_linear_pair<128>(const B200LinearDesc&, cudaStream_t, int);
+template int launch_linear_pair<64>(const B200LinearDesc&, cudaStream_t, int);
+
+}  // namespace lin
+}  // namespace b200

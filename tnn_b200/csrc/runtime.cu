@@ -68,14 +68,15 @@ static std::mutex g_map_mutex;
 static std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box) {
+                                  const uint32_t* box, int swizzle_bytes) {
     if (rank < 2 || rank > 3) return nullptr;
+    if (swizzle_bytes != 128 && swizzle_bytes != 64) return nullptr;
     int dev = 0;
     cudaGetDevice(&dev);
     MapKey key;
     std::memset(&key, 0, sizeof(key));
     key.v[0] = reinterpret_cast<uint64_t>(base);
-    key.v[1] = static_cast<uint64_t>(rank) | (static_cast<uint64_t>(dev) << 8);
+    key.v[1] = static_cast<uint64_t>(rank) | (static_cast<uint64_t>(dev) << 8) | (static_cast<uint64_t>(swizzle_bytes) << 16);
     for (int i = 0; i < rank; ++i) {
         key.v[2 + i] = dims[i];
         key.v[8 + i] = box[i];
@@ -100,7 +101,8 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
     }
     for (int i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
     CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         delete map;
