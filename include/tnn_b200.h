@@ -64,6 +64,15 @@ enum {
 B200_API int b200_pack_weight(const float* w_kn, int64_t K, int64_t N, int64_t ld_src, void* w_nk, int64_t ld_dst,
                               int dtype, b200_stream_t stream);
 
+/* Weight pre-pack with a LayerNorm folded in (see B200LinearDesc: ln_in_stats).  For y = LN(x; gamma, beta).W + bias:
+ *   w_nk[n, k] = round(gamma[k] * w_kn[k, n])           (dtype, [N, K] at row stride ld_dst)
+ *   c1[n]      = sum_k float(w_nk[n, k])                 (the rounded values, so that the mean term cancels exactly)
+ *   c2[n]      = sum_k beta[k] * w_kn[k, n] + bias[n]    (bias may be NULL)
+ * One launch; c1, c2 are fp32 [N] device arrays. */
+B200_API int b200_fold_layernorm_weight(const float* w_kn, int64_t K, int64_t N, int64_t ld_src, const float* gamma,
+                                        const float* beta, const float* bias, void* w_nk, int64_t ld_dst, int dtype,
+                                        float* c1, float* c2, b200_stream_t stream);
+
 /* Element-wise dtype conversion of `n` contiguous elements (the fp32 <-> fp16/bf16 boundary of the fused region:
  * DefaultNetwork keeps every CUDA blob fp32, source/tnn/core/blob_manager.cc:101-117).  n*sizeof must keep both
  * pointers 16-byte aligned at their start. */
@@ -95,6 +104,27 @@ typedef struct B200LinearDesc {
     int32_t      out_dtype;
     int32_t      epilogue;
     int32_t      block_n;
+    /* ---- LayerNorm folding (all optional; zero-initialise the struct to leave it off) -------------------------------
+     * The two LayerNorm layers of an encoder layer can be folded into the GEMMs around them, so that only the
+     * PRE-LayerNorm activations t are ever written to HBM, together with per-row partial sums:
+     *   row statistics: fp32 pairs (sum, sum of squares) per 32-column chunk, laid out [ceil(N/32)][M][2] ("slots").
+     *   out_stats     : this GEMM writes the statistics of its output rows y (after residual), one slot per chunk.
+     *   ln_in_stats   : x is a pre-LayerNorm activation with these statistics (K/32 slots of M rows).  w_nk must have
+     *                   been packed with gamma folded in and ln_c1 / ln_c2 computed (b200_fold_layernorm_weight);
+     *                   the kernel then evaluates LN(x).W + b as rstd*(x.W' - mean*c1) + c2.  `bias` is ignored.
+     *   res_ln_stats  : the residual operand is a pre-LayerNorm activation with these statistics (N/32 slots); the
+     *                   kernel adds LN(residual) = (r - mean)*rstd*res_ln_gamma + res_ln_beta instead of r.
+     *   ln_eps        : epsilon of both normalisations.
+     */
+    float*       out_stats;
+    const float* ln_in_stats;
+    const float* ln_c1;
+    const float* ln_c2;
+    const float* res_ln_stats;
+    const float* res_ln_gamma;
+    const float* res_ln_beta;
+    float        ln_eps;
+    int32_t      reserved_;
 } B200LinearDesc;
 B200_API int b200_linear_fwd(const B200LinearDesc* desc, b200_stream_t stream);
 
@@ -164,9 +194,16 @@ B200_API int b200_add_layernorm_fwd(const B200LayerNormDesc* desc, b200_stream_t
 /* -------------------------------------------------------------------------------------------------------------------
  * One post-LN transformer-encoder layer (the fused form of the ~30 TNN layers of one BERT layer) and a whole encoder
  * stack, as a fixed sequence of the launchers above.  All buffers are the caller's.
- *   hidden  : `dtype` [tokens, H]   in/out (layer input, overwritten with the layer output)
+ *   hidden  : `dtype` [tokens, H]   in/out (stack input, overwritten with the stack output)
  *   w_qkv   : [3H, H] packed, b_qkv fp32 [3H];  w_o : [H, H];  w_ffn1 : [F, H];  w_ffn2 : [H, F]  (all `[N,K]` packed)
  *   workspace: b200_encoder_workspace_bytes(tokens, H, F, dtype) bytes, 256-byte aligned.
+ * fold_layernorm = 0: seven launches per layer (QKV, attention, out-proj+residual, LayerNorm, FFN1+GELU,
+ *   FFN2+residual, LayerNorm).
+ * fold_layernorm = 1: five launches per layer; both LayerNorms are folded into the neighbouring GEMMs (see
+ *   B200LinearDesc) and only pre-LayerNorm activations are written.  The weights must then have been prepared with
+ *   b200_fold_layernorm_weight: w_ffn1/ffn1_c1/ffn1_c2 from (W1, ln1 gamma/beta, b1) of the same layer, and for every
+ *   layer but the first w_qkv/qkv_c1/qkv_c2 from (Wqkv, ln2 gamma/beta of the PREVIOUS layer, b_qkv).  One LayerNorm
+ *   launch after the last layer produces the stack output.
  */
 typedef struct B200EncoderLayerWeights {
     const void*  w_qkv;  const float* b_qkv;
@@ -175,6 +212,8 @@ typedef struct B200EncoderLayerWeights {
     const void*  w_ffn1; const float* b_ffn1;
     const void*  w_ffn2; const float* b_ffn2;
     const float* ln2_gamma; const float* ln2_beta;
+    const float* qkv_c1;  const float* qkv_c2;     /* fold_layernorm only, layers > 0 */
+    const float* ffn1_c1; const float* ffn1_c2;    /* fold_layernorm only */
 } B200EncoderLayerWeights;
 
 typedef struct B200EncoderDesc {
@@ -189,6 +228,7 @@ typedef struct B200EncoderDesc {
     int32_t                        dtype;
     float                          ln_eps;
     float                          mask_exclude_below;
+    int32_t                        fold_layernorm;
 } B200EncoderDesc;
 B200_API size_t b200_encoder_workspace_bytes(int64_t tokens, int64_t H, int64_t F, int dtype);
 B200_API int    b200_encoder_fwd(const B200EncoderDesc* desc, b200_stream_t stream);

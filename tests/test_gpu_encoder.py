@@ -15,8 +15,8 @@ from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
 pytestmark = pytest.mark.gpu
 
 
-def _run(wl, dtype, single_call=True):
-    enc = Encoder.from_workload(wl, dtype)
+def _run(wl, dtype, single_call=True, fold=True):
+    enc = Encoder.from_workload(wl, dtype, fold_layernorm=fold)
     x = torch.from_numpy(wl.x).cuda()
     m = torch.from_numpy(wl.mask_add).cuda()
     y = enc.forward(x, m) if single_call else enc.forward_ops(x, m)
@@ -27,10 +27,11 @@ def _run(wl, dtype, single_call=True):
 
 @pytest.mark.parametrize("name", sorted(CASES))
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_against_reference_x86_fixture(cuda_device, name, dtype):
+@pytest.mark.parametrize("fold", [True, False])   # LayerNorms folded into the GEMMs (5 launches/layer) or kept (7)
+def test_against_reference_x86_fixture(cuda_device, name, dtype, fold):
     g = np.load(os.path.join(GOLDEN, name + ".npz"))
     wl = golden_workload(**CASES[name])
-    y = _run(wl, dtype)
+    y = _run(wl, dtype, fold=fold)
     ref = g["x86"]
     # full tensor: padded query rows are computed like any other row, as the reference does
     tol = MAX_ABS_TOL if dtype == torch.float16 else 4 * MAX_ABS_TOL   # bf16 carries 3 fewer mantissa bits
@@ -39,10 +40,11 @@ def test_against_reference_x86_fixture(cuda_device, name, dtype):
     assert max_abs(valid_rows(y, wl.lengths), valid_rows(ref, wl.lengths)) <= tol
 
 
-def test_single_call_equals_layer_by_layer(cuda_device):
+@pytest.mark.parametrize("fold", [True, False])
+def test_single_call_equals_layer_by_layer(cuda_device, fold):
     wl = golden_workload(**CASES["base_2layer_ragged"])
-    a = _run(wl, torch.float16, single_call=True)
-    b = _run(wl, torch.float16, single_call=False)
+    a = _run(wl, torch.float16, single_call=True, fold=fold)
+    b = _run(wl, torch.float16, single_call=False, fold=fold)
     assert np.array_equal(a, b)
 
 

@@ -26,7 +26,10 @@ class LinearDesc(_c.Structure):
     _fields_ = [("x", _vp), ("w_nk", _vp), ("bias", _vp), ("residual", _vp), ("y", _vp),
                 ("M", _i64), ("N", _i64), ("K", _i64),
                 ("ldx", _i64), ("ldw", _i64), ("ldr", _i64), ("ldy", _i64),
-                ("dtype", _i32), ("out_dtype", _i32), ("epilogue", _i32), ("block_n", _i32)]
+                ("dtype", _i32), ("out_dtype", _i32), ("epilogue", _i32), ("block_n", _i32),
+                ("out_stats", _vp), ("ln_in_stats", _vp), ("ln_c1", _vp), ("ln_c2", _vp),
+                ("res_ln_stats", _vp), ("res_ln_gamma", _vp), ("res_ln_beta", _vp),
+                ("ln_eps", _f32), ("reserved_", _i32)]
 
 
 class AttentionDesc(_c.Structure):
@@ -48,7 +51,8 @@ class EncoderLayerWeights(_c.Structure):
     _fields_ = [("w_qkv", _vp), ("b_qkv", _vp), ("w_o", _vp), ("b_o", _vp),
                 ("ln1_gamma", _vp), ("ln1_beta", _vp),
                 ("w_ffn1", _vp), ("b_ffn1", _vp), ("w_ffn2", _vp), ("b_ffn2", _vp),
-                ("ln2_gamma", _vp), ("ln2_beta", _vp)]
+                ("ln2_gamma", _vp), ("ln2_beta", _vp),
+                ("qkv_c1", _vp), ("qkv_c2", _vp), ("ffn1_c1", _vp), ("ffn1_c2", _vp)]
 
 
 class EncoderDesc(_c.Structure):
@@ -56,12 +60,13 @@ class EncoderDesc(_c.Structure):
                 ("workspace", _vp),
                 ("B", _i64), ("S", _i64), ("H", _i64), ("F", _i64),
                 ("heads", _i32), ("num_layers", _i32), ("dtype", _i32),
-                ("ln_eps", _f32), ("mask_exclude_below", _f32)]
+                ("ln_eps", _f32), ("mask_exclude_below", _f32), ("fold_layernorm", _i32)]
 
 
 # name -> (restype, argtypes); every symbol include/tnn_b200.h declares
 SYMBOLS = {
     "b200_pack_weight": (_c.c_int, [_vp, _i64, _i64, _i64, _vp, _i64, _c.c_int, _vp]),
+    "b200_fold_layernorm_weight": (_c.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _c.c_int, _vp, _vp, _vp]),
     "b200_convert": (_c.c_int, [_vp, _c.c_int, _vp, _c.c_int, _i64, _vp]),
     "b200_linear_fwd": (_c.c_int, [_c.POINTER(LinearDesc), _vp]),
     "b200_attention_fwd": (_c.c_int, [_c.POINTER(AttentionDesc), _vp]),

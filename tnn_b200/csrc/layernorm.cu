@@ -246,14 +246,15 @@ __global__ void __launch_bounds__(256) convert_kernel(const void* src, int sdt, 
 
 // ---------------------------------------------------------------- weight pre-pack: fp32 [K,N] -> half [N,K]
 __global__ void __launch_bounds__(256) pack_weight_kernel(const float* src, long long K, long long N, long long ld_src,
-                                                          uint16_t* dst, long long ld_dst, int dtype) {
+                                                          uint16_t* dst, long long ld_dst, int dtype,
+                                                          const float* row_scale) {
     __shared__ float tile[32][33];
     const long long k0 = static_cast<long long>(blockIdx.y) * 32;
     const long long n0 = static_cast<long long>(blockIdx.x) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
     for (int r = ty; r < 32; r += 8) {
         const long long k = k0 + r, n = n0 + tx;
-        tile[r][tx] = (k < K && n < N) ? src[k * ld_src + n] : 0.f;
+        tile[r][tx] = (k < K && n < N) ? src[k * ld_src + n] * (row_scale ? row_scale[k] : 1.0f) : 0.f;
     }
     __syncthreads();
     for (int r = ty; r < 32; r += 8) {
@@ -270,6 +271,34 @@ __global__ void __launch_bounds__(256) pack_weight_kernel(const float* src, long
             }
             dst[n * ld_dst + k] = bits;
         }
+    }
+}
+
+// c1[n] = sum_k packed[n,k] (the rounded, gamma-scaled weights), c2[n] = sum_k beta[k] * w[k,n] + bias[n].
+// One warp per output column; runs once per weight at Init.
+__global__ void __launch_bounds__(256) fold_vectors_kernel(const float* w_kn, long long K, long long N, long long ld_src,
+                                                           const uint16_t* packed, long long ld_dst, int dtype,
+                                                           const float* beta, const float* bias, float* c1, float* c2) {
+    const long long n = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float s1 = 0.f, s2 = 0.f;
+    for (long long k = lane; k < K; k += 32) {
+        const uint16_t bits = packed[n * ld_dst + k];
+        float w;
+        if (dtype == B200_F16) w = __half2float(*reinterpret_cast<const __half*>(&bits));
+        else w = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&bits));
+        s1 += w;
+        s2 = fmaf(beta[k], w_kn[k * ld_src + n], s2);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane == 0) {
+        c1[n] = s1;
+        c2[n] = s2 + (bias ? bias[n] : 0.f);
     }
 }
 
@@ -355,9 +384,26 @@ int b200_pack_weight(const float* w_kn, int64_t K, int64_t N, int64_t ld_src, vo
     if (!w_kn || !w_nk || K <= 0 || N <= 0 || ld_src < N || ld_dst < K || !is_half_dtype(dtype)) return B200_ERR_PARAM;
     dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32));
     if (grid.y > 65535) return B200_ERR_UNSUPPORTED;
-    pack_weight_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(w_kn, K, N, ld_src,
-                                                                            static_cast<uint16_t*>(w_nk), ld_dst, dtype);
+    pack_weight_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        w_kn, K, N, ld_src, static_cast<uint16_t*>(w_nk), ld_dst, dtype, nullptr);
     count_launch();
+    return check_launch();
+}
+
+int b200_fold_layernorm_weight(const float* w_kn, int64_t K, int64_t N, int64_t ld_src, const float* gamma,
+                               const float* beta, const float* bias, void* w_nk, int64_t ld_dst, int dtype, float* c1,
+                               float* c2, b200_stream_t stream_) {
+    using namespace b200;
+    if (!w_kn || !w_nk || !gamma || !beta || !c1 || !c2) return B200_ERR_PARAM;
+    if (K <= 0 || N <= 0 || ld_src < N || ld_dst < K || !is_half_dtype(dtype)) return B200_ERR_PARAM;
+    dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32));
+    if (grid.y > 65535) return B200_ERR_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    pack_weight_kernel<<<grid, 256, 0, stream>>>(w_kn, K, N, ld_src, static_cast<uint16_t*>(w_nk), ld_dst, dtype, gamma);
+    const unsigned blocks = static_cast<unsigned>((N * 32 + 255) / 256);
+    fold_vectors_kernel<<<blocks, 256, 0, stream>>>(w_kn, K, N, ld_src, static_cast<const uint16_t*>(w_nk), ld_dst, dtype,
+                                                    beta, bias, c1, c2);
+    count_launch(2);
     return check_launch();
 }
 

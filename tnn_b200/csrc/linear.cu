@@ -23,7 +23,7 @@ struct Cfg {
     static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;               // output staging strips (TMA store)
     static constexpr int BAR_OFFSET = OUT_OFFSET + kEpiWarps * kStageBytesPerWarp;
     static constexpr int BIAS_OFFSET = BAR_OFFSET + 256;         // per-epilogue-warp bias slice: 8 x (BN/2) floats
-    static constexpr int SMEM_BYTES = BIAS_OFFSET + kEpiWarps * (BN / 2) * 4 + 1024;  // + slack for 1024-byte alignment
+    static constexpr int SMEM_BYTES = BIAS_OFFSET + kEpiWarps * kVecStrips * (BN / 2) * 4 + 1024;  // + slack for 1024-byte alignment
     static constexpr int TMEM_COLS = 2 * BN;                    // 128, 256 or 512: powers of two
 };
 
@@ -129,7 +129,7 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int half = ew >> 2;      // which half of the BN columns
         constexpr int COLS = BN / 2;
         constexpr int CHUNKS = COLS / 32;
-        float* bias_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * COLS;  // private to this warp
+        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * kVecStrips * COLS;  // private to this warp
         WarpEpilogue<CHUNKS, false> epi{p, &tm_y, nullptr, smem + C::OUT_OFFSET + ew * kStageBytesPerWarp, nullptr,
                                         abort_flag, lane, 0u};
         uint32_t tcount = 0;
@@ -140,13 +140,14 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const uint32_t buf = tcount & 1u;
             const uint32_t aph = (tcount >> 1) & 1u;
             // Stage this tile's bias slice while the accumulator is still being produced.
-            stage_bias(p, bias_w, n_blk * BN + half * COLS, COLS, lane);
+            const long long row = static_cast<long long>(m_blk) * BM + quarter * 32 + lane;
+            epi.begin_tile(n_blk * BN + half * COLS, static_cast<int>(row) - lane);
+            stage_vectors(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();  // tcgen05.ld is warp-collective
             tcgen05_fence_after();
-            const long long row = static_cast<long long>(m_blk) * BM + quarter * 32 + lane;
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            epi.run(bias_w, tacc, row, n_blk * BN, half * COLS);
+            epi.template run<COLS>(vec_w, tacc, row, n_blk * BN, half * COLS);
             // This warp has read everything it needs from accumulator `buf`.
             tcgen05_fence_before();
             __syncwarp();
@@ -218,6 +219,16 @@ int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     p.num_k_blocks = (p.K + BK - 1) / BK;
     p.idesc = make_idesc_f16(BM, BN, d.dtype == B200_BF16 ? 1 : 0, 0, 0);
     p.status = device_status_ptr();
+    p.out_stats = d.out_stats;
+    p.ln_in_stats = d.ln_in_stats;
+    p.ln_c1 = d.ln_c1;
+    p.ln_c2 = d.ln_c2;
+    p.res_ln_stats = d.res_ln_stats;
+    p.res_ln_gamma = d.res_ln_gamma;
+    p.res_ln_beta = d.res_ln_beta;
+    p.ln_eps = d.ln_eps;
+    p.k_slots = (p.K + 31) / 32;
+    p.n_slots = (p.N + 31) / 32;
 
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -291,6 +302,9 @@ extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
     if (!aligned16(d->x) || !aligned16(d->w_nk) || !aligned16(d->y)) return B200_ERR_PARAM;
     if (d->bias && !aligned16(d->bias)) return B200_ERR_PARAM;
     if (d->epilogue == B200_EPI_BIAS_RESIDUAL && ((d->ldr % 8) || d->ldr < d->N || !aligned16(d->residual)))
+        return B200_ERR_PARAM;
+    if (d->ln_in_stats && (!d->ln_c1 || !d->ln_c2)) return B200_ERR_PARAM;
+    if (d->res_ln_stats && (!d->res_ln_gamma || !d->res_ln_beta || d->epilogue != B200_EPI_BIAS_RESIDUAL))
         return B200_ERR_PARAM;
     const int sms = device_sm_count();
     if (sms <= 0) return B200_ERR_NOT_SM100;

@@ -22,7 +22,19 @@ struct LinearParams {
     int num_n_tiles, num_tiles, num_k_blocks;
     uint32_t idesc;
     unsigned int* status;
+    // LayerNorm folding (see B200LinearDesc): all null when off
+    float* out_stats;
+    const float* ln_in_stats;
+    const float* ln_c1;
+    const float* ln_c2;
+    const float* res_ln_stats;
+    const float* res_ln_gamma;
+    const float* res_ln_beta;
+    float ln_eps;
+    int k_slots, n_slots;   // ceil(K/32), ceil(N/32)
 };
+
+constexpr int kVecStrips = 4;   // per epilogue warp: bias|c2, c1, gamma, beta — COLS floats each
 
 // erf-form GELU, 0.5 x (1 + erf(x / sqrt 2)) = x * Phi(x), as the reference's CPU accs compute it, evaluated as
 // 0.5 x (1 + tanh(x (a + b x^2 + c x^4))) with a, b, c fitted to the erf form (max abs deviation of the formula
@@ -40,19 +52,50 @@ __device__ __forceinline__ float gelu_erf(float x) {
     return fmaf(h, t, h);
 }
 
-// Stage one warp's bias slice (COLS floats starting at column n_first) in its private shared-memory strip.
-__device__ __forceinline__ void stage_bias(const LinearParams& p, float* bias_w, int n_first, int cols, int lane) {
+// Stage one warp's per-column vectors (COLS floats each, starting at column n_first) in its private shared-memory
+// strips: strip 0 = bias (or c2 when the input LayerNorm is folded), 1 = c1, 2 = gamma, 3 = beta of a folded residual
+// LayerNorm.  Columns at or beyond N read as 0, so that they contribute nothing anywhere.
+__device__ __forceinline__ void stage_vectors(const LinearParams& p, float* vec_w, int n_first, int cols, int lane) {
     __syncwarp();
+    const float* s0 = p.ln_in_stats ? p.ln_c2 : p.bias;
     for (int i = lane; i < cols; i += 32) {
         const int n = n_first + i;
-        bias_w[i] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.f;
+        const bool in = n < p.N;
+        vec_w[i] = (s0 != nullptr && in) ? __ldg(s0 + n) : 0.f;
+        if (p.ln_in_stats) vec_w[cols + i] = in ? __ldg(p.ln_c1 + n) : 0.f;
+        if (p.res_ln_stats) {
+            vec_w[2 * cols + i] = in ? __ldg(p.res_ln_gamma + n) : 0.f;
+            vec_w[3 * cols + i] = in ? __ldg(p.res_ln_beta + n) : 0.f;
+        }
     }
     __syncwarp();
 }
 
-// Drain this warp's part of one accumulator: rows = the warp's 32 TMEM lanes (thread = row `row`), columns
-// [col_first, col_first + 32*CHUNKS) of the tile whose first global column is n_tile0.  `tacc` is the TMEM address of
-// the accumulator's column 0 with this warp's lane offset already applied.
+// mean and 1/sqrt(var + eps) of one row from its per-chunk partial sums, layout [slots][M][2].
+__device__ __forceinline__ void row_stats(const float* stats, int slots, long long row, int M, int width, float eps,
+                                          float* mean, float* rstd) {
+    float s = 0.f, q = 0.f;
+    const float2* base = reinterpret_cast<const float2*>(stats) + row;
+    // Batches of 8 independent loads: the whole batch is in flight at once (one L2 round trip per batch instead of
+    // one per slot).
+    for (int i0 = 0; i0 < slots; i0 += 8) {
+        float2 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            v[j] = (i0 + j < slots) ? __ldg(base + static_cast<long long>(i0 + j) * M) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s += v[j].x;
+            q += v[j].y;
+        }
+    }
+    const float inv = 1.0f / static_cast<float>(width);
+    const float m = s * inv;
+    const float var = fmaxf(q * inv - m * m, 0.f);
+    *mean = m;
+    *rstd = 1.0f / sqrtf(var + eps);
+}
+
 // Half-precision outputs leave through shared memory: the warp writes its 32 x 32 chunk (64 bytes per row, 64-byte
 // swizzle so that the 16-byte stores of a quarter warp hit distinct banks) into a private 2 KB strip, and one lane
 // issues a TMA tile store, which writes whole 32-byte sectors and clips rows / columns outside the tensor.
@@ -74,6 +117,40 @@ struct WarpEpilogue {
     volatile uint32_t* abort_flag;
     int lane;
     uint32_t cc;                  // chunks processed so far by this warp (selects strip / barrier / phase when RES)
+    float mean_x = 0.f, rstd_x = 0.f;   // folded input LayerNorm: statistics of this thread's row of x
+    float mean_r = 0.f, rstd_r = 0.f;   // folded residual LayerNorm: statistics of this thread's row of the residual
+    // Row statistics of the NEXT tile, in flight while the current tile is drained: one L2 round trip per tile would
+    // otherwise sit on the epilogue's critical path (measured: +2.4 us per tile).  Serves the folded input LayerNorm
+    // if there is one, else the folded residual LayerNorm; up to kPrefetchSlots slots (768 columns).
+    static constexpr int kPrefetchSlots = 24;
+    float2 pf[kPrefetchSlots];
+    long long pf_row = -1;
+
+    __device__ __forceinline__ const float* pf_stats() const { return p.ln_in_stats ? p.ln_in_stats : p.res_ln_stats; }
+    __device__ __forceinline__ int pf_slots() const { return p.ln_in_stats ? p.k_slots : p.n_slots; }
+    __device__ __forceinline__ void prefetch_stats(long long row) {
+        pf_row = -1;
+        const float* st = pf_stats();
+        if (st == nullptr || pf_slots() > kPrefetchSlots || row >= p.M || row < 0) return;
+        const float2* base = reinterpret_cast<const float2*>(st) + row;
+        const int slots = pf_slots();
+#pragma unroll
+        for (int j = 0; j < kPrefetchSlots; ++j)
+            pf[j] = (j < slots) ? __ldg(base + static_cast<long long>(j) * p.M) : make_float2(0.f, 0.f);
+        pf_row = row;
+    }
+    __device__ __forceinline__ void finish_stats(int width, float* mean, float* rstd) const {
+        float s = 0.f, q = 0.f;
+#pragma unroll
+        for (int j = 0; j < kPrefetchSlots; ++j) {
+            s += pf[j].x;
+            q += pf[j].y;
+        }
+        const float inv = 1.0f / static_cast<float>(width);
+        const float m = s * inv;
+        *mean = m;
+        *rstd = 1.0f / sqrtf(fmaxf(q * inv - m * m, 0.f) + p.ln_eps);
+    }
 
     __device__ __forceinline__ bool chunk_valid(int c, int n_first, int row0) const {
         return c < CHUNKS && n_first + c * 32 < p.N && row0 < p.M;
@@ -90,12 +167,45 @@ struct WarpEpilogue {
     // Call before waiting for the accumulator: overlaps the first residual load with the tile's mainloop.
     __device__ __forceinline__ void begin_tile(int n_first, int row0) {
         if (RES && chunk_valid(0, n_first, row0)) issue_residual(cc, n_first, row0);
+        const long long row = static_cast<long long>(row0) + lane;
+        const bool have_pf = pf_row == row && row < p.M;
+        if (p.ln_in_stats) {
+            mean_x = rstd_x = 0.f;
+            if (have_pf) finish_stats(p.K, &mean_x, &rstd_x);
+            else if (row < p.M) row_stats(p.ln_in_stats, p.k_slots, row, p.M, p.K, p.ln_eps, &mean_x, &rstd_x);
+        }
+        if (p.res_ln_stats) {
+            mean_r = rstd_r = 0.f;
+            if (have_pf && !p.ln_in_stats) finish_stats(p.N, &mean_r, &rstd_r);
+            else if (row < p.M) row_stats(p.res_ln_stats, p.n_slots, row, p.M, p.N, p.ln_eps, &mean_r, &rstd_r);
+        }
+    }
+
+    // v[0..7] += residual (8 half-precision values in q), through the folded residual LayerNorm if there is one.
+    template <int COLS>
+    __device__ __forceinline__ void add_residual8(const uint4& q, const float* vec_w, int col, float* v) const {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        float r[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2(w[e], p.dtype);
+            r[2 * e] = f.x;
+            r[2 * e + 1] = f.y;
+        }
+        if (p.res_ln_stats) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                r[e] = fmaf((r[e] - mean_r) * rstd_r, vec_w[2 * COLS + col + e], vec_w[3 * COLS + col + e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += r[e];
     }
 
     // Drain this warp's part of one accumulator: rows = the warp's 32 TMEM lanes (thread = row `row`), columns
     // [col_first, col_first + 32*CHUNKS) of the tile whose first global column is n_tile0.  `tacc` is the TMEM address
     // of the accumulator's column 0 with this warp's lane offset already applied.  Returns false if a wait ran out.
-    __device__ __forceinline__ bool run(const float* bias_w, uint32_t tacc, long long row, int n_tile0, int col_first) {
+    template <int COLS>
+    __device__ __forceinline__ bool run(const float* vec_w, uint32_t tacc, long long row, int n_tile0, int col_first) {
         const bool row_ok = row < p.M;
         const int row0 = static_cast<int>(row) - lane;
         const int n_first = n_tile0 + col_first;
@@ -111,13 +221,27 @@ struct WarpEpilogue {
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (p.ln_in_stats) {
+                // LN(x).W + b = rstd * (x.W' - mean * c1) + c2
+                const float nm = -mean_x;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const float4 b = *reinterpret_cast<const float4*>(bias_w + c * 32 + g * 4);
-                v[g * 4 + 0] += b.x;
-                v[g * 4 + 1] += b.y;
-                v[g * 4 + 2] += b.z;
-                v[g * 4 + 3] += b.w;
+                for (int g = 0; g < 8; ++g) {
+                    const float4 c2 = *reinterpret_cast<const float4*>(vec_w + c * 32 + g * 4);
+                    const float4 c1 = *reinterpret_cast<const float4*>(vec_w + COLS + c * 32 + g * 4);
+                    v[g * 4 + 0] = fmaf(rstd_x, fmaf(nm, c1.x, v[g * 4 + 0]), c2.x);
+                    v[g * 4 + 1] = fmaf(rstd_x, fmaf(nm, c1.y, v[g * 4 + 1]), c2.y);
+                    v[g * 4 + 2] = fmaf(rstd_x, fmaf(nm, c1.z, v[g * 4 + 2]), c2.z);
+                    v[g * 4 + 3] = fmaf(rstd_x, fmaf(nm, c1.w, v[g * 4 + 3]), c2.w);
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 b = *reinterpret_cast<const float4*>(vec_w + c * 32 + g * 4);
+                    v[g * 4 + 0] += b.x;
+                    v[g * 4 + 1] += b.y;
+                    v[g * 4 + 2] += b.z;
+                    v[g * 4 + 3] += b.w;
+                }
             }
             if (p.epilogue == B200_EPI_BIAS_GELU) {
 #pragma unroll
@@ -131,13 +255,7 @@ struct WarpEpilogue {
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const uint4 q = *reinterpret_cast<const uint4*>(srow + ((g ^ ((lane >> 1) & 3)) << 4));
-                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = unpack2(w[e], p.dtype);
-                        v[g * 8 + e * 2 + 0] += f.x;
-                        v[g * 8 + e * 2 + 1] += f.y;
-                    }
+                    add_residual8<COLS>(q, vec_w, c * 32 + g * 8, &v[g * 8]);
                 }
             } else if (p.epilogue == B200_EPI_BIAS_RESIDUAL && row_ok) {
                 const uint16_t* rp = reinterpret_cast<const uint16_t*>(p.residual) + row * p.ldr + n0;
@@ -145,15 +263,19 @@ struct WarpEpilogue {
                 for (int g = 0; g < 4; ++g) {
                     if (n0 + g * 8 < p.N) {
                         const uint4 q = __ldg(reinterpret_cast<const uint4*>(rp + g * 8));
-                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 f = unpack2(w[e], p.dtype);
-                            v[g * 8 + e * 2 + 0] += f.x;
-                            v[g * 8 + e * 2 + 1] += f.y;
-                        }
+                        add_residual8<COLS>(q, vec_w, c * 32 + g * 8, &v[g * 8]);
                     }
                 }
+            }
+            if (p.out_stats != nullptr && row_ok) {
+                float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    s1 += v[j];
+                    s2 = fmaf(v[j], v[j], s2);
+                }
+                // slot-major layout: the 32 rows of the warp write 256 contiguous bytes
+                reinterpret_cast<float2*>(p.out_stats)[static_cast<long long>(n0 >> 5) * p.M + row] = make_float2(s1, s2);
             }
             if (p.out_dtype == B200_F32) {
                 if (row_ok) {

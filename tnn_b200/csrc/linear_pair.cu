@@ -25,7 +25,7 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // output staging strips (TMA store); with RES two per warp, which also receive the residual tile (TMA load)
     static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * (RES ? 2 : 1);
-    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * (BN / 2) * 4;   // + barriers + bias strips
+    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * kVecStrips * (BN / 2) * 4;   // + barriers + bias strips
     static constexpr int STAGES = (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES > 8
                                       ? 8 : (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
@@ -202,25 +202,33 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const int half = ew >> 2;
         constexpr int COLS = BN / 2;
         constexpr int CHUNKS = COLS / 32;
-        float* bias_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * COLS;
+        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * kVecStrips * COLS;
         WarpEpilogue<CHUNKS, RES> epi{p, &tm_y, &tm_r,
                                       smem + C::OUT_OFFSET + ew * kStageBytesPerWarp * (RES ? 2 : 1),
                                       res_bars + 2 * ew, abort_flag, lane, 0u};
         uint32_t tcount = 0;
         bool ok = true;
+        const long long row_in_tile = static_cast<long long>(rank) * 128 + quarter * 32 + lane;
+        if (pair_id < p.num_tiles)
+            epi.prefetch_stats(static_cast<long long>(pair_id / p.num_n_tiles) * 256 + row_in_tile);
         for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tcount) {
             const int m_blk = tile / p.num_n_tiles;
             const int n_blk = tile % p.num_n_tiles;
             const uint32_t buf = tcount & 1u;
             const uint32_t aph = (tcount >> 1) & 1u;
-            const long long row = static_cast<long long>(m_blk) * 256 + rank * 128 + quarter * 32 + lane;
+            const long long row = static_cast<long long>(m_blk) * 256 + row_in_tile;
             epi.begin_tile(n_blk * BN + half * COLS, static_cast<int>(row) - lane);
-            stage_bias(p, bias_w, n_blk * BN + half * COLS, COLS, lane);
+            {   // the next tile's row statistics fly while this tile is drained
+                const int next = tile + num_pairs;
+                epi.prefetch_stats(next < p.num_tiles
+                                       ? static_cast<long long>(next / p.num_n_tiles) * 256 + row_in_tile : -1);
+            }
+            stage_vectors(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();
             tcgen05_fence_after();
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-            if (!epi.run(bias_w, tacc, row, n_blk * BN, half * COLS)) { ok = false; break; }
+            if (!epi.template run<COLS>(vec_w, tacc, row, n_blk * BN, half * COLS)) { ok = false; break; }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -292,6 +300,16 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     p.num_k_blocks = (p.K + BK - 1) / BK;
     p.idesc = make_idesc_f16(256, BN, d.dtype == B200_BF16 ? 1 : 0, 0, 0);
     p.status = device_status_ptr();
+    p.out_stats = d.out_stats;
+    p.ln_in_stats = d.ln_in_stats;
+    p.ln_c1 = d.ln_c1;
+    p.ln_c2 = d.ln_c2;
+    p.res_ln_stats = d.res_ln_stats;
+    p.res_ln_gamma = d.res_ln_gamma;
+    p.res_ln_beta = d.res_ln_beta;
+    p.ln_eps = d.ln_eps;
+    p.k_slots = (p.K + 31) / 32;
+    p.n_slots = (p.N + 31) / 32;
 
     static bool attr_set[64] = {false};
     int dev = 0;

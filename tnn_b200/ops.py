@@ -32,6 +32,27 @@ def pack_weight(w_kn, dtype=torch.float16, out=None):
     return out
 
 
+def fold_layernorm_weight(w_kn, gamma, beta, bias=None, dtype=torch.float16, out=None):
+    """For y = LayerNorm(x; gamma, beta).W + bias: returns (w_nk with gamma folded in, c1, c2), see include/tnn_b200.h."""
+    _require_cuda(w_kn, gamma, beta, bias)
+    K, N = w_kn.shape
+    if out is None:
+        out = torch.empty((N, K), dtype=dtype, device=w_kn.device)
+    c1 = torch.empty((N,), dtype=torch.float32, device=w_kn.device)
+    c2 = torch.empty((N,), dtype=torch.float32, device=w_kn.device)
+    rc = capi.lib().b200_fold_layernorm_weight(w_kn.data_ptr(), K, N, w_kn.stride(0), gamma.data_ptr(),
+                                               beta.data_ptr(), capi.ptr(bias), out.data_ptr(), out.stride(0),
+                                               capi.dtype_code(out.dtype), c1.data_ptr(), c2.data_ptr(),
+                                               capi.stream_ptr())
+    capi.check(rc, "b200_fold_layernorm_weight")
+    return out, c1, c2
+
+
+def stats_buffer(rows, width, device):
+    """Row-statistics buffer of a `[rows, width]` activation: `[ceil(width/32), rows, 2]` fp32."""
+    return torch.empty(((width + 31) // 32, rows, 2), dtype=torch.float32, device=device)
+
+
 def convert(src, dtype, out=None):
     _require_cuda(src)
     assert src.is_contiguous()
@@ -44,7 +65,8 @@ def convert(src, dtype, out=None):
     return out
 
 
-def linear(x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out_dtype=None, out=None, block_n=0):
+def linear(x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out_dtype=None, out=None, block_n=0,
+           out_stats=None, ln_in=None, res_ln=None, ln_eps=1e-12):
     """y[M,N] = epilogue(x[M,K] . w_nk[N,K]^T + bias (+ residual)); x may be `[..., K]`."""
     _require_cuda(x, w_nk, bias, residual, out)
     K = x.shape[-1]
@@ -66,6 +88,14 @@ def linear(x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out_dtype=None,
         d.residual, d.ldr = r2.data_ptr(), r2.stride(0)
     d.dtype, d.out_dtype = capi.dtype_code(x.dtype), capi.dtype_code(out.dtype)
     d.epilogue, d.block_n = epilogue, block_n
+    # LayerNorm folding: ln_in = (stats of x, c1, c2); res_ln = (stats of residual, gamma, beta)
+    d.ln_eps = float(ln_eps)
+    if out_stats is not None:
+        d.out_stats = out_stats.data_ptr()
+    if ln_in is not None:
+        d.ln_in_stats, d.ln_c1, d.ln_c2 = (t.data_ptr() for t in ln_in)
+    if res_ln is not None:
+        d.res_ln_stats, d.res_ln_gamma, d.res_ln_beta = (t.data_ptr() for t in res_ln)
     rc = capi.lib().b200_linear_fwd(ctypes.byref(d), capi.stream_ptr())
     capi.check(rc, "b200_linear_fwd")
     return out

@@ -23,6 +23,9 @@ def main():
     ap.add_argument("--K", type=int, default=768)
     ap.add_argument("--epilogue", default="bias", choices=["bias", "gelu", "residual"])
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--ln-in", action="store_true", help="linear: x is pre-LayerNorm, LayerNorm folded into the GEMM")
+    ap.add_argument("--res-ln", action="store_true", help="linear: residual goes through a folded LayerNorm")
+    ap.add_argument("--out-stats", action="store_true", help="linear: write row statistics of the output")
     ap.add_argument("--B", type=int, default=64)
     ap.add_argument("--S", type=int, default=128)
     ap.add_argument("--heads", type=int, default=12)
@@ -32,6 +35,7 @@ def main():
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--eager", action="store_true", help="time host-launched calls instead of a CUDA graph replay")
     a = ap.parse_args()
     dt = torch.float16 if a.dtype == "f16" else torch.bfloat16
     dev = torch.device("cuda:0")
@@ -45,7 +49,16 @@ def main():
         r = torch.randn(a.M, a.N, device=dev).to(dt) if a.epilogue == "residual" else None
         y = torch.empty(a.M, a.N, device=dev, dtype=dt)
         epi = {"bias": ops.EPI_BIAS, "gelu": ops.EPI_BIAS_GELU, "residual": ops.EPI_BIAS_RESIDUAL}[a.epilogue]
-        fn = lambda: ops.linear(x, w, b, residual=r, epilogue=epi, out=y, block_n=a.block_n)  # noqa: E731
+        kw = {}
+        if a.ln_in:
+            kw["ln_in"] = (torch.rand(ops.stats_buffer(a.M, a.K, dev).shape, device=dev) + 32.0,
+                           torch.randn(a.N, device=dev), torch.randn(a.N, device=dev))
+        if a.res_ln:
+            kw["res_ln"] = (torch.rand(ops.stats_buffer(a.M, a.N, dev).shape, device=dev) + 32.0,
+                            torch.ones(a.N, device=dev), torch.zeros(a.N, device=dev))
+        if a.out_stats:
+            kw["out_stats"] = ops.stats_buffer(a.M, a.N, dev)
+        fn = lambda: ops.linear(x, w, b, residual=r, epilogue=epi, out=y, block_n=a.block_n, **kw)  # noqa: E731
         work = 2.0 * a.M * a.N * a.K
         unit = "TFLOP/s"
     elif a.kernel == "attention":
@@ -80,10 +93,27 @@ def main():
     for _ in range(a.warmup):
         fn()
     torch.cuda.synchronize()
+    # The `iters` launches are replayed from a CUDA graph so that host launch overhead (tens of microseconds per
+    # call through ctypes) does not enter the measurement of short kernels.
+    run = None
+    if not a.eager:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(a.iters):
+                    fn()
+            run = g.replay
+            run()
+            torch.cuda.synchronize()
+        except Exception:
+            run = None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(a.iters):
-        fn()
+    if run is not None:
+        run()
+    else:
+        for _ in range(a.iters):
+            fn()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / a.iters
