@@ -41,7 +41,8 @@ enum {
     B200_ERR_LAUNCH           = -3, /* cudaLaunch / cudaGetLastError reported an error                            */
     B200_ERR_DRIVER           = -4, /* tensor-map encode entry point missing or it refused the descriptor          */
     B200_ERR_DEVICE_TIMEOUT   = -5, /* reported by b200_device_status(): a bounded device-side wait ran out        */
-    B200_ERR_NOT_SM100        = -6  /* the current device is not compute capability 10.x                           */
+    B200_ERR_NOT_SM100        = -6, /* the current device is not compute capability 10.x                           */
+    B200_ERR_STATIC_LIMIT     = -7  /* b200_attention_masked_fwd_static: batch larger than its built-in scratch      */
 };
 
 enum { B200_F16 = 0, B200_BF16 = 1, B200_F32 = 2 };
@@ -163,6 +164,28 @@ typedef struct B200AttentionDesc {
     float          mask_exclude_below;
 } B200AttentionDesc;
 B200_API int b200_attention_fwd(const B200AttentionDesc* desc, b200_stream_t stream);
+
+/* Masked attention for callers that must not allocate.  (No counterpart in the reference: TNN's accs allocate their
+ * temporaries freely, even inside Forward — source/tnn/device/cuda/cuda_context.cc:137-145.)
+ *
+ * b200_attention_fwd with a mask wants a kv_len array, and somebody has to own those B ints of device memory.  Some
+ * hosts cannot provide them: an acc whose Forward is forbidden to allocate and was not given a workspace at Init, a
+ * process running inside a fixed memory budget handed out once at start-up, a plug-in loaded into a server whose
+ * allocator it may not touch.  This entry point takes the same descriptor (mask_add required, kv_len ignored),
+ * derives kv_len on the device into a scratch array that is part of the library image — a static __device__ array
+ * of B200_STATIC_MAX_BATCH int32 (16 KB, resident on every GPU that has loaded the library until the process
+ * exits) — and then runs the same attention kernels.  It calls no cudaMalloc / cudaFree and no allocating routine,
+ * on the device or on the host (its tensor maps live on the stack).
+ *   - B > B200_STATIC_MAX_BATCH is refused with B200_ERR_STATIC_LIMIT; nothing is launched.
+ *   - The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress, with that device
+ *     current) and sets the kernels' shared-memory attribute; make that first call before starting any stream
+ *     capture on that device.  Later calls only launch.
+ *   - All calls on one GPU share the one scratch array.  Nothing in it needs clearing: each call overwrites the B
+ *     entries it then reads, and entries beyond B are never read.  Two calls whose kernels can overlap on the GPU
+ *     (different streams without an ordering between them) race on it: keep such calls on one stream, or order them.
+ */
+#define B200_STATIC_MAX_BATCH 4096
+B200_API int b200_attention_masked_fwd_static(const B200AttentionDesc* desc, b200_stream_t stream);
 
 /* kv_len[b] = 1 + max{k : mask_add[b,k] > exclude_below}, 0 if there is none.  The mask is a run-time input of the
  * graph, so this runs on the device once per Forward. */

@@ -17,6 +17,8 @@ EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL = 0, 1, 2
 
 OK = 0
 ERR_PARAM, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_DRIVER, ERR_DEVICE_TIMEOUT, ERR_NOT_SM100 = -1, -2, -3, -4, -5, -6
+ERR_STATIC_LIMIT = -7
+STATIC_MAX_BATCH = 4096
 
 _c = ctypes
 _i64, _i32, _f32, _vp = _c.c_int64, _c.c_int32, _c.c_float, _c.c_void_p
@@ -70,6 +72,7 @@ SYMBOLS = {
     "b200_convert": (_c.c_int, [_vp, _c.c_int, _vp, _c.c_int, _i64, _vp]),
     "b200_linear_fwd": (_c.c_int, [_c.POINTER(LinearDesc), _vp]),
     "b200_attention_fwd": (_c.c_int, [_c.POINTER(AttentionDesc), _vp]),
+    "b200_attention_masked_fwd_static": (_c.c_int, [_c.POINTER(AttentionDesc), _vp]),
     "b200_mask_to_kv_len": (_c.c_int, [_vp, _i64, _i64, _f32, _vp, _vp]),
     "b200_add_layernorm_fwd": (_c.c_int, [_c.POINTER(LayerNormDesc), _vp]),
     "b200_encoder_workspace_bytes": (_c.c_size_t, [_i64, _i64, _i64, _c.c_int]),

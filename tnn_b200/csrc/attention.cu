@@ -540,3 +540,96 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
     count_launch();
     return check_launch();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// The allocation-free variant of masked attention (see include/tnn_b200.h).  Its only scratch, the kv_len array,
+// is this file-scope device array.  In host code the name below is merely a handle for the symbol — not a device
+// address — so the address is looked up once per device with cudaGetSymbolAddress and that pointer is what the
+// kernels receive.
+static __device__ __align__(256) int g_static_kv_len[B200_STATIC_MAX_BATCH];
+
+namespace {
+int* g_static_kv_len_ptr[64] = {nullptr};   // per device, filled by the first call on that device
+bool g_static_attr_set[64] = {false};
+}
+
+extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200_stream_t stream_) {
+    using namespace b200;
+    if (!d || !d->q || !d->k || !d->v || !d->out || !d->mask_add) return B200_ERR_PARAM;
+    if (d->B <= 0 || d->S <= 0 || d->heads <= 0) return B200_ERR_PARAM;
+    if (d->B > B200_STATIC_MAX_BATCH) return B200_ERR_STATIC_LIMIT;
+    if (d->head_dim != HD) return B200_ERR_UNSUPPORTED;
+    if (!is_half_dtype(d->dtype)) return B200_ERR_PARAM;
+    const int64_t width = static_cast<int64_t>(d->heads) * HD;
+    if ((d->ldq % 8) || (d->ldk % 8) || (d->ldv % 8) || (d->ldo % 8)) return B200_ERR_PARAM;
+    if (d->ldq < width || d->ldk < width || d->ldv < width || d->ldo < width) return B200_ERR_PARAM;
+    if (!aligned16(d->q) || !aligned16(d->k) || !aligned16(d->v) || !aligned16(d->out)) return B200_ERR_PARAM;
+    if (d->heads > 65535 || d->S > (1 << 24)) return B200_ERR_UNSUPPORTED;
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_ERR_LAUNCH;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) return B200_ERR_NOT_SM100;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    // One-time set-up on this device (current device = the one the launches below go to).
+    if (g_static_kv_len_ptr[dev] == nullptr) {
+        int* ptr = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_kv_len) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return B200_ERR_LAUNCH;
+        }
+        g_static_kv_len_ptr[dev] = ptr;
+    }
+    if (!g_static_attr_set[dev]) {
+        if (cudaFuncSetAttribute(attention_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S1_SMEM) !=
+                cudaSuccess ||
+            cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) {
+            cudaGetLastError();
+            return B200_ERR_LAUNCH;
+        }
+        g_static_attr_set[dev] = true;
+    }
+    int* kv_len = g_static_kv_len_ptr[dev];
+
+    // kv_len of this call's mask into the static scratch (every entry that is read below is written here first)
+    int rc = b200_mask_to_kv_len(d->mask_add, d->B, d->S, d->mask_exclude_below, kv_len, stream_);
+    if (rc != B200_OK) return rc;
+
+    // Tensor maps on the stack: nothing is cached, nothing allocated.
+    const uint64_t dims[3] = {static_cast<uint64_t>(width), static_cast<uint64_t>(d->S), static_cast<uint64_t>(d->B)};
+    const uint32_t box[3] = {HD, 128, 1};
+    const uint64_t sq[2] = {static_cast<uint64_t>(d->ldq) * 2, static_cast<uint64_t>(d->ldq) * 2 * d->S};
+    const uint64_t sk[2] = {static_cast<uint64_t>(d->ldk) * 2, static_cast<uint64_t>(d->ldk) * 2 * d->S};
+    const uint64_t sv[2] = {static_cast<uint64_t>(d->ldv) * 2, static_cast<uint64_t>(d->ldv) * 2 * d->S};
+    const uint64_t so[2] = {static_cast<uint64_t>(d->ldo) * 2, static_cast<uint64_t>(d->ldo) * 2 * d->S};
+    CUtensorMap tq, tk, tv, to;
+    if (!encode_tensor_map(&tq, d->q, 3, dims, sq, box) || !encode_tensor_map(&tk, d->k, 3, dims, sk, box) ||
+        !encode_tensor_map(&tv, d->v, 3, dims, sv, box) || !encode_tensor_map(&to, d->out, 3, dims, so, box))
+        return B200_ERR_DRIVER;
+
+    AttnParams p;
+    p.mask_add = d->mask_add;
+    p.kv_len = kv_len;
+    p.out = d->out;
+    p.S = static_cast<int>(d->S);
+    p.heads = d->heads;
+    p.ldo = d->ldo;
+    p.dtype = d->dtype;
+    p.scale_log2 = d->scale * 1.4426950408889634f;
+    p.mask_below = d->mask_exclude_below;
+    const int fmt = d->dtype == B200_BF16 ? 1 : 0;
+    p.idesc_qk = make_idesc_f16(128, TK, fmt, 0, 0);
+    p.idesc_pv = make_idesc_f16(128, HD, fmt, 0, 1);
+    p.status = device_status_ptr();
+
+    if (d->S <= 128) {
+        dim3 grid1(1, static_cast<unsigned>(d->heads), static_cast<unsigned>(d->B));
+        attention_single_kernel<<<grid1, kAttnThreads, S1_SMEM, stream>>>(tq, tk, tv, to, p);
+    } else {
+        dim3 grid(static_cast<unsigned>((d->S + TQ - 1) / TQ), static_cast<unsigned>(d->heads),
+                  static_cast<unsigned>(d->B));
+        attention_kernel<<<grid, kAttnThreads, ATTN_SMEM, stream>>>(tq, tk, tv, p);
+    }
+    count_launch();
+    return check_launch();
+}

@@ -53,6 +53,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                                   const uint32_t* box, int swizzle_bytes = 128);
 
+// The same encoding into caller-provided storage: no cache entry, no allocation of any kind.
+bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                       const uint32_t* box, int swizzle_bytes = 128);
+
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH; }
 
 }  // namespace b200

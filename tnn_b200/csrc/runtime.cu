@@ -116,6 +116,27 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
     return map;
 }
 
+// Encodes a tensor map into caller-provided storage (no cache, no allocation).  Same conventions as get_tensor_map.
+bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                       const uint32_t* box, int swizzle_bytes) {
+    if (!out || rank < 2 || rank > 3 || (swizzle_bytes != 128 && swizzle_bytes != 64)) return false;
+    EncodeTiledFn encode = resolve_encode();
+    if (!encode) return false;
+    cuuint64_t gdims[3] = {1, 1, 1};
+    cuuint64_t gstrides[2] = {0, 0};
+    cuuint32_t gbox[3] = {1, 1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    for (int i = 0; i < rank; ++i) {
+        gdims[i] = dims[i];
+        gbox[i] = box[i];
+    }
+    for (int i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
+    return encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
+                  gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -129,6 +150,7 @@ const char* b200_status_string(int status) {
         case B200_ERR_DRIVER: return "tensor-map encode failed (driver entry point missing or descriptor refused)";
         case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
         case B200_ERR_NOT_SM100: return "current device is not an sm_100 GPU";
+        case B200_ERR_STATIC_LIMIT: return "size exceeds the fixed capacity of the library's static device scratch";
         default: return "unknown status";
     }
 }
