@@ -202,7 +202,7 @@ def run_ours(args):
     B = args.batch
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
-    enc = Encoder.from_workload(wl, torch.float16, dev)
+    enc = Encoder.from_workload(wl, torch.float16, dev, fold_layernorm=args.fold_layernorm)
     x_dev = torch.from_numpy(wl.x).to(dev)
     mask_dev = torch.from_numpy(wl.mask_add.reshape(B, SEQ)).to(dev).contiguous()
     kv_len = ops.mask_to_kv_len(mask_dev)
@@ -420,6 +420,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="sequences per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fold-layernorm", action="store_true",
+                    help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
                                                             "a captured CUDA graph of one Forward")
     args = ap.parse_args()

@@ -19,6 +19,13 @@
 namespace b200 {
 namespace {
 
+// 2^x, one MUFU instruction: results below the normal range flush to zero, which is what a softmax weight wants.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 constexpr int TQ = 128;   // queries per CTA
 constexpr int TK = 128;   // keys per tile
 constexpr int HD = 64;    // head dim
@@ -271,55 +278,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Sequences of at most 128 tokens (the benchmark's S = 128): one key tile, so no running rescale.  Leaner than the
-// general kernel so that four CTAs fit per SM (48.6 KB shared memory, 128 TMEM columns, <= 128 registers): the
-// per-CTA chain load -> QK^T -> softmax -> PV -> store is latency-bound, and co-resident CTAs are what hides it.
-//   * P (128 x 128 half) overlays the Q and K tiles, dead once S = Q K^T has completed;
+// Sequences of at most 128 tokens (the benchmark's S = 128): one key tile per (sequence, head), so no running
+// rescale.  Persistent CTAs (two per SM) walk the (sequence, head) items with a grid stride; each CTA owns two
+// shared-memory sets of Q|K|V (48 KB each) and loads the next item's tiles while it works on the current one, so
+// that after the first item the chain QK^T -> softmax -> PV -> store never waits for HBM/L2 latency.
+//   * P (128 x 128 half) overlays the Q and K tiles of its set, dead once S = Q K^T has completed;
 //   * O (TMEM columns 0..63) overlays S, dead once the softmax has read it;
 //   * only ceil(kv_len / 32) 32-key chunks are computed: QK^T runs with N = 32*chunks, the softmax reads that many
 //     chunks, PV runs 2*chunks k-steps — padded tails of short sequences cost nothing;
-//   * the output tile goes through shared memory (swizzled) and one TMA store per CTA, clipped at row S.
-constexpr int S1_OFF_MASK = 3 * TILE_BYTES;
+//   * the output tile goes through shared memory (swizzled, overlaying P) and one TMA store per item, clipped at
+//     row S; the store is only waited for when its set is about to be refilled.
+constexpr int S1_SET_BYTES = 3 * TILE_BYTES;
+constexpr int S1_OFF_MASK = 2 * S1_SET_BYTES;
 constexpr int S1_OFF_BAR = S1_OFF_MASK + TK * 4;
 constexpr int S1_SMEM = S1_OFF_BAR + 64;
 constexpr int S1_TMEM_COLS = 128;
 
-__global__ void __launch_bounds__(kAttnThreads, 4)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                        const AttnParams p) {
+                        const AttnParams p, const int num_items) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S1_OFF_BAR);
-    uint64_t* bar_qk = bars + 0;
-    uint64_t* bar_v = bars + 1;
-    uint64_t* bar_s = bars + 2;
-    uint64_t* bar_o = bars + 3;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+    uint64_t* bar_qk = bars + 0;   // [2] one per set
+    uint64_t* bar_v = bars + 2;    // [2]
+    uint64_t* bar_s = bars + 4;
+    uint64_t* bar_o = bars + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* mask_s = reinterpret_cast<float*>(smem + S1_OFF_MASK);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
-    const int head = blockIdx.y;
-    const int b = blockIdx.z;
 
     if ((smem_u32(smem) & 1023u) != 0) {
         if (tid == 0 && p.status) atomicOr(p.status, 4u);
         return;
     }
-
-    int kv_eff = p.S;
-    bool additive_only = (p.mask_add == nullptr);
-    if (p.kv_len != nullptr) {
-        const int kl = p.kv_len[b];
-        if (kl <= 0) additive_only = true;
-        else kv_eff = kl < p.S ? kl : p.S;
-    }
-    const int n_chunks = (kv_eff + 31) >> 5;   // 1..4
-
     if (tid == 0) {
-        mbar_init(bar_qk, 1);
-        mbar_init(bar_v, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_qk[i], 1);
+            mbar_init(&bar_v[i], 1);
+        }
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
         *abort_flag = 0;
@@ -333,134 +333,177 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tmem_alloc(tmem_slot, S1_TMEM_COLS);
         tmem_relinquish();
     }
-    {
-        float m = -INFINITY;
-        if (tid < p.S) {
-            const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + tid] : 0.f;
-            if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
-        }
-        mask_s[tid] = m;
-    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-
-    if (tid == 0) {
-        mbar_expect_tx(bar_qk, 2 * TILE_BYTES);
-        tma_load_3d(smem + OFF_Q, &tm_q, bar_qk, head * HD, 0, b);
-        tma_load_3d(smem + OFF_K, &tm_k, bar_qk, head * HD, 0, b);
-        mbar_expect_tx(bar_v, TILE_BYTES);
-        tma_load_3d(smem + OFF_V, &tm_v, bar_v, head * HD, 0, b);
-        if (mbar_wait(bar_qk, 0, abort_flag)) {
-            tcgen05_fence_after();
-            const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + OFF_Q));
-            const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_K));
-            // N = 32 * n_chunks keys
-            const uint32_t idesc = (p.idesc_qk & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_chunks * 4) << 17);
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k)
-                umma_f16_ss(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, k != 0 ? 1u : 0u);
-            umma_commit(bar_s);
-        }
-    }
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
-    bool ok = mbar_wait(bar_s, 0, abort_flag);
-    __syncwarp();
-    tcgen05_fence_after();
-    float l_sum = 0.f;
-    if (ok) {
-        float tmax = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < n_chunks; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
-            tmem_ld_wait(r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                tmax = fmaxf(tmax, fmaf(__uint_as_float(r[i]), p.scale_log2, mask_s[c * 32 + i]));
-        }
-        const float m_use = (tmax == -INFINITY) ? 0.f : tmax;
-#pragma unroll 1
-        for (int c = 0; c < n_chunks; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
-            tmem_ld_wait(r);
-            float pv[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                pv[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mask_s[c * 32 + i]) - m_use);
-                l_sum += pv[i];
-            }
-            uint8_t* prow = smem + (c >> 1) * TILE_BYTES + tid * 128;   // P overlays Q (keys 0..63) and K (64..127)
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                uint4 qv;
-                qv.x = pack2(pv[g * 8 + 0], pv[g * 8 + 1], p.dtype);
-                qv.y = pack2(pv[g * 8 + 2], pv[g * 8 + 3], p.dtype);
-                qv.z = pack2(pv[g * 8 + 4], pv[g * 8 + 5], p.dtype);
-                qv.w = pack2(pv[g * 8 + 6], pv[g * 8 + 7], p.dtype);
-                const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
-                *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
-            }
-        }
-    }
-    fence_async_proxy_shared();
-    tcgen05_fence_before();
-    __syncthreads();
 
-    if (tid == 0 && ok) {
-        tcgen05_fence_after();
-        if (mbar_wait(bar_v, 0, abort_flag)) {
-            tcgen05_fence_after();
-            const int ksteps = n_chunks * 2;
-            for (int k = 0; k < ksteps; ++k) {
-                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + (k >> 2) * TILE_BYTES)) + 2u * (k & 3);
-                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_V + k * 2048));
-                umma_f16_ss(tmem_base, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);   // O overlays S
-            }
-            umma_commit(bar_o);
+    auto load_item = [&](int item, int set) {   // tid 0 only
+        const int bb = item / p.heads, hh = item % p.heads;
+        uint8_t* base = smem + set * S1_SET_BYTES;
+        mbar_expect_tx(&bar_qk[set], 2 * TILE_BYTES);
+        tma_load_3d(base + OFF_Q, &tm_q, &bar_qk[set], hh * HD, 0, bb);
+        tma_load_3d(base + OFF_K, &tm_k, &bar_qk[set], hh * HD, 0, bb);
+        mbar_expect_tx(&bar_v[set], TILE_BYTES);
+        tma_load_3d(base + OFF_V, &tm_v, &bar_v[set], hh * HD, 0, bb);
+    };
+    if (tid == 0 && static_cast<int>(blockIdx.x) < num_items) load_item(blockIdx.x, 0);
+
+    bool ok = true;
+    uint32_t it = 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++it) {
+        const int set = it & 1u;
+        const uint32_t ph_set = (it >> 1) & 1u;
+        const uint32_t ph = it & 1u;
+        const int b = item / p.heads;
+        const int head = item % p.heads;
+        uint8_t* sbase = smem + set * S1_SET_BYTES;
+
+        int kv_eff = p.S;
+        bool additive_only = (p.mask_add == nullptr);
+        if (p.kv_len != nullptr) {
+            const int kl = p.kv_len[b];
+            if (kl <= 0) additive_only = true;
+            else kv_eff = kl < p.S ? kl : p.S;
         }
-    }
-    ok = ok && mbar_wait(bar_o, 0, abort_flag);
-    __syncwarp();
-    tcgen05_fence_after();
-    if (ok) {
-        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-        uint8_t* orow = smem + tid * 128;   // output tile overlays P's first half (PV has completed)
+        const int n_chunks = (kv_eff + 31) >> 5;   // 1..4
+        {
+            float m = -INFINITY;
+            if (tid < p.S) {
+                const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + tid] : 0.f;
+                if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+            }
+            mask_s[tid] = m;   // the previous item's softmax finished before its closing __syncthreads
+        }
+        __syncthreads();
+
+        if (tid == 0) {
+            // Prefetch the next item into the other set; that set's last reader is the output store of the previous
+            // item, which must have drained it.
+            const int next = item + gridDim.x;
+            if (next < num_items) {
+                tma_store_wait_read<0>();
+                load_item(next, set ^ 1);
+            }
+            if (mbar_wait(&bar_qk[set], ph_set, abort_flag)) {
+                tcgen05_fence_after();
+                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_Q));
+                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_K));
+                const uint32_t idesc = (p.idesc_qk & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_chunks * 4) << 17);
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
-            tmem_ld_wait(r);
+                for (int k = 0; k < HD / 16; ++k)
+                    umma_f16_ss(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, k != 0 ? 1u : 0u);
+                umma_commit(bar_s);
+            }
+        }
+        if (!mbar_wait(bar_s, ph, abort_flag)) { ok = false; break; }
+        __syncwarp();
+        tcgen05_fence_after();
+        float l_sum = 0.f;
+        {
+            float tmax = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < n_chunks; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_wait(r);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                uint4 qv;
-                qv.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv, p.dtype);
-                qv.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv, p.dtype);
-                qv.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv, p.dtype);
-                qv.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv, p.dtype);
-                const int chunk = (c * 4 + g) ^ (tid & 7);
-                *reinterpret_cast<uint4*>(orow + chunk * 16) = qv;
+                for (int g = 0; g < 8; ++g) {
+                    const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
+                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
+                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
+                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
+                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                }
+            }
+            const float m_use = (tmax == -INFINITY) ? 0.f : tmax;
+#pragma unroll 1
+            for (int c = 0; c < n_chunks; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_wait(r);
+                float pv[32];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
+                    pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
+                    pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
+                    pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
+                    pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) l_sum += pv[i];
+                uint8_t* prow = sbase + (c >> 1) * TILE_BYTES + tid * 128;   // P overlays Q (keys 0..63), K (64..127)
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 qv;
+                    qv.x = pack2(pv[g * 8 + 0], pv[g * 8 + 1], p.dtype);
+                    qv.y = pack2(pv[g * 8 + 2], pv[g * 8 + 3], p.dtype);
+                    qv.z = pack2(pv[g * 8 + 4], pv[g * 8 + 5], p.dtype);
+                    qv.w = pack2(pv[g * 8 + 6], pv[g * 8 + 7], p.dtype);
+                    const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
+                }
             }
         }
         fence_async_proxy_shared();
+        tcgen05_fence_before();
+        __syncthreads();
+
+        if (tid == 0) {
+            tcgen05_fence_after();
+            if (mbar_wait(&bar_v[set], ph_set, abort_flag)) {
+                tcgen05_fence_after();
+                const int ksteps = n_chunks * 2;
+                for (int k = 0; k < ksteps; ++k) {
+                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sbase + (k >> 2) * TILE_BYTES)) + 2u * (k & 3);
+                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_V + k * 2048));
+                    umma_f16_ss(tmem_base, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);   // O overlays S
+                }
+                umma_commit(bar_o);
+            }
+        }
+        if (!mbar_wait(bar_o, ph, abort_flag)) { ok = false; break; }
+        __syncwarp();
+        tcgen05_fence_after();
+        {
+            const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+            uint8_t* orow = sbase + tid * 128;   // output tile overlays P's first half (PV has completed)
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_wait(r);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 qv;
+                    qv.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv, p.dtype);
+                    qv.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv, p.dtype);
+                    qv.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv, p.dtype);
+                    qv.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv, p.dtype);
+                    const int chunk = (c * 4 + g) ^ (tid & 7);
+                    *reinterpret_cast<uint4*>(orow + chunk * 16) = qv;
+                }
+            }
+            fence_async_proxy_shared();
+        }
+        tcgen05_fence_before();
+        __syncthreads();   // also orders this item's TMEM reads before the next item's UMMAs
+        if (tid == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_o)), "r"(smem_u32(sbase)), "r"(head * HD), "r"(0), "r"(b)
+                         : "memory");
+            tma_store_commit();
+        }
+    }
+    if (tid == 0) {
+        if (ok) tma_store_wait_all<0>();
+        else for (int i = 0; i < 64; ++i) nanosleep(10000);   // let copies in flight land
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (tid == 0) {
-        if (ok) {
-            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&tm_o)), "r"(smem_u32(smem)), "r"(head * HD), "r"(0), "r"(b)
-                         : "memory");
-            tma_store_commit();
-            tma_store_wait_all<0>();
-        } else {
-            for (int i = 0; i < 64; ++i) nanosleep(10000);
-        }
-    }
     if (warp == 0) {
-        __syncwarp();
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, S1_TMEM_COLS);
     }
@@ -522,9 +565,13 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
                 return B200_ERR_LAUNCH;
             attr1_set[dev] = true;
         }
-        dim3 grid1(1, static_cast<unsigned>(d->heads), static_cast<unsigned>(d->B));
-        attention_single_kernel<<<grid1, kAttnThreads, S1_SMEM, static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to,
-                                                                                                      p);
+        const long long items = static_cast<long long>(d->heads) * d->B;
+        if (items > 0x7fffffff) return B200_ERR_UNSUPPORTED;
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long grid1 = items < 2ll * sms ? items : 2ll * sms;   // two persistent CTAs per SM
+        attention_single_kernel<<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
+                                  static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p, static_cast<int>(items));
         count_launch();
         return check_launch();
     }
@@ -623,8 +670,12 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
     p.status = device_status_ptr();
 
     if (d->S <= 128) {
-        dim3 grid1(1, static_cast<unsigned>(d->heads), static_cast<unsigned>(d->B));
-        attention_single_kernel<<<grid1, kAttnThreads, S1_SMEM, stream>>>(tq, tk, tv, to, p);
+        const long long items = static_cast<long long>(d->heads) * d->B;
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long grid1 = items < 2ll * sms ? items : 2ll * sms;
+        attention_single_kernel<<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
+            tq, tk, tv, to, p, static_cast<int>(items));
     } else {
         dim3 grid(static_cast<unsigned>((d->S + TQ - 1) / TQ), static_cast<unsigned>(d->heads),
                   static_cast<unsigned>(d->B));

@@ -112,11 +112,6 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
     extern __shared__ float gb[];   // gamma[H] | beta[H]
     const int lane = threadIdx.x & 31;
     const int H = static_cast<int>(d.H);
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-        *reinterpret_cast<float4*>(gb + i) = __ldg(reinterpret_cast<const float4*>(d.gamma + i));
-        *reinterpret_cast<float4*>(gb + H + i) = __ldg(reinterpret_cast<const float4*>(d.beta + i));
-    }
-    __syncthreads();
     const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * 8;
     const int groups = H >> 3;
@@ -163,7 +158,12 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
     };
     const float inv_h = 1.0f / static_cast<float>(d.H);
     long long row = warp0;
-    if (row < d.rows) fetch(row);
+    if (row < d.rows) fetch(row);   // the first row's loads are in flight while gamma/beta are staged
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        *reinterpret_cast<float4*>(gb + i) = __ldg(reinterpret_cast<const float4*>(d.gamma + i));
+        *reinterpret_cast<float4*>(gb + H + i) = __ldg(reinterpret_cast<const float4*>(d.beta + i));
+    }
+    __syncthreads();
     for (; row < d.rows; row += nwarps) {
         float v[NV][8];
         float sum = 0.f;

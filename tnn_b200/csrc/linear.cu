@@ -15,7 +15,7 @@
 namespace b200 {
 namespace lin {
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool FOLD>
 struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
@@ -23,15 +23,15 @@ struct Cfg {
     static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;               // output staging strips (TMA store)
     static constexpr int BAR_OFFSET = OUT_OFFSET + kEpiWarps * kStageBytesPerWarp;
     static constexpr int BIAS_OFFSET = BAR_OFFSET + 256;         // per-epilogue-warp bias slice: 8 x (BN/2) floats
-    static constexpr int SMEM_BYTES = BIAS_OFFSET + kEpiWarps * kVecStrips * (BN / 2) * 4 + 1024;  // + slack for 1024-byte alignment
+    static constexpr int SMEM_BYTES = BIAS_OFFSET + kEpiWarps * vec_strips<FOLD>() * (BN / 2) * 4 + 1024;  // + slack for 1024-byte alignment
     static constexpr int TMEM_COLS = 2 * BN;                    // 128, 256 or 512: powers of two
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool FOLD>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
               const __grid_constant__ CUtensorMap tm_y, const LinearParams p) {
-    using C = Cfg<BN, STAGES>;
+    using C = Cfg<BN, STAGES, FOLD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
@@ -129,8 +129,8 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int half = ew >> 2;      // which half of the BN columns
         constexpr int COLS = BN / 2;
         constexpr int CHUNKS = COLS / 32;
-        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * kVecStrips * COLS;  // private to this warp
-        WarpEpilogue<CHUNKS, false> epi{p, &tm_y, nullptr, smem + C::OUT_OFFSET + ew * kStageBytesPerWarp, nullptr,
+        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * vec_strips<FOLD>() * COLS;  // private to this warp
+        WarpEpilogue<CHUNKS, false, FOLD> epi{p, &tm_y, nullptr, smem + C::OUT_OFFSET + ew * kStageBytesPerWarp, nullptr,
                                         abort_flag, lane, 0u};
         uint32_t tcount = 0;
         bool ok = true;
@@ -142,7 +142,7 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             // Stage this tile's bias slice while the accumulator is still being produced.
             const long long row = static_cast<long long>(m_blk) * BM + quarter * 32 + lane;
             epi.begin_tile(n_blk * BN + half * COLS, static_cast<int>(row) - lane);
-            stage_vectors(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
+            stage_vectors<FOLD>(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();  // tcgen05.ld is warp-collective
             tcgen05_fence_after();
@@ -181,9 +181,9 @@ int device_sm_count() {
     return sms[dev];
 }
 
-template <int BN, int STAGES>
-int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
-    using C = Cfg<BN, STAGES>;
+template <int BN, int STAGES, bool FOLD>
+int launch_linear_t(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
+    using C = Cfg<BN, STAGES, FOLD>;
     const uint64_t xd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.M)};
     const uint64_t xs[1] = {static_cast<uint64_t>(d.ldx) * 2};
     const uint32_t xb[2] = {BK, BM};
@@ -234,15 +234,21 @@ int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(linear_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(linear_kernel<BN, STAGES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::SMEM_BYTES) != cudaSuccess)
             return B200_ERR_LAUNCH;
         attr_set[dev] = true;
     }
     const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-    linear_kernel<BN, STAGES><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, p);
+    linear_kernel<BN, STAGES, FOLD><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, p);
     count_launch();
     return check_launch();
+}
+
+template <int BN, int STAGES>
+int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
+    if (wants_fold(d)) return launch_linear_t<BN, STAGES - 1, true>(d, stream, sm_count);
+    return launch_linear_t<BN, STAGES, false>(d, stream, sm_count);
 }
 
 // Tile choice.  Estimated time ~ waves * (columns per tile * cost per column + fixed per-tile cost), in units of

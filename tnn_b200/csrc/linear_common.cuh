@@ -34,7 +34,6 @@ struct LinearParams {
     int k_slots, n_slots;   // ceil(K/32), ceil(N/32)
 };
 
-constexpr int kVecStrips = 4;   // per epilogue warp: bias|c2, c1, gamma, beta — COLS floats each
 
 // erf-form GELU, 0.5 x (1 + erf(x / sqrt 2)) = x * Phi(x), as the reference's CPU accs compute it, evaluated as
 // 0.5 x (1 + tanh(x (a + b x^2 + c x^4))) with a, b, c fitted to the erf form (max abs deviation of the formula
@@ -55,15 +54,16 @@ __device__ __forceinline__ float gelu_erf(float x) {
 // Stage one warp's per-column vectors (COLS floats each, starting at column n_first) in its private shared-memory
 // strips: strip 0 = bias (or c2 when the input LayerNorm is folded), 1 = c1, 2 = gamma, 3 = beta of a folded residual
 // LayerNorm.  Columns at or beyond N read as 0, so that they contribute nothing anywhere.
+template <bool FOLD>
 __device__ __forceinline__ void stage_vectors(const LinearParams& p, float* vec_w, int n_first, int cols, int lane) {
     __syncwarp();
-    const float* s0 = p.ln_in_stats ? p.ln_c2 : p.bias;
+    const float* s0 = (FOLD && p.ln_in_stats) ? p.ln_c2 : p.bias;
     for (int i = lane; i < cols; i += 32) {
         const int n = n_first + i;
         const bool in = n < p.N;
         vec_w[i] = (s0 != nullptr && in) ? __ldg(s0 + n) : 0.f;
-        if (p.ln_in_stats) vec_w[cols + i] = in ? __ldg(p.ln_c1 + n) : 0.f;
-        if (p.res_ln_stats) {
+        if (FOLD && p.ln_in_stats) vec_w[cols + i] = in ? __ldg(p.ln_c1 + n) : 0.f;
+        if (FOLD && p.res_ln_stats) {
             vec_w[2 * cols + i] = in ? __ldg(p.res_ln_gamma + n) : 0.f;
             vec_w[3 * cols + i] = in ? __ldg(p.res_ln_beta + n) : 0.f;
         }
@@ -97,43 +97,51 @@ __device__ __forceinline__ void row_stats(const float* stats, int slots, long lo
 }
 
 // Half-precision outputs leave through shared memory: the warp writes its 32 x 32 chunk (64 bytes per row, 64-byte
-// swizzle so that the 16-byte stores of a quarter warp hit distinct banks) into a private 2 KB strip, and one lane
-// issues a TMA tile store, which writes whole 32-byte sectors and clips rows / columns outside the tensor.
+// swizzle so that the 16-byte stores of a quarter warp hit distinct banks) into one of its private 2 KB strips, and
+// one lane issues a TMA tile store, which writes whole 32-byte sectors and clips rows / columns outside the tensor.
 // (A thread storing its own row directly issues 16-byte pieces to 32 different rows per instruction; measured, that
 // store pattern alone held the 768-deep GEMMs at 60 % of what the mainloop delivers.)  fp32 outputs (graph edge only)
-// are stored directly.
+// are stored directly.  (Rotating more strips per warp was tried: the wait for the TMA engine to have read a strip is
+// not on the critical path, while the extra shared memory costs a pipeline stage.)
 //
-// With RES the residual tile comes in the same way: a TMA load of the 32 x 32 chunk into the strip (one chunk ahead,
-// two strips), read back swizzled, added, and the strip is then reused for the output of that chunk.
+// With RES the residual tile comes in the same way: a TMA load of the 32 x 32 chunk into the strip one chunk ahead,
+// read back swizzled, added, and the strip is then reused for the output of that chunk.
+//
+// FOLD compiles the LayerNorm-folding paths in (row statistics in/out, folded input / residual LayerNorm); without
+// it the kernel carries neither their registers nor their shared-memory strips.
 constexpr int kStageBytesPerWarp = 32 * 64;
+template <bool RES> constexpr int strips_per_warp() { return RES ? 2 : 1; }
+template <bool FOLD> constexpr int vec_strips() { return FOLD ? 4 : 1; }   // bias|c2, c1, gamma, beta
 
-template <int CHUNKS, bool RES>
+template <int CHUNKS, bool RES, bool FOLD>
 struct WarpEpilogue {
+    static constexpr int NSTRIPS = RES ? 2 : 1;
     const LinearParams& p;
     const CUtensorMap* tm_y;
     const CUtensorMap* tm_r;
-    uint8_t* strips;              // RES: 2 strips, else 1
-    uint64_t* rbars;              // RES: 2 mbarriers of this warp
+    uint8_t* strips;              // NSTRIPS strips of this warp
+    uint64_t* rbars;              // RES: NSTRIPS mbarriers of this warp
     volatile uint32_t* abort_flag;
     int lane;
-    uint32_t cc;                  // chunks processed so far by this warp (selects strip / barrier / phase when RES)
+    uint32_t cc;                  // chunks processed so far by this warp (selects strip / barrier / phase)
     float mean_x = 0.f, rstd_x = 0.f;   // folded input LayerNorm: statistics of this thread's row of x
     float mean_r = 0.f, rstd_r = 0.f;   // folded residual LayerNorm: statistics of this thread's row of the residual
-    // Row statistics of the NEXT tile, in flight while the current tile is drained: one L2 round trip per tile would
-    // otherwise sit on the epilogue's critical path (measured: +2.4 us per tile).  Serves the folded input LayerNorm
-    // if there is one, else the folded residual LayerNorm; up to kPrefetchSlots slots (768 columns).
-    static constexpr int kPrefetchSlots = 24;
+    // Row statistics of the NEXT tile, in flight while the current tile is drained (one L2 round trip per tile would
+    // otherwise sit on the epilogue's critical path).  Serves the folded input LayerNorm if there is one, else the
+    // folded residual LayerNorm; up to kPrefetchSlots slots (768 columns), wider rows take the slow path.
+    static constexpr int kPrefetchSlots = FOLD ? 24 : 1;
     float2 pf[kPrefetchSlots];
     long long pf_row = -1;
 
-    __device__ __forceinline__ const float* pf_stats() const { return p.ln_in_stats ? p.ln_in_stats : p.res_ln_stats; }
-    __device__ __forceinline__ int pf_slots() const { return p.ln_in_stats ? p.k_slots : p.n_slots; }
+    __device__ __forceinline__ bool ln_in() const { return FOLD && p.ln_in_stats != nullptr; }
+    __device__ __forceinline__ bool res_ln() const { return FOLD && p.res_ln_stats != nullptr; }
     __device__ __forceinline__ void prefetch_stats(long long row) {
+        if (!FOLD) return;
         pf_row = -1;
-        const float* st = pf_stats();
-        if (st == nullptr || pf_slots() > kPrefetchSlots || row >= p.M || row < 0) return;
+        const float* st = p.ln_in_stats ? p.ln_in_stats : p.res_ln_stats;
+        const int slots = p.ln_in_stats ? p.k_slots : p.n_slots;
+        if (st == nullptr || slots > kPrefetchSlots || row >= p.M || row < 0) return;
         const float2* base = reinterpret_cast<const float2*>(st) + row;
-        const int slots = pf_slots();
 #pragma unroll
         for (int j = 0; j < kPrefetchSlots; ++j)
             pf[j] = (j < slots) ? __ldg(base + static_cast<long long>(j) * p.M) : make_float2(0.f, 0.f);
@@ -155,18 +163,20 @@ struct WarpEpilogue {
     __device__ __forceinline__ bool chunk_valid(int c, int n_first, int row0) const {
         return c < CHUNKS && n_first + c * 32 < p.N && row0 < p.M;
     }
-    // lane 0: start the residual load of the chunk that will be processed as number `seq`
+    // lane 0: start the residual load of the chunk that will be processed as number `seq`.  Its strip last held the
+    // output of chunk seq-2, the most recent store of this warp.
     __device__ __forceinline__ void issue_residual(uint32_t seq, int n0, int row0) {
         if (lane == 0) {
-            tma_store_wait_read<0>();   // the strip's previous output store has been read out
-            uint64_t* bar = rbars + (seq & 1u);
-            mbar_expect_tx(bar, kStageBytesPerWarp);
-            tma_load_2d(strips + (seq & 1u) * kStageBytesPerWarp, tm_r, bar, n0, row0);
+            tma_store_wait_read<0>();
+            const uint32_t si = seq % NSTRIPS;
+            mbar_expect_tx(rbars + si, kStageBytesPerWarp);
+            tma_load_2d(strips + si * kStageBytesPerWarp, tm_r, rbars + si, n0, row0);
         }
     }
     // Call before waiting for the accumulator: overlaps the first residual load with the tile's mainloop.
     __device__ __forceinline__ void begin_tile(int n_first, int row0) {
         if (RES && chunk_valid(0, n_first, row0)) issue_residual(cc, n_first, row0);
+        if (!FOLD) return;
         const long long row = static_cast<long long>(row0) + lane;
         const bool have_pf = pf_row == row && row < p.M;
         if (p.ln_in_stats) {
@@ -192,7 +202,7 @@ struct WarpEpilogue {
             r[2 * e] = f.x;
             r[2 * e + 1] = f.y;
         }
-        if (p.res_ln_stats) {
+        if (res_ln()) {
 #pragma unroll
             for (int e = 0; e < 8; ++e)
                 r[e] = fmaf((r[e] - mean_r) * rstd_r, vec_w[2 * COLS + col + e], vec_w[3 * COLS + col + e]);
@@ -209,19 +219,22 @@ struct WarpEpilogue {
         const bool row_ok = row < p.M;
         const int row0 = static_cast<int>(row) - lane;
         const int n_first = n_tile0 + col_first;
+        uint32_t r[32];
+        if (chunk_valid(0, n_first, row0)) tmem_ld_32x32b_x32(tacc + col_first, r);
 #pragma unroll 1
         for (int c = 0; c < CHUNKS; ++c) {
-            if (!chunk_valid(c, n_first, row0)) continue;   // uniform across the warp
+            if (!chunk_valid(c, n_first, row0)) break;   // uniform across the warp; validity is monotone in c
             const int col0 = col_first + c * 32;
             const int n0 = n_tile0 + col0;
-            if (RES && chunk_valid(c + 1, n_first, row0)) issue_residual(cc + 1, n0 + 32, row0);
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tacc + col0, r);
+            const bool next_valid = chunk_valid(c + 1, n_first, row0);
+            if (RES && next_valid) issue_residual(cc + 1, n0 + 32, row0);
             tmem_ld_wait(r);
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            if (p.ln_in_stats) {
+            // the next chunk's accumulator columns travel while this chunk is processed
+            if (next_valid) tmem_ld_32x32b_x32(tacc + col0 + 32, r);
+            if (ln_in()) {
                 // LN(x).W + b = rstd * (x.W' - mean * c1) + c2
                 const float nm = -mean_x;
 #pragma unroll
@@ -247,10 +260,11 @@ struct WarpEpilogue {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
             }
-            uint8_t* strip = strips + (RES ? (cc & 1u) * kStageBytesPerWarp : 0u);
+            const uint32_t si = cc % NSTRIPS;
+            uint8_t* strip = strips + si * kStageBytesPerWarp;
             uint8_t* srow = strip + lane * 64;
             if (RES) {
-                if (!mbar_wait(rbars + (cc & 1u), (cc >> 1) & 1u, abort_flag)) return false;
+                if (!mbar_wait(rbars + si, (cc / NSTRIPS) & 1u, abort_flag)) return false;
                 __syncwarp();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -267,7 +281,7 @@ struct WarpEpilogue {
                     }
                 }
             }
-            if (p.out_stats != nullptr && row_ok) {
+            if (FOLD && p.out_stats != nullptr && row_ok) {
                 float s1 = 0.f, s2 = 0.f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -290,7 +304,7 @@ struct WarpEpilogue {
                 }
             } else {
                 if (!RES) {
-                    // the previous TMA store of this warp must have finished reading the strip
+                    // the previous store of this warp must have finished reading the strip
                     if (lane == 0) tma_store_wait_read<0>();
                     __syncwarp();
                 }
@@ -319,6 +333,7 @@ struct WarpEpilogue {
 // CTA-pair kernel (linear_pair.cu).  BN in {64, 128, 192, 256}.
 template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count);
+inline bool wants_fold(const B200LinearDesc& d) { return d.out_stats || d.ln_in_stats || d.res_ln_stats; }
 // Number of CTA pairs of the pair kernel that can be co-resident on the current device (cached; 0 if unknown).
 int max_active_pairs(int bn);
 

@@ -18,14 +18,14 @@ namespace lin {
 
 namespace {
 
-template <int BN, bool RES>
+template <int BN, bool RES, bool FOLD>
 struct PairCfg {
     static constexpr int A_BYTES = 128 * BK * 2;          // this CTA's 128 rows of x
     static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this CTA's BN/2 rows of w
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // output staging strips (TMA store); with RES two per warp, which also receive the residual tile (TMA load)
-    static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * (RES ? 2 : 1);
-    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * kVecStrips * (BN / 2) * 4;   // + barriers + bias strips
+    static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * strips_per_warp<RES>();
+    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * vec_strips<FOLD>() * (BN / 2) * 4;   // + barriers + bias strips
     static constexpr int STAGES = (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES > 8
                                       ? 8 : (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
@@ -91,12 +91,12 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-template <int BN, bool RES>
+template <int BN, bool RES, bool FOLD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_r,
                    const LinearParams p) {
-    using C = PairCfg<BN, RES>;
+    using C = PairCfg<BN, RES, FOLD>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of a pair must lay their buffers out at identical offsets: the dynamic shared-memory window starts at
@@ -202,10 +202,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const int half = ew >> 2;
         constexpr int COLS = BN / 2;
         constexpr int CHUNKS = COLS / 32;
-        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * kVecStrips * COLS;
-        WarpEpilogue<CHUNKS, RES> epi{p, &tm_y, &tm_r,
-                                      smem + C::OUT_OFFSET + ew * kStageBytesPerWarp * (RES ? 2 : 1),
-                                      res_bars + 2 * ew, abort_flag, lane, 0u};
+        float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * vec_strips<FOLD>() * COLS;
+        WarpEpilogue<CHUNKS, RES, FOLD> epi{p, &tm_y, &tm_r,
+                                            smem + C::OUT_OFFSET + ew * kStageBytesPerWarp * strips_per_warp<RES>(),
+                                            res_bars + 2 * ew, abort_flag, lane, 0u};
         uint32_t tcount = 0;
         bool ok = true;
         const long long row_in_tile = static_cast<long long>(rank) * 128 + quarter * 32 + lane;
@@ -223,7 +223,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 epi.prefetch_stats(next < p.num_tiles
                                        ? static_cast<long long>(next / p.num_n_tiles) * 256 + row_in_tile : -1);
             }
-            stage_vectors(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
+            stage_vectors<FOLD>(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();
             tcgen05_fence_after();
@@ -253,9 +253,9 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
 }  // namespace
 
-template <int BN, bool RES>
+template <int BN, bool RES, bool FOLD>
 int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
-    using C = PairCfg<BN, RES>;
+    using C = PairCfg<BN, RES, FOLD>;
     static_assert(C::STAGES >= 3, "pipeline too shallow");
     const uint64_t xd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.M)};
     const uint64_t xs[1] = {static_cast<uint64_t>(d.ldx) * 2};
@@ -315,7 +315,7 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::SMEM_BYTES) != cudaSuccess)
             return B200_ERR_LAUNCH;
         attr_set[dev] = true;
@@ -323,7 +323,7 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     int pairs = max_active_pairs(BN);   // (the RES variant uses no more shared memory per CTA than its stage count allows)
     if (pairs <= 0) pairs = sm_count / 2;
     if (p.num_tiles < pairs) pairs = p.num_tiles;
-    linear_pair_kernel<BN, RES><<<2 * pairs, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, *tr, p);
+    linear_pair_kernel<BN, RES, FOLD><<<2 * pairs, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, *tr, p);
     count_launch();
     return check_launch();
 }
@@ -333,8 +333,8 @@ template <int BN>
 int query_pairs(int sm_count) {
     // A persistent grid must not exceed what is co-resident: a pair that cannot be placed (GPCs with an odd number
     // of free SMs) would otherwise run as a second wave after the first has finished all the work.
-    using C = PairCfg<BN, false>;
-    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    using C = PairCfg<BN, false, false>;
+    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -351,7 +351,7 @@ int query_pairs(int sm_count) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false, false>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -379,8 +379,10 @@ int max_active_pairs(int bn) {
 template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     // The TMA residual path needs 16-byte aligned residual rows (checked by the caller) and a half-precision residual.
-    if (d.epilogue == B200_EPI_BIAS_RESIDUAL) return launch_pair<BN, true>(d, stream, sm_count);
-    return launch_pair<BN, false>(d, stream, sm_count);
+    const bool fold = wants_fold(d);
+    if (d.epilogue == B200_EPI_BIAS_RESIDUAL)
+        return fold ? launch_pair<BN, true, true>(d, stream, sm_count) : launch_pair<BN, true, false>(d, stream, sm_count);
+    return fold ? launch_pair<BN, false, true>(d, stream, sm_count) : launch_pair<BN, false, false>(d, stream, sm_count);
 }
 
 template int launch_linear_pair<256>(const B200LinearDesc&, cudaStream_t, int);

@@ -98,11 +98,11 @@ def main():
     run = None
     if not a.eager:
         try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
                 for _ in range(a.iters):
                     fn()
-            run = g.replay
+            run = graph.replay
             run()
             torch.cuda.synchronize()
         except Exception:
