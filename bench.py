@@ -361,6 +361,29 @@ def run_ours(args):
     attn_ms = statistics.mean(kernel_ms["attention"])
     attn_flops = 4.0 * SEQ * SEQ * 64 * cfg.heads * B
 
+    # ---- the benchmark's standalone attention sweep (16 heads x d64, batch 16, S = 512/1024/2048, all-ones mask)
+    attention_sweep = []
+    if rank == 0 and not args.no_attention_sweep:
+        for S_ in (512, 1024, 2048):
+            qkv_ = torch.randn(16, S_, 3 * 16 * 64, device=dev).to(torch.float16)
+            msk_ = torch.zeros(16, S_, device=dev)
+            kvl_ = ops.mask_to_kv_len(msk_)
+            out_ = torch.empty(16, S_, 16 * 64, device=dev, dtype=torch.float16)
+            for _ in range(3):
+                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(10):
+                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+            a1.record()
+            torch.cuda.synchronize()
+            ms_ = a0.elapsed_time(a1) / 10
+            fl_ = 4.0 * S_ * S_ * 64 * 16 * 16
+            attention_sweep.append({"S": S_, "ms": round(ms_, 4), "tflops": round(fl_ / ms_ / 1e9, 1),
+                                    "frac_of_tensor_peak": round(fl_ / ms_ / 1e9 / peaks["tflops"], 4)})
+            del qkv_, out_
+
     # ---- reduce over ranks
     ms_t = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
     ms_t = reduce_max_over_ranks(ms_t, world)
@@ -398,6 +421,7 @@ def run_ours(args):
                          "peak_sustained": peaks["tflops_sustained"],
                          "flops_per_launch_avg": gemm_flops / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm,
                          "launches_timed": n_gemm, "per_shape": per_shape, "traffic": None},
+            "attention_sweep": attention_sweep,
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
                                  "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
             "layernorm_kernel": {"ms": statistics.mean(kernel_ms["layernorm"]),
@@ -420,6 +444,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="sequences per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-attention-sweep", action="store_true")
     ap.add_argument("--fold-layernorm", action="store_true",
                     help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "

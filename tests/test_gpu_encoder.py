@@ -74,3 +74,28 @@ def test_sequences_are_independent_at_full_batch(cuda_device):
     sub = model_synth.Workload(wl.cfg, wl.weights, wl.x[:4], wl.lengths[:4], wl.mask_add[:4], wl.meta)
     y4 = _run(sub, torch.float16)
     assert np.array_equal(y[:4], y4)
+
+
+def test_config4_geometry_bf16_and_f16_against_oracle(cuda_device):
+    """Config 4 geometry: BERT-large (H=1024, 16 heads, FFN 4096), S=384, lengths ~ U[128,384]; first 2 sequences of the
+    seeded batch and the first 4 of the 24 layers (sequences are independent; the oracle needs ~10 s per layer here)."""
+    wl = model_synth.config_workload(4, batch=2, num_layers=4)
+    want = bert_oracle.encoder_forward(wl)
+    vw = valid_rows(want, wl.lengths)
+    y = _run(wl, torch.float16, fold=False)
+    assert max_abs(valid_rows(y, wl.lengths), vw) <= MAX_ABS_TOL
+    assert cosine(valid_rows(y, wl.lengths), vw) >= COS_TOL
+    yb = _run(wl, torch.bfloat16, fold=False)
+    assert max_abs(valid_rows(yb, wl.lengths), vw) <= 4 * MAX_ABS_TOL
+    assert cosine(valid_rows(yb, wl.lengths), vw) >= 0.999
+
+
+def test_config5_batch_shard_is_a_slice_of_the_full_batch(cuda_device):
+    """Config 5 shards one batch over GPUs: a rank's shard must give what the same rows give in the full batch
+    (128 sequences = the per-GPU shard at 8 GPUs, against its first and last 16-sequence slices; 2 layers)."""
+    wl = model_synth.config_workload(5, batch=128, num_layers=2)
+    y = _run(wl, torch.float16, fold=False)
+    for lo in (0, 112):
+        sub = model_synth.Workload(wl.cfg, wl.weights, wl.x[lo:lo + 16], wl.lengths[lo:lo + 16],
+                                   wl.mask_add[lo:lo + 16], wl.meta)
+        assert np.array_equal(y[lo:lo + 16], _run(sub, torch.float16, fold=False))

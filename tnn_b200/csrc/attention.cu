@@ -1,17 +1,15 @@
-// Fused multi-head attention for sm_100a, head_dim 64:  out = softmax(scale * Q K^T + mask) V, one CTA per
-// (128-query tile, head, sequence), flash-style loop over 128-key tiles with online softmax.
+// Fused multi-head attention for sm_100a, head_dim 64:  out = softmax(scale * Q K^T + mask) V, flash-style: no score
+// matrix ever leaves the SM.  Two kernels share the building blocks below:
+//   attention_single_kernel   S <= 128: persistent CTAs, one (sequence, head) item at a time, next item prefetched;
+//   attention_pingpong_kernel S  > 128: two 128-query tiles per CTA in ping-pong over a ring of 128-key tiles.
 //
 //   TMA   : Q, K, V tiles [128 x 64] straight out of the token-major QKV activation (the head split of the unfused
 //           graph's Reshape+Permute is just the TMA column coordinate h*64) into 128-byte-swizzled shared memory.
-//   UMMA  : S = Q K^T (128 x 128 x 64, both operands K-major) into TMEM columns [0,128);
-//           O_j = P V (128 x 64 x 128, P K-major from shared memory, V MN-major exactly as TMA delivered it) into
-//           TMEM columns [128,192).
+//   UMMA  : S = Q K^T (128 x 128 x 64, both operands K-major) and O = P V (128 x 64 x 128, P K-major from shared
+//           memory, V MN-major exactly as TMA delivered it), fp32 accumulation in TMEM.
 //   softmax: thread t owns query row t (TMEM lane t), so row max / row sum are in-thread; scores are scaled, the
 //           additive key mask is applied in registers, excluded keys get weight exactly 0 (exp2(-inf)), P is written
 //           to shared memory as half precision in the swizzled K-major layout the second UMMA reads.
-//   The running output is kept in registers and rescaled per key tile; K_{j+1} is fetched while tile j is in softmax
-//   and PV, V_{j+1} while tile j+1 is in QK^T and softmax.  Two CTAs fit per SM (81 KB shared memory, 256 TMEM
-//   columns each), which overlaps one CTA's softmax with the other's UMMAs.
 // Algorithmic work per launch: 4 * S^2 * 64 * heads * B flop (QK^T and PV); HBM bytes: Q, K, V read once per CTA, O written.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -55,224 +53,317 @@ struct AttnParams {
     unsigned int* status;
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
-attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+// ---------------------------------------------------------------------------------------------------------------
+// Long sequences: two 128-query tiles per CTA, processed by two softmax warpgroups in ping-pong, so that the tensor
+// pipe works on one tile's QK^T / PV while the other tile is in its softmax, and every K/V tile is loaded once for
+// 256 queries.  Roles (320 threads, one CTA per SM):
+//   warp 0      : producer — lane 0 issues the TMA loads (Q tiles once, then K/V tiles through a 2-stage ring); all 32
+//                 lanes write the tile's key mask (log2 units, -inf = dropped) next to it;
+//   warp 1      : one lane issues every UMMA: S_w = Q_w K^T into TMEM columns [128w, 128w+128), O_w = P_w V into
+//                 [256+64w, 256+64w+64), in the order S0 S1 | PV0 S0' | PV1 S1' | ... so that a warpgroup's next
+//                 scores are already on their way while it rescales its output;
+//   warps 2..5  : softmax warpgroup 0 (query rows q0 .. q0+127), warps 6..9: warpgroup 1 (q0+128 .. q0+255);
+//                 thread = row, running max / sum / output in registers, P_w written to shared memory for the UMMA.
+// All hand-offs are mbarriers with bounded waits (no named barriers: a role that gives up cannot strand another).
+constexpr int PP_THREADS = 320;
+constexpr int PP_OFF_Q = 0;                          // 2 x 16 KB
+constexpr int PP_OFF_K = 2 * TILE_BYTES;             // 2 stages
+constexpr int PP_OFF_V = 4 * TILE_BYTES;             // 2 stages
+constexpr int PP_OFF_P = 6 * TILE_BYTES;             // 2 warpgroups x 32 KB
+constexpr int PP_OFF_MASK = 10 * TILE_BYTES;         // 2 stages x 128 floats
+constexpr int PP_OFF_BAR = PP_OFF_MASK + 2 * TK * 4;
+constexpr int PP_SMEM = PP_OFF_BAR + 256;
+constexpr int PP_TMEM_COLS = 512;
+
+template <int DT>
+__global__ void __launch_bounds__(PP_THREADS, 1)
+attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t* bar_q = bars + 0;
-    uint64_t* bar_k = bars + 1;
-    uint64_t* bar_v = bars + 2;
-    uint64_t* bar_s = bars + 3;
-    uint64_t* bar_o = bars + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_OFF_BAR);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;    // [2]
+    uint64_t* v_full = bars + 3;    // [2]
+    uint64_t* k_empty = bars + 5;   // [2]
+    uint64_t* v_empty = bars + 7;   // [2]
+    uint64_t* m_full = bars + 9;    // [2] mask of the stage written (32 arrivals)
+    uint64_t* s_full = bars + 11;   // [2] per warpgroup
+    uint64_t* p_full = bars + 13;   // [2] (128 arrivals)
+    uint64_t* o_full = bars + 15;   // [2]
+    uint64_t* o_empty = bars + 17;  // [2] (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* mask_s = reinterpret_cast<float*>(smem + OFF_MASK);
+    float* mask_s = reinterpret_cast<float*>(smem + PP_OFF_MASK);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
-    const int q0 = blockIdx.x * TQ;
+    const int lane = tid & 31;
+    const int q0 = blockIdx.x * 2 * TQ;
     const int head = blockIdx.y;
     const int b = blockIdx.z;
 
-    // The swizzled tiles need 1024-byte alignment; refuse to run rather than compute garbage if it is ever violated.
     if ((smem_u32(smem) & 1023u) != 0) {
         if (tid == 0 && p.status) atomicOr(p.status, 4u);
         return;
     }
-
     int kv_eff = p.S;
     bool additive_only = (p.mask_add == nullptr);
     if (p.kv_len != nullptr) {
         const int kl = p.kv_len[b];
-        if (kl <= 0) additive_only = true;          // no key above the threshold: the reference's behaviour
+        if (kl <= 0) additive_only = true;
         else kv_eff = kl < p.S ? kl : p.S;
     }
     const int n_tiles = (kv_eff + TK - 1) / TK;
+    const bool two = (p.S - q0) > TQ;   // the second query tile exists
 
     if (tid == 0) {
-        mbar_init(bar_q, 1);
-        mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&m_full[i], 32);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&o_full[i], 1);
+            mbar_init(&o_empty[i], 128);
+        }
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tmap(&tm_q);
         prefetch_tmap(&tm_k);
         prefetch_tmap(&tm_v);
     }
-    if (warp == 0) {
-        tmem_alloc(tmem_slot, ATTN_TMEM_COLS);
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, PP_TMEM_COLS);
         tmem_relinquish();
     }
-
-    // Key mask of a tile, in log2 units: -inf drops the key exactly.
-    auto write_mask = [&](int j) {
-        const int key = j * TK + tid;
-        float m = -INFINITY;
-        if (key < p.S) {
-            const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + key] : 0.f;
-            if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
-        }
-        mask_s[(j & 1) * TK + tid] = m;
-    };
-    write_mask(0);
-
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (tid == 0) {
-        mbar_expect_tx(bar_q, TILE_BYTES);
-        tma_load_3d(smem + OFF_Q, &tm_q, bar_q, head * HD, q0, b);
-        mbar_expect_tx(bar_k, TILE_BYTES);
-        tma_load_3d(smem + OFF_K, &tm_k, bar_k, head * HD, 0, b);
-        mbar_expect_tx(bar_v, TILE_BYTES);
-        tma_load_3d(smem + OFF_V, &tm_v, bar_v, head * HD, 0, b);
-    }
-
-    const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
-    float o[HD];
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (two ? 2 : 1) * TILE_BYTES);
+            tma_load_3d(smem + PP_OFF_Q, &tm_q, q_full, head * HD, q0, b);
+            if (two) tma_load_3d(smem + PP_OFF_Q + TILE_BYTES, &tm_q, q_full, head * HD, q0 + TQ, b);
+        }
+        bool ok = true;
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = (static_cast<uint32_t>(j) >> 1) & 1u;
+            if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+            if (lane == 0) {
+                mbar_expect_tx(&k_full[st], TILE_BYTES);
+                tma_load_3d(smem + PP_OFF_K + st * TILE_BYTES, &tm_k, &k_full[st], head * HD, j * TK, b);
+            }
+            // v_empty also says that both warpgroups are done with this stage's mask
+            if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+            if (lane == 0) {
+                mbar_expect_tx(&v_full[st], TILE_BYTES);
+                tma_load_3d(smem + PP_OFF_V + st * TILE_BYTES, &tm_v, &v_full[st], head * HD, j * TK, b);
+            }
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
-
-    for (int j = 0; j < n_tiles; ++j) {
-        const uint32_t ph = static_cast<uint32_t>(j) & 1u;
-        // ---- S = Q K^T
-        if (tid == 0) {
-            bool w = true;
-            if (j == 0) w = mbar_wait(bar_q, 0, abort_flag);
-            w = w && mbar_wait(bar_k, ph, abort_flag);
-            if (w) {
-                tcgen05_fence_after();
-                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + OFF_Q));
-                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_K));
+            for (int i = 0; i < 4; ++i) {
+                const int key = j * TK + lane * 4 + i;
+                float m = -INFINITY;
+                if (key < p.S) {
+                    const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + key] : 0.f;
+                    if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+                }
+                mask_s[st * TK + lane * 4 + i] = m;
+            }
+            mbar_arrive(&m_full[st]);
+        }
+        if (!ok && lane == 0) {
+            for (int i = 0; i < 64; ++i) nanosleep(10000);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            const int nwg = two ? 2 : 1;
+            auto issue_s = [&](int wg, int st) {
+                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q + wg * TILE_BYTES));
+                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K + st * TILE_BYTES));
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    umma_f16_ss(tmem_base + TMEM_S, a_desc + 2u * k, b_desc + 2u * k, p.idesc_qk, k != 0 ? 1u : 0u);
-                umma_commit(bar_s);
+                    umma_f16_ss(tmem_base + wg * 128, a_desc + 2u * k, b_desc + 2u * k, p.idesc_qk, k != 0 ? 1u : 0u);
+                umma_commit(&s_full[wg]);
+            };
+            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+            if (ok) {
+                tcgen05_fence_after();
+                for (int wg = 0; wg < nwg; ++wg) issue_s(wg, 0);
+                umma_commit(&k_empty[0]);
+            }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = static_cast<uint32_t>(j) & 1u;
+                const uint32_t ph_st = (static_cast<uint32_t>(j) >> 1) & 1u;
+                for (int wg = 0; ok && wg < nwg; ++wg) {
+                    if (!mbar_wait(&p_full[wg], ph, abort_flag)) { ok = false; break; }
+                    if (wg == 0 && !mbar_wait(&v_full[st], ph_st, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&o_empty[wg], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int k = 0; k < TK / 16; ++k) {
+                        const uint64_t a_desc =
+                            make_smem_desc_sw128(smem_u32(smem + PP_OFF_P + wg * 2 * TILE_BYTES + (k >> 2) * TILE_BYTES)) +
+                            2u * (k & 3);
+                        const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V + st * TILE_BYTES + k * 2048));
+                        umma_f16_ss(tmem_base + 256 + wg * 64, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&o_full[wg]);
+                    if (wg == nwg - 1) umma_commit(&v_empty[st]);
+                    if (j + 1 < n_tiles) {
+                        if (wg == 0 && !mbar_wait(&k_full[st ^ 1], ((static_cast<uint32_t>(j + 1)) >> 1) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tcgen05_fence_after();
+                        issue_s(wg, st ^ 1);   // this warpgroup has finished reading its previous scores (p_full)
+                        if (wg == nwg - 1) umma_commit(&k_empty[st ^ 1]);
+                    }
+                }
             }
         }
-        if (j + 1 < n_tiles) write_mask(j + 1);
-        if (!mbar_wait(bar_s, ph, abort_flag)) { ok = false; break; }
-        __syncwarp();  // tcgen05.ld is warp-collective: lane 0 took a longer path through the issue block
-        tcgen05_fence_after();
-        if (tid == 0 && j + 1 < n_tiles) {  // K tile is free again: fetch the next one under the softmax
-            mbar_expect_tx(bar_k, TILE_BYTES);
-            tma_load_3d(smem + OFF_K, &tm_k, bar_k, head * HD, (j + 1) * TK, b);
-        }
-
-        // ---- online softmax on row `tid`
-        const float* mrow = mask_s + (j & 1) * TK;
-        float tmax = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < TK / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_S + c * 32, r);
-            tmem_ld_wait(r);
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax warpgroups
+        const int wg = (warp - 2) >> 2;
+        const int r_in_tile = ((warp & 3) << 5) + lane;          // TMEM lane = query row of the tile
+        const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t t_s = tmem_base + lane_field + wg * 128;
+        const uint32_t t_o = tmem_base + lane_field + 256 + wg * 64;
+        uint8_t* p_base = smem + PP_OFF_P + wg * 2 * TILE_BYTES;
+        if (wg == 0 || two) {
+            float o[HD];
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                tmax = fmaxf(tmax, fmaf(__uint_as_float(r[i]), p.scale_log2, mrow[c * 32 + i]));
-        }
-        const float m_new = fmaxf(m_run, tmax);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m_run - m_use);
-        float psum = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < TK / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_S + c * 32, r);
-            tmem_ld_wait(r);
-            float pv[32];
+            for (int i = 0; i < HD; ++i) o[i] = 0.f;
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = static_cast<uint32_t>(j) & 1u;
+                if (!mbar_wait(&m_full[st], (static_cast<uint32_t>(j) >> 1) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&s_full[wg], ph, abort_flag)) { ok = false; break; }
+                __syncwarp();
+                tcgen05_fence_after();
+                const float* mrow = mask_s + st * TK;
+                // Two sweeps over the 128 scores of this row (max, then exp / sum / P), 32 columns at a time, software
+                // pipelined: the TMEM load of the next 32 columns is in flight while the current 32 are processed.
+                float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (latency)
+                float ps[4] = {0.f, 0.f, 0.f, 0.f};
+                float m_new = m_run, m_use = 0.f, alpha = 1.f;
+                auto work = [&](const int i, uint32_t (&r)[32]) {
+                    const int c = i & 3;
+                    if (i < 4) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                pv[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mrow[c * 32 + i]) - m_use);
-                psum += pv[i];
-            }
-            // P[row tid][keys c*32 .. c*32+31] -> swizzled K-major tile: 16-byte chunk index ^= (row & 7)
-            uint8_t* prow = smem + OFF_P + (c >> 1) * TILE_BYTES + tid * 128;
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
+                            tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
+                            tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
+                            tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
+                            tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                        }
+                        if (i == 3) {
+                            m_new = fmaxf(m_run, fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3])));
+                            m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                            alpha = fast_exp2(m_run - m_use);
+                        }
+                    } else {
+                        float pv[32];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                uint4 qv;
-                qv.x = pack2(pv[g * 8 + 0], pv[g * 8 + 1], p.dtype);
-                qv.y = pack2(pv[g * 8 + 2], pv[g * 8 + 3], p.dtype);
-                qv.z = pack2(pv[g * 8 + 4], pv[g * 8 + 5], p.dtype);
-                qv.w = pack2(pv[g * 8 + 6], pv[g * 8 + 7], p.dtype);
-                const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
-                *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
-            }
-        }
-        l_run = l_run * alpha + psum;
-        m_run = m_new;
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
+                            pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
+                            pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
+                            pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
+                            pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                        }
+#pragma unroll
+                        for (int q4 = 0; q4 < 32; q4 += 4) {
+                            ps[0] += pv[q4];
+                            ps[1] += pv[q4 + 1];
+                            ps[2] += pv[q4 + 2];
+                            ps[3] += pv[q4 + 3];
+                        }
+                        uint8_t* prow = p_base + (c >> 1) * TILE_BYTES + r_in_tile * 128;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 qv;
+                            qv.x = pack2t<DT>(pv[g * 8 + 0], pv[g * 8 + 1]);
+                            qv.y = pack2t<DT>(pv[g * 8 + 2], pv[g * 8 + 3]);
+                            qv.z = pack2t<DT>(pv[g * 8 + 4], pv[g * 8 + 5]);
+                            qv.w = pack2t<DT>(pv[g * 8 + 6], pv[g * 8 + 7]);
+                            const int chunk = ((c & 1) * 4 + g) ^ (r_in_tile & 7);
+                            *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
+                        }
+                    }
+                };
+                {
+                    uint32_t ra[32], rb[32];
+                    tmem_ld_32x32b_x32(t_s, ra);
+                    tmem_ld_wait(ra);
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        tmem_ld_32x32b_x32(t_s + ((i + 1) & 3) * 32, rb);
+                        work(i, ra);
+                        tmem_ld_wait(rb);
+                        if (i + 2 < 8) tmem_ld_32x32b_x32(t_s + ((i + 2) & 3) * 32, ra);
+                        work(i + 1, rb);
+                        if (i + 2 < 8) tmem_ld_wait(ra);
+                    }
+                }
+                const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+                l_run = l_run * alpha + psum;
+                m_run = m_new;
+                fence_async_proxy_shared();   // P visible to the UMMA
+                tcgen05_fence_before();       // this thread's reads of S are done
+                mbar_arrive(&p_full[wg]);
 
-        fence_async_proxy_shared();   // P (generic-proxy stores) must be visible to the UMMA (async proxy)
-        tcgen05_fence_before();
-        __syncthreads();
-
-        // ---- O_j = P V
-        if (tid == 0) {
-            tcgen05_fence_after();
-            if (mbar_wait(bar_v, ph, abort_flag)) {
+                if (!mbar_wait(&o_full[wg], ph, abort_flag)) { ok = false; break; }
+                __syncwarp();
                 tcgen05_fence_after();
 #pragma unroll
-                for (int k = 0; k < TK / 16; ++k) {
-                    const uint64_t a_desc =
-                        make_smem_desc_sw128(smem_u32(smem + OFF_P + (k >> 2) * TILE_BYTES)) + 2u * (k & 3);
-                    // V rows are keys: 16 keys = 2 groups of 8 rows = 2048 bytes per UMMA step
-                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + OFF_V + k * 2048));
-                    umma_f16_ss(tmem_base + TMEM_O, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_o + c * 32, r);
+                    tmem_ld_wait(r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
                 }
-                umma_commit(bar_o);
+                tcgen05_fence_before();
+                mbar_arrive(&o_empty[wg]);
+            }
+            const int q = q0 + wg * TQ + r_in_tile;
+            if (ok && q < p.S) {
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                uint16_t* dst =
+                    reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + q) * p.ldo + head * HD;
+#pragma unroll
+                for (int g = 0; g < HD / 8; ++g) {
+                    uint4 qv;
+                    qv.x = pack2t<DT>(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
+                    qv.y = pack2t<DT>(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+                    qv.z = pack2t<DT>(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
+                    qv.w = pack2t<DT>(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+                    *reinterpret_cast<uint4*>(dst + g * 8) = qv;
+                }
             }
         }
-        if (!mbar_wait(bar_o, ph, abort_flag)) { ok = false; break; }
-        __syncwarp();
-        tcgen05_fence_after();
-        if (tid == 0 && j + 1 < n_tiles) {  // V tile is free again
-            mbar_expect_tx(bar_v, TILE_BYTES);
-            tma_load_3d(smem + OFF_V, &tm_v, bar_v, head * HD, (j + 1) * TK, b);
-        }
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_field + TMEM_O + c * 32, r);
-            tmem_ld_wait(r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
-        }
-        // The next iteration's UMMAs overwrite S (after the next bar_k wait, issued by tid 0 only after it has itself
-        // passed this point) and O/P (after the next __syncthreads), so TMEM reads above are ordered before them.
-        tcgen05_fence_before();
-    }
-
-    if (ok) {
-        const int q = q0 + tid;
-        if (q < p.S) {
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;  // every key excluded and no kv_len given: zeros
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + q) * p.ldo + head * HD;
-#pragma unroll
-            for (int g = 0; g < HD / 8; ++g) {
-                uint4 qv;
-                qv.x = pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv, p.dtype);
-                qv.y = pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv, p.dtype);
-                qv.z = pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv, p.dtype);
-                qv.w = pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv, p.dtype);
-                *reinterpret_cast<uint4*>(dst + g * 8) = qv;
-            }
-        }
-    } else if (tid == 0) {
-        for (int i = 0; i < 64; ++i) nanosleep(10000);  // let copies in flight land before shared memory is released
     }
 
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 1) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem_base, ATTN_TMEM_COLS);
+        tmem_dealloc(tmem_base, PP_TMEM_COLS);
     }
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
 }
@@ -294,6 +385,7 @@ constexpr int S1_OFF_BAR = S1_OFF_MASK + TK * 4;
 constexpr int S1_SMEM = S1_OFF_BAR + 64;
 constexpr int S1_TMEM_COLS = 128;
 
+template <int DT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -402,7 +494,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tcgen05_fence_after();
         float l_sum = 0.f;
         {
-            float tmax = -INFINITY;
+            float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (latency)
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 uint32_t r[32];
@@ -411,12 +503,13 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
-                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
-                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
-                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
-                    tmax = fmaxf(tmax, fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                    tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
+                    tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
+                    tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
+                    tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
                 }
             }
+            const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
             const float m_use = (tmax == -INFINITY) ? 0.f : tmax;
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
@@ -432,16 +525,25 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
                     pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
                 }
+                {
+                    float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < 32; ++i) l_sum += pv[i];
+                    for (int i = 0; i < 32; i += 4) {
+                        ps[0] += pv[i];
+                        ps[1] += pv[i + 1];
+                        ps[2] += pv[i + 2];
+                        ps[3] += pv[i + 3];
+                    }
+                    l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+                }
                 uint8_t* prow = sbase + (c >> 1) * TILE_BYTES + tid * 128;   // P overlays Q (keys 0..63), K (64..127)
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     uint4 qv;
-                    qv.x = pack2(pv[g * 8 + 0], pv[g * 8 + 1], p.dtype);
-                    qv.y = pack2(pv[g * 8 + 2], pv[g * 8 + 3], p.dtype);
-                    qv.z = pack2(pv[g * 8 + 4], pv[g * 8 + 5], p.dtype);
-                    qv.w = pack2(pv[g * 8 + 6], pv[g * 8 + 7], p.dtype);
+                    qv.x = pack2t<DT>(pv[g * 8 + 0], pv[g * 8 + 1]);
+                    qv.y = pack2t<DT>(pv[g * 8 + 2], pv[g * 8 + 3]);
+                    qv.z = pack2t<DT>(pv[g * 8 + 4], pv[g * 8 + 5]);
+                    qv.w = pack2t<DT>(pv[g * 8 + 6], pv[g * 8 + 7]);
                     const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
                     *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
                 }
@@ -478,10 +580,10 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     uint4 qv;
-                    qv.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv, p.dtype);
-                    qv.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv, p.dtype);
-                    qv.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv, p.dtype);
-                    qv.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv, p.dtype);
+                    qv.x = pack2t<DT>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+                    qv.y = pack2t<DT>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+                    qv.z = pack2t<DT>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+                    qv.w = pack2t<DT>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
                     const int chunk = (c * 4 + g) ^ (tid & 7);
                     *reinterpret_cast<uint4*>(orow + chunk * 16) = qv;
                 }
@@ -560,8 +662,10 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         if (!to) return B200_ERR_DRIVER;
         static bool attr1_set[64] = {false};
         if (dev >= 0 && dev < 64 && !attr1_set[dev]) {
-            if (cudaFuncSetAttribute(attention_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S1_SMEM) !=
-                cudaSuccess)
+            if (cudaFuncSetAttribute(attention_single_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     S1_SMEM) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     S1_SMEM) != cudaSuccess)
                 return B200_ERR_LAUNCH;
             attr1_set[dev] = true;
         }
@@ -570,20 +674,35 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long grid1 = items < 2ll * sms ? items : 2ll * sms;   // two persistent CTAs per SM
-        attention_single_kernel<<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
-                                  static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p, static_cast<int>(items));
+        if (d->dtype == B200_F16)
+            attention_single_kernel<B200_F16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
+                                                static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p,
+                                                                                      static_cast<int>(items));
+        else
+            attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
+                                                 static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p,
+                                                                                       static_cast<int>(items));
         count_launch();
         return check_launch();
     }
 
     static bool attr_set[64] = {false};
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PP_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PP_SMEM) != cudaSuccess)
             return B200_ERR_LAUNCH;
         attr_set[dev] = true;
     }
-    dim3 grid(static_cast<unsigned>((d->S + TQ - 1) / TQ), static_cast<unsigned>(d->heads), static_cast<unsigned>(d->B));
-    attention_kernel<<<grid, kAttnThreads, ATTN_SMEM, static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, p);
+    dim3 grid(static_cast<unsigned>((d->S + 2 * TQ - 1) / (2 * TQ)), static_cast<unsigned>(d->heads),
+              static_cast<unsigned>(d->B));
+    if (d->dtype == B200_F16)
+        attention_pingpong_kernel<B200_F16><<<grid, PP_THREADS, PP_SMEM, static_cast<cudaStream_t>(stream_)>>>(*tq, *tk,
+                                                                                                             *tv, p);
+    else
+        attention_pingpong_kernel<B200_BF16><<<grid, PP_THREADS, PP_SMEM, static_cast<cudaStream_t>(stream_)>>>(
+            *tq, *tk, *tv, p);
     count_launch();
     return check_launch();
 }
@@ -628,9 +747,14 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
         g_static_kv_len_ptr[dev] = ptr;
     }
     if (!g_static_attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S1_SMEM) !=
-                cudaSuccess ||
-            cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) {
+        if (cudaFuncSetAttribute(attention_single_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 S1_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 S1_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PP_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PP_SMEM) != cudaSuccess) {
             cudaGetLastError();
             return B200_ERR_LAUNCH;
         }
@@ -674,12 +798,19 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long grid1 = items < 2ll * sms ? items : 2ll * sms;
-        attention_single_kernel<<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
-            tq, tk, tv, to, p, static_cast<int>(items));
+        if (d->dtype == B200_F16)
+            attention_single_kernel<B200_F16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
+                tq, tk, tv, to, p, static_cast<int>(items));
+        else
+            attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
+                tq, tk, tv, to, p, static_cast<int>(items));
     } else {
-        dim3 grid(static_cast<unsigned>((d->S + TQ - 1) / TQ), static_cast<unsigned>(d->heads),
+        dim3 grid(static_cast<unsigned>((d->S + 2 * TQ - 1) / (2 * TQ)), static_cast<unsigned>(d->heads),
                   static_cast<unsigned>(d->B));
-        attention_kernel<<<grid, kAttnThreads, ATTN_SMEM, stream>>>(tq, tk, tv, p);
+        if (d->dtype == B200_F16)
+            attention_pingpong_kernel<B200_F16><<<grid, PP_THREADS, PP_SMEM, stream>>>(tq, tk, tv, p);
+        else
+            attention_pingpong_kernel<B200_BF16><<<grid, PP_THREADS, PP_SMEM, stream>>>(tq, tk, tv, p);
     }
     count_launch();
     return check_launch();

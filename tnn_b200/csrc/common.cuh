@@ -32,6 +32,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int dtype) {
         return *reinterpret_cast<uint32_t*>(&h);
     }
 }
+// Compile-time variant: with the dtype as a run-time value the compiler emits both conversions and a select.
+template <int DT>
+__device__ __forceinline__ uint32_t pack2t(float a, float b) {
+    if (DT == B200_F16) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+}
 __device__ __forceinline__ float2 unpack2(uint32_t u, int dtype) {
     if (dtype == B200_F16) {
         return __half22float2(*reinterpret_cast<__half2*>(&u));

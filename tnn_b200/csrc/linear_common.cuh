@@ -211,6 +211,20 @@ struct WarpEpilogue {
         for (int e = 0; e < 8; ++e) v[e] += r[e];
     }
 
+    // 32 fp32 values of this thread's row -> half precision -> the row's 64 bytes of the strip (64-byte swizzle)
+    template <int DT>
+    __device__ __forceinline__ void stage_chunk(const float (&v)[32], uint8_t* srow) const {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint4 q;
+            q.x = pack2t<DT>(v[g * 8 + 0], v[g * 8 + 1]);
+            q.y = pack2t<DT>(v[g * 8 + 2], v[g * 8 + 3]);
+            q.z = pack2t<DT>(v[g * 8 + 4], v[g * 8 + 5]);
+            q.w = pack2t<DT>(v[g * 8 + 6], v[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(srow + ((g ^ ((lane >> 1) & 3)) << 4)) = q;
+        }
+    }
+
     // Drain this warp's part of one accumulator: rows = the warp's 32 TMEM lanes (thread = row `row`), columns
     // [col_first, col_first + 32*CHUNKS) of the tile whose first global column is n_tile0.  `tacc` is the TMEM address
     // of the accumulator's column 0 with this warp's lane offset already applied.  Returns false if a wait ran out.
@@ -308,15 +322,8 @@ struct WarpEpilogue {
                     if (lane == 0) tma_store_wait_read<0>();
                     __syncwarp();
                 }
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 q;
-                    q.x = pack2(v[g * 8 + 0], v[g * 8 + 1], p.out_dtype);
-                    q.y = pack2(v[g * 8 + 2], v[g * 8 + 3], p.out_dtype);
-                    q.z = pack2(v[g * 8 + 4], v[g * 8 + 5], p.out_dtype);
-                    q.w = pack2(v[g * 8 + 6], v[g * 8 + 7], p.out_dtype);
-                    *reinterpret_cast<uint4*>(srow + ((g ^ ((lane >> 1) & 3)) << 4)) = q;
-                }
+                if (p.out_dtype == B200_F16) stage_chunk<B200_F16>(v, srow);   // warp-uniform branch, specialised bodies
+                else stage_chunk<B200_BF16>(v, srow);
                 fence_async_proxy_shared();
                 __syncwarp();
                 if (lane == 0) {
