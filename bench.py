@@ -415,12 +415,16 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "pinned fp32 host buffers, copies double-buffered on side streams, wall clock"},
             "gpu_launches": launches,
-            "roofline": {"bound": "tensor", "kernel": "linear_kernel (projection/FFN GEMM, tcgen05)",
+            "roofline": {"bound": "tensor", "kernel": "linear_pair_kernel (projection/FFN GEMM, tcgen05 cta_group::2)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": "of " + peaks["source"] + " (burst)",
                          "peak_sustained": peaks["tflops_sustained"],
                          "flops_per_launch_avg": gemm_flops / n_gemm, "ms_per_launch_avg": gemm_ms / n_gemm,
-                         "launches_timed": n_gemm, "per_shape": per_shape, "traffic": None},
+                         "launches_timed": n_gemm, "per_shape": per_shape,
+                         "traffic": ncu_traffic_per_launch(B, per_shape),
+                         "traffic_note": "DRAM read+write bytes per launch from one ncu capture per GEMM shape "
+                                         "(profiles/linear_pair_kernel_config2_shapes.md), averaged over the shapes "
+                                         "captured; equals the operand bytes, outputs stay in L2"},
             "attention_sweep": attention_sweep,
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
                                  "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
@@ -434,6 +438,18 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of linear_pair_kernel, from ncu captures of the GEMM shapes
+# of the default workload (batch 64 x seq 128: M = 8192).  The figures belong to that M only.
+NCU_DRAM_BYTES_M8192 = {"qkv": 16.16e6 + 0.69e6, "ffn1": 17.34e6 + 3.41e6, "ffn2": 67.73e6 + 3.61e6}
+
+
+def ncu_traffic_per_launch(batch, per_shape):
+    if batch != BATCH_PER_GPU:
+        return None
+    vals = [NCU_DRAM_BYTES_M8192[k] for k in per_shape if k in NCU_DRAM_BYTES_M8192]
+    return sum(vals) / len(vals) if vals else None
 
 
 def main():
