@@ -203,6 +203,7 @@ def run_ours(args):
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
     enc = Encoder.from_workload(wl, torch.float16, dev, fold_layernorm=args.fold_layernorm)
+    enc.layernorm_in_gemm = args.layernorm_in_gemm
     x_dev = torch.from_numpy(wl.x).to(dev)
     mask_dev = torch.from_numpy(wl.mask_add.reshape(B, SEQ)).to(dev).contiguous()
     kv_len = ops.mask_to_kv_len(mask_dev)
@@ -338,14 +339,22 @@ def run_ours(args):
                                                   epilogue=ops.EPI_BIAS_RESIDUAL))
             h = timed("layernorm", lambda: ops.add_layernorm(t2, L["ln2_g"], L["ln2_b"], cfg.ln_eps))
 
+    # The host needs ~20 us per launch-plus-two-events, the kernels 10-35 us: issued naively, the event pairs would time
+    # the host.  Each instrumented step is therefore queued behind a spin kernel that holds the stream for a few
+    # milliseconds, so that all its launches and events are already in the queue when the GPU reaches them and every
+    # event pair spans exactly one kernel on the device (launch gap included).
+    def hold_stream():
+        torch.cuda._sleep(int(12e6))          # ~6 ms of GPU clock cycles
+
     for _ in range(2):
         instrumented_step()
     torch.cuda.synchronize()
     for k in ev_pairs:
         ev_pairs[k].clear()
     for _ in range(min(args.steps, 20)):
+        hold_stream()
         instrumented_step()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
     kernel_ms = {k: [a.elapsed_time(b2) for a, b2 in v] for k, v in ev_pairs.items()}
     gemm_flops = gemm_ms = 0.0
     per_shape = {}
@@ -408,7 +417,9 @@ def run_ours(args):
                        "batch_per_gpu": B, "seq_len": SEQ, "layers": len(enc.layers),
                        "parallelism": "independent replicas, batch-sharded, no collective",
                        "launch": "CUDA graph of one Forward" if graph is not None else "eager launches",
-                       "layernorm": "folded into the GEMM epilogues" if enc.fold else "separate kernels",
+                       "layernorm": ("folded into the GEMM epilogues" if enc.fold else
+                                     ("inside the launch of the producing GEMM" if enc.layernorm_in_gemm else
+                                      "separate kernels")),
                        "l2": "per-step working set (170 MB fp16 weights + activations) exceeds the 126 MB L2; "
                              "no explicit flush"},
             "clocks": clocks,
@@ -463,6 +474,9 @@ def main():
     ap.add_argument("--no-attention-sweep", action="store_true")
     ap.add_argument("--fold-layernorm", action="store_true",
                     help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
+    ap.add_argument("--layernorm-in-gemm", action="store_true",
+                    help="run each LayerNorm inside the launch of the GEMM that feeds it (5 launches per layer "
+                         "instead of 7; measured slower at this size)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
                                                             "a captured CUDA graph of one Forward")
     args = ap.parse_args()

@@ -15,8 +15,9 @@ from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
 pytestmark = pytest.mark.gpu
 
 
-def _run(wl, dtype, single_call=True, fold=True):
+def _run(wl, dtype, single_call=True, fold=True, layernorm_in_gemm=False):
     enc = Encoder.from_workload(wl, dtype, fold_layernorm=fold)
+    enc.layernorm_in_gemm = layernorm_in_gemm
     x = torch.from_numpy(wl.x).cuda()
     m = torch.from_numpy(wl.mask_add).cuda()
     y = enc.forward(x, m) if single_call else enc.forward_ops(x, m)
@@ -45,6 +46,20 @@ def test_single_call_equals_layer_by_layer(cuda_device, fold):
     wl = golden_workload(**CASES["base_2layer_ragged"])
     a = _run(wl, torch.float16, single_call=True, fold=fold)
     b = _run(wl, torch.float16, single_call=False, fold=fold)
+    assert np.array_equal(a, b)
+
+
+def test_layernorm_in_gemm_launch_equals_separate_launches(cuda_device):
+    """b200_encoder_fwd with the LayerNorms inside the producing GEMM launches (5 launches per layer) against the
+    same stack with separate LayerNorm launches (7): the arithmetic is the same, so is every bit."""
+    for case in ("base_2layer_ragged", "large_1layer_s96"):
+        wl = golden_workload(**CASES[case])
+        a = _run(wl, torch.float16, fold=False)
+        b = _run(wl, torch.float16, fold=False, layernorm_in_gemm=True)
+        assert np.array_equal(a, b)
+    wl = model_synth.config_workload(2, batch=16, num_layers=2)
+    a = _run(wl, torch.float16, fold=False)
+    b = _run(wl, torch.float16, fold=False, layernorm_in_gemm=True)
     assert np.array_equal(a, b)
 
 

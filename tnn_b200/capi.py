@@ -31,7 +31,9 @@ class LinearDesc(_c.Structure):
                 ("dtype", _i32), ("out_dtype", _i32), ("epilogue", _i32), ("block_n", _i32),
                 ("out_stats", _vp), ("ln_in_stats", _vp), ("ln_c1", _vp), ("ln_c2", _vp),
                 ("res_ln_stats", _vp), ("res_ln_gamma", _vp), ("res_ln_beta", _vp),
-                ("ln_eps", _f32), ("reserved_", _i32)]
+                ("ln_eps", _f32), ("reserved_", _i32),
+                ("post_ln_gamma", _vp), ("post_ln_beta", _vp), ("post_ln_out", _vp), ("post_ln_ld", _i64),
+                ("post_ln_sync", _vp)]
 
 
 class AttentionDesc(_c.Structure):
@@ -47,6 +49,14 @@ class LayerNormDesc(_c.Structure):
                 ("rows", _i64), ("H", _i64),
                 ("ldx", _i64), ("ldr", _i64), ("ldy", _i64),
                 ("in_dtype", _i32), ("out_dtype", _i32), ("eps", _f32)]
+
+
+PHASE_LINEAR, PHASE_ADD_LAYERNORM = 0, 1
+CHAIN_MAX_PHASES, CHAIN_MAX_LINEAR = 8, 4
+
+
+class ChainPhase(_c.Structure):
+    _fields_ = [("kind", _i32), ("reserved_", _i32), ("linear", LinearDesc), ("layernorm", LayerNormDesc)]
 
 
 class EncoderLayerWeights(_c.Structure):
@@ -75,6 +85,8 @@ SYMBOLS = {
     "b200_attention_masked_fwd_static": (_c.c_int, [_c.POINTER(AttentionDesc), _vp]),
     "b200_mask_to_kv_len": (_c.c_int, [_vp, _i64, _i64, _f32, _vp, _vp]),
     "b200_add_layernorm_fwd": (_c.c_int, [_c.POINTER(LayerNormDesc), _vp]),
+    "b200_chain_sync_bytes": (_c.c_size_t, [_i64, _i32]),
+    "b200_chain_fwd": (_c.c_int, [_c.POINTER(ChainPhase), _i32, _vp, _vp]),
     "b200_encoder_workspace_bytes": (_c.c_size_t, [_i64, _i64, _i64, _c.c_int]),
     "b200_encoder_fwd": (_c.c_int, [_c.POINTER(EncoderDesc), _vp]),
     "b200_status_string": (_c.c_char_p, [_c.c_int]),

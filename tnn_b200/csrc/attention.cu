@@ -143,6 +143,8 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -430,6 +432,8 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+    pdl_launch_dependents();
+    pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
 
     auto load_item = [&](int item, int set) {   // tid 0 only
         const int bb = item / p.heads, hh = item % p.heads;
@@ -674,14 +678,13 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long grid1 = items < 2ll * sms ? items : 2ll * sms;   // two persistent CTAs per SM
+        const cudaStream_t st = static_cast<cudaStream_t>(stream_);
         if (d->dtype == B200_F16)
-            attention_single_kernel<B200_F16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
-                                                static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p,
-                                                                                      static_cast<int>(items));
+            launch_kernel(attention_single_kernel<B200_F16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
+                          S1_SMEM, st, *tq, *tk, *tv, *to, p, static_cast<int>(items));
         else
-            attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM,
-                                                 static_cast<cudaStream_t>(stream_)>>>(*tq, *tk, *tv, *to, p,
-                                                                                       static_cast<int>(items));
+            launch_kernel(attention_single_kernel<B200_BF16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
+                          S1_SMEM, st, *tq, *tk, *tv, *to, p, static_cast<int>(items));
         count_launch();
         return check_launch();
     }
@@ -698,11 +701,11 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
     dim3 grid(static_cast<unsigned>((d->S + 2 * TQ - 1) / (2 * TQ)), static_cast<unsigned>(d->heads),
               static_cast<unsigned>(d->B));
     if (d->dtype == B200_F16)
-        attention_pingpong_kernel<B200_F16><<<grid, PP_THREADS, PP_SMEM, static_cast<cudaStream_t>(stream_)>>>(*tq, *tk,
-                                                                                                             *tv, p);
+        launch_kernel(attention_pingpong_kernel<B200_F16>, grid, dim3(PP_THREADS), PP_SMEM,
+                      static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
     else
-        attention_pingpong_kernel<B200_BF16><<<grid, PP_THREADS, PP_SMEM, static_cast<cudaStream_t>(stream_)>>>(
-            *tq, *tk, *tv, p);
+        launch_kernel(attention_pingpong_kernel<B200_BF16>, grid, dim3(PP_THREADS), PP_SMEM,
+                      static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
     count_launch();
     return check_launch();
 }

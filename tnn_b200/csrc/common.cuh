@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/tnn_b200.h"
 
 namespace b200 {
@@ -69,5 +71,29 @@ bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint6
                        const uint32_t* box, int swizzle_bytes = 128);
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH; }
+
+// ---------------------------------------------------------------- launches
+// Every kernel of the library is launched with programmatic stream serialization allowed: its CTAs may be placed while
+// the previous kernel of the stream drains, run their set-up, and block in griddepcontrol.wait until that kernel has
+// completed (each kernel calls it before its first access to global memory other than constants).  This hides launch
+// latency and prologues between the seven short kernels of an encoder layer.  TNN_B200_PDL=0 in the environment
+// turns the attribute off (plain stream order), for comparison.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace b200

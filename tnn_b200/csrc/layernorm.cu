@@ -2,6 +2,7 @@
 // the one-time weight pre-pack (fp32 [K,N] -> half [N,K]) and the mask -> kv_len reduction.
 // All are plain coalesced 16-byte-vector kernels; their roofline is HBM bandwidth.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 namespace {
@@ -47,6 +48,8 @@ template <int NV>
 __global__ void __launch_bounds__(256) add_layernorm_kernel(B200LayerNormDesc d) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     if (warp >= d.rows) return;
     const long long row = warp;
     const int groups = static_cast<int>(d.H >> 3);
@@ -158,11 +161,14 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
     };
     const float inv_h = 1.0f / static_cast<float>(d.H);
     long long row = warp0;
-    if (row < d.rows) fetch(row);   // the first row's loads are in flight while gamma/beta are staged
+    // gamma/beta are constants: they are staged while the producer of x may still be running
+    pdl_launch_dependents();
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
         *reinterpret_cast<float4*>(gb + i) = __ldg(reinterpret_cast<const float4*>(d.gamma + i));
         *reinterpret_cast<float4*>(gb + H + i) = __ldg(reinterpret_cast<const float4*>(d.beta + i));
     }
+    pdl_wait();
+    if (row < d.rows) fetch(row);
     __syncthreads();
     for (; row < d.rows; row += nwarps) {
         float v[NV][8];
@@ -224,6 +230,8 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
 __global__ void __launch_bounds__(256) convert_kernel(const void* src, int sdt, void* dst, int ddt, long long n8,
                                                       long long n) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    pdl_launch_dependents();
+    pdl_wait();
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
         float v[8];
         load8(src, i * 8, sdt, v);
@@ -348,17 +356,17 @@ int b200_add_layernorm_fwd(const B200LayerNormDesc* d, b200_stream_t stream_) {
         const unsigned g2 = static_cast<unsigned>(blocks);
         const size_t sm = static_cast<size_t>(d->H) * 2 * sizeof(float);
         if (nv <= 1) {
-            if (f32) add_layernorm_rows_kernel<1, true><<<g2, 256, sm, stream>>>(*d);
-            else add_layernorm_rows_kernel<1, false><<<g2, 256, sm, stream>>>(*d);
+            if (f32) launch_kernel(add_layernorm_rows_kernel<1, true>, dim3(g2), dim3(256), sm, stream, *d);
+            else launch_kernel(add_layernorm_rows_kernel<1, false>, dim3(g2), dim3(256), sm, stream, *d);
         } else if (nv <= 3) {
-            if (f32) add_layernorm_rows_kernel<3, true><<<g2, 256, sm, stream>>>(*d);
-            else add_layernorm_rows_kernel<3, false><<<g2, 256, sm, stream>>>(*d);
+            if (f32) launch_kernel(add_layernorm_rows_kernel<3, true>, dim3(g2), dim3(256), sm, stream, *d);
+            else launch_kernel(add_layernorm_rows_kernel<3, false>, dim3(g2), dim3(256), sm, stream, *d);
         } else {
-            if (f32) add_layernorm_rows_kernel<4, true><<<g2, 256, sm, stream>>>(*d);
-            else add_layernorm_rows_kernel<4, false><<<g2, 256, sm, stream>>>(*d);
+            if (f32) launch_kernel(add_layernorm_rows_kernel<4, true>, dim3(g2), dim3(256), sm, stream, *d);
+            else launch_kernel(add_layernorm_rows_kernel<4, false>, dim3(g2), dim3(256), sm, stream, *d);
         }
-    } else if (nv <= 8) add_layernorm_kernel<8><<<grid, 256, 0, stream>>>(*d);
-    else add_layernorm_kernel<16><<<grid, 256, 0, stream>>>(*d);
+    } else if (nv <= 8) launch_kernel(add_layernorm_kernel<8>, dim3(grid), dim3(256), 0, stream, *d);
+    else launch_kernel(add_layernorm_kernel<16>, dim3(grid), dim3(256), 0, stream, *d);
     count_launch();
     return check_launch();
 }
@@ -372,8 +380,8 @@ int b200_convert(const void* src, int sdt, void* dst, int ddt, int64_t n, b200_s
     long long blocks = (n8 + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    convert_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(src, sdt, dst, ddt,
-                                                                                                   n8, n);
+    launch_kernel(convert_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream_),
+                  src, sdt, dst, ddt, n8, n);
     count_launch();
     return check_launch();
 }

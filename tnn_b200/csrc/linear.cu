@@ -66,6 +66,8 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();   // inputs come from earlier kernels; the output may still be read by one
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -240,7 +242,7 @@ int launch_linear_t(const B200LinearDesc& d, cudaStream_t stream, int sm_count) 
         attr_set[dev] = true;
     }
     const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-    linear_kernel<BN, STAGES, FOLD><<<grid, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, p);
+    launch_kernel(linear_kernel<BN, STAGES, FOLD>, dim3(grid), dim3(kThreads), C::SMEM_BYTES, stream, *tx, *tw, *ty, p);
     count_launch();
     return check_launch();
 }
@@ -258,10 +260,10 @@ struct TileChoice {
     bool pair;
     int bn;
 };
-TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
+TileChoice choose_tile(int64_t M, int64_t N, int sm_count, bool pair_only = false) {
     TileChoice best = {false, 128};
     double best_t = 1e300;
-    if (M > 128) {
+    if (M > 128 || pair_only) {
         const int bns[4] = {256, 192, 128, 64};
         const double cost[4] = {1.0, 1.03, 1.10, 1.40};
         for (int i = 0; i < 4; ++i) {
@@ -278,7 +280,7 @@ TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
     }
     const int bns1[3] = {256, 128, 64};
     const double cost1[3] = {1.35, 1.50, 1.90};
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 3 && !pair_only; ++i) {
         const int64_t tiles = ((M + BM - 1) / BM) * ((N + bns1[i] - 1) / bns1[i]);
         const int64_t waves = (tiles + sm_count - 1) / sm_count;
         const double t = static_cast<double>(waves) * (bns1[i] * cost1[i] + 16.0);
@@ -290,12 +292,7 @@ TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
     return best;
 }
 
-}  // namespace lin
-}  // namespace b200
-
-extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
-    using namespace b200;
-    using namespace b200::lin;
+int validate_linear_desc(const B200LinearDesc* d) {
     if (!d || !d->x || !d->w_nk || !d->y) return B200_ERR_PARAM;
     if (d->M <= 0 || d->N <= 0 || d->K <= 0) return B200_ERR_PARAM;
     if (d->M > (1ll << 30) || d->N > (1ll << 30) || d->K > (1ll << 30)) return B200_ERR_UNSUPPORTED;
@@ -312,15 +309,37 @@ extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
     if (d->ln_in_stats && (!d->ln_c1 || !d->ln_c2)) return B200_ERR_PARAM;
     if (d->res_ln_stats && (!d->res_ln_gamma || !d->res_ln_beta || d->epilogue != B200_EPI_BIAS_RESIDUAL))
         return B200_ERR_PARAM;
+    if (d->post_ln_out) {
+        if (!d->post_ln_gamma || !d->post_ln_beta || !d->post_ln_sync) return B200_ERR_PARAM;
+        if (d->out_dtype != d->dtype || d->N > 1024) return B200_ERR_UNSUPPORTED;
+        if ((d->post_ln_ld % 8) || d->post_ln_ld < d->N || !aligned16(d->post_ln_out)) return B200_ERR_PARAM;
+        if (!aligned16(d->post_ln_gamma) || !aligned16(d->post_ln_beta)) return B200_ERR_PARAM;
+        if (reinterpret_cast<uintptr_t>(d->post_ln_sync) & 3u) return B200_ERR_PARAM;
+        if (d->out_stats || d->ln_in_stats || d->res_ln_stats) return B200_ERR_UNSUPPORTED;
+    }
+    return B200_OK;
+}
+
+}  // namespace lin
+}  // namespace b200
+
+extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
+    using namespace b200;
+    using namespace b200::lin;
+    const int valid = validate_linear_desc(d);
+    if (valid != B200_OK) return valid;
     const int sms = device_sm_count();
     if (sms <= 0) return B200_ERR_NOT_SM100;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     TileChoice tc;
+    const bool post_ln = wants_post_ln(*d);
     if (d->block_n == 0) {
-        tc = choose_tile(d->M, d->N, sms);
+        tc = choose_tile(d->M, d->N, sms, post_ln);
+        if (post_ln && !tc.pair) return B200_ERR_UNSUPPORTED;
     } else if (d->block_n > 0) {
-        tc = {d->M > 128, d->block_n};
+        tc = {d->M > 128 || post_ln, d->block_n};
     } else {
+        if (post_ln) return B200_ERR_UNSUPPORTED;
         tc = {false, -d->block_n};
     }
     if (tc.pair) {

@@ -32,6 +32,13 @@ struct LinearParams {
     const float* res_ln_beta;
     float ln_eps;
     int k_slots, n_slots;   // ceil(K/32), ceil(N/32)
+    // LayerNorm of the output rows in the same launch (pair kernel, LN template flag): null ln_out = off
+    void* ln_out;
+    const float* ln_gamma;
+    const float* ln_beta;
+    long long ld_ln;
+    int* ln_sync;           // one counter per 256-row block
+    int ln_rows_per_tile;   // rows of a block normalised by the pair that owns tile n of it (multiple of 16)
 };
 
 
@@ -132,6 +139,10 @@ struct WarpEpilogue {
     static constexpr int kPrefetchSlots = FOLD ? 24 : 1;
     float2 pf[kPrefetchSlots];
     long long pf_row = -1;
+    // RES kernels only: a kernel that runs several GEMMs in one launch switches the residual path per GEMM (`res_on`);
+    // bit s of `rpar` is the phase parity of strip s's residual barrier (it flips with every residual tile received).
+    uint32_t rpar = 0;
+    bool res_on = true;
 
     __device__ __forceinline__ bool ln_in() const { return FOLD && p.ln_in_stats != nullptr; }
     __device__ __forceinline__ bool res_ln() const { return FOLD && p.res_ln_stats != nullptr; }
@@ -175,7 +186,7 @@ struct WarpEpilogue {
     }
     // Call before waiting for the accumulator: overlaps the first residual load with the tile's mainloop.
     __device__ __forceinline__ void begin_tile(int n_first, int row0) {
-        if (RES && chunk_valid(0, n_first, row0)) issue_residual(cc, n_first, row0);
+        if (RES && res_on && chunk_valid(0, n_first, row0)) issue_residual(cc, n_first, row0);
         if (!FOLD) return;
         const long long row = static_cast<long long>(row0) + lane;
         const bool have_pf = pf_row == row && row < p.M;
@@ -241,7 +252,7 @@ struct WarpEpilogue {
             const int col0 = col_first + c * 32;
             const int n0 = n_tile0 + col0;
             const bool next_valid = chunk_valid(c + 1, n_first, row0);
-            if (RES && next_valid) issue_residual(cc + 1, n0 + 32, row0);
+            if (RES && res_on && next_valid) issue_residual(cc + 1, n0 + 32, row0);
             tmem_ld_wait(r);
             float v[32];
 #pragma unroll
@@ -277,8 +288,9 @@ struct WarpEpilogue {
             const uint32_t si = cc % NSTRIPS;
             uint8_t* strip = strips + si * kStageBytesPerWarp;
             uint8_t* srow = strip + lane * 64;
-            if (RES) {
-                if (!mbar_wait(rbars + si, (cc / NSTRIPS) & 1u, abort_flag)) return false;
+            if (RES && res_on) {
+                if (!mbar_wait(rbars + si, (rpar >> si) & 1u, abort_flag)) return false;
+                rpar ^= 1u << si;
                 __syncwarp();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -317,9 +329,10 @@ struct WarpEpilogue {
                     }
                 }
             } else {
-                if (!RES) {
-                    // the previous store of this warp must have finished reading the strip
-                    if (lane == 0) tma_store_wait_read<0>();
+                if (!(RES && res_on)) {
+                    // the previous store of this warp from this strip must have finished reading it (with a residual
+                    // the wait sits in issue_residual)
+                    if (lane == 0) tma_store_wait_read<NSTRIPS - 1>();
                     __syncwarp();
                 }
                 if (p.out_dtype == B200_F16) stage_chunk<B200_F16>(v, srow);   // warp-uniform branch, specialised bodies
@@ -337,10 +350,125 @@ struct WarpEpilogue {
     }
 };
 
+// LayerNorm of `nrows` consecutive rows (from row0, rows >= M skipped) of a half-precision matrix by one warp, two rows
+// at a time so that their loads are in flight together.  The arithmetic and its order are those of
+// add_layernorm_rows_kernel (layernorm.cu): fp32 sum -> mean, fp32 sum of squared deviations -> 1/sqrt(var + eps).
+// x may have been written by other SMs during this launch, so it is read through L2 (ld.global.cg), never through the
+// non-coherent path.  NV = 16-byte groups per lane: H <= NV * 256, H % 8 == 0.
+template <int NV>
+__device__ __forceinline__ void layernorm_rows_warp(const void* x, long long ldx, void* y, long long ldy,
+                                                    const float* gamma, const float* beta, int H, float eps, int dtype,
+                                                    long long row0, int nrows, int M, int lane) {
+    const int groups = H >> 3;
+    const float inv_h = 1.0f / static_cast<float>(H);
+    const uint16_t* xin = reinterpret_cast<const uint16_t*>(x);
+    uint16_t* yout = reinterpret_cast<uint16_t*>(y);
+#pragma unroll 1
+    for (int b2 = 0; b2 < nrows; b2 += 2) {
+        uint4 raw[2][NV];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const long long row = row0 + b2 + r;
+#pragma unroll
+            for (int g = 0; g < NV; ++g) {
+                const int gi = g * 32 + lane;
+                if (b2 + r < nrows && row < M && gi < groups)
+                    raw[r][g] = __ldcg(reinterpret_cast<const uint4*>(xin + row * ldx + gi * 8));
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const long long row = row0 + b2 + r;
+            if (b2 + r >= nrows || row >= M) continue;   // uniform across the warp
+            float v[NV][8];
+            float sum = 0.f;
+#pragma unroll
+            for (int g = 0; g < NV; ++g) {
+                const int gi = g * 32 + lane;
+                if (gi < groups) {
+                    const uint32_t w[4] = {raw[r][g].x, raw[r][g].y, raw[r][g].z, raw[r][g].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = unpack2(w[e], dtype);
+                        v[g][2 * e] = f.x;
+                        v[g][2 * e + 1] = f.y;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sum += v[g][e];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float mean = sum * inv_h;
+            float sq = 0.f;
+#pragma unroll
+            for (int g = 0; g < NV; ++g) {
+                const int gi = g * 32 + lane;
+                if (gi < groups) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float c = v[g][e] - mean;
+                        sq += c * c;
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            const float rstd = 1.0f / sqrtf(sq * inv_h + eps);
+#pragma unroll
+            for (int g = 0; g < NV; ++g) {
+                const int gi = g * 32 + lane;
+                if (gi < groups) {
+                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + gi * 8));
+                    const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + gi * 8 + 4));
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + gi * 8));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + gi * 8 + 4));
+                    const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                    float o[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[e] + bt[e];
+                    uint4 q;
+                    q.x = pack2(o[0], o[1], dtype);
+                    q.y = pack2(o[2], o[3], dtype);
+                    q.z = pack2(o[4], o[5], dtype);
+                    q.w = pack2(o[6], o[7], dtype);
+                    *reinterpret_cast<uint4*>(yout + row * ldy + gi * 8) = q;
+                }
+            }
+        }
+    }
+}
+
+// Row-block completion counters in global memory (release / acquire at gpu scope), used where CTAs of one launch
+// exchange rows: one warp adds 1 when its part of a row block is in memory; readers poll, bounded.
+__device__ __forceinline__ int load_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void add_release(int* p) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p) : "memory");
+}
+constexpr uint32_t kDepPollLimit = 1u << 21;
+__device__ __forceinline__ bool wait_rows(const int* ctr, int target, volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < kDepPollLimit; ++i) {
+        if (load_acquire(ctr) >= target) return true;
+        if (i > 16) nanosleep(200);
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+
 // CTA-pair kernel (linear_pair.cu).  BN in {64, 128, 192, 256}.
 template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count);
+int device_sm_count();   // SMs of the current device, <= 0 if it is not an sm_100 GPU
+// Argument checks of b200_linear_fwd (pointers, alignment, leading dimensions, epilogue consistency).
+int validate_linear_desc(const B200LinearDesc* d);
 inline bool wants_fold(const B200LinearDesc& d) { return d.out_stats || d.ln_in_stats || d.res_ln_stats; }
+inline bool wants_post_ln(const B200LinearDesc& d) { return d.post_ln_out != nullptr; }
 // Number of CTA pairs of the pair kernel that can be co-resident on the current device (cached; 0 if unknown).
 int max_active_pairs(int bn);
 

@@ -11,87 +11,29 @@
 //                 tcgen05.mma.cta_group::2 (256 x BN x 16) and commits, multicast to both CTAs' `empty` / `acc_full`.
 //   warps 2..9  : epilogue of this CTA's 128 rows (its own TMEM), then arrive on the leader's `acc_empty`.
 // Every wait is bounded; the two CTAs meet at a cluster barrier before either releases TMEM or exits.
-#include "linear_common.cuh"
+#include "pair.cuh"
 
 namespace b200 {
 namespace lin {
 
 namespace {
 
-template <int BN, bool RES, bool FOLD>
-struct PairCfg {
-    static constexpr int A_BYTES = 128 * BK * 2;          // this CTA's 128 rows of x
-    static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this CTA's BN/2 rows of w
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    // output staging strips (TMA store); with RES two per warp, which also receive the residual tile (TMA load)
-    static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * strips_per_warp<RES>();
-    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * vec_strips<FOLD>() * (BN / 2) * 4;   // + barriers + bias strips
-    static constexpr int STAGES = (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES > 8
-                                      ? 8 : (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES;
-    static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFFSET = OUT_OFFSET + OUT_BYTES;
-    static constexpr int BIAS_OFFSET = BAR_OFFSET + 512;
-    static constexpr int SMEM_BYTES = OUT_OFFSET + TAIL_BYTES + 1024;
-    static constexpr int TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512);   // two accumulators of BN columns
-};
+// Phase timestamps per CTA for performance work: compiled in only with -DB200_TRACE (never in the shipped library).
+#ifdef B200_TRACE
+__device__ unsigned long long g_trace[512][16];
+#define TRACE_MARK(i)                                                      \
+    do {                                                                   \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 512) {                 \
+            unsigned long long t_;                                         \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));         \
+            g_trace[blockIdx.x][i] = t_;                                   \
+        }                                                                  \
+    } while (0)
+#else
+#define TRACE_MARK(i)
+#endif
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address of the same shared-memory object in the pair's leader CTA (cluster rank 0): the shared::cta address of a
-// CTA in a cluster carries its rank in bit 24.
-__device__ __forceinline__ uint32_t leader_addr(const void* p) { return smem_u32(p) & 0xFEFFFFFFu; }
-
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int32_t c0,
-                                                 int32_t c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// One arrival on the barrier at this shared-memory offset in both CTAs of the pair once all UMMAs issued so far are done.
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
-    const uint16_t mask = 3;
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(smem_u32(bar)), "h"(mask)
-        : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
-    asm volatile(
-        "{\n\t.reg .b32 remote;\n\t"
-        "mapa.shared::cluster.u32 remote, %0, 0;\n\t"
-        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}\n"
-        ::"r"(smem_u32(bar))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
-template <int BN, bool RES, bool FOLD>
+template <int BN, bool RES, bool FOLD, bool LN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_r,
@@ -116,6 +58,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const bool leader = rank == 0;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    if (warp == 0) TRACE_MARK(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -141,6 +84,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     cluster_sync_all();   // the peer's barriers are initialised and its TMEM allocated before anything is signalled
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (warp == 0) TRACE_MARK(1);
+    pdl_launch_dependents();
+    pdl_wait();   // x, the residual and the statistics come from earlier kernels; y may still be read by one
+    if (warp == 0) TRACE_MARK(2);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -182,6 +129,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     const uint32_t s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    if (it == 0) TRACE_MARK(3);
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
                     const uint64_t a_desc = make_smem_desc_sw128(a_addr);
@@ -192,6 +140,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     umma_commit_pair(&empty[s]);
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
+                TRACE_MARK(4);   // last value: all UMMAs of the CTA pair issued
             }
         }
         __syncwarp();
@@ -226,6 +175,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             stage_vectors<FOLD>(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();
+            if (ew == 0) {
+                if (tcount == 0) TRACE_MARK(5);   // first accumulator complete
+                TRACE_MARK(6);                    // last value: last accumulator complete
+            }
             tcgen05_fence_after();
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             if (!epi.template run<COLS>(vec_w, tacc, row, n_blk * BN, half * COLS)) { ok = false; break; }
@@ -235,9 +188,32 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 if (leader) mbar_arrive(&acc_empty[buf]);
                 else mbar_arrive_leader(&acc_empty[buf]);
             }
+            if (LN) {
+                // This warp's part of the tile is in memory -> count it; when all 16 warps of all tiles of the row
+                // block have counted, normalise this warp's rows of the block.  The tiles of one row block belong to
+                // different pairs (the launcher keeps #pairs >= tiles per block) and every pair counts before it
+                // waits, so the wait cannot be circular.
+                int ready = 0;
+                if (lane == 0) {
+                    tma_store_wait_all<0>();
+                    add_release(p.ln_sync + m_blk);
+                    ready = wait_rows(p.ln_sync + m_blk, p.num_n_tiles * 2 * kEpiWarps, abort_flag) ? 1 : 0;
+                }
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (!ready) { ok = false; break; }
+                const int per_warp = p.ln_rows_per_tile / (2 * kEpiWarps);
+                const int part0 = n_blk * p.ln_rows_per_tile;                       // first row of this tile's share
+                const int mine = part0 + (static_cast<int>(rank) * kEpiWarps + ew) * per_warp;
+                int nrows = min(per_warp, 256 - mine);
+                if (nrows > 0)
+                    layernorm_rows_warp<4>(p.y, p.ldy, p.ln_out, p.ld_ln, p.ln_gamma, p.ln_beta, p.N, p.ln_eps, p.dtype,
+                                           static_cast<long long>(m_blk) * 256 + mine, nrows, p.M, lane);
+            }
         }
+        if (ew == 0) TRACE_MARK(7);               // last tile drained (stores issued)
         if (lane == 0) tma_store_wait_all<0>();   // this warp's tile stores have left shared memory and landed
         __syncwarp();
+        if (ew == 0) TRACE_MARK(8);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -249,11 +225,18 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 1u);
+    if (warp == 0) TRACE_MARK(9);
 }
 
 }  // namespace
 
-template <int BN, bool RES, bool FOLD>
+#ifdef B200_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_debug_trace(unsigned long long* host) {
+    return cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+template <int BN, bool RES, bool FOLD, bool LN = false>
 int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     using C = PairCfg<BN, RES, FOLD>;
     static_assert(C::STAGES >= 3, "pipeline too shallow");
@@ -310,12 +293,19 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     p.ln_eps = d.ln_eps;
     p.k_slots = (p.K + 31) / 32;
     p.n_slots = (p.N + 31) / 32;
+    p.ln_out = d.post_ln_out;
+    p.ln_gamma = d.post_ln_gamma;
+    p.ln_beta = d.post_ln_beta;
+    p.ld_ln = d.post_ln_ld;
+    p.ln_sync = static_cast<int*>(d.post_ln_sync);
+    // 256 rows of a block shared out over its tiles, in units of 16 rows (one per consumer warp of the pair)
+    p.ln_rows_per_tile = ((256 + p.num_n_tiles - 1) / p.num_n_tiles + 15) / 16 * 16;
 
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES, FOLD, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::SMEM_BYTES) != cudaSuccess)
             return B200_ERR_LAUNCH;
         attr_set[dev] = true;
@@ -323,7 +313,9 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     int pairs = max_active_pairs(BN);   // (the RES variant uses no more shared memory per CTA than its stage count allows)
     if (pairs <= 0) pairs = sm_count / 2;
     if (p.num_tiles < pairs) pairs = p.num_tiles;
-    linear_pair_kernel<BN, RES, FOLD><<<2 * pairs, kThreads, C::SMEM_BYTES, stream>>>(*tx, *tw, *ty, *tr, p);
+    if (LN && pairs < p.num_n_tiles) return B200_ERR_UNSUPPORTED;   // the tiles of a row block need distinct owners
+    launch_kernel(linear_pair_kernel<BN, RES, FOLD, LN>, dim3(2 * pairs), dim3(kThreads), C::SMEM_BYTES, stream, *tx, *tw,
+                  *ty, *tr, p);
     count_launch();
     return check_launch();
 }
@@ -334,7 +326,7 @@ int query_pairs(int sm_count) {
     // A persistent grid must not exceed what is co-resident: a pair that cannot be placed (GPCs with an odd number
     // of free SMs) would otherwise run as a second wave after the first has finished all the work.
     using C = PairCfg<BN, false, false>;
-    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -351,7 +343,7 @@ int query_pairs(int sm_count) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false, false>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false, false, false>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -380,6 +372,11 @@ template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     // The TMA residual path needs 16-byte aligned residual rows (checked by the caller) and a half-precision residual.
     const bool fold = wants_fold(d);
+    if (wants_post_ln(d)) {
+        if (fold) return B200_ERR_UNSUPPORTED;
+        if (d.epilogue == B200_EPI_BIAS_RESIDUAL) return launch_pair<BN, true, false, true>(d, stream, sm_count);
+        return launch_pair<BN, false, false, true>(d, stream, sm_count);
+    }
     if (d.epilogue == B200_EPI_BIAS_RESIDUAL)
         return fold ? launch_pair<BN, true, true>(d, stream, sm_count) : launch_pair<BN, true, false>(d, stream, sm_count);
     return fold ? launch_pair<BN, false, true>(d, stream, sm_count) : launch_pair<BN, false, false>(d, stream, sm_count);

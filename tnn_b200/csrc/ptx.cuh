@@ -66,6 +66,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void fence_async_proxy_shared() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders this thread's generic-proxy accesses (all state spaces) and the async proxy (TMA) against each other.
+__device__ __forceinline__ void fence_async_proxy_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -193,5 +195,15 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
 }
 
 __device__ __forceinline__ void nanosleep(uint32_t ns) { asm volatile("nanosleep.u32 %0;" ::"r"(ns)); }
+
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream
+// is still running; `pdl_wait` blocks until every predecessor grid has completed and its memory is visible, so a
+// kernel does its own set-up (barrier init, TMEM allocation, descriptor prefetch, constant staging) first and calls it
+// before touching anything a predecessor may have written or may still read.  `pdl_launch_dependents` tells the
+// scheduler that the successor may be started as soon as resources free up.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 }  // namespace b200

@@ -1,6 +1,7 @@
 // Host-side runtime of the kernel library: the per-device status word, the tensor-map cache, the launch counter and
 // the small housekeeping entry points of the C ABI.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -14,6 +15,14 @@ __device__ unsigned int g_device_status = 0;
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+    static const bool on = []() {
+        const char* e = std::getenv("TNN_B200_PDL");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
 
 static constexpr int kMaxDevices = 64;
 static unsigned int* g_status_addr[kMaxDevices] = {nullptr};
