@@ -86,6 +86,15 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     if (warp == 0) TRACE_MARK(1);
     pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        // The weights are constants: while the previous kernel of the stream drains, the grid brings them from HBM
+        // into L2 (every CTA a share of the (k-block, BN/2-row) boxes), so that the first wave of tiles does not pay
+        // the HBM latency on its critical path.
+        const int row_boxes = (p.N + BN / 2 - 1) / (BN / 2);
+        const int boxes = p.num_k_blocks * row_boxes;
+        for (int b = blockIdx.x; b < boxes; b += gridDim.x)
+            tma_prefetch_l2_2d(&tm_w, (b % p.num_k_blocks) * BK, (b / p.num_k_blocks) * (BN / 2));
+    }
     pdl_wait();   // x, the residual and the statistics come from earlier kernels; y may still be read by one
     if (warp == 0) TRACE_MARK(2);
 
@@ -211,7 +220,8 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
         }
         if (ew == 0) TRACE_MARK(7);               // last tile drained (stores issued)
-        if (lane == 0) tma_store_wait_all<0>();   // this warp's tile stores have left shared memory and landed
+        // this warp's tile stores have read their strips; the writes themselves are complete when the grid is
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         if (ew == 0) TRACE_MARK(8);
     }
