@@ -11,6 +11,8 @@
 //           additive key mask is applied in registers, excluded keys get weight exactly 0 (exp2(-inf)), P is written
 //           to shared memory as half precision in the swizzled K-major layout the second UMMA reads.
 // Algorithmic work per launch: 4 * S^2 * 64 * heads * B flop (QK^T and PV); HBM bytes: Q, K, V read once per CTA, O written.
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -74,6 +76,7 @@ constexpr int PP_OFF_MASK = 10 * TILE_BYTES;         // 2 stages x 128 floats
 constexpr int PP_OFF_BAR = PP_OFF_MASK + 2 * TK * 4;
 constexpr int PP_SMEM = PP_OFF_BAR + 256;
 constexpr int PP_TMEM_COLS = 512;
+constexpr float kLazyLog2 = 8.0f;   // the running maximum moves only when a tile exceeds it by more than 2^8
 
 template <int DT>
 __global__ void __launch_bounds__(PP_THREADS, 1)
@@ -94,6 +97,7 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* mask_s = reinterpret_cast<float*>(smem + PP_OFF_MASK);
+    volatile uint32_t* plain_s = reinterpret_cast<uint32_t*>(bars + 24);   // [2] per stage: every key valid, mask 0
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -168,6 +172,7 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 mbar_expect_tx(&v_full[st], TILE_BYTES);
                 tma_load_3d(smem + PP_OFF_V + st * TILE_BYTES, &tm_v, &v_full[st], head * HD, j * TK, b);
             }
+            bool zero = true;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = j * TK + lane * 4 + i;
@@ -177,7 +182,11 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                     if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
                 }
                 mask_s[st * TK + lane * 4 + i] = m;
+                zero = zero && m == 0.f;
             }
+            // a "plain" tile (all 128 keys valid, additive mask 0) lets the softmax skip the mask altogether
+            const bool plain_tile = __all_sync(0xffffffffu, zero) && p.scale_log2 > 0.f;
+            if (lane == 0) plain_s[st] = plain_tile ? 1u : 0u;
             mbar_arrive(&m_full[st]);
         }
         if (!ok && lane == 0) {
@@ -210,7 +219,6 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 for (int wg = 0; ok && wg < nwg; ++wg) {
                     if (!mbar_wait(&p_full[wg], ph, abort_flag)) { ok = false; break; }
                     if (wg == 0 && !mbar_wait(&v_full[st], ph_st, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(&o_empty[wg], ph ^ 1u, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
 #pragma unroll
                     for (int k = 0; k < TK / 16; ++k) {
@@ -218,7 +226,8 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                             make_smem_desc_sw128(smem_u32(smem + PP_OFF_P + wg * 2 * TILE_BYTES + (k >> 2) * TILE_BYTES)) +
                             2u * (k & 3);
                         const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V + st * TILE_BYTES + k * 2048));
-                        umma_f16_ss(tmem_base + 256 + wg * 64, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);
+                        // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must)
+                        umma_f16_ss(tmem_base + 256 + wg * 64, a_desc, b_desc, p.idesc_pv, (j | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(&o_full[wg]);
                     if (wg == nwg - 1) umma_commit(&v_empty[st]);
@@ -244,9 +253,6 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const uint32_t t_o = tmem_base + lane_field + 256 + wg * 64;
         uint8_t* p_base = smem + PP_OFF_P + wg * 2 * TILE_BYTES;
         if (wg == 0 || two) {
-            float o[HD];
-#pragma unroll
-            for (int i = 0; i < HD; ++i) o[i] = 0.f;
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_tiles; ++j) {
@@ -257,36 +263,79 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 __syncwarp();
                 tcgen05_fence_after();
                 const float* mrow = mask_s + st * TK;
+                const bool plain_tile = plain_s[st] != 0u;
                 // Two sweeps over the 128 scores of this row (max, then exp / sum / P), 32 columns at a time, software
                 // pipelined: the TMEM load of the next 32 columns is in flight while the current 32 are processed.
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (latency)
                 float ps[4] = {0.f, 0.f, 0.f, 0.f};
-                float m_new = m_run, m_use = 0.f, alpha = 1.f;
-                auto work = [&](const int i, uint32_t (&r)[32]) {
+                float m_new = m_run, m_use = 0.f, alpha = 1.f, neg_m = 0.f;
+                bool wait_ok = true;
+                auto work = [&](auto plain_c, const int i, uint32_t (&r)[32]) {
+                    constexpr bool plain = decltype(plain_c)::value;   // compile-time inside each sweep instance
                     const int c = i & 3;
                     if (i < 4) {
+                        if (plain) {
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
-                            tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
-                            tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
-                            tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
-                            tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                            for (int g = 0; g < 8; ++g) {
+                                tmx[0] = fmaxf(tmx[0], __uint_as_float(r[g * 4 + 0]));
+                                tmx[1] = fmaxf(tmx[1], __uint_as_float(r[g * 4 + 1]));
+                                tmx[2] = fmaxf(tmx[2], __uint_as_float(r[g * 4 + 2]));
+                                tmx[3] = fmaxf(tmx[3], __uint_as_float(r[g * 4 + 3]));
+                            }
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
+                                tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
+                                tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
+                                tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
+                                tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                            }
                         }
                         if (i == 3) {
-                            m_new = fmaxf(m_run, fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3])));
+                            float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
+                            if (plain) tmax *= p.scale_log2;   // = max of the scaled scores: the scale is positive
+                            // Lazy reference maximum: it only moves when the tile's maximum exceeds it by more than
+                            // 2^kLazyLog2 (weights stay <= 2^kLazyLog2, exact in half precision and harmless in the
+                            // fp32 sums), so most tiles leave the output accumulator in TMEM untouched.
+                            const bool move = tmax > m_run + kLazyLog2;
+                            m_new = move ? tmax : m_run;
                             m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                            alpha = fast_exp2(m_run - m_use);
+                            neg_m = -m_use;
+                            alpha = move ? fast_exp2(m_run - m_use) : 1.f;
+                            // PV of the previous tile must be complete: it reads the P buffer the second sweep
+                            // overwrites, and it writes the accumulator a rescale would touch.
+                            if (j > 0) wait_ok = mbar_wait(&o_full[wg], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
+                            __syncwarp();
+                            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                                tcgen05_fence_after();
+#pragma unroll
+                                for (int cc = 0; cc < HD / 32; ++cc) {
+                                    uint32_t ro[32];
+                                    tmem_ld_32x32b_x32(t_o + cc * 32, ro);
+                                    tmem_ld_wait(ro);
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
+                                    tmem_st_32x32b_x32(t_o + cc * 32, ro);
+                                }
+                                tmem_st_wait();
+                            }
                         }
                     } else {
                         float pv[32];
+                        if (plain) {
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
-                            pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
-                            pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
-                            pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
-                            pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                            for (int e = 0; e < 32; ++e)
+                                pv[e] = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
+                                pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
+                                pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
+                                pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
+                                pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                            }
                         }
 #pragma unroll
                         for (int q4 = 0; q4 < 32; q4 += 4) {
@@ -308,54 +357,55 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                         }
                     }
                 };
-                {
+                auto sweep = [&](auto plain_c) {
                     uint32_t ra[32], rb[32];
                     tmem_ld_32x32b_x32(t_s, ra);
                     tmem_ld_wait(ra);
 #pragma unroll
                     for (int i = 0; i < 8; i += 2) {
                         tmem_ld_32x32b_x32(t_s + ((i + 1) & 3) * 32, rb);
-                        work(i, ra);
+                        work(plain_c, i, ra);
                         tmem_ld_wait(rb);
                         if (i + 2 < 8) tmem_ld_32x32b_x32(t_s + ((i + 2) & 3) * 32, ra);
-                        work(i + 1, rb);
+                        work(plain_c, i + 1, rb);
                         if (i + 2 < 8) tmem_ld_wait(ra);
                     }
-                }
+                };
+                if (plain_tile) sweep(std::true_type{});
+                else sweep(std::false_type{});
+                if (!wait_ok) { ok = false; break; }
                 const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
                 l_run = l_run * alpha + psum;
                 m_run = m_new;
                 fence_async_proxy_shared();   // P visible to the UMMA
-                tcgen05_fence_before();       // this thread's reads of S are done
+                tcgen05_fence_before();       // this thread's reads of S and its rescale of O are done
                 mbar_arrive(&p_full[wg]);
-
-                if (!mbar_wait(&o_full[wg], ph, abort_flag)) { ok = false; break; }
-                __syncwarp();
-                tcgen05_fence_after();
+            }
+            // the last PV
+            if (ok && n_tiles > 0 && !mbar_wait(&o_full[wg], static_cast<uint32_t>(n_tiles - 1) & 1u, abort_flag)) ok = false;
+            __syncwarp();
+            tcgen05_fence_after();
+            const int q = q0 + wg * TQ + r_in_tile;
+            if (ok) {   // warp-uniform: the TMEM loads are collective
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                uint16_t* dst =
+                    reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + q) * p.ldo + head * HD;
 #pragma unroll
                 for (int c = 0; c < HD / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(t_o + c * 32, r);
                     tmem_ld_wait(r);
+                    if (q < p.S) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
-                }
-                tcgen05_fence_before();
-                mbar_arrive(&o_empty[wg]);
-            }
-            const int q = q0 + wg * TQ + r_in_tile;
-            if (ok && q < p.S) {
-                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-                uint16_t* dst =
-                    reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + q) * p.ldo + head * HD;
-#pragma unroll
-                for (int g = 0; g < HD / 8; ++g) {
-                    uint4 qv;
-                    qv.x = pack2t<DT>(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
-                    qv.y = pack2t<DT>(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
-                    qv.z = pack2t<DT>(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
-                    qv.w = pack2t<DT>(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + g * 8) = qv;
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 qv;
+                            qv.x = pack2t<DT>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+                            qv.y = pack2t<DT>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+                            qv.z = pack2t<DT>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+                            qv.w = pack2t<DT>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = qv;
+                        }
+                    }
                 }
             }
         }
@@ -472,7 +522,10 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
             mask_s[tid] = m;   // the previous item's softmax finished before its closing __syncthreads
         }
-        __syncthreads();
+        // "Plain" item: every key of the chunks that are computed is valid with additive mask 0 (the common case: a
+        // full-length sequence, or all tiles below a ragged sequence's end).  The softmax then needs no mask reads and
+        // can take the row maximum of the raw scores (the scale is positive).
+        const bool plain = __syncthreads_and(tid >= n_chunks * 32 || mask_s[tid] == 0.f) != 0 && p.scale_log2 > 0.f;
 
         if (tid == 0) {
             // Prefetch the next item into the other set; that set's last reader is the output store of the previous
@@ -504,30 +557,47 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
                 tmem_ld_wait(r);
+                if (plain) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
-                    tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
-                    tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
-                    tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
-                    tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                    for (int g = 0; g < 8; ++g) {
+                        tmx[0] = fmaxf(tmx[0], __uint_as_float(r[g * 4 + 0]));
+                        tmx[1] = fmaxf(tmx[1], __uint_as_float(r[g * 4 + 1]));
+                        tmx[2] = fmaxf(tmx[2], __uint_as_float(r[g * 4 + 2]));
+                        tmx[3] = fmaxf(tmx[3], __uint_as_float(r[g * 4 + 3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
+                        tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
+                        tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
+                        tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
+                        tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
+                    }
                 }
             }
-            const float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
+            float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
+            if (plain) tmax *= p.scale_log2;   // fma(s, scale, 0) = s * scale exactly, and the scale is positive
             const float m_use = (tmax == -INFINITY) ? 0.f : tmax;
+            const float neg_m = -m_use;
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
                 tmem_ld_wait(r);
                 float pv[32];
+                if (plain) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
-                    pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
-                    pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
-                    pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
-                    pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                    for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 mk = *reinterpret_cast<const float4*>(mask_s + c * 32 + g * 4);
+                        pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
+                        pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
+                        pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
+                        pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
+                    }
                 }
                 {
                     float ps[4] = {0.f, 0.f, 0.f, 0.f};
