@@ -8,8 +8,9 @@
 //   UMMA  : S = Q K^T (128 x 128 x 64, both operands K-major) and O = P V (128 x 64 x 128, P K-major from shared
 //           memory, V MN-major exactly as TMA delivered it), fp32 accumulation in TMEM.
 //   softmax: thread t owns query row t (TMEM lane t), so row max / row sum are in-thread; scores are scaled, the
-//           additive key mask is applied in registers, excluded keys get weight exactly 0 (exp2(-inf)), P is written
-//           to shared memory as half precision in the swizzled K-major layout the second UMMA reads.
+//           additive key mask is applied in registers, excluded keys get weight exactly 0 (exp2(-inf)); P goes to the
+//           second UMMA as half precision — through swizzled shared memory in the single-tile kernel, through tensor
+//           memory in the long-sequence kernel.
 // Algorithmic work per launch: 4 * S^2 * 64 * heads * B flop (QK^T and PV); HBM bytes: Q, K, V read once per CTA, O written.
 #include <type_traits>
 
@@ -25,6 +26,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// Timestamps of the first CTA's hand-offs for performance work: compiled in only with -DB200_TRACE.
+#ifdef B200_TRACE
+__device__ unsigned long long g_attn_trace[3][32][8];   // [role: wg0, wg1, mma][tile][event]
+#define ATTN_MARK(role, tile, ev)                                                                 \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) {               \
+            unsigned long long t_;                                                                \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                \
+            g_attn_trace[role][tile][ev] = t_;                                                    \
+        }                                                                                         \
+    } while (0)
+#else
+#define ATTN_MARK(role, tile, ev)
+#endif
 
 constexpr int TQ = 128;   // queries per CTA
 constexpr int TK = 128;   // keys per tile
@@ -59,22 +75,26 @@ struct AttnParams {
 // Long sequences: two 128-query tiles per CTA, processed by two softmax warpgroups in ping-pong, so that the tensor
 // pipe works on one tile's QK^T / PV while the other tile is in its softmax, and every K/V tile is loaded once for
 // 256 queries.  Roles (320 threads, one CTA per SM):
-//   warp 0      : producer — lane 0 issues the TMA loads (Q tiles once, then K/V tiles through a 2-stage ring); all 32
-//                 lanes write the tile's key mask (log2 units, -inf = dropped) next to it;
-//   warp 1      : one lane issues every UMMA: S_w = Q_w K^T into TMEM columns [128w, 128w+128), O_w = P_w V into
-//                 [256+64w, 256+64w+64), in the order S0 S1 | PV0 S0' | PV1 S1' | ... so that a warpgroup's next
-//                 scores are already on their way while it rescales its output;
+//   warp 0      : producer — lane 0 issues the TMA loads (Q tiles once, then K/V tiles through a 4-stage ring); all 32
+//                 lanes write the tile's key mask (log2 units, -inf = dropped) next to it and flag "plain" tiles;
+//   warp 1      : one lane issues every UMMA, per warpgroup w and key tile j in the order S_w(j+1), then P_w V(j):
+//                 S_w = Q_w K^T (both operands from shared memory) into TMEM columns [128w, 128w+128);
+//                 O_w += P_w V with P_w read from TMEM columns [384+64w, +64) and V from shared memory, accumulated
+//                 over all key tiles in TMEM columns [256+64w, +64);
 //   warps 2..5  : softmax warpgroup 0 (query rows q0 .. q0+127), warps 6..9: warpgroup 1 (q0+128 .. q0+255);
-//                 thread = row, running max / sum / output in registers, P_w written to shared memory for the UMMA.
-// All hand-offs are mbarriers with bounded waits (no named barriers: a role that gives up cannot strand another).
+//                 thread = row: a max sweep over the 128 scores, then an exp sweep that writes P_w back to TMEM as
+//                 packed half precision.  The running maximum is lazy: it only moves when a tile exceeds it by more
+//                 than 2^8, and only then is O_w rescaled in place (tcgen05.ld / st); the row sum follows along.
+// TMEM: 512 columns = 2 x (S 128 + O 64 + P 64).  All hand-offs are mbarriers with bounded waits (no named barriers:
+// a role that gives up cannot strand another).
 constexpr int PP_THREADS = 320;
 constexpr int PP_OFF_Q = 0;                          // 2 x 16 KB
-constexpr int PP_OFF_K = 2 * TILE_BYTES;             // 2 stages
-constexpr int PP_OFF_V = 4 * TILE_BYTES;             // 2 stages
-constexpr int PP_OFF_P = 6 * TILE_BYTES;             // 2 warpgroups x 32 KB
-constexpr int PP_OFF_MASK = 10 * TILE_BYTES;         // 2 stages x 128 floats
-constexpr int PP_OFF_BAR = PP_OFF_MASK + 2 * TK * 4;
-constexpr int PP_SMEM = PP_OFF_BAR + 256;
+constexpr int PP_NST = 4;                            // K/V/mask ring depth (key tiles in flight)
+constexpr int PP_OFF_K = 2 * TILE_BYTES;
+constexpr int PP_OFF_V = PP_OFF_K + PP_NST * TILE_BYTES;
+constexpr int PP_OFF_MASK = PP_OFF_V + PP_NST * TILE_BYTES;   // PP_NST x 128 floats
+constexpr int PP_OFF_BAR = PP_OFF_MASK + PP_NST * TK * 4;
+constexpr int PP_SMEM = PP_OFF_BAR + 512;
 constexpr int PP_TMEM_COLS = 512;
 constexpr float kLazyLog2 = 8.0f;   // the running maximum moves only when a tile exceeds it by more than 2^8
 
@@ -85,19 +105,18 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_OFF_BAR);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;    // [2]
-    uint64_t* v_full = bars + 3;    // [2]
-    uint64_t* k_empty = bars + 5;   // [2]
-    uint64_t* v_empty = bars + 7;   // [2]
-    uint64_t* m_full = bars + 9;    // [2] mask of the stage written (32 arrivals)
-    uint64_t* s_full = bars + 11;   // [2] per warpgroup
-    uint64_t* p_full = bars + 13;   // [2] (128 arrivals)
-    uint64_t* o_full = bars + 15;   // [2]
-    uint64_t* o_empty = bars + 17;  // [2] (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+    uint64_t* k_full = bars + 1;                  // [PP_NST]
+    uint64_t* v_full = k_full + PP_NST;           // [PP_NST]
+    uint64_t* k_empty = v_full + PP_NST;          // [PP_NST]
+    uint64_t* v_empty = k_empty + PP_NST;         // [PP_NST]
+    uint64_t* m_full = v_empty + PP_NST;          // [PP_NST] mask of the stage written (32 arrivals)
+    uint64_t* s_full = m_full + PP_NST;           // [2] per warpgroup
+    uint64_t* p_full = s_full + 2;                // [2] (128 arrivals)
+    uint64_t* o_full = p_full + 2;                // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* mask_s = reinterpret_cast<float*>(smem + PP_OFF_MASK);
-    volatile uint32_t* plain_s = reinterpret_cast<uint32_t*>(bars + 24);   // [2] per stage: every key valid, mask 0
+    volatile uint32_t* plain_s = tmem_slot + 2;   // [PP_NST] per stage: every key valid, mask 0
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -122,16 +141,17 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 
     if (tid == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < PP_NST; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&v_full[i], 1);
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&m_full[i], 32);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
             mbar_init(&o_full[i], 1);
-            mbar_init(&o_empty[i], 128);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -159,8 +179,8 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         }
         bool ok = true;
         for (int j = 0; ok && j < n_tiles; ++j) {
-            const int st = j & 1;
-            const uint32_t ph = (static_cast<uint32_t>(j) >> 1) & 1u;
+            const int st = j % PP_NST;
+            const uint32_t ph = (static_cast<uint32_t>(j) / PP_NST) & 1u;
             if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
             if (lane == 0) {
                 mbar_expect_tx(&k_full[st], TILE_BYTES);
@@ -198,12 +218,23 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         if (lane == 0) {
             bool ok = mbar_wait(q_full, 0, abort_flag);
             const int nwg = two ? 2 : 1;
+            // A tcgen05.mma costs its issuing thread ~130 cycles whatever its size, and the UMMAs here are short (32-64
+            // tensor-pipe cycles): this thread is the pacemaker of the CTA.  All descriptors are built once, per issue
+            // only an immediate is added (descriptor address fields count 16-byte units).  (A second issuing thread,
+            // one per warpgroup, was tried: the two warpgroups then fall into lockstep, their exp sweeps collide on the
+            // SM's exp unit, and the kernel gets slower.)
+            const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+            const uint64_t dq[2] = {make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q)),
+                                    make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q + TILE_BYTES))};
+            const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
+            const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
             auto issue_s = [&](int wg, int st) {
-                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q + wg * TILE_BYTES));
-                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K + st * TILE_BYTES));
+                const uint64_t a_desc = dq[wg];
+                const uint64_t b_desc = dk0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                const uint32_t d_tmem = tmem_base + wg * 128;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    umma_f16_ss(tmem_base + wg * 128, a_desc + 2u * k, b_desc + 2u * k, p.idesc_qk, k != 0 ? 1u : 0u);
+                    umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
                 umma_commit(&s_full[wg]);
             };
             if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
@@ -213,53 +244,66 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 umma_commit(&k_empty[0]);
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                const int st = j & 1;
+                const int st = j % PP_NST;
+                const int st_next = (j + 1) % PP_NST;
                 const uint32_t ph = static_cast<uint32_t>(j) & 1u;
-                const uint32_t ph_st = (static_cast<uint32_t>(j) >> 1) & 1u;
+                const uint32_t ph_st = (static_cast<uint32_t>(j) / PP_NST) & 1u;
                 for (int wg = 0; ok && wg < nwg; ++wg) {
                     if (!mbar_wait(&p_full[wg], ph, abort_flag)) { ok = false; break; }
-                    if (wg == 0 && !mbar_wait(&v_full[st], ph_st, abort_flag)) { ok = false; break; }
-                    tcgen05_fence_after();
-#pragma unroll
-                    for (int k = 0; k < TK / 16; ++k) {
-                        const uint64_t a_desc =
-                            make_smem_desc_sw128(smem_u32(smem + PP_OFF_P + wg * 2 * TILE_BYTES + (k >> 2) * TILE_BYTES)) +
-                            2u * (k & 3);
-                        const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V + st * TILE_BYTES + k * 2048));
-                        // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must)
-                        umma_f16_ss(tmem_base + 256 + wg * 64, a_desc, b_desc, p.idesc_pv, (j | k) != 0 ? 1u : 0u);
-                    }
-                    umma_commit(&o_full[wg]);
-                    if (wg == nwg - 1) umma_commit(&v_empty[st]);
+                    ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
+                    // The warpgroup has read its scores and written P: its next scores go first (it waits for them),
+                    // then P V, which it needs only after its next max sweep.
                     if (j + 1 < n_tiles) {
-                        if (wg == 0 && !mbar_wait(&k_full[st ^ 1], ((static_cast<uint32_t>(j + 1)) >> 1) & 1u, abort_flag)) {
+                        if (wg == 0 &&
+                            !mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag)) {
                             ok = false;
                             break;
                         }
                         tcgen05_fence_after();
-                        issue_s(wg, st ^ 1);   // this warpgroup has finished reading its previous scores (p_full)
-                        if (wg == nwg - 1) umma_commit(&k_empty[st ^ 1]);
+                        ATTN_MARK(2, j, wg * 4 + 2);   // K of the next tile present
+                        issue_s(wg, st_next);
+                        if (wg == nwg - 1) umma_commit(&k_empty[st_next]);
+                        ATTN_MARK(2, j, wg * 4 + 3);   // next scores issued
                     }
+                    if (wg == 0 && !mbar_wait(&v_full[st], ph_st, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    {
+                        const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                        const uint32_t d_tmem = tmem_base + 256 + wg * 64;
+                        const uint32_t a_tmem = tmem_base + 384 + wg * 64;
+                        const uint32_t acc0 = j != 0 ? 1u : 0u;
+                        // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must);
+                        // P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
+#pragma unroll
+                        for (int k = 0; k < TK / 16; ++k)
+                            umma_f16_ts(d_tmem, a_tmem + k * 8, b_desc + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
+                                        k != 0 ? 1u : acc0);
+                    }
+                    umma_commit(&o_full[wg]);
+                    if (wg == nwg - 1) umma_commit(&v_empty[st]);
+                    ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
                 }
             }
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax warpgroups
-        const int wg = (warp - 2) >> 2;
+        const int wg = (warp - 2) >> 2;   // warps 2..5 -> 0, 6..9 -> 1
         const int r_in_tile = ((warp & 3) << 5) + lane;          // TMEM lane = query row of the tile
         const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem_base + lane_field + wg * 128;
         const uint32_t t_o = tmem_base + lane_field + 256 + wg * 64;
-        uint8_t* p_base = smem + PP_OFF_P + wg * 2 * TILE_BYTES;
+        const uint32_t t_p = tmem_base + lane_field + 384 + wg * 64;
         if (wg == 0 || two) {
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_tiles; ++j) {
-                const int st = j & 1;
+                const int st = j % PP_NST;
                 const uint32_t ph = static_cast<uint32_t>(j) & 1u;
-                if (!mbar_wait(&m_full[st], (static_cast<uint32_t>(j) >> 1) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&m_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) { ok = false; break; }
+                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 0);   // tile start
                 if (!mbar_wait(&s_full[wg], ph, abort_flag)) { ok = false; break; }
+                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 1);   // scores present
                 __syncwarp();
                 tcgen05_fence_after();
                 const float* mrow = mask_s + st * TK;
@@ -305,7 +349,9 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                             alpha = move ? fast_exp2(m_run - m_use) : 1.f;
                             // PV of the previous tile must be complete: it reads the P buffer the second sweep
                             // overwrites, and it writes the accumulator a rescale would touch.
+                            if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 2);   // max sweep done
                             if (j > 0) wait_ok = mbar_wait(&o_full[wg], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
+                            if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 3);   // previous PV complete
                             __syncwarp();
                             if (j > 0 && __any_sync(0xffffffffu, move)) {
                                 tcgen05_fence_after();
@@ -344,17 +390,13 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                             ps[2] += pv[q4 + 2];
                             ps[3] += pv[q4 + 3];
                         }
-                        uint8_t* prow = p_base + (c >> 1) * TILE_BYTES + r_in_tile * 128;
+                        // P goes to tensor memory as the A operand of the PV UMMA: two consecutive keys per 32-bit
+                        // column, this chunk's 32 keys in columns [16c, 16c + 16) of the warpgroup's P region.
+                        uint32_t pk[16];
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint4 qv;
-                            qv.x = pack2t<DT>(pv[g * 8 + 0], pv[g * 8 + 1]);
-                            qv.y = pack2t<DT>(pv[g * 8 + 2], pv[g * 8 + 3]);
-                            qv.z = pack2t<DT>(pv[g * 8 + 4], pv[g * 8 + 5]);
-                            qv.w = pack2t<DT>(pv[g * 8 + 6], pv[g * 8 + 7]);
-                            const int chunk = ((c & 1) * 4 + g) ^ (r_in_tile & 7);
-                            *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
-                        }
+                        for (int e = 0; e < 16; ++e) pk[e] = pack2t<DT>(pv[2 * e], pv[2 * e + 1]);
+                        tmem_st_32x32b_x16(t_p + c * 16, pk);
+
                     }
                 };
                 auto sweep = [&](auto plain_c) {
@@ -377,9 +419,10 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
                 l_run = l_run * alpha + psum;
                 m_run = m_new;
-                fence_async_proxy_shared();   // P visible to the UMMA
-                tcgen05_fence_before();       // this thread's reads of S and its rescale of O are done
+                tmem_st_wait();               // P (and a rescaled O) have reached tensor memory
+                tcgen05_fence_before();       // ... and this thread's reads of S are done
                 mbar_arrive(&p_full[wg]);
+                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 4);   // P written
             }
             // the last PV
             if (ok && n_tiles > 0 && !mbar_wait(&o_full[wg], static_cast<uint32_t>(n_tiles - 1) & 1u, abort_flag)) ok = false;
@@ -688,6 +731,12 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
 }  // namespace
 }  // namespace b200
+
+#ifdef B200_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_debug_attn_trace(unsigned long long* host) {
+    return cudaMemcpyFromSymbol(host, b200::g_attn_trace, sizeof(b200::g_attn_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stream_) {
     using namespace b200;
