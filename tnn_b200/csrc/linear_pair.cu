@@ -34,11 +34,12 @@ __device__ unsigned long long g_trace[512][16];
 #endif
 
 template <int BN, bool RES, bool FOLD, bool LN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epi_warps<BN>(), 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_r,
                    const LinearParams p) {
-    using C = PairCfg<BN, RES, FOLD>;
+    constexpr int EW = pair_epi_warps<BN>();
+    using C = PairCfg<BN, RES, FOLD, EW>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of a pair must lay their buffers out at identical offsets: the dynamic shared-memory window starts at
@@ -49,7 +50,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint64_t* res_bars = acc_empty + 2;                       // 2 per epilogue warp (RES only)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + 2 * kEpiWarps);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + 2 * EW);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -67,9 +68,9 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 2 * kEpiWarps);   // leader's copy: epilogue warps of both CTAs
+            mbar_init(&acc_empty[b], 2 * EW);   // leader's copy: epilogue warps of both CTAs
         }
-        for (int b = 0; b < 2 * kEpiWarps; ++b) mbar_init(&res_bars[b], 1);
+        for (int b = 0; b < 2 * EW; ++b) mbar_init(&res_bars[b], 1);
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tmap(&tm_x);
@@ -157,8 +158,8 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
         const int ew = warp - 2;
         const int quarter = warp & 3;
-        const int half = ew >> 2;
-        constexpr int COLS = BN / 2;
+        const int half = ew >> 2;           // which COLS-wide part of the tile's columns this warp drains
+        constexpr int COLS = C::COLS;
         constexpr int CHUNKS = COLS / 32;
         float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * vec_strips<FOLD>() * COLS;
         WarpEpilogue<CHUNKS, RES, FOLD> epi{p, &tm_y, &tm_r,
@@ -206,13 +207,13 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 if (lane == 0) {
                     tma_store_wait_all<0>();
                     add_release(p.ln_sync + m_blk);
-                    ready = wait_rows(p.ln_sync + m_blk, p.num_n_tiles * 2 * kEpiWarps, abort_flag) ? 1 : 0;
+                    ready = wait_rows(p.ln_sync + m_blk, p.num_n_tiles * 2 * EW, abort_flag) ? 1 : 0;
                 }
                 ready = __shfl_sync(0xffffffffu, ready, 0);
                 if (!ready) { ok = false; break; }
-                const int per_warp = p.ln_rows_per_tile / (2 * kEpiWarps);
+                const int per_warp = p.ln_rows_per_tile / (2 * EW);
                 const int part0 = n_blk * p.ln_rows_per_tile;                       // first row of this tile's share
-                const int mine = part0 + (static_cast<int>(rank) * kEpiWarps + ew) * per_warp;
+                const int mine = part0 + (static_cast<int>(rank) * EW + ew) * per_warp;
                 int nrows = min(per_warp, 256 - mine);
                 if (nrows > 0)
                     layernorm_rows_warp<4>(p.y, p.ldy, p.ln_out, p.ld_ln, p.ln_gamma, p.ln_beta, p.N, p.ln_eps, p.dtype,
@@ -248,8 +249,10 @@ extern "C" __attribute__((visibility("default"))) int b200_debug_trace(unsigned 
 
 template <int BN, bool RES, bool FOLD, bool LN = false>
 int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
-    using C = PairCfg<BN, RES, FOLD>;
+    constexpr int EW = pair_epi_warps<BN>();
+    using C = PairCfg<BN, RES, FOLD, EW>;
     static_assert(C::STAGES >= 3, "pipeline too shallow");
+    static_assert(C::COLS % 32 == 0 && EW % 4 == 0, "every epilogue warp drains whole 32-column chunks");
     const uint64_t xd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.M)};
     const uint64_t xs[1] = {static_cast<uint64_t>(d.ldx) * 2};
     const uint32_t xb[2] = {BK, 128};
@@ -308,8 +311,8 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     p.ln_beta = d.post_ln_beta;
     p.ld_ln = d.post_ln_ld;
     p.ln_sync = static_cast<int*>(d.post_ln_sync);
-    // 256 rows of a block shared out over its tiles, in units of 16 rows (one per consumer warp of the pair)
-    p.ln_rows_per_tile = ((256 + p.num_n_tiles - 1) / p.num_n_tiles + 15) / 16 * 16;
+    // 256 rows of a block shared out over its tiles, in units of one row per epilogue warp of the pair
+    p.ln_rows_per_tile = ((256 + p.num_n_tiles - 1) / p.num_n_tiles + 2 * EW - 1) / (2 * EW) * (2 * EW);
 
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -324,7 +327,7 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     if (pairs <= 0) pairs = sm_count / 2;
     if (p.num_tiles < pairs) pairs = p.num_tiles;
     if (LN && pairs < p.num_n_tiles) return B200_ERR_UNSUPPORTED;   // the tiles of a row block need distinct owners
-    launch_kernel(linear_pair_kernel<BN, RES, FOLD, LN>, dim3(2 * pairs), dim3(kThreads), C::SMEM_BYTES, stream, *tx, *tw,
+    launch_kernel(linear_pair_kernel<BN, RES, FOLD, LN>, dim3(2 * pairs), dim3(C::THREADS), C::SMEM_BYTES, stream, *tx, *tw,
                   *ty, *tr, p);
     count_launch();
     return check_launch();
@@ -335,7 +338,7 @@ template <int BN>
 int query_pairs(int sm_count) {
     // A persistent grid must not exceed what is co-resident: a pair that cannot be placed (GPCs with an odd number
     // of free SMs) would otherwise run as a second wave after the first has finished all the work.
-    using C = PairCfg<BN, false, false>;
+    using C = PairCfg<BN, false, false, pair_epi_warps<BN>()>;
     if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess) {
         cudaGetLastError();
@@ -343,7 +346,7 @@ int query_pairs(int sm_count) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;

@@ -6,14 +6,22 @@
 namespace b200 {
 namespace lin {
 
-template <int BN, bool RES, bool FOLD>
+// Epilogue warps per CTA of the pair GEMM for a tile width: every warp drains 32 TMEM lanes (its quarter) x 64 or 128
+// columns.  192-wide tiles get 12 warps (64 columns each): their GEMMs are short-K and the epilogue (GELU, residual)
+// is what bounds them; more warps hide its latencies, and the register budget (128 per thread at 448 threads) holds.
+template <int BN> constexpr int pair_epi_warps() { return BN == 192 ? 12 : 8; }
+
+template <int BN, bool RES, bool FOLD, int EW = kEpiWarps>
 struct PairCfg {
     static constexpr int A_BYTES = 128 * BK * 2;          // this CTA's 128 rows of x
     static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this CTA's BN/2 rows of w
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // output staging strips (TMA store); with RES two per warp, which also receive the residual tile (TMA load)
-    static constexpr int OUT_BYTES = kEpiWarps * kStageBytesPerWarp * strips_per_warp<RES>();
-    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + kEpiWarps * vec_strips<FOLD>() * (BN / 2) * 4;   // + barriers + bias strips
+    static constexpr int EPI_WARPS = EW;
+    static constexpr int THREADS = 64 + 32 * EW;
+    static constexpr int COLS = BN / (EW / 4);            // accumulator columns drained by one epilogue warp
+    static constexpr int OUT_BYTES = EW * kStageBytesPerWarp * strips_per_warp<RES>();
+    static constexpr int TAIL_BYTES = OUT_BYTES + 512 + EW * vec_strips<FOLD>() * COLS * 4;   // + barriers + bias strips
     static constexpr int STAGES = (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES > 8
                                       ? 8 : (227 * 1024 - 1024 - TAIL_BYTES) / STAGE_BYTES;
     static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
