@@ -31,6 +31,43 @@ BATCH_PER_GPU = 64
 SEQ = 128
 
 
+def tnn_plugin_seq_per_s(wl, warmup=5, iters=30):
+    """The same workload through the drop-in path: the unmodified reference framework (oracle/_ref/libTNN.so) with the
+    tnn_b200 plug-in serving DEVICE_CUDA — Instance::Forward over the fused graph, fp32 blobs at both ends.  Returns a
+    dict (Forward-only and host-to-host figures) or None when the reference build is not present."""
+    try:
+        from tnn_b200 import model_synth, tnn_runtime
+        if not tnn_runtime.available():
+            return None
+        import shutil
+        import tempfile
+        d = tempfile.mkdtemp(prefix="tnnb200_bench_")
+        try:
+            proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+            model_synth.write_tnn_model(wl, proto, model)
+            inst = tnn_runtime.Instance(proto, model, device=tnn_runtime.DEVICE_CUDA)
+            inst.set_input("x", wl.x)
+            inst.set_input("mask", wl.mask_add)
+            ms = inst.time_forward(warmup, iters)               # Instance::Forward incl. its stream synchronise
+            n = min(iters, 10)
+            t0 = time.perf_counter()
+            for _ in range(n):
+                inst.set_input("x", wl.x)                       # host Mat -> device blob
+                inst.forward()
+                inst.get_output()                               # device blob -> host Mat
+            host_ms = (time.perf_counter() - t0) / n * 1e3
+            inst.close()
+        finally:
+            shutil.rmtree(d, ignore_errors=True)
+        B = wl.x.shape[0]
+        return {"forward_value": B / ms * 1e3, "forward_ms": ms, "host_to_host_value": B / host_ms * 1e3,
+                "host_to_host_ms": host_ms, "unit": UNIT,
+                "note": "TNN Instance::Forward on DEVICE_CUDA served by the plug-in (fused graph, eager launches, "
+                        "blocking Forward); host_to_host adds SetInputMat/GetOutputMat with pageable fp32 host Mats"}
+    except Exception as e:   # the drop-in measurement is supplementary: never fail the bench line over it
+        return {"error": str(e)[:300]}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -442,6 +479,10 @@ def run_ours(args):
         v, kind, desc = cpu_reference_seq_per_s(8, 1, layers=12, warmup=1, iters=2)
         cpu_baseline = {"value": v, "unit": UNIT, "cores": 1, "kind": kind, "sample": desc}
 
+    tnn_plugin = None
+    if rank == 0 and world == 1 and not args.no_tnn_plugin:
+        tnn_plugin = tnn_plugin_seq_per_s(wl)
+
     if rank == 0:
         flops_per_seq = model_synth.layer_flops(SEQ, H, F) * len(enc.layers)
         line = {
@@ -487,6 +528,7 @@ def run_ours(args):
             "model_tflops": value * flops_per_seq / 1e12,
             "model_frac_of_tensor_peak": value * flops_per_seq / 1e12 / peaks["tflops"] / world,
             "cpu_baseline": cpu_baseline,
+            "tnn_plugin": tnn_plugin,
         }
         print(json.dumps(line))
     if world > 1:
@@ -515,6 +557,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="sequences per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-attention-sweep", action="store_true")
+    ap.add_argument("--no-tnn-plugin", action="store_true", help="skip the measurement through TNN + plug-in")
     ap.add_argument("--fold-layernorm", action="store_true",
                     help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
     ap.add_argument("--layernorm-in-gemm", action="store_true",

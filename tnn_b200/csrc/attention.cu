@@ -47,16 +47,10 @@ constexpr int TK = 128;   // keys per tile
 constexpr int HD = 64;    // head dim
 constexpr int kAttnThreads = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 16 KB
+// offsets of the Q, K and V tiles inside one shared-memory set of the single-tile kernel
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + TILE_BYTES;
 constexpr int OFF_V = OFF_K + TILE_BYTES;
-constexpr int OFF_P = OFF_V + TILE_BYTES;       // 2 x 16 KB (keys 0..63, 64..127)
-constexpr int OFF_MASK = OFF_P + 2 * TILE_BYTES;  // 2 x 128 floats
-constexpr int OFF_BAR = OFF_MASK + 2 * TK * 4;
-constexpr int ATTN_SMEM = OFF_BAR + 128;
-constexpr int ATTN_TMEM_COLS = 256;
-constexpr int TMEM_S = 0;
-constexpr int TMEM_O = 128;
 
 struct AttnParams {
     const float* mask_add;
