@@ -42,7 +42,8 @@ enum {
     B200_ERR_DRIVER           = -4, /* tensor-map encode entry point missing or it refused the descriptor          */
     B200_ERR_DEVICE_TIMEOUT   = -5, /* reported by b200_device_status(): a bounded device-side wait ran out        */
     B200_ERR_NOT_SM100        = -6, /* the current device is not compute capability 10.x                           */
-    B200_ERR_STATIC_LIMIT     = -7  /* b200_attention_masked_fwd_static: batch larger than its built-in scratch      */
+    B200_ERR_STATIC_LIMIT     = -7, /* b200_attention_masked_fwd_static: batch larger than its built-in scratch      */
+    B200_ERR_INDEX            = -8  /* reported by b200_device_status(): an embedding index was outside its table      */
 };
 
 enum { B200_F16 = 0, B200_BF16 = 1, B200_F32 = 2 };
@@ -207,6 +208,44 @@ B200_API int b200_mask_to_kv_len(const float* mask_add, int64_t B, int64_t S, fl
                                  b200_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------------------------
+ * The step in front of the encoder path: embedding lookups + LayerNorm, and the additive key mask from the 0/1 input
+ * mask.  Replaces, in a converted BERT graph, Gather(word) + Gather(segment) -> Add -> Add(position slice) ->
+ * LayerNorm (source/tnn/device/x86/acc/x86_gather_layer_acc.cc:23-76, x86_add_layer_acc.cc:66-92,
+ * x86_layer_norm_layer_acc.cc:26-86) and Unsqueeze -> Cast -> Sub -> Mul on the mask
+ * (source/tnn/device/x86/acc/x86_binary_op_layer_acc.cc:536-805); int32 graph inputs as the reference's tokenizer
+ * produces them (examples/base/bert_tokenizer.cc:351-355).
+ *   out[t, :] = LayerNorm(word_emb[input_ids[t]] + type_emb[segment_ids[t]] + pos_emb[t mod S]) * gamma + beta
+ *   tables    : `table_dtype` (F32, F16 or BF16) `[rows, H]` with row stride ld_table (elements); type_emb and
+ *               segment_ids may both be NULL; pos_emb needs at least S rows.
+ *   out       : `out_dtype` (F16/BF16/F32) `[B*S, ld_out]`.   Requirements: H % 8 == 0, H <= 1024, 16-byte aligned.
+ *   An index outside its table makes the reference's Gather fail (TNNERR_MODEL_ERR); here the row is written as
+ *   LayerNorm of the remaining terms with that term 0, and b200_device_status() reports B200_ERR_INDEX.
+ */
+typedef struct B200EmbeddingDesc {
+    const int32_t* input_ids;
+    const int32_t* segment_ids;
+    const void*    word_emb;
+    const void*    type_emb;
+    const void*    pos_emb;
+    const float*   gamma;
+    const float*   beta;
+    void*          out;
+    int64_t        B, S, H;
+    int64_t        vocab, type_vocab;
+    int64_t        ld_table, ld_out;
+    int32_t        table_dtype;
+    int32_t        out_dtype;
+    float          eps;
+} B200EmbeddingDesc;
+B200_API int b200_embedding_layernorm_fwd(const B200EmbeddingDesc* desc, b200_stream_t stream);
+
+/* mask_add[b, s] = (1 - input_mask[b, s]) * masked_value (fp32, the reference's Sub and Mul; masked_value = -10000 in
+ * BERT exports) and, if kv_len is not NULL, kv_len[b] = 1 + the last s with mask_add[b, s] > exclude_below — the two
+ * arrays b200_attention_fwd takes.  input_mask: int32 `[B, S]`. */
+B200_API int b200_mask_from_input_mask(const int32_t* input_mask, int64_t B, int64_t S, float masked_value,
+                                       float exclude_below, float* mask_add, int32_t* kv_len, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
  * (residual +) LayerNorm over the last dimension:  y = (x (+ r) - mean) * rsqrt(var + eps) * gamma + beta.
  * Replaces Add(residual) + LayerNorm (source/tnn/device/x86/acc/x86_layer_norm_layer_acc.cc:26-86; gamma and beta are
  * the layer's input blobs 1 and 2, source/tnn/layer/layer_norm_layer.cc:28-30).  One warp per row, fp32 statistics,
@@ -313,7 +352,8 @@ B200_API int    b200_encoder_fwd(const B200EncoderDesc* desc, b200_stream_t stre
 /* -------------------------------------------------------------------------------------------------------------------
  * Housekeeping. */
 B200_API const char* b200_status_string(int status);
-/* Reads and clears the current device's status word (synchronous, small).  0 or B200_ERR_DEVICE_TIMEOUT. */
+/* Reads and clears the current device's status word (synchronous, small).  0, B200_ERR_DEVICE_TIMEOUT or
+ * B200_ERR_INDEX (a timeout takes precedence). */
 B200_API int         b200_device_status(void);
 /* Number of kernel launches issued by this library in this process (all devices, all threads). */
 B200_API uint64_t    b200_launch_count(void);

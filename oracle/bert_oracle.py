@@ -116,3 +116,28 @@ def attention_core(q, k, v, mask_add, scale):
         B, S = mask_add.shape
         scores = scores + mask_add.reshape(B, 1, 1, S).astype(F32)
     return matmul(softmax_last(scores.astype(F32)), v)
+
+
+# --------------------------------------------------------------------------------------------- embedding front-end
+def gather_rows(table, indices):
+    """Gather along axis 0 with a resource table: out[i...] = table[indices[i...]]
+    (source/tnn/device/x86/acc/x86_gather_layer_acc.cc:23-76: a memcpy per index; an index outside [0, rows) is an
+    error there, TNNERR_MODEL_ERR)."""
+    idx = np.asarray(indices)
+    if idx.size and (idx.min() < 0 or idx.max() >= table.shape[0]):
+        raise IndexError("gather index out of range")
+    return table[idx]
+
+
+def embedding_frontend(fw):
+    """word + segment + position embeddings, LayerNorm; the additive key mask (1 - m) * -10000 as [B,1,1,S].
+    Gather as above; Add: source/tnn/device/x86/acc/x86_add_layer_acc.cc:66-92 (the position slice [1,S,H] is
+    broadcast over the batch); LayerNorm: x86_layer_norm_layer_acc.cc:26-86; Unsqueeze / Cast(int32 -> float) move no
+    values; Sub with the constant as input 0 (weight_input_index 0) computes 1 - m, Mul scales by -10000
+    (source/tnn/device/x86/acc/x86_binary_op_layer_acc.cc:536-805)."""
+    B, S = fw.input_ids.shape
+    e = gather_rows(fw.word_emb, fw.input_ids) + gather_rows(fw.type_emb, fw.segment_ids)
+    e = e + fw.pos_emb[:S].reshape(1, S, -1)
+    out = layer_norm(e.astype(np.float32), fw.gamma, fw.beta, fw.eps)
+    mask_add = ((np.float32(1.0) - fw.input_mask.astype(np.float32)) * np.float32(-10000.0)).reshape(B, 1, 1, S)
+    return out.astype(np.float32), mask_add.astype(np.float32)

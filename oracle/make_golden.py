@@ -36,6 +36,28 @@ CASES = {
 }
 
 
+# name -> keyword arguments of model_synth.make_frontend_workload(): the embedding front-end + mask builder
+FRONTEND_CASES = {
+    "frontend_base_s48": dict(hidden=768, batch=3, seq=48, vocab=2000, type_vocab=2, max_pos=64, seed=5,
+                              length_range=(5, 48)),
+}
+
+
+def run_frontend(fw, device):
+    import tempfile
+    d = tempfile.mkdtemp(prefix="tnnref_frontend_")
+    proto, model = os.path.join(d, "f.tnnproto"), os.path.join(d, "f.tnnmodel")
+    ms.write_tnn_frontend_model(fw, proto, model)
+    inst = tnn_ref.TnnInstance(proto, model, device=device)
+    inst.set_input_i32("input_ids", fw.input_ids)
+    inst.set_input_i32("segment_ids", fw.segment_ids)
+    inst.set_input_i32("input_mask", fw.input_mask)
+    inst.forward()
+    out = inst.get_output("emb_out"), inst.get_output("mask_add")
+    inst.close()
+    return out
+
+
 def golden_workload(kind, geometry=None, batch=None, seq=None, layers=None, seed=0, length_range=None,
                     randomize_affine=False):
     if kind == "config1":
@@ -47,7 +69,10 @@ def golden_workload(kind, geometry=None, batch=None, seq=None, layers=None, seed
 
 def main():
     os.makedirs(GOLDEN, exist_ok=True)
+    only = sys.argv[1:]      # optional: names of the cases to (re)generate
     for name, kw in CASES.items():
+        if only and name not in only:
+            continue
         wl = golden_workload(**kw)
         x86, _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_X86)
         naive, _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_NAIVE)
@@ -56,6 +81,15 @@ def main():
         np.savez(path, x86=x86.astype(np.float32), lengths=wl.lengths,
                  x86_vs_naive_max_abs=np.float32(np.abs(x86 - naive).max()))
         print(name, x86.shape, "x86-vs-naive max-abs", float(np.abs(x86 - naive).max()))
+    for name, kw in FRONTEND_CASES.items():
+        if only and name not in only:
+            continue
+        fw = ms.make_frontend_workload(**kw)
+        e86, m86 = run_frontend(fw, tnn_ref.DEVICE_X86)
+        en, mn = run_frontend(fw, tnn_ref.DEVICE_NAIVE)
+        np.savez(os.path.join(GOLDEN, name + ".npz"), emb_x86=e86.astype(np.float32), mask_x86=m86.astype(np.float32),
+                 x86_vs_naive_max_abs=np.float32(max(np.abs(e86 - en).max(), np.abs(m86 - mn).max())))
+        print(name, e86.shape, m86.shape, "x86-vs-naive max-abs", float(np.abs(e86 - en).max()))
 
 
 if __name__ == "__main__":

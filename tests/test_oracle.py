@@ -11,7 +11,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 from oracle import bert_oracle  # noqa: E402
-from oracle.make_golden import CASES, GOLDEN, golden_workload  # noqa: E402
+from oracle.make_golden import CASES, FRONTEND_CASES, GOLDEN, golden_workload  # noqa: E402
+from tnn_b200 import model_synth  # noqa: E402
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
@@ -27,6 +28,23 @@ def test_restatement_matches_reference_x86(name):
     assert cosine(y, ref) > 1 - 1e-9
     # the reference's two CPU devices agreed with each other when the fixture was made
     assert float(g["x86_vs_naive_max_abs"]) < 5e-5
+
+
+@pytest.mark.parametrize("name", sorted(FRONTEND_CASES))
+def test_frontend_restatement_matches_reference_x86(name):
+    """Embedding gathers + adds + LayerNorm and the mask builder against the reference's own run of that graph."""
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    fw = model_synth.make_frontend_workload(**FRONTEND_CASES[name])
+    emb, mask = bert_oracle.embedding_frontend(fw)
+    assert emb.shape == g["emb_x86"].shape and mask.shape == g["mask_x86"].shape
+    assert max_abs(emb, g["emb_x86"]) < 5e-6
+    assert np.array_equal(mask, g["mask_x86"])           # (1 - m) * -10000 is exact in fp32
+    assert float(g["x86_vs_naive_max_abs"]) < 5e-6
+
+
+def test_gather_out_of_range_is_an_error():
+    with pytest.raises(IndexError):
+        bert_oracle.gather_rows(np.zeros((4, 2), np.float32), np.array([0, 4]))
 
 
 def test_softmax_masked_keys_underflow_to_zero():

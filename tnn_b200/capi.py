@@ -18,6 +18,7 @@ EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL = 0, 1, 2
 OK = 0
 ERR_PARAM, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_DRIVER, ERR_DEVICE_TIMEOUT, ERR_NOT_SM100 = -1, -2, -3, -4, -5, -6
 ERR_STATIC_LIMIT = -7
+ERR_INDEX = -8
 STATIC_MAX_BATCH = 4096
 
 _c = ctypes
@@ -49,6 +50,14 @@ class LayerNormDesc(_c.Structure):
                 ("rows", _i64), ("H", _i64),
                 ("ldx", _i64), ("ldr", _i64), ("ldy", _i64),
                 ("in_dtype", _i32), ("out_dtype", _i32), ("eps", _f32)]
+
+
+class EmbeddingDesc(_c.Structure):
+    _fields_ = [("input_ids", _vp), ("segment_ids", _vp), ("word_emb", _vp), ("type_emb", _vp), ("pos_emb", _vp),
+                ("gamma", _vp), ("beta", _vp), ("out", _vp),
+                ("B", _i64), ("S", _i64), ("H", _i64), ("vocab", _i64), ("type_vocab", _i64),
+                ("ld_table", _i64), ("ld_out", _i64),
+                ("table_dtype", _i32), ("out_dtype", _i32), ("eps", _f32)]
 
 
 PHASE_LINEAR, PHASE_ADD_LAYERNORM = 0, 1
@@ -85,6 +94,8 @@ SYMBOLS = {
     "b200_attention_masked_fwd_static": (_c.c_int, [_c.POINTER(AttentionDesc), _vp]),
     "b200_mask_to_kv_len": (_c.c_int, [_vp, _i64, _i64, _f32, _vp, _vp]),
     "b200_add_layernorm_fwd": (_c.c_int, [_c.POINTER(LayerNormDesc), _vp]),
+    "b200_embedding_layernorm_fwd": (_c.c_int, [_c.POINTER(EmbeddingDesc), _vp]),
+    "b200_mask_from_input_mask": (_c.c_int, [_vp, _i64, _i64, _f32, _f32, _vp, _vp, _vp]),
     "b200_chain_sync_bytes": (_c.c_size_t, [_i64, _i32]),
     "b200_chain_fwd": (_c.c_int, [_c.POINTER(ChainPhase), _i32, _vp, _vp]),
     "b200_encoder_workspace_bytes": (_c.c_size_t, [_i64, _i64, _i64, _c.c_int]),

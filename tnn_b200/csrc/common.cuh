@@ -14,7 +14,8 @@
 namespace b200 {
 
 // ---------------------------------------------------------------- device status word
-// Bit 0: a bounded wait ran out in a GEMM CTA; bit 1: in an attention CTA.  The word itself is a __device__ variable
+// Bit 0: a bounded wait ran out in a GEMM CTA; bit 1: in an attention CTA; bit 2: misaligned dynamic shared memory
+// (attention); bit 3: an embedding index outside its table.  The word itself is a __device__ variable
 // of runtime.cu; kernels receive its address as a parameter (no relocatable device code needed).
 unsigned int* device_status_ptr();  // address of the word on the current device (looked up once per device)
 

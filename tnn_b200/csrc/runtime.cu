@@ -160,6 +160,7 @@ const char* b200_status_string(int status) {
         case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
         case B200_ERR_NOT_SM100: return "current device is not an sm_100 GPU";
         case B200_ERR_STATIC_LIMIT: return "size exceeds the fixed capacity of the library's static device scratch";
+        case B200_ERR_INDEX: return "an embedding index was outside its table";
         default: return "unknown status";
     }
 }
@@ -172,7 +173,7 @@ int b200_device_status(void) {
     if (v != 0) {
         unsigned int zero = 0;
         cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice);
-        return B200_ERR_DEVICE_TIMEOUT;
+        return (v & ~8u) != 0 ? B200_ERR_DEVICE_TIMEOUT : B200_ERR_INDEX;   // bit 3: index out of range
     }
     return B200_OK;
 }

@@ -20,7 +20,7 @@ import numpy as np
 MAGIC = 0x0FABC0002   # untyped-input proto / model magic (source/tnn/interpreter/tnn/objseri.h:29-30)
 MAGIC_RAW = 0x0FABC0004
 # LayerType enum values used in the binary (source/tnn/core/layer_type.h); the parser keys on the type string.
-_TYPE_ID = {"MatMul": 105, "Add": 38, "Mul": 42}
+_TYPE_ID = {"MatMul": 105, "Add": 38, "Mul": 42, "Gather": 104, "Sub": 108}
 
 
 @dataclass
@@ -215,6 +215,92 @@ def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"
     with open(model_path, "wb") as fh:
         fh.write(m)
     return x
+
+
+# --------------------------------------------------------------------------------------------- embedding front-end
+@dataclass
+class FrontendWorkload:
+    """The step before the encoder path: token / segment / position embeddings + LayerNorm, and the additive key mask
+    built from the 0/1 input mask (int32 graph inputs as in examples/base/bert_tokenizer.cc:351-355)."""
+    hidden: int
+    word_emb: np.ndarray      # [vocab, H] fp32
+    type_emb: np.ndarray      # [type_vocab, H]
+    pos_emb: np.ndarray       # [max_pos, H]
+    gamma: np.ndarray
+    beta: np.ndarray
+    eps: float
+    input_ids: np.ndarray     # [B, S] int32
+    segment_ids: np.ndarray   # [B, S] int32
+    input_mask: np.ndarray    # [B, S] int32, 1 = token, 0 = padding
+    lengths: np.ndarray
+
+
+def make_frontend_workload(hidden, batch, seq, vocab=30522, type_vocab=2, max_pos=512, seed=0, length_range=None,
+                           eps=1e-12):
+    rng = np.random.default_rng(seed)
+    n = lambda *shape: rng.normal(0.0, 0.02, shape).astype(np.float32)   # noqa: E731
+    word, typ, pos = n(vocab, hidden), n(type_vocab, hidden), n(max_pos, hidden)
+    gamma = (1.0 + rng.normal(0, 0.1, hidden)).astype(np.float32)
+    beta = rng.normal(0, 0.1, hidden).astype(np.float32)
+    ids = rng.integers(0, vocab, size=(batch, seq)).astype(np.int32)
+    seg = rng.integers(0, type_vocab, size=(batch, seq)).astype(np.int32)
+    if length_range is None:
+        lengths = np.full((batch,), seq, np.int64)
+    else:
+        lengths = rng.integers(length_range[0], length_range[1] + 1, size=(batch,))
+    mask = (np.arange(seq)[None, :] < lengths[:, None]).astype(np.int32)
+    return FrontendWorkload(hidden, word, typ, pos, gamma, beta, eps, ids, seg, mask, np.asarray(lengths, np.int64))
+
+
+def write_tnn_frontend_model(fw, proto_path, model_path):
+    """The unfused front-end graph as a converter emits it: Gather(word) + Gather(segment) -> Add -> Add(position
+    slice, a constant) -> LayerNorm = `emb_out`; Unsqueeze(1,2) -> Cast(float) -> Sub(1 - m) -> Mul(-10000) =
+    `mask_add`.  Typed (v2) inputs: input_ids, segment_ids, input_mask int32 [B, S].
+    Grammar: Gather source/tnn/interpreter/tnn/layer_interpreter/gather_layer_interpreter.cc:23-47, Unsqueeze
+    unsqueeze_layer_interpreter.cc:20-30, Cast cast_layer_interpreter.cc:21-25, Sub sub_layer_interpreter.cc:23-47."""
+    B, S = fw.input_ids.shape
+    H = fw.hidden
+    layers, res, consts = [], [], {}
+
+    def layer(t, name, ins, outs, params=""):
+        layers.append('"%s %s %d %d %s %s %s,"' % (t, name, len(ins), len(outs), " ".join(ins), " ".join(outs), params))
+
+    def head(t, name):
+        return struct.pack("<i", _TYPE_ID[t]) + _pstr(t) + _pstr(name)
+
+    layer("Gather", "word_e", ["input_ids"], ["word_e"], "0 1 0")
+    res.append(head("Gather", "word_e") + struct.pack("<i", 1) + _raw(fw.word_emb) + struct.pack("<i", 0))
+    layer("Gather", "type_e", ["segment_ids"], ["type_e"], "0 1 0")
+    res.append(head("Gather", "type_e") + struct.pack("<i", 1) + _raw(fw.type_emb) + struct.pack("<i", 0))
+    layer("Add", "wt_e", ["word_e", "type_e"], ["wt_e"], "-1")
+    layer("Add", "wtp_e", ["wt_e"], ["wtp_e"], "1")
+    res.append(head("Add", "wtp_e") + _raw(fw.pos_emb[:S].reshape(1, S, H)))
+    consts["emb_g"], consts["emb_be"] = fw.gamma, fw.beta
+    layer("LayerNorm", "emb_out", ["wtp_e", "emb_g", "emb_be"], ["emb_out"], "1 %.1e" % fw.eps)
+    layer("Unsqueeze", "mask_u", ["input_mask"], ["mask_u"], "2 1 2")
+    layer("Cast", "mask_f", ["mask_u"], ["mask_f"], "0")
+    layer("Sub", "mask_inv", ["mask_f"], ["mask_inv"], "0")
+    res.append(head("Sub", "mask_inv") + _raw(np.array([1.0], np.float32)))
+    layer("Mul", "mask_add", ["mask_inv"], ["mask_add"], "1")
+    res.append(head("Mul", "mask_add") + _raw(np.array([-10000.0], np.float32)))
+    blobs = set()
+    for ln in layers:
+        t = ln.strip('",').split()
+        ni, no = int(t[2]), int(t[3])
+        blobs.update(t[4:4 + ni + no])
+    inputs = " : ".join("%s 2 %d %d 3" % (n, B, S) for n in ("input_ids", "segment_ids", "input_mask"))
+    proto = ['"1 %d 1 %d ,"' % (len(blobs), MAGIC_RAW),
+             '"%s ,"' % inputs,
+             '" ' + " ".join(sorted(blobs)) + ' ,"',
+             '"emb_out mask_add ,"',
+             '" %d ,"' % len(layers)] + layers
+    with open(proto_path, "w") as fh:
+        fh.write("\n".join(proto) + "\n")
+    m = struct.pack("<I", MAGIC) + struct.pack("<i", len(res)) + b"".join(res)
+    m += struct.pack("<Ii", MAGIC, len(consts)) + b"".join(_pstr(k) + _raw(v) for k, v in consts.items())
+    with open(model_path, "wb") as fh:
+        fh.write(m)
+    return "emb_out", "mask_add"
 
 
 # --------------------------------------------------------------------------------------------- FLOP accounting

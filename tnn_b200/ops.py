@@ -184,6 +184,45 @@ def add_layernorm(x, gamma, beta, eps, residual=None, out_dtype=None, out=None):
     return out
 
 
+def embedding_layernorm(input_ids, segment_ids, word_emb, type_emb, pos_emb, gamma, beta, eps, out_dtype=torch.float16,
+                        out=None):
+    """`[B,S]` int32 ids (+ segment ids or None) -> LayerNorm(word + segment + position embeddings) `[B,S,H]`."""
+    _require_cuda(input_ids, segment_ids, word_emb, type_emb, pos_emb, gamma, beta, out)
+    B, S = input_ids.shape
+    H = word_emb.shape[1]
+    assert input_ids.dtype == torch.int32 and input_ids.is_contiguous()
+    assert word_emb.stride(1) == 1 and pos_emb.dtype == word_emb.dtype and pos_emb.shape[0] >= S
+    assert pos_emb.stride(0) == word_emb.stride(0)
+    if out is None:
+        out = torch.empty((B, S, H), dtype=out_dtype, device=input_ids.device)
+    d = capi.EmbeddingDesc()
+    d.input_ids, d.word_emb, d.pos_emb = input_ids.data_ptr(), word_emb.data_ptr(), pos_emb.data_ptr()
+    if segment_ids is not None:
+        assert segment_ids.dtype == torch.int32 and segment_ids.is_contiguous() and type_emb is not None
+        assert type_emb.dtype == word_emb.dtype and type_emb.stride(0) == word_emb.stride(0)
+        d.segment_ids, d.type_emb, d.type_vocab = segment_ids.data_ptr(), type_emb.data_ptr(), type_emb.shape[0]
+    d.gamma, d.beta, d.out = gamma.data_ptr(), beta.data_ptr(), out.data_ptr()
+    d.B, d.S, d.H, d.vocab = B, S, H, word_emb.shape[0]
+    d.ld_table, d.ld_out = word_emb.stride(0), out.reshape(-1, H).stride(0)
+    d.table_dtype, d.out_dtype, d.eps = capi.dtype_code(word_emb.dtype), capi.dtype_code(out.dtype), float(eps)
+    rc = capi.lib().b200_embedding_layernorm_fwd(ctypes.byref(d), capi.stream_ptr())
+    capi.check(rc, "b200_embedding_layernorm_fwd")
+    return out
+
+
+def mask_from_input_mask(input_mask, masked_value=-10000.0, exclude_below=-5000.0):
+    """int32 0/1 `[B,S]` -> (additive fp32 mask `[B,S]`, int32 kv_len `[B]`)."""
+    _require_cuda(input_mask)
+    B, S = input_mask.shape
+    assert input_mask.dtype == torch.int32 and input_mask.is_contiguous()
+    mask_add = torch.empty((B, S), dtype=torch.float32, device=input_mask.device)
+    kv_len = torch.empty((B,), dtype=torch.int32, device=input_mask.device)
+    rc = capi.lib().b200_mask_from_input_mask(input_mask.data_ptr(), B, S, masked_value, exclude_below,
+                                              mask_add.data_ptr(), kv_len.data_ptr(), capi.stream_ptr())
+    capi.check(rc, "b200_mask_from_input_mask")
+    return mask_add, kv_len
+
+
 class Chain:
     """Dependent GEMMs / LayerNorms of an encoder layer in one launch (b200_chain_fwd).
 

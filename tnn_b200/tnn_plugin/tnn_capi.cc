@@ -118,6 +118,30 @@ TNNC_API int tnnc_set_input(void* handle, const char* name, const float* data, i
     return 0;
 }
 
+// The same for an int32 input blob (token ids, segment ids, 0/1 masks: typed graph inputs).
+TNNC_API int tnnc_set_input_i32(void* handle, const char* name, const int32_t* data, int64_t n) {
+    Handle* h = static_cast<Handle*>(handle);
+    BlobMap blobs;
+    Status st = h->inst->GetAllInputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    auto it = blobs.find(name);
+    if (it == blobs.end()) { h->last_error = std::string("no input named ") + name; return -1; }
+    Blob* blob = it->second;
+    const DimsVector dims = blob->GetBlobDesc().dims;
+    if (count(dims) != n) { h->last_error = "input element count mismatch"; return -2; }
+    if (blob->GetBlobDesc().data_type != DATA_TYPE_INT32) { h->last_error = "input blob is not int32"; return -3; }
+    if (h->device == DEVICE_CUDA) {
+        auto mat = std::make_shared<Mat>(DEVICE_NAIVE, NC_INT32, dims, const_cast<int32_t*>(data));
+        MatConvertParam param;
+        st = h->inst->SetInputMat(mat, param, name);
+        if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    } else {
+        BlobHandle bh = blob->GetHandle();
+        std::memcpy(static_cast<char*>(bh.base) + bh.bytes_offset, data, static_cast<size_t>(n) * sizeof(int32_t));
+    }
+    return 0;
+}
+
 TNNC_API int tnnc_forward(void* handle) {
     Handle* h = static_cast<Handle*>(handle);
     Status st = h->inst->Forward();

@@ -44,6 +44,7 @@ def load():
         shim.tnnc_last_error.restype = ctypes.c_char_p
         shim.tnnc_last_error.argtypes = [ctypes.c_void_p]
         shim.tnnc_set_input.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64]
+        shim.tnnc_set_input_i32.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64]
         shim.tnnc_forward.argtypes = [ctypes.c_void_p]
         shim.tnnc_time_forward.restype = ctypes.c_double
         shim.tnnc_time_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
@@ -99,6 +100,11 @@ class Instance:
     def set_input(self, name, arr):
         a = np.ascontiguousarray(arr, dtype=np.float32)
         self._check(self.shim.tnnc_set_input(self.h, name.encode(), a.ctypes.data, a.size), "set_input(%s)" % name)
+
+    def set_input_i32(self, name, arr):
+        a = np.ascontiguousarray(arr, dtype=np.int32)
+        self._check(self.shim.tnnc_set_input_i32(self.h, name.encode(), a.ctypes.data, a.size),
+                    "set_input_i32(%s)" % name)
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
