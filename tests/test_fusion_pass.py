@@ -44,6 +44,25 @@ def test_attention_block_only_and_large_geometry():
     assert [ln.split()[0] for ln in lines].count("FusedLinear") == 4
 
 
+def test_bert_graph_with_frontend_fuses_embedding_and_mask():
+    """int32 inputs -> Gather x2 + Add x2 + LayerNorm and Unsqueeze/Cast/Sub/Mul in front of the encoder layers."""
+    cfg = ms.EncoderConfig(1, 256, 4, 1024)
+    wl = ms.make_workload(cfg, 2, 16, seed=1)
+    fw = ms.make_frontend_workload(256, 2, 16, vocab=100, max_pos=32, seed=2)
+    d = tempfile.mkdtemp(prefix="fuse_bert_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    out = ms.write_tnn_bert_model(fw, wl, proto, model)
+    lines = rt.fuse_report(proto, model)
+    types = [ln.split()[0] for ln in lines]
+    assert types == ["FusedEmbedding", "FusedMask", "FusedLinear", "FusedAttention", "FusedLinear", "LayerNorm",
+                     "FusedLinear", "FusedLinear", "LayerNorm"]
+    emb, mask = lines[0].split(), lines[1].split()
+    assert emb[2:6] == ["input_ids", "segment_ids", "emb_g", "emb_be"] and mask[2] == "input_mask"
+    # the encoder consumes the fused front-end's outputs, and the graph output keeps its name
+    assert lines[2].split()[2] == emb[-1] and lines[3].split()[3] == mask[-1]
+    assert lines[-1].split()[-1] == out
+
+
 def test_precision_high_is_refused():
     with pytest.raises(RuntimeError):
         _fuse(ms.config_workload(1), rt.PRECISION_HIGH)

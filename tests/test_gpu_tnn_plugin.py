@@ -91,3 +91,38 @@ def test_unfusable_graph_fails_loudly(cuda_device):
     proto, model = _files(wl)
     with pytest.raises(RuntimeError):
         rt.Instance(proto, model, device=rt.DEVICE_CUDA, precision=rt.PRECISION_HIGH)
+
+
+def test_bert_graph_with_frontend_matches_x86_instance(cuda_device):
+    """A converted-BERT-shaped graph: int32 input_ids / segment_ids / input_mask -> embedding gathers + LayerNorm and the
+    mask builder -> two encoder layers.  DEVICE_CUDA (FusedEmbedding, FusedMask, fused encoder) against DEVICE_X86."""
+    from oracle import bert_oracle
+    cfg = ms.EncoderConfig(2, 768, 12, 3072)
+    wl = ms.make_workload(cfg, 4, 128, seed=11, randomize_affine=True)
+    fw = ms.make_frontend_workload(768, 4, 128, vocab=5000, type_vocab=2, max_pos=512, seed=12, length_range=(9, 128))
+    d = tempfile.mkdtemp(prefix="plug_bert_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    out_name = ms.write_tnn_bert_model(fw, wl, proto, model)
+    lines = rt.fuse_report(proto, model)
+    types = [ln.split()[0] for ln in lines]
+    assert types[:2] == ["FusedEmbedding", "FusedMask"] and "Gather" not in types and "Cast" not in types
+
+    def run(device, precision):
+        inst = rt.Instance(proto, model, device=device, precision=precision)
+        inst.set_input_i32("input_ids", fw.input_ids)
+        inst.set_input_i32("segment_ids", fw.segment_ids)
+        inst.set_input_i32("input_mask", fw.input_mask)
+        inst.forward()
+        y = inst.get_output(out_name)
+        inst.close()
+        return y
+
+    y = run(rt.DEVICE_CUDA, rt.PRECISION_AUTO)
+    ref = run(rt.DEVICE_X86, rt.PRECISION_HIGH)
+    emb, mask_add = bert_oracle.embedding_frontend(fw)
+    want = bert_oracle.encoder_forward(wl, x=emb, mask_add=mask_add)
+    assert max_abs(ref, want) < 5e-5                 # the reference and the restatement agree on the composed graph
+    assert y.shape == ref.shape
+    assert max_abs(y, ref) <= MAX_ABS_TOL
+    assert cosine(y, ref) >= COS_TOL
+    assert max_abs(valid_rows(y, fw.lengths), valid_rows(ref, fw.lengths)) <= MAX_ABS_TOL

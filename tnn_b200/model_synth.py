@@ -145,8 +145,8 @@ def _raw(a):
             b"".join(struct.pack("<i", d) for d in dims) + a.tobytes())
 
 
-def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"):
-    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name."""
+def _encoder_graph(wl, input_name, mask_name):
+    """Layer lines, resource records and constants of the unfused encoder graph; returns them with the output name."""
     cfg = wl.cfg
     B, S, H = wl.x.shape
     NH, D, F = cfg.heads, cfg.head_dim, cfg.ffn
@@ -198,15 +198,19 @@ def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"
             x = lnorm(p + "ln2", p + "res2", lw.ln2_g, lw.ln2_b)
         else:
             x = a
+    return layers, res, consts, x
+
+
+def _write_files(proto_path, model_path, magic, inputs_line, outputs, layers, res, consts):
     blobs = set()
     for ln in layers:
         t = ln.strip('",').split()
         ni, no = int(t[2]), int(t[3])
         blobs.update(t[4:4 + ni + no])
-    proto = ['"1 %d 1 %d ,"' % (len(blobs), MAGIC),
-             '"%s %d 1 1 %d : %s %d %d %d ,"' % (mask_name, B, S, input_name, B, S, H),
+    proto = ['"1 %d 1 %d ,"' % (len(blobs), magic),
+             '"%s ,"' % inputs_line,
              '" ' + " ".join(sorted(blobs)) + ' ,"',
-             '"%s ,"' % x,
+             '"%s ,"' % " ".join(outputs),
              '" %d ,"' % len(layers)] + layers
     with open(proto_path, "w") as fh:
         fh.write("\n".join(proto) + "\n")
@@ -214,7 +218,15 @@ def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"
     m += struct.pack("<Ii", MAGIC, len(consts)) + b"".join(_pstr(k) + _raw(v) for k, v in consts.items())
     with open(model_path, "wb") as fh:
         fh.write(m)
-    return x
+
+
+def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"):
+    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name."""
+    B, S, H = wl.x.shape
+    layers, res, consts, out = _encoder_graph(wl, input_name, mask_name)
+    _write_files(proto_path, model_path, MAGIC, "%s %d 1 1 %d : %s %d %d %d" % (mask_name, B, S, input_name, B, S, H),
+                 [out], layers, res, consts)
+    return out
 
 
 # --------------------------------------------------------------------------------------------- embedding front-end
@@ -258,6 +270,17 @@ def write_tnn_frontend_model(fw, proto_path, model_path):
     `mask_add`.  Typed (v2) inputs: input_ids, segment_ids, input_mask int32 [B, S].
     Grammar: Gather source/tnn/interpreter/tnn/layer_interpreter/gather_layer_interpreter.cc:23-47, Unsqueeze
     unsqueeze_layer_interpreter.cc:20-30, Cast cast_layer_interpreter.cc:21-25, Sub sub_layer_interpreter.cc:23-47."""
+    layers, res, consts = _frontend_graph(fw)
+    _write_files(proto_path, model_path, MAGIC_RAW, _frontend_inputs(fw), ["emb_out", "mask_add"], layers, res, consts)
+    return "emb_out", "mask_add"
+
+
+def _frontend_inputs(fw):
+    B, S = fw.input_ids.shape
+    return " : ".join("%s 2 %d %d 3" % (n, B, S) for n in ("input_ids", "segment_ids", "input_mask"))
+
+
+def _frontend_graph(fw):
     B, S = fw.input_ids.shape
     H = fw.hidden
     layers, res, consts = [], [], {}
@@ -283,24 +306,19 @@ def write_tnn_frontend_model(fw, proto_path, model_path):
     res.append(head("Sub", "mask_inv") + _raw(np.array([1.0], np.float32)))
     layer("Mul", "mask_add", ["mask_inv"], ["mask_add"], "1")
     res.append(head("Mul", "mask_add") + _raw(np.array([-10000.0], np.float32)))
-    blobs = set()
-    for ln in layers:
-        t = ln.strip('",').split()
-        ni, no = int(t[2]), int(t[3])
-        blobs.update(t[4:4 + ni + no])
-    inputs = " : ".join("%s 2 %d %d 3" % (n, B, S) for n in ("input_ids", "segment_ids", "input_mask"))
-    proto = ['"1 %d 1 %d ,"' % (len(blobs), MAGIC_RAW),
-             '"%s ,"' % inputs,
-             '" ' + " ".join(sorted(blobs)) + ' ,"',
-             '"emb_out mask_add ,"',
-             '" %d ,"' % len(layers)] + layers
-    with open(proto_path, "w") as fh:
-        fh.write("\n".join(proto) + "\n")
-    m = struct.pack("<I", MAGIC) + struct.pack("<i", len(res)) + b"".join(res)
-    m += struct.pack("<Ii", MAGIC, len(consts)) + b"".join(_pstr(k) + _raw(v) for k, v in consts.items())
-    with open(model_path, "wb") as fh:
-        fh.write(m)
-    return "emb_out", "mask_add"
+    return layers, res, consts
+
+
+def write_tnn_bert_model(fw, wl, proto_path, model_path):
+    """Front-end + encoder as one graph, the shape of a converted BERT: int32 inputs input_ids / segment_ids /
+    input_mask [B, S]; `emb_out` feeds the first encoder layer, `mask_add` every attention block.  Returns the output
+    blob name.  (`wl.x` and `wl.mask_add` are not used: the graph computes them.)"""
+    assert fw.hidden == wl.cfg.hidden and fw.input_ids.shape == wl.x.shape[:2]
+    l1, r1, c1 = _frontend_graph(fw)
+    l2, r2, c2, out = _encoder_graph(wl, "emb_out", "mask_add")
+    c1.update(c2)
+    _write_files(proto_path, model_path, MAGIC_RAW, _frontend_inputs(fw), [out], l1 + l2, r1 + r2, c1)
+    return out
 
 
 # --------------------------------------------------------------------------------------------- FLOP accounting

@@ -180,6 +180,114 @@ Status B200CudaFusedAttentionLayerAcc::Forward(const std::vector<Blob*>& inputs,
 }
 B200_REGISTER_CUDA_ACC(FusedAttention, LAYER_B200_FUSED_ATTENTION)
 
+// ================================================================= FusedEmbedding
+B200_DECLARE_CUDA_ACC(FusedEmbedding)
+    Status Upload(RawBuffer& table, int64_t rows, int64_t H, int dtype, void** out);
+
+    void* word_ = nullptr;   // [vocab, H] compute dtype
+    void* type_ = nullptr;   // [type_vocab, H]
+    void* pos_  = nullptr;   // [S, H]
+    int64_t vocab_ = 0, type_vocab_ = 0, pos_rows_ = 0;
+};
+
+// fp32 host table -> device, converted to the compute dtype (tables are read once per token: half the bytes)
+Status B200CudaFusedEmbeddingLayerAcc::Upload(RawBuffer& table, int64_t rows, int64_t H, int dtype, void** out) {
+    if (table.GetDataType() != DATA_TYPE_FLOAT || table.GetDataCount() != rows * H)
+        return Status(TNNERR_PARAM_ERR, "FusedEmbedding: tables must be fp32 [rows, H]");
+    cudaStream_t stream = context_->GetStream();
+    size_t cap = 0;
+    RETURN_ON_NEQ(EnsureBuffer(out, &cap, static_cast<size_t>(rows) * H * 2), TNN_OK);
+    void* tmp = nullptr;
+    RETURN_ON_NEQ(device_->Allocate(&tmp, static_cast<size_t>(rows) * H * sizeof(float)), TNN_OK);
+    Status st = TNN_OK;
+    if (cudaMemcpyAsync(tmp, table.force_to<float*>(), static_cast<size_t>(rows) * H * sizeof(float),
+                        cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+        cudaGetLastError();
+        st = Status(TNNERR_CUDA_MEMCPY_ERROR, "FusedEmbedding: table upload failed");
+    }
+    if (st == TNN_OK) st = B200ToStatus(b200_convert(tmp, B200_F32, *out, dtype, rows * H, stream), "b200_convert");
+    cudaStreamSynchronize(stream);   // Init time: the staging copy is released right away
+    device_->Free(tmp);
+    return st;
+}
+
+Status B200CudaFusedEmbeddingLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                            const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    auto* p = dynamic_cast<FusedEmbeddingLayerParam*>(param);
+    auto* r = dynamic_cast<FusedEmbeddingLayerResource*>(resource);
+    if (!p || !r || p->hidden <= 0) return Status(TNNERR_PARAM_ERR, "FusedEmbedding: param/resource missing");
+    if (inputs.size() != 4 || inputs[0]->GetBlobDesc().data_type != DATA_TYPE_INT32 ||
+        inputs[1]->GetBlobDesc().data_type != DATA_TYPE_INT32)
+        return Status(TNNERR_PARAM_ERR, "FusedEmbedding: ids and segment ids must be int32 blobs");
+    if (inputs[2]->GetBlobDesc().data_type != DATA_TYPE_FLOAT || inputs[3]->GetBlobDesc().data_type != DATA_TYPE_FLOAT)
+        return Status(TNNERR_PARAM_ERR, "FusedEmbedding: scale and bias must be fp32");
+    const int64_t H = p->hidden;
+    vocab_      = r->word.GetDataCount() / H;
+    type_vocab_ = r->type.GetDataCount() / H;
+    pos_rows_   = r->position.GetDataCount() / H;
+    RETURN_ON_NEQ(Upload(r->word, vocab_, H, p->compute_dtype, &word_), TNN_OK);
+    RETURN_ON_NEQ(Upload(r->type, type_vocab_, H, p->compute_dtype, &type_), TNN_OK);
+    RETURN_ON_NEQ(Upload(r->position, pos_rows_, H, p->compute_dtype, &pos_), TNN_OK);
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaFusedEmbeddingLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    if (dims.size() != 2 || dims[1] > pos_rows_)
+        return Status(TNNERR_PARAM_ERR, "FusedEmbedding: sequence longer than the position table of the graph");
+    return TNN_OK;
+}
+
+Status B200CudaFusedEmbeddingLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedEmbeddingLayerParam*>(param_);
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    B200EmbeddingDesc d;
+    std::memset(&d, 0, sizeof(d));
+    d.input_ids   = static_cast<const int32_t*>(DevicePtr(inputs[0]));
+    d.segment_ids = static_cast<const int32_t*>(DevicePtr(inputs[1]));
+    d.word_emb = word_; d.type_emb = type_; d.pos_emb = pos_;
+    d.gamma = static_cast<const float*>(DevicePtr(inputs[2]));
+    d.beta  = static_cast<const float*>(DevicePtr(inputs[3]));
+    d.out = DevicePtr(outputs[0]);
+    d.B = dims[0]; d.S = dims[1]; d.H = p->hidden;
+    d.vocab = vocab_; d.type_vocab = type_vocab_;
+    d.ld_table = p->hidden; d.ld_out = p->hidden;
+    d.table_dtype = p->compute_dtype;
+    d.out_dtype   = B200DataType(outputs[0]->GetBlobDesc().data_type);
+    d.eps = p->eps;
+    if (d.out_dtype < 0) return Status(TNNERR_PARAM_ERR, "FusedEmbedding: unsupported output data type");
+    return B200ToStatus(b200_embedding_layernorm_fwd(&d, context_->GetStream()), "b200_embedding_layernorm_fwd");
+}
+B200_REGISTER_CUDA_ACC(FusedEmbedding, LAYER_B200_FUSED_EMBEDDING)
+
+// ================================================================= FusedMask
+B200_DECLARE_CUDA_ACC(FusedMask)
+};
+
+Status B200CudaFusedMaskLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                       const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    if (!dynamic_cast<FusedMaskLayerParam*>(param)) return Status(TNNERR_PARAM_ERR, "FusedMask: param missing");
+    if (inputs[0]->GetBlobDesc().data_type != DATA_TYPE_INT32 || outputs[0]->GetBlobDesc().data_type != DATA_TYPE_FLOAT)
+        return Status(TNNERR_PARAM_ERR, "FusedMask: int32 in, fp32 out");
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaFusedMaskLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return TNN_OK;
+}
+
+Status B200CudaFusedMaskLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedMaskLayerParam*>(param_);
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    return B200ToStatus(b200_mask_from_input_mask(static_cast<const int32_t*>(DevicePtr(inputs[0])), dims[0], dims[1],
+                                                  p->masked_value, -5000.0f, static_cast<float*>(DevicePtr(outputs[0])),
+                                                  nullptr, context_->GetStream()),
+                        "b200_mask_from_input_mask");
+}
+B200_REGISTER_CUDA_ACC(FusedMask, LAYER_B200_FUSED_MASK)
+
 // ================================================================= LayerNorm
 // The graph's own LayerNorm layer (gamma, beta = input blobs 1 and 2, uploaded by ReloadConstantBlobs).  The reference's
 // CUDA acc (source/tnn/device/cuda/acc/cuda_layer_norm_layer_acc.cu:28-146) reads gamma/beta in the activation's

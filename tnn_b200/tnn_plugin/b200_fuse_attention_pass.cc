@@ -11,7 +11,10 @@
 //   2. MatMul -> Add(bias) -> GELU            becomes FusedLinear(epilogue GELU)
 //   3. MatMul -> Add(bias) -> Add(residual)   becomes FusedLinear(epilogue residual), either operand order of the Add
 //   4. MatMul -> Add(bias)                    becomes FusedLinear
-// LayerNorm layers stay as they are (the device has an acc for them).
+//   5. the embedding front-end  Gather(word) + Gather(segment) -> Add -> Add(position slice) -> LayerNorm
+//                                              becomes FusedEmbedding(ids, segments, gamma, beta)
+//   6. the mask builder  Unsqueeze(1,2) -> Cast(float) -> Sub(1 - m) -> Mul(c)   becomes FusedMask(input_mask)
+// Other LayerNorm layers stay as they are (the device has an acc for them).
 //
 // The matcher compares layer types, input/output counts and topology only, so everything else — permute orders,
 // reshape targets, softmax axis, weight positions, bias shapes — is validated in the generator, which declines
@@ -197,13 +200,136 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
 
     // Already fused (the pass must be idempotent: Instance::Init may run the optimizers twice on one structure).
     for (auto& l : structure->layers)
-        if (l->type == LAYER_B200_FUSED_LINEAR || l->type == LAYER_B200_FUSED_ATTENTION) return TNN_OK;
+        if (l->type == LAYER_B200_FUSED_LINEAR || l->type == LAYER_B200_FUSED_ATTENTION ||
+            l->type == LAYER_B200_FUSED_EMBEDDING || l->type == LAYER_B200_FUSED_MASK)
+            return TNN_OK;
 
     std::shared_ptr<Graph> graph = std::make_shared<Graph>();
     Status status = graph->fromInterpreted(structure, resource);
     if (status != TNN_OK) {
         LOGE("%s", status.description().c_str());
         return TNN_OK;   // leave the graph alone, as the reference's passes do
+    }
+
+    // ---------------------------------------------------------------- 5. embedding front-end
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%ids, %seg, %g, %be):
+                %w   = Gather(%ids)
+                %t   = Gather(%seg)
+                %wt  = Add(%w, %t)
+                %wtp = Add(%wt)
+                %ln  = LayerNorm(%wtp, %g, %be)
+                return (%ln)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 4 || in->outputs().size() != 1) return nullptr;
+            auto node = [&](const char* n) { return in->getNodeByTensorName(std::string("@") + n); };
+            // table rows gathered along axis 0 by a blob of indices; the table is the layer's resource
+            auto table = [&](const std::shared_ptr<Node>& n, RawBuffer* out) {
+                if (!n || n->info->inputs.size() != 1) return false;
+                auto gp = std::dynamic_pointer_cast<GatherLayerParam>(n->info->param);
+                if (!gp || gp->axis != 0 || !gp->data_in_resource || gp->indices_in_resource) return false;
+                auto it = resource->resource_map.find(n->info->name);
+                if (it == resource->resource_map.end()) return false;
+                auto gr = std::dynamic_pointer_cast<GatherLayerResource>(it->second);
+                if (!gr || gr->data.GetDataType() != DATA_TYPE_FLOAT || gr->data.GetBufferDims().size() != 2) return false;
+                *out = gr->data;
+                return true;
+            };
+            RawBuffer word, type;
+            if (!table(node("w"), &word) || !table(node("t"), &type)) return nullptr;
+            const int H = word.GetBufferDims()[1];
+            if (type.GetBufferDims()[1] != H || H <= 0 || (H % 8) != 0 || H > 1024) return nullptr;
+            auto wt = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(node("wt")->info->param);
+            if (!wt || wt->weight_input_index != -1 || node("wt")->info->inputs.size() != 2) return nullptr;
+            // position rows: a constant [1, S, H] (or [S, H]) added to every sequence
+            auto wtp = node("wtp");
+            auto wtp_param = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(wtp->info->param);
+            if (!wtp_param || wtp->info->inputs.size() != 1) return nullptr;
+            auto pr = resource->resource_map.find(wtp->info->name);
+            if (pr == resource->resource_map.end()) return nullptr;
+            auto pos_res = std::dynamic_pointer_cast<EltwiseLayerResource>(pr->second);
+            if (!pos_res || pos_res->element_handle.GetDataType() != DATA_TYPE_FLOAT) return nullptr;
+            const DimsVector pd = pos_res->element_handle.GetBufferDims();
+            if (pd.size() < 2 || pd.back() != H || pos_res->element_handle.GetDataCount() % H != 0) return nullptr;
+            if (pd.size() == 3 && pd[0] != 1) return nullptr;
+            if (pd.size() > 3) return nullptr;
+            auto ln = std::dynamic_pointer_cast<LayerNormLayerParam>(node("ln")->info->param);
+            if (!ln || ln->reduce_dims_size != 1) return nullptr;
+
+            auto g = std::make_shared<Graph>();
+            const std::vector<std::string> ins = {"in_0", "in_1", "in_2", "in_3"};
+            for (auto& n : ins) g->getNodeOrCreatePlaceHolder(n);
+            const std::string out = node("ln")->info->name + "_b200_emb";
+            if (g->createNode(LAYER_B200_FUSED_EMBEDDING, ins, {out}) != TNN_OK) return nullptr;
+            auto fused = g->getNodeByTensorName(out);
+            if (!fused || fused->createParam<FusedEmbeddingLayerParam>() != TNN_OK) return nullptr;
+            auto fp           = fused->param<FusedEmbeddingLayerParam>();
+            fp->type          = kFusedEmbeddingTypeName;
+            fp->name          = out;
+            fp->hidden        = H;
+            fp->eps           = ln->eps;
+            fp->compute_dtype = dtype;
+            if (fused->createResource<FusedEmbeddingLayerResource>() != TNN_OK) return nullptr;
+            auto fr      = fused->resource<FusedEmbeddingLayerResource>();
+            fr->name     = out;
+            fr->word     = word;
+            fr->type     = type;
+            fr->position = pos_res->element_handle;
+            if (g->setInputsOrder(ins) != TNN_OK) return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 6. mask builder
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%m):
+                %u = Unsqueeze(%m)
+                %f = Cast(%u)
+                %s = Sub(%f)
+                %o = Mul(%s)
+                return (%o)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 1 || in->outputs().size() != 1) return nullptr;
+            auto node = [&](const char* n) { return in->getNodeByTensorName(std::string("@") + n); };
+            auto up = std::dynamic_pointer_cast<UnsqueezeLayerParam>(node("u")->info->param);
+            if (!up || up->axes != std::vector<int>({1, 2})) return nullptr;
+            auto cp = std::dynamic_pointer_cast<CastLayerParam>(node("f")->info->param);
+            if (!cp || cp->to != DATA_TYPE_FLOAT) return nullptr;
+            auto scalar = [&](const std::shared_ptr<Node>& n, int want_index, float* value) {
+                auto bp = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(n->info->param);
+                if (!bp || n->info->inputs.size() != 1) return false;
+                if (want_index >= 0 && bp->weight_input_index != want_index) return false;
+                auto it = resource->resource_map.find(n->info->name);
+                if (it == resource->resource_map.end()) return false;
+                auto er = std::dynamic_pointer_cast<EltwiseLayerResource>(it->second);
+                if (!er || er->element_handle.GetDataCount() != 1 || er->element_handle.GetDataType() != DATA_TYPE_FLOAT)
+                    return false;
+                *value = er->element_handle.force_to<float*>()[0];
+                return true;
+            };
+            float one = 0.f, masked_value = 0.f;
+            if (!scalar(node("s"), 0, &one) || one != 1.0f) return nullptr;    // the constant is the minuend: 1 - m
+            if (!scalar(node("o"), -1, &masked_value)) return nullptr;         // multiplication commutes
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            const std::string out = node("o")->info->name + "_b200_mask";
+            if (g->createNode(LAYER_B200_FUSED_MASK, {"in_0"}, {out}) != TNN_OK) return nullptr;
+            auto fused = g->getNodeByTensorName(out);
+            if (!fused || fused->createParam<FusedMaskLayerParam>() != TNN_OK) return nullptr;
+            auto fp          = fused->param<FusedMaskLayerParam>();
+            fp->type         = kFusedMaskTypeName;
+            fp->name         = out;
+            fp->masked_value = masked_value;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
     }
 
     // ---------------------------------------------------------------- 1. attention

@@ -16,6 +16,8 @@ struct B200LayerTypeNames {
         auto& m = const_cast<std::map<std::string, LayerType>&>(GetGlobalLayerTypeMap());
         m[kFusedLinearTypeName]    = LAYER_B200_FUSED_LINEAR;
         m[kFusedAttentionTypeName] = LAYER_B200_FUSED_ATTENTION;
+        m[kFusedEmbeddingTypeName] = LAYER_B200_FUSED_EMBEDDING;
+        m[kFusedMaskTypeName]      = LAYER_B200_FUSED_MASK;
     }
 };
 static B200LayerTypeNames g_b200_layer_type_names;
@@ -89,5 +91,56 @@ Status B200FusedAttentionLayer::InferOutputShape(bool ignore_error) {
     return TNN_OK;
 }
 REGISTER_LAYER(B200FusedAttention, LAYER_B200_FUSED_ATTENTION);
+
+// ---------------------------------------------------------------- FusedEmbedding
+DECLARE_LAYER(B200FusedEmbedding, LAYER_B200_FUSED_EMBEDDING);
+
+Status B200FusedEmbeddingLayer::InferOutputDataType() {
+    BaseLayer::InferOutputDataType();
+    auto* p = dynamic_cast<FusedEmbeddingLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    for (auto* b : output_blobs_) b->GetBlobDesc().data_type = TnnDataType(p->compute_dtype);
+    return TNN_OK;
+}
+
+// ids [B, S] -> [B, S, H] (the Gather rule: index dims followed by the table's trailing dims,
+// source/tnn/layer/gather_layer.cc:49-90)
+Status B200FusedEmbeddingLayer::InferOutputShape(bool ignore_error) {
+    BaseLayer::InferOutputShape(ignore_error);
+    auto* p = dynamic_cast<FusedEmbeddingLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    if (input_blobs_.size() != 4) return Status(TNNERR_PARAM_ERR, "FusedEmbedding: needs ids, segments, gamma, beta");
+    DimsVector dims = input_blobs_[0]->GetBlobDesc().dims;
+    if (dims.size() != 2 || input_blobs_[1]->GetBlobDesc().dims != dims) {
+        LOGE_IF(!ignore_error, "FusedEmbedding: ids and segment ids must both be [B, S]\n");
+        return Status(TNNERR_PARAM_ERR, "FusedEmbedding: ids and segment ids must both be [B, S]");
+    }
+    dims.push_back(p->hidden);
+    output_blobs_[0]->GetBlobDesc().dims = dims;
+    return TNN_OK;
+}
+REGISTER_LAYER(B200FusedEmbedding, LAYER_B200_FUSED_EMBEDDING);
+
+// ---------------------------------------------------------------- FusedMask
+DECLARE_LAYER(B200FusedMask, LAYER_B200_FUSED_MASK);
+
+Status B200FusedMaskLayer::InferOutputDataType() {
+    BaseLayer::InferOutputDataType();
+    for (auto* b : output_blobs_) b->GetBlobDesc().data_type = DATA_TYPE_FLOAT;
+    return TNN_OK;
+}
+
+// [B, S] -> [B, 1, 1, S] (Unsqueeze at axes 1 and 2)
+Status B200FusedMaskLayer::InferOutputShape(bool ignore_error) {
+    BaseLayer::InferOutputShape(ignore_error);
+    const DimsVector dims = input_blobs_[0]->GetBlobDesc().dims;
+    if (dims.size() != 2) {
+        LOGE_IF(!ignore_error, "FusedMask: input mask must be [B, S]\n");
+        return Status(TNNERR_PARAM_ERR, "FusedMask: input mask must be [B, S]");
+    }
+    output_blobs_[0]->GetBlobDesc().dims = {dims[0], 1, 1, dims[1]};
+    return TNN_OK;
+}
+REGISTER_LAYER(B200FusedMask, LAYER_B200_FUSED_MASK);
 
 }  // namespace TNN_NS

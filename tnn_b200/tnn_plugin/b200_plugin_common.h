@@ -24,8 +24,12 @@ namespace TNN_NS {
 // Free slots between LAYER_CBAM_FUSED_POOLING (801) and LAYER_DUMMY_TYPE (1000).
 static const LayerType LAYER_B200_FUSED_LINEAR    = static_cast<LayerType>(810);
 static const LayerType LAYER_B200_FUSED_ATTENTION = static_cast<LayerType>(811);
+static const LayerType LAYER_B200_FUSED_EMBEDDING = static_cast<LayerType>(812);
+static const LayerType LAYER_B200_FUSED_MASK      = static_cast<LayerType>(813);
 static const char* const kFusedLinearTypeName     = "FusedLinear";
 static const char* const kFusedAttentionTypeName  = "FusedAttention";
+static const char* const kFusedEmbeddingTypeName  = "FusedEmbedding";
+static const char* const kFusedMaskTypeName       = "FusedMask";
 
 // y = epilogue(x . W + bias (+ residual)); replaces MatMul -> Add(bias) [-> GELU | -> Add(residual)].
 // Inputs: x [, residual].  Several matched MatMul+Add pairs that share x (Q, K, V) are merged: their weights are kept
@@ -54,6 +58,29 @@ struct FusedAttentionLayerParam : public LayerParam {
     float mask_exclude_below = -5000.0f;  // mask values at or below this drop the key exactly
     int compute_dtype        = B200_F16;
     PARAM_COPY(FusedAttentionLayerParam)
+};
+
+// out = LayerNorm(word_emb[ids] + type_emb[segments] + pos_emb[position]); replaces
+// Gather(word) + Gather(segment) -> Add -> Add(position slice) -> LayerNorm in front of the first encoder layer.
+// Inputs: input_ids [B,S] int32, segment_ids [B,S] int32, gamma [H], beta [H] (the LayerNorm's constant inputs).
+struct FusedEmbeddingLayerParam : public LayerParam {
+    int hidden        = 0;
+    float eps         = 1e-12f;
+    int compute_dtype = B200_F16;   // table and output type
+    PARAM_COPY(FusedEmbeddingLayerParam)
+};
+
+struct FusedEmbeddingLayerResource : public LayerResource {
+    RawBuffer word;       // fp32 [vocab, H]       (storage shared with the matched Gather's resource)
+    RawBuffer type;       // fp32 [type_vocab, H]
+    RawBuffer position;   // fp32 [1, S, H] or [S, H]: the position rows 0..S-1
+};
+
+// mask_add = (1 - input_mask) * masked_value as fp32 [B,1,1,S]; replaces Unsqueeze -> Cast -> Sub -> Mul.
+// Input: input_mask [B,S] int32.
+struct FusedMaskLayerParam : public LayerParam {
+    float masked_value = -10000.0f;
+    PARAM_COPY(FusedMaskLayerParam)
 };
 
 inline DataType TnnDataType(int b200_dtype) {
