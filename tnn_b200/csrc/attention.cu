@@ -1,6 +1,6 @@
 // Fused multi-head attention for sm_100a, head_dim 64:  out = softmax(scale * Q K^T + mask) V, flash-style: no score
 // matrix ever leaves the SM.  Two kernels share the building blocks below:
-//   attention_single_kernel   S <= 128: persistent CTAs, one (sequence, head) item at a time, next item prefetched;
+//   attention_single_kernel   S <= 128: persistent CTAs (four per SM), one (sequence, head) item at a time;
 //   attention_pingpong_kernel S  > 128: two 128-query tiles per CTA in ping-pong over a ring of 128-key tiles.
 //
 //   TMA   : Q, K, V tiles [128 x 64] straight out of the token-major QKV activation (the head split of the unfused
@@ -459,33 +459,35 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 
 // ---------------------------------------------------------------------------------------------------------------
 // Sequences of at most 128 tokens (the benchmark's S = 128): one key tile per (sequence, head), so no running
-// rescale.  Persistent CTAs (two per SM) walk the (sequence, head) items with a grid stride; each CTA owns two
-// shared-memory sets of Q|K|V (48 KB each) and loads the next item's tiles while it works on the current one, so
-// that after the first item the chain QK^T -> softmax -> PV -> store never waits for HBM/L2 latency.
-//   * P (128 x 128 half) overlays the Q and K tiles of its set, dead once S = Q K^T has completed;
-//   * O (TMEM columns 0..63) overlays S, dead once the softmax has read it;
+// rescale.  An item is tiny (4.2 MFLOP on 48 KB of operands) and its steps depend on each other (loads -> QK^T ->
+// max sweep -> exp sweep -> PV -> output), so throughput comes from overlapping items: persistent CTAs of 128 threads,
+// four per SM (50 KB of shared memory and 128 TMEM columns each), walk the (sequence, head) items with a grid stride.
+//   * TMEM columns: S in [0, 32*chunks); P (half precision, the A operand of the PV UMMA) is written over S columns
+//     [0, 64) chunk by chunk — a thread has read the scores a P chunk replaces before it writes it; O in [64, 128),
+//     scores that are dead by then;
 //   * only ceil(kv_len / 32) 32-key chunks are computed: QK^T runs with N = 32*chunks, the softmax reads that many
 //     chunks, PV runs 2*chunks k-steps — padded tails of short sequences cost nothing;
-//   * the output tile goes through shared memory (swizzled, overlaying P) and one TMA store per item, clipped at
-//     row S; the store is only waited for when its set is about to be refilled.
-constexpr int S1_SET_BYTES = 3 * TILE_BYTES;
-constexpr int S1_OFF_MASK = 2 * S1_SET_BYTES;
+//   * when PV has completed all three operand tiles are dead: the next item's Q and K loads are issued at once, the
+//     output tile is staged (swizzled) in the V tile and leaves through one TMA store, clipped at row S, and the next
+//     V load follows as soon as that store has read its source.
+constexpr int S1_OFF_MASK = 3 * TILE_BYTES;
 constexpr int S1_OFF_BAR = S1_OFF_MASK + TK * 4;
 constexpr int S1_SMEM = S1_OFF_BAR + 64;
 constexpr int S1_TMEM_COLS = 128;
+constexpr int S1_CTAS_PER_SM = 4;
 
 template <int DT>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+__global__ void __launch_bounds__(kAttnThreads, S1_CTAS_PER_SM)
 attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                         const AttnParams p, const int num_items) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S1_OFF_BAR);
-    uint64_t* bar_qk = bars + 0;   // [2] one per set
-    uint64_t* bar_v = bars + 2;    // [2]
-    uint64_t* bar_s = bars + 4;
-    uint64_t* bar_o = bars + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    uint64_t* bar_qk = bars + 0;
+    uint64_t* bar_v = bars + 1;
+    uint64_t* bar_s = bars + 2;
+    uint64_t* bar_o = bars + 3;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* mask_s = reinterpret_cast<float*>(smem + S1_OFF_MASK);
 
@@ -497,10 +499,8 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         return;
     }
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bar_qk[i], 1);
-            mbar_init(&bar_v[i], 1);
-        }
+        mbar_init(bar_qk, 1);
+        mbar_init(bar_v, 1);
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
         *abort_flag = 0;
@@ -519,29 +519,38 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_row = tmem_base + lane_field;   // this thread's TMEM lane (= query row), column 0
     pdl_launch_dependents();
     pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
 
-    auto load_item = [&](int item, int set) {   // tid 0 only
+    auto load_qk = [&](int item) {   // tid 0 only
         const int bb = item / p.heads, hh = item % p.heads;
-        uint8_t* base = smem + set * S1_SET_BYTES;
-        mbar_expect_tx(&bar_qk[set], 2 * TILE_BYTES);
-        tma_load_3d(base + OFF_Q, &tm_q, &bar_qk[set], hh * HD, 0, bb);
-        tma_load_3d(base + OFF_K, &tm_k, &bar_qk[set], hh * HD, 0, bb);
-        mbar_expect_tx(&bar_v[set], TILE_BYTES);
-        tma_load_3d(base + OFF_V, &tm_v, &bar_v[set], hh * HD, 0, bb);
+        mbar_expect_tx(bar_qk, 2 * TILE_BYTES);
+        tma_load_3d(smem + OFF_Q, &tm_q, bar_qk, hh * HD, 0, bb);
+        tma_load_3d(smem + OFF_K, &tm_k, bar_qk, hh * HD, 0, bb);
     };
-    if (tid == 0 && static_cast<int>(blockIdx.x) < num_items) load_item(blockIdx.x, 0);
+    auto load_v = [&](int item) {    // tid 0 only
+        const int bb = item / p.heads, hh = item % p.heads;
+        mbar_expect_tx(bar_v, TILE_BYTES);
+        tma_load_3d(smem + OFF_V, &tm_v, bar_v, hh * HD, 0, bb);
+    };
+    // UMMA descriptors of the three tiles (tid 0 issues): built once
+    const uint64_t desc_q = make_smem_desc_sw128(smem_u32(smem + OFF_Q));
+    const uint64_t desc_k = make_smem_desc_sw128(smem_u32(smem + OFF_K));
+    const uint64_t desc_v = make_smem_desc_sw128(smem_u32(smem + OFF_V));
+    const uint32_t idesc_qk_base = p.idesc_qk & ~(0x3Fu << 17);
+    const uint32_t idesc_pv = p.idesc_pv;
+    if (tid == 0 && static_cast<int>(blockIdx.x) < num_items) {
+        load_qk(blockIdx.x);
+        load_v(blockIdx.x);
+    }
 
     bool ok = true;
     uint32_t it = 0;
     for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++it) {
-        const int set = it & 1u;
-        const uint32_t ph_set = (it >> 1) & 1u;
         const uint32_t ph = it & 1u;
         const int b = item / p.heads;
         const int head = item % p.heads;
-        uint8_t* sbase = smem + set * S1_SET_BYTES;
 
         int kv_eff = p.S;
         bool additive_only = (p.mask_add == nullptr);
@@ -565,21 +574,12 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const bool plain = __syncthreads_and(tid >= n_chunks * 32 || mask_s[tid] == 0.f) != 0 && p.scale_log2 > 0.f;
 
         if (tid == 0) {
-            // Prefetch the next item into the other set; that set's last reader is the output store of the previous
-            // item, which must have drained it.
-            const int next = item + gridDim.x;
-            if (next < num_items) {
-                tma_store_wait_read<0>();
-                load_item(next, set ^ 1);
-            }
-            if (mbar_wait(&bar_qk[set], ph_set, abort_flag)) {
+            if (mbar_wait(bar_qk, ph, abort_flag)) {
                 tcgen05_fence_after();
-                const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_Q));
-                const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_K));
-                const uint32_t idesc = (p.idesc_qk & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_chunks * 4) << 17);
+                const uint32_t idesc = idesc_qk_base | (static_cast<uint32_t>(n_chunks * 4) << 17);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    umma_f16_ss(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, k != 0 ? 1u : 0u);
+                    umma_f16_ss(tmem_base, desc_q + 2u * k, desc_k + 2u * k, idesc, k != 0 ? 1u : 0u);
                 umma_commit(bar_s);
             }
         }
@@ -592,7 +592,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_32x32b_x32(t_row + c * 32, r);
                 tmem_ld_wait(r);
                 if (plain) {
 #pragma unroll
@@ -620,7 +620,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_32x32b_x32(t_row + c * 32, r);
                 tmem_ld_wait(r);
                 float pv[32];
                 if (plain) {
@@ -647,46 +647,42 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                     }
                     l_sum += (ps[0] + ps[1]) + (ps[2] + ps[3]);
                 }
-                uint8_t* prow = sbase + (c >> 1) * TILE_BYTES + tid * 128;   // P overlays Q (keys 0..63), K (64..127)
+                // P chunk c -> TMEM columns [16c, 16c + 16): two keys per 32-bit column.  Those columns held the
+                // scores of keys 32*(c/2) .. which this thread consumed above or in an earlier turn of this loop.
+                uint32_t pk[16];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 qv;
-                    qv.x = pack2t<DT>(pv[g * 8 + 0], pv[g * 8 + 1]);
-                    qv.y = pack2t<DT>(pv[g * 8 + 2], pv[g * 8 + 3]);
-                    qv.z = pack2t<DT>(pv[g * 8 + 4], pv[g * 8 + 5]);
-                    qv.w = pack2t<DT>(pv[g * 8 + 6], pv[g * 8 + 7]);
-                    const int chunk = ((c & 1) * 4 + g) ^ (tid & 7);
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) = qv;
-                }
+                for (int e = 0; e < 16; ++e) pk[e] = pack2t<DT>(pv[2 * e], pv[2 * e + 1]);
+                tmem_st_32x32b_x16(t_row + c * 16, pk);
             }
         }
-        fence_async_proxy_shared();
+        tmem_st_wait();
         tcgen05_fence_before();
         __syncthreads();
 
         if (tid == 0) {
             tcgen05_fence_after();
-            if (mbar_wait(&bar_v[set], ph_set, abort_flag)) {
+            if (mbar_wait(bar_v, ph, abort_flag)) {
                 tcgen05_fence_after();
                 const int ksteps = n_chunks * 2;
-                for (int k = 0; k < ksteps; ++k) {
-                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sbase + (k >> 2) * TILE_BYTES)) + 2u * (k & 3);
-                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sbase + OFF_V + k * 2048));
-                    umma_f16_ss(tmem_base, a_desc, b_desc, p.idesc_pv, k != 0 ? 1u : 0u);   // O overlays S
-                }
+                for (int k = 0; k < ksteps; ++k)
+                    umma_f16_ts(tmem_base + 64, tmem_base + k * 8, desc_v + static_cast<uint64_t>(k * (2048 >> 4)),
+                                idesc_pv, k != 0 ? 1u : 0u);
                 umma_commit(bar_o);
             }
         }
         if (!mbar_wait(bar_o, ph, abort_flag)) { ok = false; break; }
+        // Q, K, V are dead now: the next item's Q and K start travelling while this item's output is written
+        const int next = item + gridDim.x;
+        if (tid == 0 && next < num_items) load_qk(next);
         __syncwarp();
         tcgen05_fence_after();
         {
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-            uint8_t* orow = sbase + tid * 128;   // output tile overlays P's first half (PV has completed)
+            uint8_t* orow = smem + OFF_V + tid * 128;   // output tile staged in the V tile
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + lane_field + c * 32, r);
+                tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
                 tmem_ld_wait(r);
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -705,13 +701,18 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         __syncthreads();   // also orders this item's TMEM reads before the next item's UMMAs
         if (tid == 0) {
             asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                         ::"l"(reinterpret_cast<uint64_t>(&tm_o)), "r"(smem_u32(sbase)), "r"(head * HD), "r"(0), "r"(b)
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_o)), "r"(smem_u32(smem + OFF_V)), "r"(head * HD), "r"(0),
+                           "r"(b)
                          : "memory");
             tma_store_commit();
+            if (next < num_items) {
+                tma_store_wait_read<0>();   // the store has read the staged tile: V may be overwritten
+                load_v(next);
+            }
         }
     }
     if (tid == 0) {
-        if (ok) tma_store_wait_all<0>();
+        if (ok) tma_store_wait_read<0>();
         else for (int i = 0; i < 64; ++i) nanosleep(10000);   // let copies in flight land
     }
     tcgen05_fence_before();
@@ -790,7 +791,7 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         if (items > 0x7fffffff) return B200_ERR_UNSUPPORTED;
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const long long grid1 = items < 2ll * sms ? items : 2ll * sms;   // two persistent CTAs per SM
+        const long long grid1 = items < 1ll * S1_CTAS_PER_SM * sms ? items : 1ll * S1_CTAS_PER_SM * sms;
         const cudaStream_t st = static_cast<cudaStream_t>(stream_);
         if (d->dtype == B200_F16)
             launch_kernel(attention_single_kernel<B200_F16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
@@ -913,7 +914,7 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
         const long long items = static_cast<long long>(d->heads) * d->B;
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const long long grid1 = items < 2ll * sms ? items : 2ll * sms;
+        const long long grid1 = items < 1ll * S1_CTAS_PER_SM * sms ? items : 1ll * S1_CTAS_PER_SM * sms;
         if (d->dtype == B200_F16)
             attention_single_kernel<B200_F16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
                 tq, tk, tv, to, p, static_cast<int>(items));
