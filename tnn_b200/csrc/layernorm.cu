@@ -110,8 +110,11 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(B200LayerNormDesc d)
 // shared memory (the generic kernel re-reads 4x more gamma/beta bytes than activation bytes per row), and every warp
 // has the next row's loads in flight while it reduces the current one, so that with 4 blocks per SM about 64 rows
 // (100 KB) per SM are in flight — enough to cover HBM latency at full bandwidth.
-template <int NV, bool F32IN>
-__global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm_rows_kernel(B200LayerNormDesc d) {
+// RESID compiles the residual operand in; without it (the encoder path: the residual is added in the GEMM epilogue)
+// the kernel fits 64 registers and four blocks per SM — LayerNorm at these sizes is latency-bound per warp, so its
+// speed is the number of resident warps.
+template <int NV, bool F32IN, bool RESID>
+__global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4)) add_layernorm_rows_kernel(B200LayerNormDesc d) {
     extern __shared__ float gb[];   // gamma[H] | beta[H]
     const int lane = threadIdx.x & 31;
     const int H = static_cast<int>(d.H);
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
     const int groups = H >> 3;
     constexpr bool f32_in = F32IN;
     constexpr int Q = F32IN ? 2 : 1;   // 16-byte pieces per group of 8 elements
-    uint4 raw[NV][Q], rres[NV][Q];
+    uint4 raw[NV][Q], rres[RESID ? NV : 1][Q];
     auto fetch = [&](long long row) {
 #pragma unroll
         for (int g = 0; g < NV; ++g) {
@@ -130,14 +133,14 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
                     const uint4* px = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.x) + row * d.ldx + gi * 8);
                     raw[g][0] = __ldg(px);
                     raw[g][Q - 1] = __ldg(px + 1);
-                    if (d.residual) {
+                    if (RESID && d.residual) {
                         const uint4* pr = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(d.residual) + row * d.ldr + gi * 8);
                         rres[g][0] = __ldg(pr);
                         rres[g][Q - 1] = __ldg(pr + 1);
                     }
                 } else {
                     raw[g][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d.x) + row * d.ldx + gi * 8));
-                    if (d.residual)
+                    if (RESID && d.residual)
                         rres[g][0] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d.residual) + row * d.ldr + gi * 8));
                 }
             }
@@ -178,7 +181,7 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : 3) add_layernorm
             const int gi = g * 32 + lane;
             if (gi < groups) {
                 decode(raw[g], v[g]);
-                if (d.residual) {
+                if (RESID && d.residual) {
                     float r[8];
                     decode(rres[g], r);
 #pragma unroll
@@ -326,6 +329,12 @@ __global__ void __launch_bounds__(128) mask_to_kv_len_kernel(const float* mask, 
 
 bool valid_dtype(int dt) { return dt == B200_F16 || dt == B200_BF16 || dt == B200_F32; }
 
+template <int NV, bool F32IN>
+void launch_rows(bool resid, unsigned grid, size_t smem, cudaStream_t stream, const B200LayerNormDesc& d) {
+    if (resid) launch_kernel(add_layernorm_rows_kernel<NV, F32IN, true>, dim3(grid), dim3(256), smem, stream, d);
+    else launch_kernel(add_layernorm_rows_kernel<NV, F32IN, false>, dim3(grid), dim3(256), smem, stream, d);
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -350,20 +359,20 @@ int b200_add_layernorm_fwd(const B200LayerNormDesc* d, b200_stream_t stream_) {
         // One resident wave of 3 (2 for the wider variants) blocks x 8 warps per SM; every warp then walks rows with a
         // grid stride.
         const bool f32 = d->in_dtype == B200_F32;
-        const long long per_sm = (nv >= 4 || f32) ? 2 : 3;
+        const long long per_sm = (nv >= 4 || f32) ? 2 : (d->residual ? 3 : 4);
         long long blocks = (d->rows + 7) / 8;
         if (blocks > 148ll * per_sm) blocks = 148ll * per_sm;
         const unsigned g2 = static_cast<unsigned>(blocks);
         const size_t sm = static_cast<size_t>(d->H) * 2 * sizeof(float);
         if (nv <= 1) {
-            if (f32) launch_kernel(add_layernorm_rows_kernel<1, true>, dim3(g2), dim3(256), sm, stream, *d);
-            else launch_kernel(add_layernorm_rows_kernel<1, false>, dim3(g2), dim3(256), sm, stream, *d);
+            if (f32) launch_rows<1, true>(d->residual != nullptr, g2, sm, stream, *d);
+            else launch_rows<1, false>(d->residual != nullptr, g2, sm, stream, *d);
         } else if (nv <= 3) {
-            if (f32) launch_kernel(add_layernorm_rows_kernel<3, true>, dim3(g2), dim3(256), sm, stream, *d);
-            else launch_kernel(add_layernorm_rows_kernel<3, false>, dim3(g2), dim3(256), sm, stream, *d);
+            if (f32) launch_rows<3, true>(d->residual != nullptr, g2, sm, stream, *d);
+            else launch_rows<3, false>(d->residual != nullptr, g2, sm, stream, *d);
         } else {
-            if (f32) launch_kernel(add_layernorm_rows_kernel<4, true>, dim3(g2), dim3(256), sm, stream, *d);
-            else launch_kernel(add_layernorm_rows_kernel<4, false>, dim3(g2), dim3(256), sm, stream, *d);
+            if (f32) launch_rows<4, true>(d->residual != nullptr, g2, sm, stream, *d);
+            else launch_rows<4, false>(d->residual != nullptr, g2, sm, stream, *d);
         }
     } else if (nv <= 8) launch_kernel(add_layernorm_kernel<8>, dim3(grid), dim3(256), 0, stream, *d);
     else launch_kernel(add_layernorm_kernel<16>, dim3(grid), dim3(256), 0, stream, *d);
