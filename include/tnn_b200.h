@@ -52,7 +52,9 @@ enum { B200_F16 = 0, B200_BF16 = 1, B200_F32 = 2 };
 enum {
     B200_EPI_BIAS          = 0, /* y = x.W + b                       MatMul -> Add(bias)                              */
     B200_EPI_BIAS_GELU     = 1, /* y = gelu_erf(x.W + b)             MatMul -> Add(bias) -> GELU                      */
-    B200_EPI_BIAS_RESIDUAL = 2  /* y = x.W + b + r                   MatMul -> Add(bias) -> Add(residual)             */
+    B200_EPI_BIAS_RESIDUAL = 2, /* y = x.W + b + r                   MatMul -> Add(bias) -> Add(residual)             */
+    B200_EPI_BIAS_TANH     = 3  /* y = tanh(x.W + b)                 MatMul -> Add(bias) -> Tanh  (the BERT pooler;    */
+                                /*   source/tnn/device/x86/acc/x86_tanh_layer_acc.cc:19-31)                           */
 };
 
 /* -------------------------------------------------------------------------------------------------------------------

@@ -104,6 +104,8 @@ def linear(x, w_kn, bias=None, residual=None, act=None):
         y = y + bias.astype(F32)
     if act == "gelu":
         y = gelu(y.astype(F32))
+    if act == "tanh":   # source/tnn/device/x86/acc/x86_tanh_layer_acc.cc:19-31
+        y = np.tanh(y.astype(F32))
     if residual is not None:
         y = y + residual.astype(F32)
     return y.astype(F32)

@@ -35,6 +35,12 @@ CASES = {
                              length_range=(130, 200), randomize_affine=False),
 }
 
+# encoder + pooler head (MatMul -> Add -> Tanh on the last layer's output); same keyword arguments plus `pooler_seed`
+POOLER_CASES = {
+    "base_1layer_pooler": dict(kind="encoder", geometry="base", batch=2, seq=64, layers=1, seed=4,
+                               length_range=(7, 64), randomize_affine=True, pooler_seed=9),
+}
+
 
 # name -> keyword arguments of model_synth.make_frontend_workload(): the embedding front-end + mask builder
 FRONTEND_CASES = {
@@ -79,6 +85,17 @@ def main():
         path = os.path.join(GOLDEN, name + ".npz")
         # DEVICE_NAIVE (the reference's own unit-test oracle) is recorded as its distance from DEVICE_X86 only.
         np.savez(path, x86=x86.astype(np.float32), lengths=wl.lengths,
+                 x86_vs_naive_max_abs=np.float32(np.abs(x86 - naive).max()))
+        print(name, x86.shape, "x86-vs-naive max-abs", float(np.abs(x86 - naive).max()))
+    for name, kw in POOLER_CASES.items():
+        if only and name not in only:
+            continue
+        kw = dict(kw)
+        pooler = ms.make_pooler(768 if kw["geometry"] == "base" else 1024, kw.pop("pooler_seed"))
+        wl = golden_workload(**kw)
+        x86, _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_X86, pooler=pooler)
+        naive, _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_NAIVE, pooler=pooler)
+        np.savez(os.path.join(GOLDEN, name + ".npz"), x86=x86.astype(np.float32), lengths=wl.lengths,
                  x86_vs_naive_max_abs=np.float32(np.abs(x86 - naive).max()))
         print(name, x86.shape, "x86-vs-naive max-abs", float(np.abs(x86 - naive).max()))
     for name, kw in FRONTEND_CASES.items():

@@ -106,12 +106,12 @@ class TnnInstance:
         return out.reshape([dims[i] for i in range(nd.value)])
 
 
-def run_workload(wl, device=DEVICE_X86, threads=1, time_iters=0, warmup=1, workdir=None):
+def run_workload(wl, device=DEVICE_X86, threads=1, time_iters=0, warmup=1, workdir=None, pooler=None):
     """Write `wl` as TNN files, run it on the reference CPU device; returns (output, ms_per_forward or None)."""
     from tnn_b200 import model_synth
     d = workdir or tempfile.mkdtemp(prefix="tnnref_")
     proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
-    model_synth.write_tnn_model(wl, proto, model)
+    model_synth.write_tnn_model(wl, proto, model, pooler=pooler)
     inst = TnnInstance(proto, model, device=device, threads=threads)
     inst.set_input("x", wl.x)
     inst.set_input("mask", wl.mask_add)

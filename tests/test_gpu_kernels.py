@@ -281,3 +281,22 @@ def test_linear_post_layernorm_equals_separate_launches(M, N, K, block_n):
         # and against fp32 torch on the same rounded y
         want = torch.nn.functional.layer_norm(y.float(), (N,), gamma, beta, 1e-12)
         assert (out.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 768, 768), (8192, 768, 768), (300, 1024, 1024)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_linear_tanh_epilogue_against_oracle(M, N, K, dtype):
+    """The pooler head: y = tanh(x . W + b); also over a strided view of the activation (every S-th row = [CLS])."""
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    S = 4
+    full = torch.randn(M * S, K, device="cuda", generator=g).to(dtype)
+    x = full.view(M, S * K)[:, :K]                 # row stride S*K: the first token of each sequence
+    w_kn = (torch.randn(K, N, device="cuda", generator=g) * 0.05)
+    b = torch.randn(N, device="cuda", generator=g) * 0.1
+    w_nk = ops.pack_weight(w_kn, dtype)
+    y = ops.linear(x, w_nk, b, epilogue=ops.EPI_BIAS_TANH)
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.OK
+    want = bert_oracle.linear(x.float().cpu().numpy(), w_nk.float().t().cpu().numpy(), b.cpu().numpy(), act="tanh")
+    tol = 2e-3 if dtype == torch.float16 else 1.2e-2       # half-precision output rounding of values in (-1, 1)
+    assert np.abs(y.float().cpu().numpy() - want).max() < tol

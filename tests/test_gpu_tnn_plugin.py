@@ -7,7 +7,7 @@ import tempfile
 import numpy as np
 import pytest
 
-from oracle.make_golden import CASES, GOLDEN, golden_workload
+from oracle.make_golden import CASES, GOLDEN, POOLER_CASES, golden_workload
 from tnn_b200 import model_synth as ms
 from tnn_b200 import tnn_runtime as rt
 from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
@@ -126,3 +126,21 @@ def test_bert_graph_with_frontend_matches_x86_instance(cuda_device):
     assert max_abs(y, ref) <= MAX_ABS_TOL
     assert cosine(y, ref) >= COS_TOL
     assert max_abs(valid_rows(y, fw.lengths), valid_rows(ref, fw.lengths)) <= MAX_ABS_TOL
+
+
+def test_pooler_head_matches_x86_fixture(cuda_device):
+    """Encoder layer + pooler head MatMul -> Add -> Tanh: fused into a FusedLinear with the tanh epilogue."""
+    name = "base_1layer_pooler"
+    kw = dict(POOLER_CASES[name])
+    pooler = ms.make_pooler(768, kw.pop("pooler_seed"))
+    wl = golden_workload(**kw)
+    d = tempfile.mkdtemp(prefix="plug_pool_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, pooler=pooler)
+    lines = rt.fuse_report(proto, model)
+    assert [ln.split()[0] for ln in lines][-1] == "FusedLinear" and "Tanh" not in [ln.split()[0] for ln in lines]
+    y = _run(proto, model, wl, rt.DEVICE_CUDA)
+    ref = np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]
+    assert y.shape == ref.shape
+    assert max_abs(y, ref) <= MAX_ABS_TOL
+    assert cosine(y, ref) >= COS_TOL

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 from oracle import bert_oracle  # noqa: E402
-from oracle.make_golden import CASES, FRONTEND_CASES, GOLDEN, golden_workload  # noqa: E402
+from oracle.make_golden import CASES, FRONTEND_CASES, GOLDEN, POOLER_CASES, golden_workload  # noqa: E402
 from tnn_b200 import model_synth  # noqa: E402
 
 
@@ -40,6 +40,18 @@ def test_frontend_restatement_matches_reference_x86(name):
     assert max_abs(emb, g["emb_x86"]) < 5e-6
     assert np.array_equal(mask, g["mask_x86"])           # (1 - m) * -10000 is exact in fp32
     assert float(g["x86_vs_naive_max_abs"]) < 5e-6
+
+
+@pytest.mark.parametrize("name", sorted(POOLER_CASES))
+def test_pooler_restatement_matches_reference_x86(name):
+    """Encoder + pooler head (MatMul -> Add -> Tanh) against the reference's own run."""
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    kw = dict(POOLER_CASES[name])
+    pooler = model_synth.make_pooler(768 if kw["geometry"] == "base" else 1024, kw.pop("pooler_seed"))
+    wl = golden_workload(**kw)
+    y = bert_oracle.linear(bert_oracle.encoder_forward(wl), pooler[0], pooler[1], act="tanh")
+    assert max_abs(y, g["x86"]) < 5e-5
+    assert float(g["x86_vs_naive_max_abs"]) < 5e-5
 
 
 def test_gather_out_of_range_is_an_error():

@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TNN_B200_LIB", os.path.join(_HERE, "lib", "libtnn_b200.so"))
 
 F16, BF16, F32 = 0, 1, 2
-EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL = 0, 1, 2
+EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_BIAS_TANH = 0, 1, 2, 3
 
 OK = 0
 ERR_PARAM, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_DRIVER, ERR_DEVICE_TIMEOUT, ERR_NOT_SM100 = -1, -2, -3, -4, -5, -6

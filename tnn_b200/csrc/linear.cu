@@ -298,7 +298,7 @@ int validate_linear_desc(const B200LinearDesc* d) {
     if (d->M > (1ll << 30) || d->N > (1ll << 30) || d->K > (1ll << 30)) return B200_ERR_UNSUPPORTED;
     if (!is_half_dtype(d->dtype)) return B200_ERR_PARAM;
     if (d->out_dtype != B200_F16 && d->out_dtype != B200_BF16 && d->out_dtype != B200_F32) return B200_ERR_PARAM;
-    if (d->epilogue < B200_EPI_BIAS || d->epilogue > B200_EPI_BIAS_RESIDUAL) return B200_ERR_PARAM;
+    if (d->epilogue < B200_EPI_BIAS || d->epilogue > B200_EPI_BIAS_TANH) return B200_ERR_PARAM;
     if (d->epilogue == B200_EPI_BIAS_RESIDUAL && !d->residual) return B200_ERR_PARAM;
     if ((d->K % 8) || (d->N % 8) || (d->ldx % 8) || (d->ldw % 8) || (d->ldy % 8)) return B200_ERR_PARAM;
     if (d->ldx < d->K || d->ldw < d->K || d->ldy < d->N) return B200_ERR_PARAM;

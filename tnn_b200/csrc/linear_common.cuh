@@ -284,6 +284,10 @@ struct WarpEpilogue {
             if (p.epilogue == B200_EPI_BIAS_GELU) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+            } else if (p.epilogue == B200_EPI_BIAS_TANH) {
+                // hardware tanh: relative error <= 2^-11, below the half-precision rounding of the result
+#pragma unroll
+                for (int j = 0; j < 32; ++j) asm("tanh.approx.f32 %0, %1;" : "=f"(v[j]) : "f"(v[j]));
             }
             const uint32_t si = cc % NSTRIPS;
             uint8_t* strip = strips + si * kStageBytesPerWarp;

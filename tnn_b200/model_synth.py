@@ -220,10 +220,33 @@ def _write_files(proto_path, model_path, magic, inputs_line, outputs, layers, re
         fh.write(m)
 
 
-def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"):
-    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name."""
+def make_pooler(hidden, seed=0):
+    """Weights of the BERT pooler head, tanh(x . Wp + bp): (Wp [H, H] fp32, bp [H])."""
+    rng = np.random.default_rng(seed + 104729)
+    return (rng.normal(0.0, 0.02, (hidden, hidden)).astype(np.float32), rng.normal(0.0, 0.1, hidden).astype(np.float32))
+
+
+def _pooler_graph(x, pooler):
+    """MatMul -> Add(bias) -> Tanh over every token row of `x` (a converter's graph first slices the [CLS] row; the
+    slice is a strided view for the kernel and is left out here).  Type ids: Tanh has no resource."""
+    wp, bp = pooler
+    layers, res = [], []
+    layers.append('"MatMul pool_mm 1 1 %s pool_mm 1,"' % x)
+    res.append(struct.pack("<i", _TYPE_ID["MatMul"]) + _pstr("MatMul") + _pstr("pool_mm") + _raw(wp))
+    layers.append('"Add pool_b 1 1 pool_mm pool_b 1,"')
+    res.append(struct.pack("<i", _TYPE_ID["Add"]) + _pstr("Add") + _pstr("pool_b") + _raw(bp.reshape(-1)))
+    layers.append('"Tanh pooled 1 1 pool_b pooled ,"')
+    return layers, res, "pooled"
+
+
+def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None):
+    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name.  `pooler`
+    (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's output."""
     B, S, H = wl.x.shape
     layers, res, consts, out = _encoder_graph(wl, input_name, mask_name)
+    if pooler is not None:
+        l2, r2, out = _pooler_graph(out, pooler)
+        layers, res = layers + l2, res + r2
     _write_files(proto_path, model_path, MAGIC, "%s %d 1 1 %d : %s %d %d %d" % (mask_name, B, S, input_name, B, S, H),
                  [out], layers, res, consts)
     return out

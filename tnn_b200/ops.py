@@ -9,7 +9,7 @@ import ctypes
 import torch
 
 from . import capi
-from .capi import EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL  # noqa: F401
+from .capi import EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_BIAS_TANH  # noqa: F401
 
 
 def _require_cuda(*ts):

@@ -8,7 +8,7 @@
 //        MatMul+Add x3 (Q, K, V on the same input) -> Reshape -> Permute -> MatMul(QK^T) -> Mul(scale) [-> Add(mask)]
 //        -> Softmax(axis 3) -> MatMul(PV) -> Permute -> Reshape
 //      becomes  FusedLinear(x; Wq|Wk|Wv) -> FusedAttention(qkv [, mask])
-//   2. MatMul -> Add(bias) -> GELU            becomes FusedLinear(epilogue GELU)
+//   2. MatMul -> Add(bias) -> GELU            becomes FusedLinear(epilogue GELU); -> Tanh (the pooler head) likewise
 //   3. MatMul -> Add(bias) -> Add(residual)   becomes FusedLinear(epilogue residual), either operand order of the Add
 //   4. MatMul -> Add(bias)                    becomes FusedLinear
 //   5. the embedding front-end  Gather(word) + Gather(segment) -> Add -> Add(position slice) -> LayerNorm
@@ -422,6 +422,30 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
             auto g = std::make_shared<Graph>();
             g->getNodeOrCreatePlaceHolder("in_0");
             if (AddFusedLinear(g, {"in_0"}, mm->info->name + "_b200_gelu", {lp}, B200_EPI_BIAS_GELU, dtype) != TNN_OK)
+                return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 2b. MatMul -> Add -> Tanh (the pooler head)
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%x):
+                %mm  = MatMul(%x)
+                %b   = Add(%mm)
+                %act = Tanh(%b)
+                return (%act)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 1 || in->outputs().size() != 1) return nullptr;
+            LinearParts lp;
+            auto mm = in->getNodeByTensorName(std::string("@mm"));
+            if (!ExtractLinear(mm, in->getNodeByTensorName(std::string("@b")), resource, &lp)) return nullptr;
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            if (AddFusedLinear(g, {"in_0"}, mm->info->name + "_b200_tanh", {lp}, B200_EPI_BIAS_TANH, dtype) != TNN_OK)
                 return nullptr;
             return g;
         };
