@@ -144,3 +144,30 @@ def test_pooler_head_matches_x86_fixture(cuda_device):
     assert y.shape == ref.shape
     assert max_abs(y, ref) <= MAX_ABS_TOL
     assert cosine(y, ref) >= COS_TOL
+
+
+def test_half_precision_mats_in_and_out(cuda_device):
+    """A model whose activation input is declared half precision: RESERVED_FP16_TEST Mats go to / come from the device
+    as plain copies (half the PCIe bytes), and the result equals the fp32-Mat route bit for bit."""
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    d = tempfile.mkdtemp(prefix="plug_half_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, input_dtype="half")
+    inst = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    inst.set_input_half("x", wl.x.astype(np.float16))
+    inst.set_input("mask", wl.mask_add)
+    inst.forward()
+    y16 = inst.get_output_half().astype(np.float32).reshape(wl.x.shape)
+    inst.close()
+    # (Instance caches one output Mat per blob, so the other Mat type gets an instance of its own.)
+    inst = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    inst.set_input("x", wl.x)                       # an fp32 Mat into the half blob: converted on the device
+    inst.set_input("mask", wl.mask_add)
+    inst.forward()
+    y32 = inst.get_output()                         # the half-precision output blob, up-converted on the device
+    inst.close()
+    assert np.array_equal(y16, y32)
+    proto32, model32 = _files(wl)                   # the untyped (fp32 input) model
+    assert np.array_equal(_run(proto32, model32, wl, rt.DEVICE_CUDA), y32)
+    ref = np.load(os.path.join(GOLDEN, "base_2layer_ragged.npz"))["x86"]
+    assert max_abs(y32, ref) <= MAX_ABS_TOL

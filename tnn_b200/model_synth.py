@@ -239,14 +239,22 @@ def _pooler_graph(x, pooler):
     return layers, res, "pooled"
 
 
-def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None):
+def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None, input_dtype=None):
     """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name.  `pooler`
-    (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's output."""
+    (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's output.  `input_dtype`
+    "half" / "bf16" declares the activation input as a typed (v2) half-precision blob (include/tnn/core/common.h
+    DataType: 1 = half, 4 = bfp16), so that a half-precision Mat reaches the device without conversion."""
     B, S, H = wl.x.shape
     layers, res, consts, out = _encoder_graph(wl, input_name, mask_name)
     if pooler is not None:
         l2, r2, out = _pooler_graph(out, pooler)
         layers, res = layers + l2, res + r2
+    if input_dtype is not None:
+        code = {"half": 1, "bf16": 4}[input_dtype]
+        _write_files(proto_path, model_path, MAGIC_RAW,
+                     "%s 4 %d 1 1 %d 0 : %s 3 %d %d %d %d" % (mask_name, B, S, input_name, B, S, H, code),
+                     [out], layers, res, consts)
+        return out
     _write_files(proto_path, model_path, MAGIC, "%s %d 1 1 %d : %s %d %d %d" % (mask_name, B, S, input_name, B, S, H),
                  [out], layers, res, consts)
     return out

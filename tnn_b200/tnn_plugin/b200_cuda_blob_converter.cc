@@ -64,17 +64,21 @@ private:
             if (desc.data_type != DATA_TYPE_INT32) return Status(TNNERR_PARAM_ERR, "NC_INT32 Mat needs an int32 blob");
             return Copy(to_mat ? image.GetData() : blob_ptr, to_mat ? blob_ptr : image.GetData(), count * 4, kind, stream);
         }
-        if (mt != NCHW_FLOAT) return Status(TNNERR_PARAM_ERR, "tnn_b200 blob converter: Mat type not supported");
-
-        if (desc.data_type == DATA_TYPE_FLOAT)
-            return Copy(to_mat ? image.GetData() : blob_ptr, to_mat ? blob_ptr : image.GetData(), count * 4, kind, stream);
-
+        // Float Mats: NCHW_FLOAT, or half precision / bfloat16 host data (RESERVED_FP16_TEST / RESERVED_BFP16_TEST, the
+        // Mat types the reference's default converter accepts for them, source/tnn/utils/blob_converter_default.cc:
+        // 323-331): with a blob of the same type the copy is the whole conversion, which halves the bytes over PCIe.
+        const int mdt = mt == NCHW_FLOAT ? B200_F32 : (mt == RESERVED_FP16_TEST ? B200_F16 : (mt == RESERVED_BFP16_TEST ? B200_BF16 : -1));
+        if (mdt < 0) return Status(TNNERR_PARAM_ERR, "tnn_b200 blob converter: Mat type not supported");
         const int bdt = B200DataType(desc.data_type);
-        if (bdt != B200_F16 && bdt != B200_BF16) return Status(TNNERR_PARAM_ERR, "blob data type not supported");
-        // half/bf16 blob <-> fp32 Mat through a device-side fp32 staging buffer (grown on first use)
-        void* f32 = image.GetData();
+        if (bdt < 0) return Status(TNNERR_PARAM_ERR, "blob data type not supported");
+        const int64_t mes = mdt == B200_F32 ? 4 : 2;
+        if (mdt == bdt)
+            return Copy(to_mat ? image.GetData() : blob_ptr, to_mat ? blob_ptr : image.GetData(), count * mes, kind, stream);
+
+        // different types: convert on the device; a host Mat goes through a device-side staging buffer in the Mat's type
+        void* mat_dev = image.GetData();
         if (!mat_on_device) {
-            const size_t need = static_cast<size_t>(count) * 4;
+            const size_t need = static_cast<size_t>(count) * mes;
             if (need > staging_bytes_) {
                 if (staging_) cudaFree(staging_);
                 staging_ = nullptr;
@@ -85,15 +89,16 @@ private:
                 }
                 staging_bytes_ = need;
             }
-            f32 = staging_;
+            mat_dev = staging_;
         }
         if (to_mat) {
-            RETURN_ON_NEQ(B200ToStatus(b200_convert(blob_ptr, bdt, f32, B200_F32, count, stream), "b200_convert"), TNN_OK);
-            if (!mat_on_device) return Copy(image.GetData(), f32, count * 4, cudaMemcpyDeviceToHost, stream);
+            RETURN_ON_NEQ(B200ToStatus(b200_convert(blob_ptr, bdt, mat_dev, mdt, count, stream), "b200_convert"), TNN_OK);
+            if (!mat_on_device) return Copy(image.GetData(), mat_dev, count * mes, cudaMemcpyDeviceToHost, stream);
             return TNN_OK;
         }
-        if (!mat_on_device) RETURN_ON_NEQ(Copy(f32, image.GetData(), count * 4, cudaMemcpyHostToDevice, stream), TNN_OK);
-        return B200ToStatus(b200_convert(f32, B200_F32, blob_ptr, bdt, count, stream), "b200_convert");
+        if (!mat_on_device)
+            RETURN_ON_NEQ(Copy(mat_dev, image.GetData(), count * mes, cudaMemcpyHostToDevice, stream), TNN_OK);
+        return B200ToStatus(b200_convert(mat_dev, mdt, blob_ptr, bdt, count, stream), "b200_convert");
     }
 
     static Status Copy(void* dst, const void* src, int64_t bytes, cudaMemcpyKind kind, cudaStream_t stream) {

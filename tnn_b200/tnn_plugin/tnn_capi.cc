@@ -142,6 +142,44 @@ TNNC_API int tnnc_set_input_i32(void* handle, const char* name, const int32_t* d
     return 0;
 }
 
+// Half-precision host data (fp16 bit patterns, or bfloat16 when bf16 != 0) into the named input blob, as a
+// RESERVED_FP16_TEST / RESERVED_BFP16_TEST Mat through SetInputMat (every device's converter accepts these).
+TNNC_API int tnnc_set_input_half(void* handle, const char* name, const uint16_t* data, int64_t n, int bf16) {
+    Handle* h = static_cast<Handle*>(handle);
+    BlobMap blobs;
+    Status st = h->inst->GetAllInputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    auto it = blobs.find(name);
+    if (it == blobs.end()) { h->last_error = std::string("no input named ") + name; return -1; }
+    const DimsVector dims = it->second->GetBlobDesc().dims;
+    if (count(dims) != n) { h->last_error = "input element count mismatch"; return -2; }
+    auto mat = std::make_shared<Mat>(DEVICE_NAIVE, bf16 ? RESERVED_BFP16_TEST : RESERVED_FP16_TEST, dims,
+                                     const_cast<uint16_t*>(data));
+    MatConvertParam param;
+    st = h->inst->SetInputMat(mat, param, name);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    return 0;
+}
+
+// Output blob -> half-precision host data through GetOutputMat.  Returns the element count or a negative error.
+TNNC_API int64_t tnnc_get_output_half(void* handle, const char* name, uint16_t* dst, int64_t capacity, int bf16) {
+    Handle* h = static_cast<Handle*>(handle);
+    BlobMap blobs;
+    Status st = h->inst->GetAllOutputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return -1; }
+    auto it = (name && name[0]) ? blobs.find(name) : blobs.begin();
+    if (it == blobs.end()) { h->last_error = "no such output"; return -1; }
+    const int64_t n = count(it->second->GetBlobDesc().dims);
+    if (!dst) return n;
+    if (capacity < n) { h->last_error = "output buffer too small"; return -2; }
+    std::shared_ptr<Mat> mat;
+    MatConvertParam param;
+    st = h->inst->GetOutputMat(mat, param, it->first, DEVICE_NAIVE, bf16 ? RESERVED_BFP16_TEST : RESERVED_FP16_TEST);
+    if (st != TNN_OK || !mat) { h->last_error = st.description(); return -3; }
+    std::memcpy(dst, mat->GetData(), static_cast<size_t>(n) * sizeof(uint16_t));
+    return n;
+}
+
 TNNC_API int tnnc_forward(void* handle) {
     Handle* h = static_cast<Handle*>(handle);
     Status st = h->inst->Forward();

@@ -45,6 +45,9 @@ def load():
         shim.tnnc_last_error.argtypes = [ctypes.c_void_p]
         shim.tnnc_set_input.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64]
         shim.tnnc_set_input_i32.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64]
+        shim.tnnc_set_input_half.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+        shim.tnnc_get_output_half.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+        shim.tnnc_get_output_half.restype = ctypes.c_int64
         shim.tnnc_forward.argtypes = [ctypes.c_void_p]
         shim.tnnc_time_forward.restype = ctypes.c_double
         shim.tnnc_time_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
@@ -105,6 +108,21 @@ class Instance:
         a = np.ascontiguousarray(arr, dtype=np.int32)
         self._check(self.shim.tnnc_set_input_i32(self.h, name.encode(), a.ctypes.data, a.size),
                     "set_input_i32(%s)" % name)
+
+    def set_input_half(self, name, arr):
+        """`arr`: numpy float16 (or uint16 bfloat16 bit patterns with bf16=True via set_input_bits)."""
+        a = np.ascontiguousarray(arr, dtype=np.float16)
+        self._check(self.shim.tnnc_set_input_half(self.h, name.encode(), a.ctypes.data, a.size, 0),
+                    "set_input_half(%s)" % name)
+
+    def get_output_half(self, name=""):
+        n = self.shim.tnnc_get_output_half(self.h, name.encode(), None, 0, 0)
+        if n < 0:
+            raise RuntimeError("get_output_half: %s" % self.shim.tnnc_last_error(self.h).decode())
+        out = np.empty((n,), np.float16)
+        if self.shim.tnnc_get_output_half(self.h, name.encode(), out.ctypes.data, n, 0) != n:
+            raise RuntimeError("get_output_half: %s" % self.shim.tnnc_last_error(self.h).decode())
+        return out
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
