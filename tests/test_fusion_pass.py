@@ -63,6 +63,25 @@ def test_bert_graph_with_frontend_fuses_embedding_and_mask():
     assert lines[-1].split()[-1] == out
 
 
+def test_fused_model_round_trips_through_model_packer():
+    """Pass -> ModelPacker -> files -> interpreters of the fused layers: the saved model lists the same layers and the
+    pass has nothing left to do on it."""
+    cfg = ms.EncoderConfig(2, 256, 4, 1024)
+    wl = ms.make_workload(cfg, 2, 16, seed=3, randomize_affine=True)
+    fw = ms.make_frontend_workload(256, 2, 16, vocab=100, max_pos=32, seed=4)
+    d = tempfile.mkdtemp(prefix="fuse_pack_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_bert_model(fw, wl, proto, model)
+    proto2, model2 = os.path.join(d, "f.tnnproto"), os.path.join(d, "f.tnnmodel")
+    n = rt.fuse_and_pack(proto, model, proto2, model2)
+    first = rt.fuse_report(proto, model)
+    again = rt.fuse_report(proto2, model2)
+    assert n == len(first) == 2 + 7 * 2
+    assert again == first
+    text = open(proto2).read()
+    assert "FusedEmbedding" in text and "MatMul" not in text and "Gather" not in text
+
+
 def test_precision_high_is_refused():
     with pytest.raises(RuntimeError):
         _fuse(ms.config_workload(1), rt.PRECISION_HIGH)

@@ -171,3 +171,15 @@ def test_half_precision_mats_in_and_out(cuda_device):
     assert np.array_equal(_run(proto32, model32, wl, rt.DEVICE_CUDA), y32)
     ref = np.load(os.path.join(GOLDEN, "base_2layer_ragged.npz"))["x86"]
     assert max_abs(y32, ref) <= MAX_ABS_TOL
+
+
+def test_saved_fused_model_runs_identically(cuda_device):
+    """The optimised model saved by ModelPacker (fused layer types in the files) gives the same bits as the original."""
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    proto, model = _files(wl)
+    d = tempfile.mkdtemp(prefix="plug_pack_")
+    proto2, model2 = os.path.join(d, "f.tnnproto"), os.path.join(d, "f.tnnmodel")
+    rt.fuse_and_pack(proto, model, proto2, model2)
+    a = _run(proto, model, wl, rt.DEVICE_CUDA)
+    b = _run(proto2, model2, wl, rt.DEVICE_CUDA)
+    assert np.array_equal(a, b)

@@ -556,3 +556,29 @@ extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const ch
     std::memcpy(out, text.c_str(), text.size() + 1);
     return static_cast<int>(interp->GetNetStructure()->layers.size());
 }
+
+// Host-only: run the pass on a model and save the optimised model with the reference's ModelPacker.  The saved pair
+// loads through the fused layers' interpreters (b200_layer_interpreters.cc); the pass then finds nothing to do.
+#include "tnn/interpreter/tnn/model_packer.h"
+
+extern "C" __attribute__((visibility("default"))) int tnnb200_fuse_and_pack(const char* proto, size_t proto_len,
+                                                                             const char* model, size_t model_len,
+                                                                             int precision, const char* out_proto,
+                                                                             const char* out_model) {
+    using namespace TNN_NS;
+    auto* interp = dynamic_cast<DefaultModelInterpreter*>(CreateModelInterpreter(MODEL_TYPE_TNN));
+    if (!interp) return -1;
+    std::unique_ptr<DefaultModelInterpreter> guard(interp);
+    std::vector<std::string> params = {std::string(proto, proto_len), std::string(model, model_len)};
+    if (interp->Interpret(params) != TNN_OK) return -2;
+    optimizer::NetOptimizerB200FuseAttention pass;
+    NetworkConfig cfg;
+    cfg.device_type  = DEVICE_CUDA;
+    cfg.network_type = NETWORK_TYPE_DEFAULT;
+    cfg.precision    = static_cast<Precision>(precision);
+    if (!pass.IsSupported(cfg)) return -3;
+    if (pass.Optimize(interp->GetNetStructure(), interp->GetNetResource()) != TNN_OK) return -4;
+    ModelPacker packer(interp->GetNetStructure(), interp->GetNetResource());
+    if (packer.Pack(out_proto, out_model) != TNN_OK) return -5;
+    return static_cast<int>(interp->GetNetStructure()->layers.size());
+}

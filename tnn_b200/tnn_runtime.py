@@ -54,6 +54,9 @@ def load():
         shim.tnnc_get_output.restype = ctypes.c_int64
         shim.tnnc_get_output.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64,
                                          ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        plugin.tnnb200_fuse_and_pack.restype = ctypes.c_int
+        plugin.tnnb200_fuse_and_pack.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
+                                                 ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p]
         plugin.tnnb200_test_fuse.restype = ctypes.c_int
         plugin.tnnb200_test_fuse.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
                                              ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
@@ -71,6 +74,19 @@ def fuse_report(proto_path, model_path, precision=PRECISION_AUTO):
     if n < 0:
         raise RuntimeError("tnnb200_test_fuse failed: %d" % n)
     return buf.value.decode().strip().split("\n")
+
+
+def fuse_and_pack(proto_path, model_path, out_proto_path, out_model_path, precision=PRECISION_AUTO):
+    """Run the graph pass on a model and save the optimised model (fused layers) with the reference's ModelPacker.
+    Needs no GPU.  Returns the number of layers of the saved model."""
+    _, plugin = load()
+    proto = open(proto_path, "rb").read()
+    model = open(model_path, "rb").read()
+    n = plugin.tnnb200_fuse_and_pack(proto, len(proto), model, len(model), precision, out_proto_path.encode(),
+                                     out_model_path.encode())
+    if n < 0:
+        raise RuntimeError("tnnb200_fuse_and_pack failed: %d" % n)
+    return n
 
 
 class Instance:
