@@ -81,21 +81,37 @@ struct AttnParams {
 //                 than 2^8, and only then is O_w rescaled in place (tcgen05.ld / st); the row sum follows along.
 // TMEM: 512 columns = 2 x (S 128 + O 64 + P 64).  All hand-offs are mbarriers with bounded waits (no named barriers:
 // a role that gives up cannot strand another).
-constexpr int PP_THREADS = 320;
-constexpr int PP_OFF_Q = 0;                          // 2 x 16 KB
-constexpr int PP_NST = 4;                            // K/V/mask ring depth (key tiles in flight)
-constexpr int PP_OFF_K = 2 * TILE_BYTES;
-constexpr int PP_OFF_V = PP_OFF_K + PP_NST * TILE_BYTES;
-constexpr int PP_OFF_MASK = PP_OFF_V + PP_NST * TILE_BYTES;   // PP_NST x 128 floats
-constexpr int PP_OFF_BAR = PP_OFF_MASK + PP_NST * TK * 4;
-constexpr int PP_SMEM = PP_OFF_BAR + 512;
-constexpr int PP_TMEM_COLS = 512;
+// NWG = softmax warpgroups (128-query tiles) per CTA.  NWG = 2: one CTA per SM, K/V shared by 256 queries.  NWG = 1:
+// two independent CTAs per SM (each with its own producer and UMMA-issuing thread, a 2-stage ring and half the TMEM):
+// the issue rate of the SM doubles and the two CTAs' softmax phases drift apart by themselves.
+#ifndef PP_NWG
+#define PP_NWG 1
+#endif
+template <int NWG>
+struct PPCfg {
+    static constexpr int THREADS = 64 + 128 * NWG;
+    static constexpr int CTAS_PER_SM = NWG == 1 ? 2 : 1;
+    static constexpr int NST = NWG == 1 ? 2 : 4;                  // K/V/mask ring depth (key tiles in flight)
+    static constexpr int OFF_Q = 0;                               // NWG x 16 KB
+    static constexpr int OFF_K = NWG * TILE_BYTES;
+    static constexpr int OFF_V = OFF_K + NST * TILE_BYTES;
+    static constexpr int OFF_MASK = OFF_V + NST * TILE_BYTES;     // NST x 128 floats
+    static constexpr int OFF_BAR = OFF_MASK + NST * TK * 4;
+    static constexpr int SMEM = OFF_BAR + 512;
+    static constexpr int TMEM_COLS = 256 * NWG;                   // per warpgroup: S 128 + O 64 + P 64
+    static constexpr int COL_O = 128 * NWG;                       // + 64 * wg
+    static constexpr int COL_P = 192 * NWG;                       // + 64 * wg
+};
 constexpr float kLazyLog2 = 8.0f;   // the running maximum moves only when a tile exceeds it by more than 2^8
 
-template <int DT>
-__global__ void __launch_bounds__(PP_THREADS, 1)
+template <int DT, int NWG>
+__global__ void __launch_bounds__(PPCfg<NWG>::THREADS, PPCfg<NWG>::CTAS_PER_SM)
 attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    using C = PPCfg<NWG>;
+    constexpr int PP_NST = C::NST;
+    constexpr int PP_OFF_Q = C::OFF_Q, PP_OFF_K = C::OFF_K, PP_OFF_V = C::OFF_V, PP_OFF_MASK = C::OFF_MASK;
+    constexpr int PP_OFF_BAR = C::OFF_BAR, PP_TMEM_COLS = C::TMEM_COLS;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_OFF_BAR);
     uint64_t* q_full = bars + 0;
@@ -115,7 +131,7 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int q0 = blockIdx.x * 2 * TQ;
+    const int q0 = blockIdx.x * NWG * TQ;
     const int head = blockIdx.y;
     const int b = blockIdx.z;
 
@@ -131,7 +147,7 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         else kv_eff = kl < p.S ? kl : p.S;
     }
     const int n_tiles = (kv_eff + TK - 1) / TK;
-    const bool two = (p.S - q0) > TQ;   // the second query tile exists
+    const bool two = NWG == 2 && (p.S - q0) > TQ;   // the second query tile exists
 
     if (tid == 0) {
         mbar_init(q_full, 1);
@@ -209,75 +225,80 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            const int nwg = two ? 2 : 1;
-            // A tcgen05.mma costs its issuing thread ~130 cycles whatever its size, and the UMMAs here are short (32-64
-            // tensor-pipe cycles): this thread is the pacemaker of the CTA.  All descriptors are built once, per issue
-            // only an immediate is added (descriptor address fields count 16-byte units).  (A second issuing thread,
-            // one per warpgroup, was tried: the two warpgroups then fall into lockstep, their exp sweeps collide on the
-            // SM's exp unit, and the kernel gets slower.)
-            const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
-            const uint64_t dq[2] = {make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q)),
-                                    make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q + TILE_BYTES))};
-            const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
-            const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
-            auto issue_s = [&](int wg, int st) {
-                const uint64_t a_desc = dq[wg];
+        // The whole warp runs this role's control flow (all waits, all address arithmetic: warp-uniform, unrolled over
+        // the warpgroups, every descriptor an immediate offset from one built once); lane 0 alone executes the
+        // tcgen05.mma and tcgen05.commit instructions, so that each commit covers the UMMAs before it.  Issued
+        // back to back like this a tile's 4 QK^T + 8 PV UMMAs take ~530 cycles of the tensor pipe per warpgroup;
+        // with runtime-indexed descriptors the issuing thread needed ~3x that and paced the whole CTA.
+        // (A second issuing thread, one per warpgroup, was tried with the slow form: the two warpgroups then fall into
+        // lockstep, their exp sweeps collide on the SM's exp unit, and the kernel gets slower.)
+        bool ok = mbar_wait(q_full, 0, abort_flag);
+        const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+        const uint64_t dq0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q));   // descriptor addresses: 16-byte units
+        const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
+        const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
+        auto issue_s = [&](auto wg_c, const int st) {
+            constexpr int wg = decltype(wg_c)::value;
+            if (lane == 0) {
+                const uint64_t a_desc = dq0 + static_cast<uint64_t>(wg * (TILE_BYTES >> 4));
                 const uint64_t b_desc = dk0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
                 const uint32_t d_tmem = tmem_base + wg * 128;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
                     umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
                 umma_commit(&s_full[wg]);
-            };
-            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
-            if (ok) {
+            }
+            __syncwarp();
+        };
+        // One warpgroup's share of key tile j: its next scores first (it waits for them), then P V, which it needs
+        // only after its next max sweep.  `last` = this is the CTA's last warpgroup: its commits release the stages.
+        auto step = [&](auto wg_c, const int j, const bool last) -> bool {
+            constexpr int wg = decltype(wg_c)::value;
+            const int st = j % PP_NST;
+            const int st_next = (j + 1) % PP_NST;
+            if (!mbar_wait(&p_full[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
+            if (lane == 0) ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
+            if (j + 1 < n_tiles) {
+                if (wg == 0 && !mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag))
+                    return false;
                 tcgen05_fence_after();
-                for (int wg = 0; wg < nwg; ++wg) issue_s(wg, 0);
-                umma_commit(&k_empty[0]);
+                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 2);   // K of the next tile present
+                issue_s(wg_c, st_next);
+                if (last && lane == 0) umma_commit(&k_empty[st_next]);
+                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 3);   // next scores issued
             }
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int st = j % PP_NST;
-                const int st_next = (j + 1) % PP_NST;
-                const uint32_t ph = static_cast<uint32_t>(j) & 1u;
-                const uint32_t ph_st = (static_cast<uint32_t>(j) / PP_NST) & 1u;
-                for (int wg = 0; ok && wg < nwg; ++wg) {
-                    if (!mbar_wait(&p_full[wg], ph, abort_flag)) { ok = false; break; }
-                    ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
-                    // The warpgroup has read its scores and written P: its next scores go first (it waits for them),
-                    // then P V, which it needs only after its next max sweep.
-                    if (j + 1 < n_tiles) {
-                        if (wg == 0 &&
-                            !mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        ATTN_MARK(2, j, wg * 4 + 2);   // K of the next tile present
-                        issue_s(wg, st_next);
-                        if (wg == nwg - 1) umma_commit(&k_empty[st_next]);
-                        ATTN_MARK(2, j, wg * 4 + 3);   // next scores issued
-                    }
-                    if (wg == 0 && !mbar_wait(&v_full[st], ph_st, abort_flag)) { ok = false; break; }
-                    tcgen05_fence_after();
-                    {
-                        const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
-                        const uint32_t d_tmem = tmem_base + 256 + wg * 64;
-                        const uint32_t a_tmem = tmem_base + 384 + wg * 64;
-                        const uint32_t acc0 = j != 0 ? 1u : 0u;
-                        // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must);
-                        // P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
+            if (wg == 0 && !mbar_wait(&v_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) return false;
+            tcgen05_fence_after();
+            if (lane == 0) {
+                const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                const uint32_t d_tmem = tmem_base + C::COL_O + wg * 64;
+                const uint32_t a_tmem = tmem_base + C::COL_P + wg * 64;
+                const uint32_t acc0 = j != 0 ? 1u : 0u;
+                // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must);
+                // P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
 #pragma unroll
-                        for (int k = 0; k < TK / 16; ++k)
-                            umma_f16_ts(d_tmem, a_tmem + k * 8, b_desc + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
-                                        k != 0 ? 1u : acc0);
-                    }
-                    umma_commit(&o_full[wg]);
-                    if (wg == nwg - 1) umma_commit(&v_empty[st]);
-                    ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
-                }
+                for (int k = 0; k < TK / 16; ++k)
+                    umma_f16_ts(d_tmem, a_tmem + k * 8, b_desc + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
+                                k != 0 ? 1u : acc0);
+                umma_commit(&o_full[wg]);
+                if (last) umma_commit(&v_empty[st]);
+                ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
             }
+            __syncwarp();
+            return true;
+        };
+        if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tcgen05_fence_after();
+            issue_s(std::integral_constant<int, 0>{}, 0);
+            if (NWG == 2 && two) issue_s(std::integral_constant<int, NWG - 1>{}, 0);
+            if (lane == 0) umma_commit(&k_empty[0]);
+        }
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            ok = step(std::integral_constant<int, 0>{}, j, !two);
+            if (NWG == 2 && two && ok) ok = step(std::integral_constant<int, NWG - 1>{}, j, true);
+            ok = __all_sync(0xffffffffu, ok);
         }
         __syncwarp();
     } else {
@@ -286,8 +307,8 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const int r_in_tile = ((warp & 3) << 5) + lane;          // TMEM lane = query row of the tile
         const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem_base + lane_field + wg * 128;
-        const uint32_t t_o = tmem_base + lane_field + 256 + wg * 64;
-        const uint32_t t_p = tmem_base + lane_field + 384 + wg * 64;
+        const uint32_t t_o = tmem_base + lane_field + C::COL_O + wg * 64;
+        const uint32_t t_p = tmem_base + lane_field + C::COL_P + wg * 64;
         if (wg == 0 || two) {
             float m_run = -INFINITY, l_run = 0.f;
             bool ok = true;
@@ -805,20 +826,20 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
 
     static bool attr_set[64] = {false};
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PP_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PP_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess)
             return B200_ERR_LAUNCH;
         attr_set[dev] = true;
     }
-    dim3 grid(static_cast<unsigned>((d->S + 2 * TQ - 1) / (2 * TQ)), static_cast<unsigned>(d->heads),
+    dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
               static_cast<unsigned>(d->B));
     if (d->dtype == B200_F16)
-        launch_kernel(attention_pingpong_kernel<B200_F16>, grid, dim3(PP_THREADS), PP_SMEM,
+        launch_kernel(attention_pingpong_kernel<B200_F16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
                       static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
     else
-        launch_kernel(attention_pingpong_kernel<B200_BF16>, grid, dim3(PP_THREADS), PP_SMEM,
+        launch_kernel(attention_pingpong_kernel<B200_BF16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
                       static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
     count_launch();
     return check_launch();
@@ -868,10 +889,10 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
                                  S1_SMEM) != cudaSuccess ||
             cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  S1_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PP_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PP_SMEM) != cudaSuccess) {
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess) {
             cudaGetLastError();
             return B200_ERR_LAUNCH;
         }
@@ -922,12 +943,12 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
             attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
                 tq, tk, tv, to, p, static_cast<int>(items));
     } else {
-        dim3 grid(static_cast<unsigned>((d->S + 2 * TQ - 1) / (2 * TQ)), static_cast<unsigned>(d->heads),
+        dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
                   static_cast<unsigned>(d->B));
         if (d->dtype == B200_F16)
-            attention_pingpong_kernel<B200_F16><<<grid, PP_THREADS, PP_SMEM, stream>>>(tq, tk, tv, p);
+            attention_pingpong_kernel<B200_F16, PP_NWG><<<grid, PPCfg<PP_NWG>::THREADS, PPCfg<PP_NWG>::SMEM, stream>>>(tq, tk, tv, p);
         else
-            attention_pingpong_kernel<B200_BF16><<<grid, PP_THREADS, PP_SMEM, stream>>>(tq, tk, tv, p);
+            attention_pingpong_kernel<B200_BF16, PP_NWG><<<grid, PPCfg<PP_NWG>::THREADS, PPCfg<PP_NWG>::SMEM, stream>>>(tq, tk, tv, p);
     }
     count_launch();
     return check_launch();
