@@ -27,15 +27,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Timestamps of the first CTA's hand-offs for performance work: compiled in only with -DB200_TRACE.
+// Cycle stamps (one SM's counter) of the first CTA's hand-offs for performance work: compiled in only with -DB200_TRACE.
 #ifdef B200_TRACE
 __device__ unsigned long long g_attn_trace[3][32][8];   // [role: wg0, wg1, mma][tile][event]
 #define ATTN_MARK(role, tile, ev)                                                                 \
     do {                                                                                          \
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) {               \
-            unsigned long long t_;                                                                \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                \
-            g_attn_trace[role][tile][ev] = t_;                                                    \
+            g_attn_trace[role][tile][ev] = static_cast<unsigned long long>(clock64());            \
         }                                                                                         \
     } while (0)
 #else
@@ -66,30 +64,40 @@ struct AttnParams {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
-// Long sequences: two 128-query tiles per CTA, processed by two softmax warpgroups in ping-pong, so that the tensor
-// pipe works on one tile's QK^T / PV while the other tile is in its softmax, and every K/V tile is loaded once for
-// 256 queries.  Roles (320 threads, one CTA per SM):
+// Long sequences: two 128-query tiles per CTA, one softmax warpgroup each, so that the tensor pipe works on one tile's
+// QK^T / PV while the other tile is in its softmax, and every K/V tile is loaded once for 256 queries.
+// Roles (384 threads = 3 warpgroups, one CTA per SM; the control warpgroup hands most of its registers to the softmax
+// warpgroups with setmaxnreg, 72 against 216 per thread):
 //   warp 0      : producer — lane 0 issues the TMA loads (Q tiles once, then K/V tiles through a 4-stage ring); all 32
 //                 lanes write the tile's key mask (log2 units, -inf = dropped) next to it and flag "plain" tiles;
-//   warp 1      : one lane issues every UMMA, per warpgroup w and key tile j in the order S_w(j+1), then P_w V(j):
-//                 S_w = Q_w K^T (both operands from shared memory) into TMEM columns [128w, 128w+128);
-//                 O_w += P_w V with P_w read from TMEM columns [384+64w, +64) and V from shared memory, accumulated
-//                 over all key tiles in TMEM columns [256+64w, +64);
-//   warps 2..5  : softmax warpgroup 0 (query rows q0 .. q0+127), warps 6..9: warpgroup 1 (q0+128 .. q0+255);
-//                 thread = row: a max sweep over the 128 scores, then an exp sweep that writes P_w back to TMEM as
-//                 packed half precision.  The running maximum is lazy: it only moves when a tile exceeds it by more
-//                 than 2^8, and only then is O_w rescaled in place (tcgen05.ld / st); the row sum follows along.
+//   warps 1, 2  : UMMA issuers, one per softmax warpgroup w.  As soon as the warpgroup has taken S_w(j) into registers
+//                 the warp issues S_w(j+1) = Q_w K^T (both operands from shared memory) into TMEM columns
+//                 [128w, 128w+128); when the warpgroup has written P_w(j) it issues O_w += P_w V with P_w read from TMEM
+//                 columns [384+64w, +64) and V from shared memory, accumulated over all key tiles in TMEM columns
+//                 [256+64w, +64).  A K/V stage is released by the commits of both warps;
+//   warp 3      : idle;
+//   warps 4..7  : softmax warpgroup 0 (query rows q0 .. q0+127), warps 8..11: warpgroup 1 (q0+128 .. q0+255);
+//                 thread = row: the row's 128 scores come to registers in one TMEM load (the score columns are free for
+//                 the next tile at once), maximum, then an exp pass (packed fp32 FMA / add, one MUFU per score) that
+//                 writes P_w back to TMEM as packed half precision.  The running maximum is lazy: it only moves when a
+//                 tile exceeds it by more than 2^8, and only then is O_w rescaled in place (tcgen05.ld / st); the row
+//                 sum follows along.
 // TMEM: 512 columns = 2 x (S 128 + O 64 + P 64).  All hand-offs are mbarriers with bounded waits (no named barriers:
 // a role that gives up cannot strand another).
-// NWG = softmax warpgroups (128-query tiles) per CTA.  NWG = 2: one CTA per SM, K/V shared by 256 queries.  NWG = 1:
-// two independent CTAs per SM (each with its own producer and UMMA-issuing thread, a 2-stage ring and half the TMEM):
-// the issue rate of the SM doubles and the two CTAs' softmax phases drift apart by themselves.
+// What bounds it (d = 64): 128 x 128 scores cost 2 048 cycles of a scheduler's exp unit against 1 024 of the tensor pipe
+// and ~1 100 of UMMA issue (a tcgen05.mma of these sizes occupies the pipe 44-57 cycles back to back).  The exp unit
+// is saturated only while two warps of a scheduler are in their exp pass (see the phase offset below).
+// NWG = softmax warpgroups (128-query tiles) per CTA; NWG = 1 gives two independent CTAs per SM (2-stage ring, half
+// the TMEM each) and measures the same within a few percent.
 #ifndef PP_NWG
-#define PP_NWG 1
+#define PP_NWG 2
 #endif
 template <int NWG>
 struct PPCfg {
-    static constexpr int THREADS = 64 + 128 * NWG;
+    static constexpr int THREADS = 128 + 128 * NWG;               // control warpgroup + softmax warpgroups
+    // registers per thread after the control warpgroup has handed most of its share to the softmax warpgroups
+    static constexpr int REGS_CONTROL = 72;
+    static constexpr int REGS_SOFTMAX = NWG == 1 ? 184 : 216;
     static constexpr int CTAS_PER_SM = NWG == 1 ? 2 : 1;
     static constexpr int NST = NWG == 1 ? 2 : 4;                  // K/V/mask ring depth (key tiles in flight)
     static constexpr int OFF_Q = 0;                               // NWG x 16 KB
@@ -123,7 +131,8 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     uint64_t* s_full = m_full + PP_NST;           // [2] per warpgroup
     uint64_t* p_full = s_full + 2;                // [2] (128 arrivals)
     uint64_t* o_full = p_full + 2;                // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    uint64_t* s_free = o_full + 2;                // [2] the warpgroup holds its scores in registers (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* mask_s = reinterpret_cast<float*>(smem + PP_OFF_MASK);
     volatile uint32_t* plain_s = tmem_slot + 2;   // [PP_NST] per stage: every key valid, mask 0
@@ -154,14 +163,15 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         for (int i = 0; i < PP_NST; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&v_full[i], 1);
-            mbar_init(&k_empty[i], 1);
-            mbar_init(&v_empty[i], 1);
+            mbar_init(&k_empty[i], two ? 2 : 1);   // one commit per UMMA-issuing warp
+            mbar_init(&v_empty[i], two ? 2 : 1);
             mbar_init(&m_full[i], 32);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
             mbar_init(&o_full[i], 1);
+            mbar_init(&s_free[i], 128);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -180,130 +190,137 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     pdl_launch_dependents();
     pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            mbar_expect_tx(q_full, (two ? 2 : 1) * TILE_BYTES);
-            tma_load_3d(smem + PP_OFF_Q, &tm_q, q_full, head * HD, q0, b);
-            if (two) tma_load_3d(smem + PP_OFF_Q + TILE_BYTES, &tm_q, q_full, head * HD, q0 + TQ, b);
-        }
-        bool ok = true;
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const int st = j % PP_NST;
-            const uint32_t ph = (static_cast<uint32_t>(j) / PP_NST) & 1u;
-            if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+    if (warp < 4) {
+        setmaxnreg_dec<C::REGS_CONTROL>();   // the control warpgroup: producer, two UMMA issuers, an idle warp
+        if (warp == 0) {
+            // ------------------------------------------------------------ producer
             if (lane == 0) {
-                mbar_expect_tx(&k_full[st], TILE_BYTES);
-                tma_load_3d(smem + PP_OFF_K + st * TILE_BYTES, &tm_k, &k_full[st], head * HD, j * TK, b);
+                mbar_expect_tx(q_full, (two ? 2 : 1) * TILE_BYTES);
+                tma_load_3d(smem + PP_OFF_Q, &tm_q, q_full, head * HD, q0, b);
+                if (two) tma_load_3d(smem + PP_OFF_Q + TILE_BYTES, &tm_q, q_full, head * HD, q0 + TQ, b);
             }
-            // v_empty also says that both warpgroups are done with this stage's mask
-            if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
-            if (lane == 0) {
-                mbar_expect_tx(&v_full[st], TILE_BYTES);
-                tma_load_3d(smem + PP_OFF_V + st * TILE_BYTES, &tm_v, &v_full[st], head * HD, j * TK, b);
-            }
-            bool zero = true;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = j * TK + lane * 4 + i;
-                float m = -INFINITY;
-                if (key < p.S) {
-                    const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + key] : 0.f;
-                    if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+            bool ok = true;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int st = j % PP_NST;
+                const uint32_t ph = (static_cast<uint32_t>(j) / PP_NST) & 1u;
+                if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+                if (lane == 0) {
+                    mbar_expect_tx(&k_full[st], TILE_BYTES);
+                    tma_load_3d(smem + PP_OFF_K + st * TILE_BYTES, &tm_k, &k_full[st], head * HD, j * TK, b);
                 }
-                mask_s[st * TK + lane * 4 + i] = m;
-                zero = zero && m == 0.f;
+                // v_empty also says that both warpgroups are done with this stage's mask
+                if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+                if (lane == 0) {
+                    mbar_expect_tx(&v_full[st], TILE_BYTES);
+                    tma_load_3d(smem + PP_OFF_V + st * TILE_BYTES, &tm_v, &v_full[st], head * HD, j * TK, b);
+                }
+                bool zero = true;
+    #pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = j * TK + lane * 4 + i;
+                    float m = -INFINITY;
+                    if (key < p.S) {
+                        const float a = p.mask_add ? p.mask_add[static_cast<long long>(b) * p.S + key] : 0.f;
+                        if (additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+                    }
+                    mask_s[st * TK + lane * 4 + i] = m;
+                    zero = zero && m == 0.f;
+                }
+                // a "plain" tile (all 128 keys valid, additive mask 0) lets the softmax skip the mask altogether
+                const bool plain_tile = __all_sync(0xffffffffu, zero) && p.scale_log2 > 0.f;
+                if (lane == 0) plain_s[st] = plain_tile ? 1u : 0u;
+                mbar_arrive(&m_full[st]);
             }
-            // a "plain" tile (all 128 keys valid, additive mask 0) lets the softmax skip the mask altogether
-            const bool plain_tile = __all_sync(0xffffffffu, zero) && p.scale_log2 > 0.f;
-            if (lane == 0) plain_s[st] = plain_tile ? 1u : 0u;
-            mbar_arrive(&m_full[st]);
-        }
-        if (!ok && lane == 0) {
-            for (int i = 0; i < 64; ++i) nanosleep(10000);
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ UMMA issuer
-        // The whole warp runs this role's control flow (all waits, all address arithmetic: warp-uniform, unrolled over
-        // the warpgroups, every descriptor an immediate offset from one built once); lane 0 alone executes the
-        // tcgen05.mma and tcgen05.commit instructions, so that each commit covers the UMMAs before it.  Issued
-        // back to back like this a tile's 4 QK^T + 8 PV UMMAs take ~530 cycles of the tensor pipe per warpgroup;
-        // with runtime-indexed descriptors the issuing thread needed ~3x that and paced the whole CTA.
-        // (A second issuing thread, one per warpgroup, was tried with the slow form: the two warpgroups then fall into
-        // lockstep, their exp sweeps collide on the SM's exp unit, and the kernel gets slower.)
-        bool ok = mbar_wait(q_full, 0, abort_flag);
-        const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
-        const uint64_t dq0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q));   // descriptor addresses: 16-byte units
-        const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
-        const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
-        auto issue_s = [&](auto wg_c, const int st) {
-            constexpr int wg = decltype(wg_c)::value;
-            if (lane == 0) {
-                const uint64_t a_desc = dq0 + static_cast<uint64_t>(wg * (TILE_BYTES >> 4));
-                const uint64_t b_desc = dk0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
-                const uint32_t d_tmem = tmem_base + wg * 128;
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
-                umma_commit(&s_full[wg]);
+            if (!ok && lane == 0) {
+                for (int i = 0; i < 64; ++i) nanosleep(10000);
             }
             __syncwarp();
-        };
-        // One warpgroup's share of key tile j: its next scores first (it waits for them), then P V, which it needs
-        // only after its next max sweep.  `last` = this is the CTA's last warpgroup: its commits release the stages.
-        auto step = [&](auto wg_c, const int j, const bool last) -> bool {
-            constexpr int wg = decltype(wg_c)::value;
-            const int st = j % PP_NST;
-            const int st_next = (j + 1) % PP_NST;
-            if (!mbar_wait(&p_full[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
-            if (lane == 0) ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
-            if (j + 1 < n_tiles) {
-                if (wg == 0 && !mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag))
-                    return false;
+        } else if (warp == 1 || (NWG == 2 && warp == 2 && two)) {
+            // ------------------------------------------------------------ UMMA issuers (one warp per warpgroup)
+            // The whole warp runs this role's control flow (all waits, all address arithmetic: warp-uniform, every
+            // descriptor an immediate offset from one built once); lane 0 alone executes the tcgen05.mma and
+            // tcgen05.commit instructions, so that each commit covers the UMMAs before it.
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+            const uint64_t dq0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q));   // descriptor addresses: 16-byte units
+            const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
+            const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
+            auto issue_s = [&](auto wg_c, const int st) {
+                constexpr int wg = decltype(wg_c)::value;
+                if (lane == 0) {
+                    const uint64_t a_desc = dq0 + static_cast<uint64_t>(wg * (TILE_BYTES >> 4));
+                    const uint64_t b_desc = dk0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                    const uint32_t d_tmem = tmem_base + wg * 128;
+    #pragma unroll
+                    for (int k = 0; k < HD / 16; ++k)
+                        umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc_qk, k != 0 ? 1u : 0u);
+                    umma_commit(&s_full[wg]);
+                }
+                __syncwarp();
+            };
+            // Per key tile j and warpgroup w: as soon as the warpgroup holds S_w(j) in registers, S_w(j+1) is issued;
+            // when it has written P_w(j), P_w V(j) follows.  `last` = this is the CTA's last warpgroup: its commits
+            // release the K / V stages.
+            auto step_s = [&](auto wg_c, const int j, const bool last) -> bool {
+                constexpr int wg = decltype(wg_c)::value;
+                if (j + 1 >= n_tiles) return true;
+                const int st_next = (j + 1) % PP_NST;
+                if (!mbar_wait(&s_free[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
+                if (!mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag)) return false;
                 tcgen05_fence_after();
-                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 2);   // K of the next tile present
+                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 2);   // scores taken, K of the next tile present
                 issue_s(wg_c, st_next);
                 if (last && lane == 0) umma_commit(&k_empty[st_next]);
                 if (lane == 0) ATTN_MARK(2, j, wg * 4 + 3);   // next scores issued
-            }
-            if (wg == 0 && !mbar_wait(&v_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) return false;
-            tcgen05_fence_after();
-            if (lane == 0) {
-                const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
-                const uint32_t d_tmem = tmem_base + C::COL_O + wg * 64;
-                const uint32_t a_tmem = tmem_base + C::COL_P + wg * 64;
-                const uint32_t acc0 = j != 0 ? 1u : 0u;
-                // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must);
-                // P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
-#pragma unroll
-                for (int k = 0; k < TK / 16; ++k)
-                    umma_f16_ts(d_tmem, a_tmem + k * 8, b_desc + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
-                                k != 0 ? 1u : acc0);
-                umma_commit(&o_full[wg]);
-                if (last) umma_commit(&v_empty[st]);
-                ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
-            }
-            __syncwarp();
-            return true;
-        };
-        if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            tcgen05_fence_after();
-            issue_s(std::integral_constant<int, 0>{}, 0);
-            if (NWG == 2 && two) issue_s(std::integral_constant<int, NWG - 1>{}, 0);
-            if (lane == 0) umma_commit(&k_empty[0]);
-        }
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            ok = step(std::integral_constant<int, 0>{}, j, !two);
-            if (NWG == 2 && two && ok) ok = step(std::integral_constant<int, NWG - 1>{}, j, true);
+                return true;
+            };
+            auto step_pv = [&](auto wg_c, const int j, const bool last) -> bool {
+                constexpr int wg = decltype(wg_c)::value;
+                const int st = j % PP_NST;
+                if (!mbar_wait(&p_full[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
+                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
+                if (!mbar_wait(&v_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) return false;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                    const uint32_t d_tmem = tmem_base + C::COL_O + wg * 64;
+                    const uint32_t a_tmem = tmem_base + C::COL_P + wg * 64;
+                    const uint32_t acc0 = j != 0 ? 1u : 0u;
+                    // O_w accumulates in TMEM over all key tiles (the softmax rescales it in place when it must);
+                    // P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
+    #pragma unroll
+                    for (int k = 0; k < TK / 16; ++k)
+                        umma_f16_ts(d_tmem, a_tmem + k * 8, b_desc + static_cast<uint64_t>(k * (2048 >> 4)), idesc_pv,
+                                    k != 0 ? 1u : acc0);
+                    umma_commit(&o_full[wg]);
+                    if (last) umma_commit(&v_empty[st]);
+                    ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
+                }
+                __syncwarp();
+                return true;
+            };
+            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
+            auto run = [&](auto wg_c) {
+                if (ok) {
+                    tcgen05_fence_after();
+                    issue_s(wg_c, 0);
+                    if (lane == 0) umma_commit(&k_empty[0]);
+                }
+                for (int j = 0; ok && j < n_tiles; ++j) {
+                    ok = step_s(wg_c, j, true);
+                    if (ok) ok = step_pv(wg_c, j, true);
+                    ok = __all_sync(0xffffffffu, ok);
+                }
+            };
+            if (warp == 1) run(std::integral_constant<int, 0>{});
+            else run(std::integral_constant<int, NWG - 1>{});
+            __syncwarp();
         }
-        __syncwarp();
     } else {
+        setmaxnreg_inc<C::REGS_SOFTMAX>();
         // ------------------------------------------------------------ softmax warpgroups
-        const int wg = (warp - 2) >> 2;   // warps 2..5 -> 0, 6..9 -> 1
+        const int wg = (warp - 4) >> 2;   // warps 4..7 -> 0, 8..11 -> 1
         const int r_in_tile = ((warp & 3) << 5) + lane;          // TMEM lane = query row of the tile
         const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem_base + lane_field + wg * 128;
@@ -321,121 +338,106 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 1);   // scores present
                 __syncwarp();
                 tcgen05_fence_after();
+                // The row's 128 scores move to registers in one go and the score columns are handed back at once:
+                // the next tile's QK^T runs while this tile's softmax is still at work.
+                uint32_t s[TK];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_wait(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+                tcgen05_fence_before();
+                mbar_arrive(&s_free[wg]);
                 const float* mrow = mask_s + st * TK;
-                const bool plain_tile = plain_s[st] != 0u;
-                // Two sweeps over the 128 scores of this row (max, then exp / sum / P), 32 columns at a time, software
-                // pipelined: the TMEM load of the next 32 columns is in flight while the current 32 are processed.
+                const bool plain_tile = plain_s[st] != 0u;   // warp-uniform (CTA-uniform)
                 float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (latency)
-                float ps[4] = {0.f, 0.f, 0.f, 0.f};
-                float m_new = m_run, m_use = 0.f, alpha = 1.f, neg_m = 0.f;
-                bool wait_ok = true;
-                auto work = [&](auto plain_c, const int i, uint32_t (&r)[32]) {
-                    constexpr bool plain = decltype(plain_c)::value;   // compile-time inside each sweep instance
-                    const int c = i & 3;
-                    if (i < 4) {
-                        if (plain) {
+                if (plain_tile) {
 #pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                tmx[0] = fmaxf(tmx[0], __uint_as_float(r[g * 4 + 0]));
-                                tmx[1] = fmaxf(tmx[1], __uint_as_float(r[g * 4 + 1]));
-                                tmx[2] = fmaxf(tmx[2], __uint_as_float(r[g * 4 + 2]));
-                                tmx[3] = fmaxf(tmx[3], __uint_as_float(r[g * 4 + 3]));
-                            }
-                        } else {
+                    for (int g = 0; g < TK / 8; ++g) {
 #pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
-                                tmx[0] = fmaxf(tmx[0], fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x));
-                                tmx[1] = fmaxf(tmx[1], fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y));
-                                tmx[2] = fmaxf(tmx[2], fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z));
-                                tmx[3] = fmaxf(tmx[3], fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w));
-                            }
-                        }
-                        if (i == 3) {
-                            float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
-                            if (plain) tmax *= p.scale_log2;   // = max of the scaled scores: the scale is positive
-                            // Lazy reference maximum: it only moves when the tile's maximum exceeds it by more than
-                            // 2^kLazyLog2 (weights stay <= 2^kLazyLog2, exact in half precision and harmless in the
-                            // fp32 sums), so most tiles leave the output accumulator in TMEM untouched.
-                            const bool move = tmax > m_run + kLazyLog2;
-                            m_new = move ? tmax : m_run;
-                            m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                            neg_m = -m_use;
-                            alpha = move ? fast_exp2(m_run - m_use) : 1.f;
-                            // PV of the previous tile must be complete: it reads the P buffer the second sweep
-                            // overwrites, and it writes the accumulator a rescale would touch.
-                            if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 2);   // max sweep done
-                            if (j > 0) wait_ok = mbar_wait(&o_full[wg], static_cast<uint32_t>(j - 1) & 1u, abort_flag);
-                            if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 3);   // previous PV complete
-                            __syncwarp();
-                            if (j > 0 && __any_sync(0xffffffffu, move)) {
-                                tcgen05_fence_after();
-#pragma unroll
-                                for (int cc = 0; cc < HD / 32; ++cc) {
-                                    uint32_t ro[32];
-                                    tmem_ld_32x32b_x32(t_o + cc * 32, ro);
-                                    tmem_ld_wait(ro);
-#pragma unroll
-                                    for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
-                                    tmem_st_32x32b_x32(t_o + cc * 32, ro);
-                                }
-                                tmem_st_wait();
-                            }
-                        }
-                    } else {
-                        float pv[32];
-                        if (plain) {
-#pragma unroll
-                            for (int e = 0; e < 32; ++e)
-                                pv[e] = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
-                        } else {
-#pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                const float4 mk = *reinterpret_cast<const float4*>(mrow + c * 32 + g * 4);
-                                pv[g * 4 + 0] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 0]), p.scale_log2, mk.x - m_use));
-                                pv[g * 4 + 1] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 1]), p.scale_log2, mk.y - m_use));
-                                pv[g * 4 + 2] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 2]), p.scale_log2, mk.z - m_use));
-                                pv[g * 4 + 3] = fast_exp2(fmaf(__uint_as_float(r[g * 4 + 3]), p.scale_log2, mk.w - m_use));
-                            }
-                        }
-#pragma unroll
-                        for (int q4 = 0; q4 < 32; q4 += 4) {
-                            ps[0] += pv[q4];
-                            ps[1] += pv[q4 + 1];
-                            ps[2] += pv[q4 + 2];
-                            ps[3] += pv[q4 + 3];
-                        }
-                        // P goes to tensor memory as the A operand of the PV UMMA: two consecutive keys per 32-bit
-                        // column, this chunk's 32 keys in columns [16c, 16c + 16) of the warpgroup's P region.
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) pk[e] = pack2t<DT>(pv[2 * e], pv[2 * e + 1]);
-                        tmem_st_32x32b_x16(t_p + c * 16, pk);
-
+                        for (int c = 0; c < 4; ++c)
+                            tmx[c] = fmax3(tmx[c], __uint_as_float(s[g * 8 + c * 2]), __uint_as_float(s[g * 8 + c * 2 + 1]));
                     }
-                };
-                auto sweep = [&](auto plain_c) {
-                    uint32_t ra[32], rb[32];
-                    tmem_ld_32x32b_x32(t_s, ra);
-                    tmem_ld_wait(ra);
+                } else {
+                    // s <- score * scale + mask (log2 units; -inf drops the key): the exp pass only subtracts the maximum
+                    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
 #pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        tmem_ld_32x32b_x32(t_s + ((i + 1) & 3) * 32, rb);
-                        work(plain_c, i, ra);
-                        tmem_ld_wait(rb);
-                        if (i + 2 < 8) tmem_ld_32x32b_x32(t_s + ((i + 2) & 3) * 32, ra);
-                        work(plain_c, i + 1, rb);
-                        if (i + 2 < 8) tmem_ld_wait(ra);
+                    for (int g = 0; g < TK / 4; ++g) {
+                        const float4 mk = *reinterpret_cast<const float4*>(mrow + g * 4);
+                        float v0, v1, v2, v3;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[g * 4 + 0]), __uint_as_float(s[g * 4 + 1])), sc2,
+                                               pack_f32x2(mk.x, mk.y)), v0, v1);
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[g * 4 + 2]), __uint_as_float(s[g * 4 + 3])), sc2,
+                                               pack_f32x2(mk.z, mk.w)), v2, v3);
+                        s[g * 4 + 0] = __float_as_uint(v0);
+                        s[g * 4 + 1] = __float_as_uint(v1);
+                        s[g * 4 + 2] = __float_as_uint(v2);
+                        s[g * 4 + 3] = __float_as_uint(v3);
+                        tmx[g & 1] = fmax3(tmx[g & 1], v0, v1);
+                        tmx[2 + (g & 1)] = fmax3(tmx[2 + (g & 1)], v2, v3);
                     }
-                };
-                if (plain_tile) sweep(std::true_type{});
-                else sweep(std::false_type{});
-                if (!wait_ok) { ok = false; break; }
-                const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
-                l_run = l_run * alpha + psum;
+                }
+                float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
+                if (plain_tile) tmax *= p.scale_log2;   // = max of the scaled scores: the scale is positive
+                // Lazy reference maximum: it only moves when the tile's maximum exceeds it by more than 2^kLazyLog2
+                // (weights stay <= 2^kLazyLog2, exact in half precision and harmless in the fp32 sums), so most tiles
+                // leave the output accumulator in TMEM untouched.
+                const bool move = tmax > m_run + kLazyLog2;
+                const float m_new = move ? tmax : m_run;
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = move ? fast_exp2(m_run - m_use) : 1.f;
+                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 2);   // max known
+                // PV of the previous tile must be complete: it reads the P buffer written below, and it writes the
+                // accumulator a rescale would touch.
+                if (j > 0 && !mbar_wait(&o_full[wg], static_cast<uint32_t>(j - 1) & 1u, abort_flag)) { ok = false; break; }
+                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 3);   // previous PV complete
+                __syncwarp();
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int cc = 0; cc < HD / 32; ++cc) {
+                        uint32_t ro[32];
+                        tmem_ld_32x32b_x32(t_o + cc * 32, ro);
+                        tmem_ld_wait(ro);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
+                        tmem_st_32x32b_x32(t_o + cc * 32, ro);
+                    }
+                }
+                // Phase offset.  A scheduler's exp unit is saturated only while both of its softmax warps are in their exp
+                // pass (8.9 cycles per score per scheduler), runs at ~70 % with one (11.6) and idles with none; started
+                // together the two warpgroups stay in lockstep: both in the exp pass, then both out of it.  So warpgroup
+                // 1 begins its first exp pass only when warpgroup 0 has finished its own; for the next tiles one's exp pass
+                // covers the other's loads, maximum and hand-offs.  (The offset decays over ~6 tiles; renewing it every
+                // tile, every second or every fourth tile, or holding it with a mutual rule, all measured slower than
+                // letting it decay.)
+                if (NWG == 2 && two && wg == 1 && j == 0 && !mbar_wait(&p_full[0], 0, abort_flag)) { ok = false; break; }
+                // exp pass: P goes to tensor memory as the A operand of the PV UMMA, two consecutive keys per 32-bit
+                // column, 32 keys at a time into columns [16c, 16c + 16) of the warpgroup's P region
+                const uint64_t mul2 = plain_tile ? pack_f32x2(p.scale_log2, p.scale_log2) : pack_f32x2(1.f, 1.f);
+                const uint64_t neg2 = pack_f32x2(-m_use, -m_use);
+                uint64_t ps2[2] = {0ull, 0ull};   // 2 x 2 partial sums
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int i = c * 32 + e * 2;
+                        float x0, x1;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), mul2, neg2), x0, x1);
+                        x0 = fast_exp2(x0);
+                        x1 = fast_exp2(x1);
+                        ps2[e & 1] = add_f32x2(ps2[e & 1], pack_f32x2(x0, x1));
+                        pk[e] = pack2t<DT>(x0, x1);
+                    }
+                    tmem_st_32x32b_x16(t_p + c * 16, pk);
+                }
+                float a0, a1, a2, a3;
+                unpack_f32x2(ps2[0], a0, a1);
+                unpack_f32x2(ps2[1], a2, a3);
+                l_run = l_run * alpha + ((a0 + a1) + (a2 + a3));
                 m_run = m_new;
                 tmem_st_wait();               // P (and a rescaled O) have reached tensor memory
-                tcgen05_fence_before();       // ... and this thread's reads of S are done
+                tcgen05_fence_before();
                 mbar_arrive(&p_full[wg]);
                 if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 4);   // P written
             }
