@@ -173,6 +173,43 @@ def test_half_precision_mats_in_and_out(cuda_device):
     assert max_abs(y32, ref) <= MAX_ABS_TOL
 
 
+class _DevView:
+    """A zero-copy view of device memory for torch.as_tensor (the CUDA array interface)."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def test_device_mats_in_and_out(cuda_device):
+    """DEVICE_CUDA Mats (the converter's device branch): the input comes from a torch tensor on the GPU, the output Mat
+    stays on the GPU; equal to the host-Mat route bit for bit, for fp16 Mats (plain copies) and fp32 Mats (converted)."""
+    import torch
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    d = tempfile.mkdtemp(prefix="plug_dev_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, input_dtype="half")
+    ref = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    ref.set_input_half("x", wl.x.astype(np.float16))
+    ref.set_input("mask", wl.mask_add)
+    ref.forward()
+    want = ref.get_output_half()
+    ref.close()
+
+    for kind, dt, typestr in ((rt.Instance.MAT_F16, torch.float16, "<f2"), (rt.Instance.MAT_F32, torch.float32, "<f4")):
+        inst = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+        x = torch.from_numpy(wl.x.astype(np.float16)).to("cuda").to(dt).contiguous()
+        m = torch.from_numpy(np.ascontiguousarray(wl.mask_add, dtype=np.float32)).to("cuda").contiguous()
+        torch.cuda.synchronize()
+        inst.set_input_device("x", x.data_ptr(), x.numel(), kind)
+        inst.set_input_device("mask", m.data_ptr(), m.numel(), rt.Instance.MAT_F32)
+        inst.forward()
+        ptr, n = inst.get_output_device("", kind)
+        assert n == want.size and ptr
+        y = torch.as_tensor(_DevView(ptr, n, typestr), device="cuda").to(torch.float16).cpu().numpy()
+        np.testing.assert_array_equal(y.view(np.uint16), want.view(np.uint16))
+        inst.close()
+
+
 def test_saved_fused_model_runs_identically(cuda_device):
     """The optimised model saved by ModelPacker (fused layer types in the files) gives the same bits as the original."""
     wl = golden_workload(**CASES["base_2layer_ragged"])

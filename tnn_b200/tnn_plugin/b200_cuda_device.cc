@@ -35,7 +35,10 @@ Status B200CudaDevice::Allocate(void** handle, MatType mat_type, DimsVector dims
     desc.dims        = dims;
     desc.device_type = DEVICE_CUDA;
     desc.data_format = DATA_FORMAT_NCHW;
-    desc.data_type   = mat_type == NCHW_FLOAT ? DATA_TYPE_FLOAT : (mat_type == NC_INT32 ? DATA_TYPE_INT32 : DATA_TYPE_INT8);
+    desc.data_type   = mat_type == NCHW_FLOAT ? DATA_TYPE_FLOAT
+                       : mat_type == NC_INT32 ? DATA_TYPE_INT32
+                       : (mat_type == RESERVED_FP16_TEST || mat_type == RESERVED_BFP16_TEST) ? DATA_TYPE_HALF
+                                                                                             : DATA_TYPE_INT8;
     auto info = Calculate(desc);
     return Allocate(handle, info);
 }

@@ -180,6 +180,58 @@ TNNC_API int64_t tnnc_get_output_half(void* handle, const char* name, uint16_t* 
     return n;
 }
 
+// Device-resident Mats (zero host copies): `kind` 0 = NCHW_FLOAT, 1 = RESERVED_FP16_TEST, 2 = RESERVED_BFP16_TEST,
+// 3 = NC_INT32.  The pointer is device memory of the instance's GPU; the converter's branch for
+// image.GetDeviceType() == DEVICE_CUDA (reference: source/tnn/device/cuda/cuda_blob_converter.cc:140-149) copies or
+// converts device to device on the instance's stream.
+static bool mat_type_of(int kind, MatType* mt) {
+    switch (kind) {
+        case 0: *mt = NCHW_FLOAT; return true;
+        case 1: *mt = RESERVED_FP16_TEST; return true;
+        case 2: *mt = RESERVED_BFP16_TEST; return true;
+        case 3: *mt = NC_INT32; return true;
+        default: return false;
+    }
+}
+
+TNNC_API int tnnc_set_input_device(void* handle, const char* name, void* device_ptr, int64_t n, int kind) {
+    Handle* h = static_cast<Handle*>(handle);
+    MatType mt;
+    if (h->device != DEVICE_CUDA || !mat_type_of(kind, &mt)) { h->last_error = "device Mats need DEVICE_CUDA and a valid kind"; return -4; }
+    BlobMap blobs;
+    Status st = h->inst->GetAllInputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    auto it = blobs.find(name);
+    if (it == blobs.end()) { h->last_error = std::string("no input named ") + name; return -1; }
+    const DimsVector dims = it->second->GetBlobDesc().dims;
+    if (count(dims) != n) { h->last_error = "input element count mismatch"; return -2; }
+    auto mat = std::make_shared<Mat>(DEVICE_CUDA, mt, dims, device_ptr);
+    MatConvertParam param;
+    st = h->inst->SetInputMat(mat, param, name);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    return 0;
+}
+
+// The named output as a device Mat of the requested kind.  *device_ptr receives the Mat's device pointer, owned by the
+// instance and valid until the next call for this output; returns the element count or a negative error.
+TNNC_API int64_t tnnc_get_output_device(void* handle, const char* name, int kind, void** device_ptr) {
+    Handle* h = static_cast<Handle*>(handle);
+    MatType mt;
+    if (h->device != DEVICE_CUDA || !mat_type_of(kind, &mt) || !device_ptr) { h->last_error = "device Mats need DEVICE_CUDA and a valid kind"; return -4; }
+    BlobMap blobs;
+    Status st = h->inst->GetAllOutputBlobs(blobs);
+    if (st != TNN_OK) { h->last_error = st.description(); return -1; }
+    auto it = (name && name[0]) ? blobs.find(name) : blobs.begin();
+    if (it == blobs.end()) { h->last_error = "no such output"; return -1; }
+    const int64_t n = count(it->second->GetBlobDesc().dims);
+    std::shared_ptr<Mat> mat;
+    MatConvertParam param;
+    st = h->inst->GetOutputMat(mat, param, it->first, DEVICE_CUDA, mt);
+    if (st != TNN_OK || !mat) { h->last_error = st.description(); return -3; }
+    *device_ptr = mat->GetData();
+    return n;
+}
+
 TNNC_API int tnnc_forward(void* handle) {
     Handle* h = static_cast<Handle*>(handle);
     Status st = h->inst->Forward();

@@ -48,6 +48,10 @@ def load():
         shim.tnnc_set_input_half.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
         shim.tnnc_get_output_half.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
         shim.tnnc_get_output_half.restype = ctypes.c_int64
+        shim.tnnc_set_input_device.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+        shim.tnnc_get_output_device.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int,
+                                                ctypes.POINTER(ctypes.c_void_p)]
+        shim.tnnc_get_output_device.restype = ctypes.c_int64
         shim.tnnc_forward.argtypes = [ctypes.c_void_p]
         shim.tnnc_time_forward.restype = ctypes.c_double
         shim.tnnc_time_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
@@ -139,6 +143,23 @@ class Instance:
         if self.shim.tnnc_get_output_half(self.h, name.encode(), out.ctypes.data, n, 0) != n:
             raise RuntimeError("get_output_half: %s" % self.shim.tnnc_last_error(self.h).decode())
         return out
+
+    # Device-resident Mats: kind 0 fp32, 1 fp16, 2 bf16 bit patterns, 3 int32.
+    MAT_F32, MAT_F16, MAT_BF16, MAT_I32 = 0, 1, 2, 3
+
+    def set_input_device(self, name, device_ptr, count, kind):
+        """Input from device memory of the instance's GPU (a DEVICE_CUDA Mat): no host copy.  The caller orders the
+        producer of that memory before this call (the converter works on the instance's own stream)."""
+        self._check(self.shim.tnnc_set_input_device(self.h, name.encode(), ctypes.c_void_p(device_ptr), count, kind),
+                    "set_input_device(%s)" % name)
+
+    def get_output_device(self, name="", kind=1):
+        """(device pointer, element count) of the output as a DEVICE_CUDA Mat owned by the instance."""
+        ptr = ctypes.c_void_p()
+        n = self.shim.tnnc_get_output_device(self.h, name.encode(), kind, ctypes.byref(ptr))
+        if n < 0:
+            raise RuntimeError("get_output_device: %s" % self.shim.tnnc_last_error(self.h).decode())
+        return ptr.value, n
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
