@@ -248,6 +248,28 @@ B200_API int b200_mask_from_input_mask(const int32_t* input_mask, int64_t B, int
                                        float exclude_below, float* mask_add, int32_t* kv_len, b200_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------------------------
+ * Span-extraction (question answering) head: logits = x . W + b with very few outputs per token (start, end), then
+ * "unstack": output n of every token as its own contiguous array.  Replaces MatMul (constant weight [H, N],
+ * source/tnn/device/x86/acc/x86_mat_mul_layer_acc.cc:49) + Add(bias) + SplitV (x86_splitv_layer_acc.cc:23) +
+ * Squeeze (x86_squeeze_layer_acc.cc:23) at the end of the reading-comprehension graph, whose outputs the demo reads as
+ * "unstack:0" / "unstack:1" (examples/linux/src/BertReadingComprehension/BertReadingComprehension.cc:109).
+ *   x      : [M, H] half precision (x_dtype F16/BF16), row stride ldx (multiple of 8), 16-byte aligned
+ *   weight : fp32 [H, N] row-major (the MatMul layer's constant), bias : fp32 [N] or NULL,  1 <= N <= 4
+ *   out    : fp32, output n of token t at out[n * ld_out + t]  (ld_out >= M)
+ * fp32 accumulation; HBM-bound (one read of x). */
+typedef struct B200QAHeadDesc {
+    const void* x;
+    const float* weight;
+    const float* bias;
+    float* out;
+    int64_t M, H;
+    int64_t ldx, ld_out;
+    int32_t N;
+    int32_t x_dtype;
+} B200QAHeadDesc;
+B200_API int b200_qa_head_fwd(const B200QAHeadDesc* desc, b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------------------------
  * (residual +) LayerNorm over the last dimension:  y = (x (+ r) - mean) * rsqrt(var + eps) * gamma + beta.
  * Replaces Add(residual) + LayerNorm (source/tnn/device/x86/acc/x86_layer_norm_layer_acc.cc:26-86; gamma and beta are
  * the layer's input blobs 1 and 2, source/tnn/layer/layer_norm_layer.cc:28-30).  One warp per row, fp32 statistics,

@@ -111,6 +111,13 @@ def linear(x, w_kn, bias=None, residual=None, act=None):
     return y.astype(F32)
 
 
+def qa_head(x, w_kn, bias):
+    """Span-extraction head: logits = x . W + b with W [H, N], then one [B, S] array per output ("unstack": SplitV along
+    the last axis, source/tnn/device/x86/acc/x86_splitv_layer_acc.cc:23, + Squeeze of that axis)."""
+    y = linear(x, w_kn, bias)
+    return tuple(np.ascontiguousarray(y[..., n]) for n in range(y.shape[-1]))
+
+
 def attention_core(q, k, v, mask_add, scale):
     """q, k, v: [B, heads, S, D] fp32; mask_add: [B, S] or None.  Returns [B, heads, S, D]."""
     scores = matmul(q, k.transpose(0, 1, 3, 2)) * F32(scale)

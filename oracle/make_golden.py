@@ -42,6 +42,13 @@ POOLER_CASES = {
 }
 
 
+# encoder + span-extraction head (MatMul [H, 2] -> Add -> SplitV -> Squeeze x 2); plus `qa_seed`
+QA_CASES = {
+    "base_1layer_qa": dict(kind="encoder", geometry="base", batch=2, seq=64, layers=1, seed=6,
+                           length_range=(9, 64), randomize_affine=True, qa_seed=3),
+}
+
+
 # name -> keyword arguments of model_synth.make_frontend_workload(): the embedding front-end + mask builder
 FRONTEND_CASES = {
     "frontend_base_s48": dict(hidden=768, batch=3, seq=48, vocab=2000, type_vocab=2, max_pos=64, seed=5,
@@ -98,6 +105,18 @@ def main():
         np.savez(os.path.join(GOLDEN, name + ".npz"), x86=x86.astype(np.float32), lengths=wl.lengths,
                  x86_vs_naive_max_abs=np.float32(np.abs(x86 - naive).max()))
         print(name, x86.shape, "x86-vs-naive max-abs", float(np.abs(x86 - naive).max()))
+    for name, kw in QA_CASES.items():
+        if only and name not in only:
+            continue
+        kw = dict(kw)
+        qa = ms.make_qa_head(768 if kw["geometry"] == "base" else 1024, kw.pop("qa_seed"))
+        wl = golden_workload(**kw)
+        (s86, e86), _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_X86, qa=qa)
+        (sn, en), _ = tnn_ref.run_workload(wl, tnn_ref.DEVICE_NAIVE, qa=qa)
+        dev = max(np.abs(s86 - sn).max(), np.abs(e86 - en).max())
+        np.savez(os.path.join(GOLDEN, name + ".npz"), start_x86=s86.astype(np.float32), end_x86=e86.astype(np.float32),
+                 lengths=wl.lengths, x86_vs_naive_max_abs=np.float32(dev))
+        print(name, s86.shape, e86.shape, "x86-vs-naive max-abs", float(dev))
     for name, kw in FRONTEND_CASES.items():
         if only and name not in only:
             continue

@@ -106,12 +106,13 @@ class TnnInstance:
         return out.reshape([dims[i] for i in range(nd.value)])
 
 
-def run_workload(wl, device=DEVICE_X86, threads=1, time_iters=0, warmup=1, workdir=None, pooler=None):
-    """Write `wl` as TNN files, run it on the reference CPU device; returns (output, ms_per_forward or None)."""
+def run_workload(wl, device=DEVICE_X86, threads=1, time_iters=0, warmup=1, workdir=None, pooler=None, qa=None):
+    """Write `wl` as TNN files, run it on the reference CPU device; returns (output, ms_per_forward or None); with `qa`
+    the output is the pair (start logits, end logits)."""
     from tnn_b200 import model_synth
     d = workdir or tempfile.mkdtemp(prefix="tnnref_")
     proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
-    model_synth.write_tnn_model(wl, proto, model, pooler=pooler)
+    names = model_synth.write_tnn_model(wl, proto, model, pooler=pooler, qa=qa)
     inst = TnnInstance(proto, model, device=device, threads=threads)
     inst.set_input("x", wl.x)
     inst.set_input("mask", wl.mask_add)
@@ -120,6 +121,6 @@ def run_workload(wl, device=DEVICE_X86, threads=1, time_iters=0, warmup=1, workd
         ms = inst.time_forward(warmup, time_iters)
     else:
         inst.forward()
-    out = inst.get_output()
+    out = tuple(inst.get_output(n) for n in names) if qa is not None else inst.get_output()
     inst.close()
     return out, ms

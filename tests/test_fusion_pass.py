@@ -82,6 +82,25 @@ def test_fused_model_round_trips_through_model_packer():
     assert "FusedEmbedding" in text and "MatMul" not in text and "Gather" not in text
 
 
+def test_qa_head_fuses_to_one_layer_with_two_named_outputs():
+    """MatMul [H, 2] -> Add -> SplitV becomes one FusedQAHead; the two Squeeze layers behind it keep the graph's
+    output names; the fused model survives the ModelPacker round trip."""
+    cfg = ms.EncoderConfig(1, 256, 4, 1024)
+    wl = ms.make_workload(cfg, 2, 16, seed=5)
+    d = tempfile.mkdtemp(prefix="fuse_qa_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    outs = ms.write_tnn_model(wl, proto, model, qa=ms.make_qa_head(256, 1))
+    lines = rt.fuse_report(proto, model)
+    types = [ln.split()[0] for ln in lines]
+    assert types[-3:] == ["FusedQAHead", "Squeeze", "Squeeze"] and types.count("FusedQAHead") == 1
+    assert not {"MatMul", "SplitV", "Add"} & set(types)
+    assert [ln.split()[-1] for ln in lines[-2:]] == list(outs) == list(ms.QA_OUTPUTS)
+    assert [ln.split()[2] for ln in lines[-2:]] == lines[-3].split()[-2:]     # each Squeeze reads one head output
+    proto2, model2 = os.path.join(d, "f.tnnproto"), os.path.join(d, "f.tnnmodel")
+    assert rt.fuse_and_pack(proto, model, proto2, model2) == len(lines)
+    assert rt.fuse_report(proto2, model2) == lines
+
+
 def test_precision_high_is_refused():
     with pytest.raises(RuntimeError):
         _fuse(ms.config_workload(1), rt.PRECISION_HIGH)

@@ -300,3 +300,36 @@ def test_linear_tanh_epilogue_against_oracle(M, N, K, dtype):
     want = bert_oracle.linear(x.float().cpu().numpy(), w_nk.float().t().cpu().numpy(), b.cpu().numpy(), act="tanh")
     tol = 2e-3 if dtype == torch.float16 else 1.2e-2       # half-precision output rounding of values in (-1, 1)
     assert np.abs(y.float().cpu().numpy() - want).max() < tol
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 768, 2), (8192, 768, 2), (300, 1024, 2), (77, 768, 1), (64, 768, 4), (0, 768, 2)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_qa_head_against_oracle(M, K, N, dtype):
+    """The span-extraction head: fp32 logits = x . W + b, output n of every token as its own row (`unstack:n`)."""
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    x = torch.randn(max(M, 1), K, device="cuda", generator=g).to(dtype)[:M]
+    w = (torch.randn(K, N, device="cuda", generator=g) * 0.05).contiguous()
+    b = torch.randn(N, device="cuda", generator=g) * 0.1
+    out = ops.qa_head(x, w, b)
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.OK and out.shape == (N, M) and out.dtype == torch.float32
+    if M == 0:
+        return
+    want = bert_oracle.qa_head(_np(x.float()), _np(w), _np(b))
+    for n in range(N):
+        assert np.abs(_np(out[n]) - want[n]).max() < 2e-4      # fp32 accumulation, another summation order
+    # no bias; a strided activation (row stride 2K)
+    wide = torch.randn(M, 2 * K, device="cuda", generator=g).to(dtype)
+    out2 = ops.qa_head(wide[:, :K], w)
+    want2 = bert_oracle.qa_head(_np(wide[:, :K].float()), _np(w), np.zeros(N, np.float32))
+    torch.cuda.synchronize()
+    for n in range(N):
+        assert np.abs(_np(out2[n]) - want2[n]).max() < 2e-4
+
+
+def test_qa_head_rejects_bad_arguments():
+    x = torch.zeros(8, 768, device="cuda", dtype=torch.float16)
+    with pytest.raises(capi.B200Error):
+        ops.qa_head(x, torch.zeros(768, 5, device="cuda"))          # more outputs than the kernel holds
+    with pytest.raises(capi.B200Error):
+        ops.qa_head(x[:, :762], torch.zeros(762, 2, device="cuda"))  # H not a multiple of 8

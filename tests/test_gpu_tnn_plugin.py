@@ -7,7 +7,7 @@ import tempfile
 import numpy as np
 import pytest
 
-from oracle.make_golden import CASES, GOLDEN, POOLER_CASES, golden_workload
+from oracle.make_golden import CASES, GOLDEN, POOLER_CASES, QA_CASES, golden_workload
 from tnn_b200 import model_synth as ms
 from tnn_b200 import tnn_runtime as rt
 from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
@@ -144,6 +144,30 @@ def test_pooler_head_matches_x86_fixture(cuda_device):
     assert y.shape == ref.shape
     assert max_abs(y, ref) <= MAX_ABS_TOL
     assert cosine(y, ref) >= COS_TOL
+
+
+def test_qa_head_matches_x86_fixture(cuda_device):
+    """Encoder layer + span-extraction head: one FusedQAHead, outputs `unstack:0` / `unstack:1` as the demo reads them."""
+    name = "base_1layer_qa"
+    kw = dict(QA_CASES[name])
+    qa = ms.make_qa_head(768, kw.pop("qa_seed"))
+    wl = golden_workload(**kw)
+    d = tempfile.mkdtemp(prefix="plug_qa_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    outs = ms.write_tnn_model(wl, proto, model, qa=qa)
+    inst = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    inst.set_input("x", wl.x)
+    inst.set_input("mask", wl.mask_add)
+    inst.forward()
+    start, end = inst.get_output(outs[0]), inst.get_output(outs[1])
+    inst.close()
+    ref = np.load(os.path.join(GOLDEN, name + ".npz"))
+    assert start.size == ref["start_x86"].size == wl.x.shape[0] * wl.x.shape[1]
+    for got, want in ((start, ref["start_x86"]), (end, ref["end_x86"])):
+        got = valid_rows(got.reshape(want.shape)[..., None], wl.lengths)     # logits of the real tokens
+        want = valid_rows(want[..., None], wl.lengths)
+        assert max_abs(got, want) <= MAX_ABS_TOL
+        assert cosine(got, want) >= COS_TOL
 
 
 def test_half_precision_mats_in_and_out(cuda_device):

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 from oracle import bert_oracle  # noqa: E402
-from oracle.make_golden import CASES, FRONTEND_CASES, GOLDEN, POOLER_CASES, golden_workload  # noqa: E402
+from oracle.make_golden import CASES, FRONTEND_CASES, GOLDEN, POOLER_CASES, QA_CASES, golden_workload  # noqa: E402
 from tnn_b200 import model_synth  # noqa: E402
 
 
@@ -51,6 +51,20 @@ def test_pooler_restatement_matches_reference_x86(name):
     wl = golden_workload(**kw)
     y = bert_oracle.linear(bert_oracle.encoder_forward(wl), pooler[0], pooler[1], act="tanh")
     assert max_abs(y, g["x86"]) < 5e-5
+    assert float(g["x86_vs_naive_max_abs"]) < 5e-5
+
+
+@pytest.mark.parametrize("name", sorted(QA_CASES))
+def test_qa_head_restatement_matches_reference_x86(name):
+    """Encoder + span-extraction head (MatMul [H, 2] -> Add -> SplitV -> Squeeze x 2) against the reference's own run:
+    its two outputs `unstack:0` / `unstack:1`."""
+    g = np.load(os.path.join(GOLDEN, name + ".npz"))
+    kw = dict(QA_CASES[name])
+    qa = model_synth.make_qa_head(768 if kw["geometry"] == "base" else 1024, kw.pop("qa_seed"))
+    wl = golden_workload(**kw)
+    start, end = bert_oracle.qa_head(bert_oracle.encoder_forward(wl), qa[0], qa[1])
+    assert start.shape == g["start_x86"].shape == wl.x.shape[:2]
+    assert max_abs(start, g["start_x86"]) < 5e-5 and max_abs(end, g["end_x86"]) < 5e-5
     assert float(g["x86_vs_naive_max_abs"]) < 5e-5
 
 

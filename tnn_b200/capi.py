@@ -60,6 +60,12 @@ class EmbeddingDesc(_c.Structure):
                 ("table_dtype", _i32), ("out_dtype", _i32), ("eps", _f32)]
 
 
+class QAHeadDesc(_c.Structure):
+    _fields_ = [("x", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp),
+                ("M", _i64), ("H", _i64), ("ldx", _i64), ("ld_out", _i64),
+                ("N", _i32), ("x_dtype", _i32)]
+
+
 PHASE_LINEAR, PHASE_ADD_LAYERNORM = 0, 1
 CHAIN_MAX_PHASES, CHAIN_MAX_LINEAR = 8, 4
 
@@ -96,6 +102,7 @@ SYMBOLS = {
     "b200_add_layernorm_fwd": (_c.c_int, [_c.POINTER(LayerNormDesc), _vp]),
     "b200_embedding_layernorm_fwd": (_c.c_int, [_c.POINTER(EmbeddingDesc), _vp]),
     "b200_mask_from_input_mask": (_c.c_int, [_vp, _i64, _i64, _f32, _f32, _vp, _vp, _vp]),
+    "b200_qa_head_fwd": (_c.c_int, [_c.POINTER(QAHeadDesc), _vp]),
     "b200_chain_sync_bytes": (_c.c_size_t, [_i64, _i32]),
     "b200_chain_fwd": (_c.c_int, [_c.POINTER(ChainPhase), _i32, _vp, _vp]),
     "b200_encoder_workspace_bytes": (_c.c_size_t, [_i64, _i64, _i64, _c.c_int]),

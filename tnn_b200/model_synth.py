@@ -239,9 +239,37 @@ def _pooler_graph(x, pooler):
     return layers, res, "pooled"
 
 
-def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None, input_dtype=None):
-    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name.  `pooler`
-    (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's output.  `input_dtype`
+def make_qa_head(hidden, seed=0, outputs=2):
+    """Weights of the span-extraction head, x . Wq + bq: (Wq [H, outputs] fp32, bq [outputs])."""
+    rng = np.random.default_rng(seed + 15485863)
+    return (rng.normal(0.0, 0.05, (hidden, outputs)).astype(np.float32), rng.normal(0.0, 0.1, outputs).astype(np.float32))
+
+
+QA_OUTPUTS = ("unstack:0", "unstack:1")   # the names the reading-comprehension demo reads
+                                          # (examples/linux/src/BertReadingComprehension/BertReadingComprehension.cc:109)
+
+
+def _qa_graph(x, qa):
+    """MatMul [H, 2] -> Add(bias) -> SplitV(axis 2, sizes 1, 1) -> Squeeze(axis 2) x 2: start / end logits [B, S].
+    SplitV parameters: axis, slice count, slices (splitv_layer_interpreter.cc); Squeeze: axis count, axes."""
+    wq, bq = qa
+    assert wq.shape[1] == 2
+    layers, res = [], []
+    layers.append('"MatMul qa_mm 1 1 %s qa_mm 1,"' % x)
+    res.append(struct.pack("<i", _TYPE_ID["MatMul"]) + _pstr("MatMul") + _pstr("qa_mm") + _raw(wq))
+    layers.append('"Add qa_b 1 1 qa_mm qa_b 1,"')
+    res.append(struct.pack("<i", _TYPE_ID["Add"]) + _pstr("Add") + _pstr("qa_b") + _raw(bq.reshape(-1)))
+    layers.append('"SplitV qa_split 1 2 qa_b qa_s0 qa_s1 2 2 1 1 ,"')
+    layers.append('"Squeeze qa_sq0 1 1 qa_s0 %s 1 2 ,"' % QA_OUTPUTS[0])
+    layers.append('"Squeeze qa_sq1 1 1 qa_s1 %s 1 2 ,"' % QA_OUTPUTS[1])
+    return layers, res, list(QA_OUTPUTS)
+
+
+def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None, input_dtype=None,
+                    qa=None):
+    """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name (a list of two
+    names with `qa`).  `pooler` (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's
+    output; `qa` (from make_qa_head) appends the span-extraction head with its two unstacked outputs.  `input_dtype`
     "half" / "bf16" declares the activation input as a typed (v2) half-precision blob (include/tnn/core/common.h
     DataType: 1 = half, 4 = bfp16), so that a half-precision Mat reaches the device without conversion."""
     B, S, H = wl.x.shape
@@ -249,14 +277,19 @@ def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask"
     if pooler is not None:
         l2, r2, out = _pooler_graph(out, pooler)
         layers, res = layers + l2, res + r2
+    outs = [out]
+    if qa is not None:
+        l2, r2, outs = _qa_graph(out, qa)
+        layers, res = layers + l2, res + r2
+        out = outs
     if input_dtype is not None:
         code = {"half": 1, "bf16": 4}[input_dtype]
         _write_files(proto_path, model_path, MAGIC_RAW,
                      "%s 4 %d 1 1 %d 0 : %s 3 %d %d %d %d" % (mask_name, B, S, input_name, B, S, H, code),
-                     [out], layers, res, consts)
+                     outs, layers, res, consts)
         return out
     _write_files(proto_path, model_path, MAGIC, "%s %d 1 1 %d : %s %d %d %d" % (mask_name, B, S, input_name, B, S, H),
-                 [out], layers, res, consts)
+                 outs, layers, res, consts)
     return out
 
 

@@ -223,6 +223,28 @@ def mask_from_input_mask(input_mask, masked_value=-10000.0, exclude_below=-5000.
     return mask_add, kv_len
 
 
+def qa_head(x, weight, bias=None, out=None):
+    """Span-extraction head: `x` `[..., H]` half precision, `weight` fp32 `[H, N]` (N <= 4), `bias` fp32 `[N]` or None
+    -> fp32 `[N, M]` (M = tokens): row n is output n of every token (the graph's `unstack:n`)."""
+    _require_cuda(x, weight, bias, out)
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    M, N = x2.shape[0], weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == H and x2.stride(1) == 1
+    if out is None:
+        out = torch.empty((N, M), dtype=torch.float32, device=x.device)
+    d = capi.QAHeadDesc()
+    d.x, d.weight, d.out = x2.data_ptr(), weight.data_ptr(), out.data_ptr()
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+        d.bias = bias.data_ptr()
+    d.M, d.H, d.N = M, H, N
+    d.ldx, d.ld_out, d.x_dtype = x2.stride(0), out.stride(0), capi.dtype_code(x.dtype)
+    rc = capi.lib().b200_qa_head_fwd(ctypes.byref(d), capi.stream_ptr())
+    capi.check(rc, "b200_qa_head_fwd")
+    return out
+
+
 class Chain:
     """Dependent GEMMs / LayerNorms of an encoder layer in one launch (b200_chain_fwd).
 

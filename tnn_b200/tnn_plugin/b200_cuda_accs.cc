@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "b200_cuda_layer_acc.h"
+#include "tnn/utils/data_type_utils.h"
 #include "tnn/utils/dims_utils.h"
 
 namespace TNN_NS {
@@ -287,6 +288,126 @@ Status B200CudaFusedMaskLayerAcc::Forward(const std::vector<Blob*>& inputs, cons
                         "b200_mask_from_input_mask");
 }
 B200_REGISTER_CUDA_ACC(FusedMask, LAYER_B200_FUSED_MASK)
+
+// ================================================================= FusedQAHead
+B200_DECLARE_CUDA_ACC(FusedQAHead)
+    float* weight_ = nullptr;    // fp32 [H, outputs]
+    float* bias_   = nullptr;    // fp32 [outputs]
+    void* logits_  = nullptr;    // fp32 [outputs, M]: the kernel's output, copied into the output blobs
+    size_t logits_cap_ = 0;
+};
+
+Status B200CudaFusedQAHeadLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                         const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    RETURN_ON_NEQ(B200CudaLayerAcc::Init(context, param, resource, inputs, outputs), TNN_OK);
+    auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param);
+    auto* r = dynamic_cast<FusedQAHeadLayerResource*>(resource);
+    if (!p || !r || p->hidden <= 0 || p->outputs <= 0) return Status(TNNERR_PARAM_ERR, "FusedQAHead: param/resource missing");
+    if (r->weight.GetDataType() != DATA_TYPE_FLOAT || r->weight.GetDataCount() != p->hidden * p->outputs ||
+        r->bias.GetDataType() != DATA_TYPE_FLOAT || r->bias.GetDataCount() != p->outputs)
+        return Status(TNNERR_PARAM_ERR, "FusedQAHead: weight must be fp32 [H, outputs], bias fp32 [outputs]");
+    if (static_cast<int>(outputs.size()) != p->outputs) return Status(TNNERR_PARAM_ERR, "FusedQAHead: output count");
+    for (auto* o : outputs)
+        if (o->GetBlobDesc().data_type != DATA_TYPE_FLOAT) return Status(TNNERR_PARAM_ERR, "FusedQAHead: fp32 outputs");
+    if (B200DataType(inputs[0]->GetBlobDesc().data_type) != B200_F16 && B200DataType(inputs[0]->GetBlobDesc().data_type) != B200_BF16)
+        return Status(TNNERR_PARAM_ERR, "FusedQAHead: the input must be a half-precision activation of the fused region");
+    size_t cap = 0;
+    void* w = nullptr;
+    RETURN_ON_NEQ(EnsureBuffer(&w, &cap, static_cast<size_t>(p->hidden) * p->outputs * sizeof(float)), TNN_OK);
+    weight_ = static_cast<float*>(w);
+    cap = 0;
+    void* b = nullptr;
+    RETURN_ON_NEQ(EnsureBuffer(&b, &cap, static_cast<size_t>(p->outputs) * sizeof(float)), TNN_OK);
+    bias_ = static_cast<float*>(b);
+    cudaStream_t stream = context_->GetStream();
+    if (cudaMemcpyAsync(weight_, r->weight.force_to<float*>(), static_cast<size_t>(p->hidden) * p->outputs * sizeof(float),
+                        cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaMemcpyAsync(bias_, r->bias.force_to<float*>(), static_cast<size_t>(p->outputs) * sizeof(float),
+                        cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+        cudaGetLastError();
+        return Status(TNNERR_CUDA_MEMCPY_ERROR, "FusedQAHead: weight upload failed");
+    }
+    cudaStreamSynchronize(stream);
+    return Reshape(inputs, outputs);
+}
+
+Status B200CudaFusedQAHeadLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param_);
+    const int64_t M = Rows(inputs[0]->GetBlobDesc().dims);
+    return EnsureBuffer(&logits_, &logits_cap_, static_cast<size_t>(M > 0 ? M : 1) * p->outputs * sizeof(float));
+}
+
+Status B200CudaFusedQAHeadLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param_);
+    const DimsVector dims = inputs[0]->GetBlobDesc().dims;
+    B200QAHeadDesc d;
+    std::memset(&d, 0, sizeof(d));
+    d.x = DevicePtr(inputs[0]);
+    d.weight = weight_;
+    d.bias = bias_;
+    d.out = static_cast<float*>(logits_);
+    d.M = Rows(dims);
+    d.H = p->hidden;
+    d.ldx = d.H;
+    d.ld_out = d.M;
+    d.N = p->outputs;
+    d.x_dtype = B200DataType(inputs[0]->GetBlobDesc().data_type);
+    RETURN_ON_NEQ(B200ToStatus(b200_qa_head_fwd(&d, context_->GetStream()), "b200_qa_head_fwd"), TNN_OK);
+    for (int n = 0; n < p->outputs; ++n) {
+        if (cudaMemcpyAsync(DevicePtr(outputs[n]), static_cast<float*>(logits_) + n * d.M, static_cast<size_t>(d.M) * sizeof(float),
+                            cudaMemcpyDeviceToDevice, context_->GetStream()) != cudaSuccess) {
+            cudaGetLastError();
+            return Status(TNNERR_CUDA_MEMCPY_ERROR, "FusedQAHead: output copy failed");
+        }
+    }
+    return TNN_OK;
+}
+B200_REGISTER_CUDA_ACC(FusedQAHead, LAYER_B200_FUSED_QA_HEAD)
+
+// ================================================================= Squeeze / Unsqueeze
+// Shape-only layers: the element order does not change, the acc copies the blob (the reference's CUDA accs do the
+// same, source/tnn/device/cuda/acc/cuda_squeeze_layer_acc.cu and cuda_unsqueeze_layer_acc.cu).
+static Status CopyBlob(Blob* in, Blob* out, void* src, void* dst, cudaStream_t stream) {
+    const BlobDesc& a = in->GetBlobDesc();
+    const BlobDesc& b = out->GetBlobDesc();
+    const int64_t n = DimsVectorUtils::Count(a.dims);
+    if (n != DimsVectorUtils::Count(b.dims) || a.data_type != b.data_type)
+        return Status(TNNERR_PARAM_ERR, "shape-only layer: element counts or types differ");
+    if (cudaMemcpyAsync(dst, src, static_cast<size_t>(n) * DataTypeUtils::GetBytesSize(a.data_type), cudaMemcpyDeviceToDevice,
+                        stream) != cudaSuccess) {
+        cudaGetLastError();
+        return Status(TNNERR_CUDA_MEMCPY_ERROR, "shape-only layer: copy failed");
+    }
+    return TNN_OK;
+}
+
+B200_DECLARE_CUDA_ACC(Squeeze)
+};
+Status B200CudaSqueezeLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                     const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return B200CudaLayerAcc::Init(context, param, resource, inputs, outputs);
+}
+Status B200CudaSqueezeLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return TNN_OK;
+}
+Status B200CudaSqueezeLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return CopyBlob(inputs[0], outputs[0], DevicePtr(inputs[0]), DevicePtr(outputs[0]), context_->GetStream());
+}
+B200_REGISTER_CUDA_ACC(Squeeze, LAYER_SQUEEZE)
+
+B200_DECLARE_CUDA_ACC(Unsqueeze)
+};
+Status B200CudaUnsqueezeLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
+                                       const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return B200CudaLayerAcc::Init(context, param, resource, inputs, outputs);
+}
+Status B200CudaUnsqueezeLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return TNN_OK;
+}
+Status B200CudaUnsqueezeLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    return CopyBlob(inputs[0], outputs[0], DevicePtr(inputs[0]), DevicePtr(outputs[0]), context_->GetStream());
+}
+B200_REGISTER_CUDA_ACC(Unsqueeze, LAYER_UNSQUEEZE)
 
 // ================================================================= LayerNorm
 // The graph's own LayerNorm layer (gamma, beta = input blobs 1 and 2, uploaded by ReloadConstantBlobs).  The reference's

@@ -9,6 +9,8 @@
 //        -> Softmax(axis 3) -> MatMul(PV) -> Permute -> Reshape
 //      becomes  FusedLinear(x; Wq|Wk|Wv) -> FusedAttention(qkv [, mask])
 //   2. MatMul -> Add(bias) -> GELU            becomes FusedLinear(epilogue GELU); -> Tanh (the pooler head) likewise
+//   7. MatMul [H,2] -> Add -> SplitV(last axis, 1 + 1)   becomes FusedQAHead (two [B,S,1] outputs; the Squeeze layers
+//      behind it stay and run on the device's shape-only acc)
 //   3. MatMul -> Add(bias) -> Add(residual)   becomes FusedLinear(epilogue residual), either operand order of the Add
 //   4. MatMul -> Add(bias)                    becomes FusedLinear
 //   5. the embedding front-end  Gather(word) + Gather(segment) -> Add -> Add(position slice) -> LayerNorm
@@ -486,6 +488,50 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
                 TNN_OK)
                 return nullptr;
             if (g->setInputsOrder({"in_0", "in_1"}) != TNN_OK) return nullptr;
+            return g;
+        };
+        RETURN_ON_FAIL(graph->rewrite(pattern, gen));
+    }
+
+    // ---------------------------------------------------------------- 7. span-extraction head (before the plain linear)
+    // MatMul [H, 2] -> Add(bias) -> SplitV(last axis, sizes 1, 1); the graph goes on with one Squeeze(last axis) per
+    // slice to the two [B, S] outputs the reading-comprehension demo reads
+    // (examples/linux/src/BertReadingComprehension/BertReadingComprehension.cc:109).  The Squeeze layers stay in the
+    // graph (the device has an acc for them): a pattern that includes both is symmetric in them, the matcher finds it
+    // twice with the outputs swapped and drops overlapping matches.
+    {
+        std::shared_ptr<Graph> pattern = ParsePattern(R"(
+            graph(%x):
+                %mm      = MatMul(%x)
+                %b       = Add(%mm)
+                %s0, %s1 = SplitV(%b)
+                return (%s0, %s1)
+        )");
+        if (!pattern) return Status(TNNERR_PARAM_ERR, "invalid pattern syntax");
+        auto gen = [&](std::shared_ptr<AnchorGraph> in) -> std::shared_ptr<Graph> {
+            if (in->inputs().size() != 1 || in->outputs().size() != 2) return nullptr;
+            LinearParts lp;
+            auto mm = in->getNodeByTensorName(std::string("@mm"));
+            if (!ExtractLinear(mm, in->getNodeByTensorName(std::string("@b")), resource, &lp)) return nullptr;
+            if (lp.N != 2) return nullptr;
+            auto split = in->getNodeByTensorName(std::string("@s0"));
+            auto sp    = split ? std::dynamic_pointer_cast<SplitVLayerParam>(split->info->param) : nullptr;
+            if (!sp || (sp->axis != 2 && sp->axis != -1) || sp->slices != std::vector<int>({1, 1})) return nullptr;
+            auto g = std::make_shared<Graph>();
+            g->getNodeOrCreatePlaceHolder("in_0");
+            const std::string o0 = mm->info->name + "_b200_qa0", o1 = mm->info->name + "_b200_qa1";
+            if (g->createNode(LAYER_B200_FUSED_QA_HEAD, {"in_0"}, {o0, o1}) != TNN_OK) return nullptr;
+            auto node = g->getNodeByTensorName(o0);
+            if (!node || node->createParam<FusedQAHeadLayerParam>() != TNN_OK) return nullptr;
+            auto p     = node->param<FusedQAHeadLayerParam>();
+            p->type    = kFusedQAHeadTypeName;
+            p->name    = o0;
+            p->hidden  = lp.K;
+            p->outputs = lp.N;
+            if (node->createResource<FusedQAHeadLayerResource>() != TNN_OK) return nullptr;
+            auto r    = node->resource<FusedQAHeadLayerResource>();
+            r->weight = lp.weight;
+            r->bias   = lp.bias;
             return g;
         };
         RETURN_ON_FAIL(graph->rewrite(pattern, gen));

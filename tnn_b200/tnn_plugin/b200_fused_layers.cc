@@ -18,6 +18,7 @@ struct B200LayerTypeNames {
         m[kFusedAttentionTypeName] = LAYER_B200_FUSED_ATTENTION;
         m[kFusedEmbeddingTypeName] = LAYER_B200_FUSED_EMBEDDING;
         m[kFusedMaskTypeName]      = LAYER_B200_FUSED_MASK;
+        m[kFusedQAHeadTypeName]    = LAYER_B200_FUSED_QA_HEAD;
     }
 };
 static B200LayerTypeNames g_b200_layer_type_names;
@@ -142,5 +143,30 @@ Status B200FusedMaskLayer::InferOutputShape(bool ignore_error) {
     return TNN_OK;
 }
 REGISTER_LAYER(B200FusedMask, LAYER_B200_FUSED_MASK);
+
+// ---------------------------------------------------------------- FusedQAHead
+DECLARE_LAYER(B200FusedQAHead, LAYER_B200_FUSED_QA_HEAD);
+
+Status B200FusedQAHeadLayer::InferOutputDataType() {
+    BaseLayer::InferOutputDataType();
+    for (auto* b : output_blobs_) b->GetBlobDesc().data_type = DATA_TYPE_FLOAT;
+    return TNN_OK;
+}
+
+// x [B, S, H] -> `outputs` blobs [B, S, 1] (MatMul to [B, S, outputs], SplitV of the last axis into slices of 1)
+Status B200FusedQAHeadLayer::InferOutputShape(bool ignore_error) {
+    BaseLayer::InferOutputShape(ignore_error);
+    auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param_);
+    CHECK_PARAM_NULL(p);
+    DimsVector dims = input_blobs_[0]->GetBlobDesc().dims;
+    if (dims.size() < 2 || dims.back() != p->hidden || static_cast<int>(output_blobs_.size()) != p->outputs) {
+        LOGE_IF(!ignore_error, "FusedQAHead: input feature dim or output count does not match the weight\n");
+        return Status(TNNERR_PARAM_ERR, "FusedQAHead: input feature dim or output count does not match the weight");
+    }
+    dims.back() = 1;
+    for (auto* b : output_blobs_) b->GetBlobDesc().dims = dims;
+    return TNN_OK;
+}
+REGISTER_LAYER(B200FusedQAHead, LAYER_B200_FUSED_QA_HEAD);
 
 }  // namespace TNN_NS

@@ -8,8 +8,9 @@
 //   FusedAttention  heads head_dim scale mask_exclude_below compute_dtype
 //   FusedEmbedding  hidden eps compute_dtype
 //   FusedMask       masked_value
+//   FusedQAHead     hidden outputs
 // Resources: FusedLinear = weight_count, then (weight fp32 [K,N_i], bias fp32 [N_i]) per merged weight;
-//            FusedEmbedding = word, segment and position tables.
+//            FusedEmbedding = word, segment and position tables;  FusedQAHead = weight fp32 [H, outputs], bias.
 #include <fstream>
 
 #include "b200_plugin_common.h"
@@ -149,5 +150,35 @@ Status B200FusedMaskLayerInterpreter::SaveResource(Serializer& serializer, Layer
     return TNN_OK;
 }
 REGISTER_LAYER_INTERPRETER(B200FusedMask, LAYER_B200_FUSED_MASK);
+
+// ---------------------------------------------------------------- FusedQAHead
+DECLARE_LAYER_INTERPRETER(B200FusedQAHead, LAYER_B200_FUSED_QA_HEAD);
+
+Status B200FusedQAHeadLayerInterpreter::InterpretProto(str_arr layer_cfg_arr, int index, LayerParam** param) {
+    auto p = CreateLayerParam<FusedQAHeadLayerParam>(param);
+    GET_INT_1(p->hidden);
+    GET_INT_1(p->outputs);
+    return TNN_OK;
+}
+Status B200FusedQAHeadLayerInterpreter::InterpretResource(Deserializer& deserializer, LayerResource** resource) {
+    auto r = CreateLayerRes<FusedQAHeadLayerResource>(resource);
+    GET_BUFFER_FOR_ATTR(r, weight, deserializer);
+    GET_BUFFER_FOR_ATTR(r, bias, deserializer);
+    return TNN_OK;
+}
+Status B200FusedQAHeadLayerInterpreter::SaveProto(std::ofstream& output_stream, LayerParam* param) {
+    auto p = dynamic_cast<FusedQAHeadLayerParam*>(param);
+    if (!p) return Status(TNNERR_NULL_PARAM, "invalid layer param to save");
+    output_stream << p->hidden << " " << p->outputs << " ";
+    return TNN_OK;
+}
+Status B200FusedQAHeadLayerInterpreter::SaveResource(Serializer& serializer, LayerParam* param, LayerResource* resource) {
+    auto r = dynamic_cast<FusedQAHeadLayerResource*>(resource);
+    if (!r) return Status(TNNERR_NULL_PARAM, "invalid layer resource to save");
+    serializer.PutRaw(r->weight);
+    serializer.PutRaw(r->bias);
+    return TNN_OK;
+}
+REGISTER_LAYER_INTERPRETER(B200FusedQAHead, LAYER_B200_FUSED_QA_HEAD);
 
 }  // namespace TNN_NS

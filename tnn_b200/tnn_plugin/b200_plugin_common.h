@@ -26,10 +26,12 @@ static const LayerType LAYER_B200_FUSED_LINEAR    = static_cast<LayerType>(810);
 static const LayerType LAYER_B200_FUSED_ATTENTION = static_cast<LayerType>(811);
 static const LayerType LAYER_B200_FUSED_EMBEDDING = static_cast<LayerType>(812);
 static const LayerType LAYER_B200_FUSED_MASK      = static_cast<LayerType>(813);
+static const LayerType LAYER_B200_FUSED_QA_HEAD   = static_cast<LayerType>(814);
 static const char* const kFusedLinearTypeName     = "FusedLinear";
 static const char* const kFusedAttentionTypeName  = "FusedAttention";
 static const char* const kFusedEmbeddingTypeName  = "FusedEmbedding";
 static const char* const kFusedMaskTypeName       = "FusedMask";
+static const char* const kFusedQAHeadTypeName     = "FusedQAHead";
 
 // y = epilogue(x . W + bias (+ residual)); replaces MatMul -> Add(bias) [-> GELU | -> Add(residual)].
 // Inputs: x [, residual].  Several matched MatMul+Add pairs that share x (Q, K, V) are merged: their weights are kept
@@ -81,6 +83,19 @@ struct FusedEmbeddingLayerResource : public LayerResource {
 struct FusedMaskLayerParam : public LayerParam {
     float masked_value = -10000.0f;
     PARAM_COPY(FusedMaskLayerParam)
+};
+
+// Span-extraction head: logits = x . W + b with W [H, outputs], one fp32 [B, S, 1] output blob per logit; replaces
+// MatMul -> Add(bias) -> SplitV(last axis, sizes 1).  Input: x [B, S, H].
+struct FusedQAHeadLayerParam : public LayerParam {
+    int hidden  = 0;
+    int outputs = 0;
+    PARAM_COPY(FusedQAHeadLayerParam)
+};
+
+struct FusedQAHeadLayerResource : public LayerResource {
+    RawBuffer weight;   // fp32 [H, outputs] (storage shared with the matched MatMul's resource)
+    RawBuffer bias;     // fp32 [outputs]
 };
 
 inline DataType TnnDataType(int b200_dtype) {
