@@ -82,6 +82,26 @@ def test_fused_model_round_trips_through_model_packer():
     assert "FusedEmbedding" in text and "MatMul" not in text and "Gather" not in text
 
 
+def test_export_style_graph_fuses_like_the_resource_style():
+    """Weights and biases as constant-map inputs (MatMul weight_position -1, bias on either side of the Add) and the
+    scale written as Div(sqrt(d)): the pass brings them to the form its patterns know and fuses the same layers; two
+    instances of one model (a shared resource object, one private structure each) both fuse."""
+    wl = ms.make_workload(ms.BERT_BASE, 2, 32, seed=2, num_layers=2)
+    d = tempfile.mkdtemp(prefix="fuse_export_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, style="export")
+    text = open(proto).read()
+    assert "Div" in text and " -1," in text
+    lines = rt.fuse_report(proto, model)
+    assert [ln.split()[0] for ln in lines] == ["FusedLinear", "FusedAttention", "FusedLinear", "LayerNorm",
+                                               "FusedLinear", "FusedLinear", "LayerNorm"] * 2
+    assert rt.fuse_report(proto, model) == lines
+    # the fused model can be saved and reloaded
+    proto2, model2 = os.path.join(d, "f.tnnproto"), os.path.join(d, "f.tnnmodel")
+    assert rt.fuse_and_pack(proto, model, proto2, model2) == len(lines)
+    assert rt.fuse_report(proto2, model2) == lines
+
+
 def test_qa_head_fuses_to_one_layer_with_two_named_outputs():
     """MatMul [H, 2] -> Add -> SplitV becomes one FusedQAHead; the two Squeeze layers behind it keep the graph's
     output names; the fused model survives the ModelPacker round trip."""

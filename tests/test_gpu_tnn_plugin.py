@@ -146,6 +146,21 @@ def test_pooler_head_matches_x86_fixture(cuda_device):
     assert cosine(y, ref) >= COS_TOL
 
 
+def test_export_style_graph_matches_x86_fixture(cuda_device):
+    """Constant-map weights and biases, Div scale (a plain converter export): fused after canonicalisation, equal to the
+    resource-style graph's result bit for bit."""
+    name = "base_2layer_ragged"
+    wl = golden_workload(**CASES[name])
+    d = tempfile.mkdtemp(prefix="plug_export_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, style="export")
+    y = _run(proto, model, wl, rt.DEVICE_CUDA)
+    proto0, model0 = _files(wl)
+    assert np.array_equal(y, _run(proto0, model0, wl, rt.DEVICE_CUDA))
+    ref = np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]
+    assert max_abs(y.reshape(ref.shape), ref) <= MAX_ABS_TOL
+
+
 def test_qa_head_matches_x86_fixture(cuda_device):
     """Encoder layer + span-extraction head: one FusedQAHead, outputs `unstack:0` / `unstack:1` as the demo reads them."""
     name = "base_1layer_qa"

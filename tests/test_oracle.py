@@ -68,6 +68,27 @@ def test_qa_head_restatement_matches_reference_x86(name):
     assert float(g["x86_vs_naive_max_abs"]) < 5e-5
 
 
+def test_export_style_graph_gives_the_fixture_on_the_reference():
+    """The same weights written the way a plain converter export does (constant-map weights, Div scale) run on the
+    reference's DEVICE_X86 to the committed fixture of the resource-style graph: the two forms are one computation."""
+    import tempfile
+    from oracle import tnn_ref
+    if not tnn_ref.available():
+        pytest.skip("the reference build is not here")
+    name = "base_2layer_ragged"
+    wl = golden_workload(**CASES[name])
+    d = tempfile.mkdtemp(prefix="export_style_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    model_synth.write_tnn_model(wl, proto, model, style="export")
+    inst = tnn_ref.TnnInstance(proto, model, device=tnn_ref.DEVICE_X86)
+    inst.set_input("x", wl.x)
+    inst.set_input("mask", wl.mask_add)
+    inst.forward()
+    y = inst.get_output().reshape(wl.x.shape)
+    inst.close()
+    assert max_abs(y, np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]) < 2e-5
+
+
 def test_gather_out_of_range_is_an_error():
     with pytest.raises(IndexError):
         bert_oracle.gather_rows(np.zeros((4, 2), np.float32), np.array([0, 4]))

@@ -20,7 +20,7 @@ import numpy as np
 MAGIC = 0x0FABC0002   # untyped-input proto / model magic (source/tnn/interpreter/tnn/objseri.h:29-30)
 MAGIC_RAW = 0x0FABC0004
 # LayerType enum values used in the binary (source/tnn/core/layer_type.h); the parser keys on the type string.
-_TYPE_ID = {"MatMul": 105, "Add": 38, "Mul": 42, "Gather": 104, "Sub": 108}
+_TYPE_ID = {"MatMul": 105, "Add": 38, "Mul": 42, "Gather": 104, "Sub": 108, "Div": 175}
 
 
 @dataclass
@@ -145,8 +145,12 @@ def _raw(a):
             b"".join(struct.pack("<i", d) for d in dims) + a.tobytes())
 
 
-def _encoder_graph(wl, input_name, mask_name):
-    """Layer lines, resource records and constants of the unfused encoder graph; returns them with the output name."""
+def _encoder_graph(wl, input_name, mask_name, style="resource"):
+    """Layer lines, resource records and constants of the unfused encoder graph; returns them with the output name.
+    `style` "resource": weights and biases are layer resources and the scale is Mul(1/sqrt(d)), the form the TNN
+    converters write after constant folding; "export": weights and biases are entries of the constant map consumed as
+    second inputs (MatMul weight_position -1; every second bias written as Add(bias, x)) and the scale is
+    Div(sqrt(d)), the form of a plain converter export."""
     cfg = wl.cfg
     B, S, H = wl.x.shape
     NH, D, F = cfg.heads, cfg.head_dim, cfg.ffn
@@ -158,7 +162,17 @@ def _encoder_graph(wl, input_name, mask_name):
     def resource(t, name, arr):
         res.append(struct.pack("<i", _TYPE_ID[t]) + _pstr(t) + _pstr(name) + _raw(arr))
 
+    n_linear = [0]
+
     def linear(name, x, w, b):
+        if style == "export":
+            n_linear[0] += 1
+            consts[name + "_w"] = w
+            consts[name + "_bias"] = b.reshape(-1)
+            layer("MatMul", name + "_mm", [x, name + "_w"], [name + "_mm"], "-1")
+            ins = [name + "_mm", name + "_bias"] if n_linear[0] % 2 else [name + "_bias", name + "_mm"]
+            layer("Add", name + "_b", ins, [name + "_b"], "-1")
+            return name + "_b"
         layer("MatMul", name + "_mm", [x], [name + "_mm"], "1")
         resource("MatMul", name + "_mm", w)
         layer("Add", name + "_b", [name + "_mm"], [name + "_b"], "1")
@@ -180,8 +194,12 @@ def _encoder_graph(wl, input_name, mask_name):
             layer("Reshape", p + n + "_r", [o], [p + n + "_r"], "0 4 4 0 0 %d %d 0" % (NH, D))
             layer("Permute", p + n + "_p", [p + n + "_r"], [p + n + "_p"], "4 " + perm)
         layer("MatMul", p + "qk", [p + "q_p", p + "k_p"], [p + "qk"], "-1")
-        layer("Mul", p + "qk_s", [p + "qk"], [p + "qk_s"], "1")
-        resource("Mul", p + "qk_s", np.array([1.0 / np.sqrt(D)], np.float32))
+        if style == "export":
+            layer("Div", p + "qk_s", [p + "qk"], [p + "qk_s"], "1")
+            resource("Div", p + "qk_s", np.array([np.sqrt(D)], np.float32))
+        else:
+            layer("Mul", p + "qk_s", [p + "qk"], [p + "qk_s"], "1")
+            resource("Mul", p + "qk_s", np.array([1.0 / np.sqrt(D)], np.float32))
         layer("Add", p + "qk_m", [p + "qk_s", mask_name], [p + "qk_m"], "-1")
         layer("Softmax", p + "sm", [p + "qk_m"], [p + "sm"], "3")
         layer("MatMul", p + "ctx", [p + "sm", p + "v_p"], [p + "ctx"], "-1")
@@ -266,14 +284,14 @@ def _qa_graph(x, qa):
 
 
 def write_tnn_model(wl, proto_path, model_path, input_name="x", mask_name="mask", pooler=None, input_dtype=None,
-                    qa=None):
+                    qa=None, style="resource"):
     """Write the unfused encoder graph of `wl` as tnnproto + tnnmodel.  Returns the output blob name (a list of two
     names with `qa`).  `pooler` (from make_pooler) appends the pooler head MatMul -> Add -> Tanh to the last layer's
     output; `qa` (from make_qa_head) appends the span-extraction head with its two unstacked outputs.  `input_dtype`
     "half" / "bf16" declares the activation input as a typed (v2) half-precision blob (include/tnn/core/common.h
     DataType: 1 = half, 4 = bfp16), so that a half-precision Mat reaches the device without conversion."""
     B, S, H = wl.x.shape
-    layers, res, consts, out = _encoder_graph(wl, input_name, mask_name)
+    layers, res, consts, out = _encoder_graph(wl, input_name, mask_name, style)
     if pooler is not None:
         l2, r2, out = _pooler_graph(out, pooler)
         layers, res = layers + l2, res + r2

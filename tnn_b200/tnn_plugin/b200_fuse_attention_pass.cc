@@ -144,6 +144,91 @@ Status AddFusedLinear(const std::shared_ptr<Graph>& g, const std::vector<std::st
     return TNN_OK;
 }
 
+// Converter exports differ in where constants live and how the scale is written; the patterns below know one form.
+// This step rewrites the other forms into it, layer by layer, before matching:
+//   * MatMul(x, W) with W a 2-D fp32 entry of the constant map (weight_position -1, two inputs) becomes MatMul(x) with
+//     W as the layer's resource (weight_position 1) — both forms are handled by the reference's own pass,
+//     source/tnn/optimizer/net_optimizer_convert_matmul_to_conv.cc:112-146;
+//   * Add(x, c) / Add(c, x) / Mul(x, c) / Div(x, c) with c an fp32 entry of the constant map becomes the one-input
+//     form with c as the layer's resource (weight_input_index 1; for Div only Div(x, c));
+//   * Div by a one-element constant becomes Mul by its reciprocal (the attention scale written as / sqrt(d)).
+// Shared objects are never modified: every new resource is a new object whose RawBuffer shares the constant's storage
+// (or, for the reciprocal, owns four new bytes); the resource map is shared by the instances of a model, and a second
+// instance's pass finds the entries of the first and replaces them with equal ones.
+void Canonicalize(NetStructure* structure, NetResource* resource) {
+    auto constant = [&](const std::string& name) -> std::shared_ptr<RawBuffer> {
+        auto it = resource->constant_map.find(name);
+        if (it == resource->constant_map.end() || !it->second || it->second->GetDataType() != DATA_TYPE_FLOAT) return nullptr;
+        return it->second;
+    };
+    std::vector<std::string> absorbed;   // constants that became layer resources
+    for (auto& l : structure->layers) {
+        if (l->type == LAYER_MATMUL && l->inputs.size() == 2) {
+            auto p = std::dynamic_pointer_cast<MatMulLayerParam>(l->param);
+            auto w = constant(l->inputs[1]);
+            if (!p || !w || w->GetBufferDims().size() != 2 || constant(l->inputs[0])) continue;
+            auto r    = std::make_shared<MatMulLayerResource>();
+            r->name   = l->name;
+            r->weight = *w;
+            resource->resource_map[l->name] = r;
+            p->weight_position = 1;
+            absorbed.push_back(l->inputs[1]);
+            l->inputs.pop_back();
+        } else if ((l->type == LAYER_ADD || l->type == LAYER_MUL || l->type == LAYER_DIV) && l->inputs.size() == 2) {
+            auto p = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(l->param);
+            if (!p) continue;
+            auto c1 = constant(l->inputs[1]);
+            auto c0 = constant(l->inputs[0]);
+            if (c1 && !c0) {
+                absorbed.push_back(l->inputs[1]);
+                l->inputs.pop_back();
+            } else if (c0 && !c1 && l->type != LAYER_DIV) {
+                absorbed.push_back(l->inputs[0]);
+                l->inputs.erase(l->inputs.begin());
+                c1 = c0;
+            } else {
+                continue;
+            }
+            auto r            = std::make_shared<EltwiseLayerResource>();
+            r->name           = l->name;
+            r->element_handle = *c1;
+            r->element_shape  = c1->GetBufferDims();
+            resource->resource_map[l->name] = r;
+            p->weight_input_index = 1;
+        }
+        if (l->type == LAYER_DIV && l->inputs.size() == 1) {
+            auto it = resource->resource_map.find(l->name);
+            auto r  = it == resource->resource_map.end() ? nullptr : std::dynamic_pointer_cast<EltwiseLayerResource>(it->second);
+            auto p  = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(l->param);
+            if (!r || !p || p->weight_input_index != 1 || r->element_handle.GetDataCount() != 1 ||
+                r->element_handle.GetDataType() != DATA_TYPE_FLOAT)
+                continue;
+            const float c = r->element_handle.force_to<float*>()[0];
+            if (c == 0.f) continue;
+            const float inv = 1.0f / c;
+            auto m            = std::make_shared<EltwiseLayerResource>();
+            m->name           = l->name;
+            m->element_handle = RawBuffer(sizeof(float), reinterpret_cast<char*>(const_cast<float*>(&inv)), r->element_handle.GetBufferDims());
+            m->element_handle.SetDataType(DATA_TYPE_FLOAT);
+            m->element_shape  = r->element_shape;
+            resource->resource_map[l->name] = m;
+            l->type     = LAYER_MUL;
+            l->type_str = "Mul";
+            p->type     = "Mul";
+        }
+    }
+    // A constant nothing reads any more leaves this instance's constant map (the map is the instance's own copy; its
+    // entries are shared): the graph matcher turns every entry into a node and refuses a graph with loose nodes.
+    for (const auto& name : absorbed) {
+        bool used = false;
+        for (auto& l : structure->layers)
+            for (auto& in : l->inputs) used = used || in == name;
+        if (used) continue;
+        resource->constant_map.erase(name);
+        structure->blobs.erase(name);
+    }
+}
+
 const char* kAttentionMasked = R"(
     graph(%x, %mask):
         %q_mm = MatMul(%x)
@@ -203,8 +288,11 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
     // Already fused (the pass must be idempotent: Instance::Init may run the optimizers twice on one structure).
     for (auto& l : structure->layers)
         if (l->type == LAYER_B200_FUSED_LINEAR || l->type == LAYER_B200_FUSED_ATTENTION ||
-            l->type == LAYER_B200_FUSED_EMBEDDING || l->type == LAYER_B200_FUSED_MASK)
+            l->type == LAYER_B200_FUSED_EMBEDDING || l->type == LAYER_B200_FUSED_MASK ||
+            l->type == LAYER_B200_FUSED_QA_HEAD)
             return TNN_OK;
+
+    Canonicalize(structure, resource);
 
     std::shared_ptr<Graph> graph = std::make_shared<Graph>();
     Status status = graph->fromInterpreted(structure, resource);
