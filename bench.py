@@ -11,6 +11,7 @@ Keys of the JSON line beyond the base contract:
   roofline     the projection/FFN GEMM kernel (dominant): algorithmic FLOPs of its launches / their CUDA-event time
   cpu_baseline the reference's own DEVICE_X86 implementation timed on this host on a bounded sample (rank 0, N = 1)
   e2e          the same metric with HOST buffers: pinned fp32 input -> H2D -> Forward -> D2H of the fp32 output per step
+  e2e_half_io  the same with half-precision host buffers (half the bytes, no conversions): informational
 `--impl reference` times the reference's CPU implementation of the same path with all host cores.
 """
 import argparse
@@ -232,6 +233,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = _bind_to_gpu_cpus(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()  # fail loudly here if the CUDA library is missing
@@ -348,6 +350,39 @@ def run_ours(args):
     barrier()
     h2d = x_host.numel() * 4
     d2h = out_host[0].numel() * 4
+
+    # ---- the same with half-precision host buffers (RESERVED_FP16_TEST Mats in the plug-in): half the bytes over PCIe,
+    # no conversion launches; the copies go straight into / out of the encoder's hidden-state buffer
+    x_host16 = torch.from_numpy(wl.x.astype(np.float16)).pin_memory()
+    out_host16 = [torch.empty((B, SEQ, cfg.hidden), dtype=torch.float16).pin_memory() for _ in range(2)]
+    half_graphs = [capture(lambda b=b: enc.forward_hidden(hid[b], mask_dev, kv_len)) for b in range(2)]
+
+    def half_loop(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_copy_in):
+                s_copy_in.wait_event(ev_out[b])            # hid[b]'s previous result has been drained to the host
+                hid[b].view(B, SEQ, cfg.hidden).copy_(x_host16, non_blocking=True)
+                ev_in[b].record(s_copy_in)
+            s_main.wait_event(ev_in[b])
+            if half_graphs[b] is not None:
+                half_graphs[b].replay()
+            else:
+                enc.forward_hidden(hid[b], mask_dev, kv_len)
+            ev_done[b].record(s_main)
+            with torch.cuda.stream(s_copy_out):
+                s_copy_out.wait_event(ev_done[b])
+                out_host16[b].copy_(hid[b].view(B, SEQ, cfg.hidden), non_blocking=True)
+                ev_out[b].record(s_copy_out)
+
+    torch.cuda.synchronize()
+    half_loop(4)
+    barrier()
+    t0 = time.perf_counter()
+    half_loop(args.steps)
+    torch.cuda.synchronize()
+    e2e_half_s = time.perf_counter() - t0
+    barrier()
 
     # ---- roofline of the dominant kernel (the GEMM): an instrumented pass with an event pair around every launch
     tokens = B * SEQ
@@ -467,12 +502,13 @@ def run_ours(args):
             del qkv_, out_
 
     # ---- reduce over ranks
-    ms_t = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    ms_t = torch.tensor([ms_total, e2e_s * 1e3, e2e_half_s * 1e3], dtype=torch.float64, device=dev)
     ms_t = reduce_max_over_ranks(ms_t, world)
     ms_total_max, e2e_ms_max = float(ms_t[0]), float(ms_t[1])
     seqs = world * B * args.steps
     value = seqs / (ms_total_max / 1e3)
     e2e_value = seqs / (e2e_ms_max / 1e3)
+    e2e_half_value = seqs / (float(ms_t[2]) / 1e3)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -501,7 +537,12 @@ def run_ours(args):
                              "no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "pinned fp32 host buffers, copies double-buffered on side streams, wall clock"},
+                    "note": "pinned fp32 host buffers, copies double-buffered on side streams, wall clock"
+                            + ("" if numa is None else "; rank bound to the %d CPUs local to its GPU" % numa)},
+            "e2e_half_io": {"value": e2e_half_value, "unit": UNIT, "h2d_bytes_per_step": h2d // 2,
+                            "d2h_bytes_per_step": d2h // 2,
+                            "note": "the same with pinned fp16 host buffers (half-precision Mats): half the bytes, no "
+                                    "conversion launches; informational, the fp32 line above is the e2e number"},
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "kernel": "linear_pair_kernel (projection/FFN GEMM, tcgen05 cta_group::2)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
@@ -546,6 +587,25 @@ def ncu_traffic_per_launch(batch, per_shape):
         return None
     vals = [NCU_DRAM_BYTES_M8192[k] for k in per_shape if k in NCU_DRAM_BYTES_M8192]
     return sum(vals) / len(vals) if vals else None
+
+
+def _bind_to_gpu_cpus(index):
+    """One rank per GPU: run this process (and first-touch its pinned host buffers) on the CPUs NVML reports as local
+    to its GPU, so that H2D / D2H copies do not cross the socket interconnect.  Host-side process affinity only; no
+    setting of the GPU is touched.  Returns the number of CPUs bound to, or None when NVML or the cpuset refuses."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {w * 64 + b for w, m in enumerate(words) for b in range(64) if (int(m) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
 
 
 def main():
