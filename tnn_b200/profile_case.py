@@ -4,6 +4,8 @@
     python -m tnn_b200.profile_case attention --B 64 --S 128 --heads 12
     python -m tnn_b200.profile_case layernorm --rows 8192 --H 768
     python -m tnn_b200.profile_case encoder --B 64 --S 128 --layers 2
+    python -m tnn_b200.profile_case qa_head --rows 131072 --H 768
+    python -m tnn_b200.profile_case embedding --B 1024 --S 128 --H 768
 
 Prints the mean CUDA-event time per launch.  Operands are seeded random device tensors; sizes default to the
 benchmark's config 2 shapes.
@@ -17,7 +19,7 @@ from . import capi, ops
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["linear", "attention", "layernorm", "encoder"])
+    ap.add_argument("kernel", choices=["linear", "attention", "layernorm", "encoder", "qa_head", "embedding"])
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=768)
@@ -77,6 +79,27 @@ def main():
         y = torch.empty_like(x)
         fn = lambda: ops.add_layernorm(x, g, be, 1e-12, out=y)  # noqa: E731
         work = 2.0 * a.rows * a.H * 2 * 1e3   # bytes, scaled so that the print below reads GB/s
+        unit = "GB/s"
+    elif a.kernel == "qa_head":
+        x = torch.randn(a.rows, a.H, device=dev).to(dt)
+        w = (torch.randn(a.H, 2, device=dev) * 0.05).contiguous()
+        b = torch.randn(2, device=dev)
+        out = torch.empty(2, a.rows, device=dev)
+        fn = lambda: ops.qa_head(x, w, b, out=out)  # noqa: E731
+        work = (a.rows * a.H * 2 + a.rows * 8) * 1e3   # bytes: x once, two fp32 logits per token
+        unit = "GB/s"
+    elif a.kernel == "embedding":
+        vocab = 30522
+        ids = torch.randint(0, vocab, (a.B, a.S), device=dev, dtype=torch.int32)
+        seg = torch.randint(0, 2, (a.B, a.S), device=dev, dtype=torch.int32)
+        word = torch.randn(vocab, a.H, device=dev).to(dt)
+        typ = torch.randn(2, a.H, device=dev).to(dt)
+        pos = torch.randn(512, a.H, device=dev).to(dt)
+        g = torch.ones(a.H, device=dev)
+        be = torch.zeros(a.H, device=dev)
+        out = torch.empty(a.B, a.S, a.H, device=dev, dtype=dt)
+        fn = lambda: ops.embedding_layernorm(ids, seg, word, typ, pos, g, be, 1e-12, out=out)  # noqa: E731
+        work = a.B * a.S * a.H * 2 * 4 * 1e3   # bytes per token: three table rows in, one row out
         unit = "GB/s"
     else:
         from . import model_synth
