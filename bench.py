@@ -238,6 +238,32 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()  # fail loudly here if the CUDA library is missing
 
+    # ---- the benchmark's standalone attention sweep (16 heads x d64, batch 16, S = 512/1024/2048, all-ones mask).
+    # A kernel timed alone, so it runs first, before the long loops bring the GPU to its power cap (the measured
+    # tensor peak it is compared with is a burst figure too).
+    peaks = measured_peaks()
+    attention_sweep = []
+    if rank == 0 and not args.no_attention_sweep:
+        for S_ in (512, 1024, 2048):
+            qkv_ = torch.randn(16, S_, 3 * 16 * 64, device=dev).to(torch.float16)
+            msk_ = torch.zeros(16, S_, device=dev)
+            kvl_ = ops.mask_to_kv_len(msk_)
+            out_ = torch.empty(16, S_, 16 * 64, device=dev, dtype=torch.float16)
+            for _ in range(3):
+                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(10):
+                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+            a1.record()
+            torch.cuda.synchronize()
+            ms_ = a0.elapsed_time(a1) / 10
+            fl_ = 4.0 * S_ * S_ * 64 * 16 * 16
+            attention_sweep.append({"S": S_, "ms": round(ms_, 4), "tflops": round(fl_ / ms_ / 1e9, 1),
+                                    "frac_of_tensor_peak": round(fl_ / ms_ / 1e9 / peaks["tflops"], 4)})
+            del qkv_, out_
+
     B = args.batch
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
@@ -478,29 +504,6 @@ def run_ours(args):
     attn_ms = statistics.mean(kernel_ms["attention"])
     attn_flops = 4.0 * SEQ * SEQ * 64 * cfg.heads * B
 
-    # ---- the benchmark's standalone attention sweep (16 heads x d64, batch 16, S = 512/1024/2048, all-ones mask)
-    attention_sweep = []
-    if rank == 0 and not args.no_attention_sweep:
-        for S_ in (512, 1024, 2048):
-            qkv_ = torch.randn(16, S_, 3 * 16 * 64, device=dev).to(torch.float16)
-            msk_ = torch.zeros(16, S_, device=dev)
-            kvl_ = ops.mask_to_kv_len(msk_)
-            out_ = torch.empty(16, S_, 16 * 64, device=dev, dtype=torch.float16)
-            for _ in range(3):
-                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
-            torch.cuda.synchronize()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(10):
-                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
-            a1.record()
-            torch.cuda.synchronize()
-            ms_ = a0.elapsed_time(a1) / 10
-            fl_ = 4.0 * S_ * S_ * 64 * 16 * 16
-            attention_sweep.append({"S": S_, "ms": round(ms_, 4), "tflops": round(fl_ / ms_ / 1e9, 1),
-                                    "frac_of_tensor_peak": round(fl_ / ms_ / 1e9 / peaks["tflops"], 4)})
-            del qkv_, out_
-
     # ---- reduce over ranks
     ms_t = torch.tensor([ms_total, e2e_s * 1e3, e2e_half_s * 1e3], dtype=torch.float64, device=dev)
     ms_t = reduce_max_over_ranks(ms_t, world)
@@ -548,6 +551,9 @@ def run_ours(args):
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": "of " + peaks["source"] + " (burst)",
                          "peak_sustained": peaks["tflops_sustained"],
+                         "frac_of_sustained": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
+                         "thermal_note": "the replays follow the timed loops, i.e. they run at the sustained (power-capped) "
+                                         "clocks the `clocks` key shows; `frac` nevertheless divides by the burst peak",
                          "flops_per_launch_avg": flops_per_pass / gemm_launches_per_pass,
                          "ms_per_launch_avg": gemm_pass_ms / gemm_launches_per_pass,
                          "launches_timed": gemm_launches_per_pass * reps,
@@ -562,6 +568,8 @@ def run_ours(args):
                                          "(profiles/linear_pair_kernel_config2_shapes.md), averaged over the shapes "
                                          "captured; equals the operand bytes, outputs stay in L2"},
             "attention_sweep": attention_sweep,
+            "attention_sweep_note": "each point: 10 launches between one CUDA-event pair, timed before the long loops "
+                                    "(burst clocks, as the measured tensor peak was)",
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
                                  "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
             "layernorm_kernel": {"ms": statistics.mean(kernel_ms["layernorm"]),
