@@ -268,7 +268,6 @@ def run_ours(args):
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
     enc = Encoder.from_workload(wl, torch.float16, dev, fold_layernorm=args.fold_layernorm)
-    enc.layernorm_in_gemm = args.layernorm_in_gemm
     x_dev = torch.from_numpy(wl.x).to(dev)
     mask_dev = torch.from_numpy(wl.mask_add.reshape(B, SEQ)).to(dev).contiguous()
     kv_len = ops.mask_to_kv_len(mask_dev)
@@ -533,9 +532,7 @@ def run_ours(args):
                        "batch_per_gpu": B, "seq_len": SEQ, "layers": len(enc.layers),
                        "parallelism": "independent replicas, batch-sharded, no collective",
                        "launch": "CUDA graph of one Forward" if graph is not None else "eager launches",
-                       "layernorm": ("folded into the GEMM epilogues" if enc.fold else
-                                     ("inside the launch of the producing GEMM" if enc.layernorm_in_gemm else
-                                      "separate kernels")),
+                       "layernorm": "folded into the GEMM epilogues" if enc.fold else "separate kernels",
                        "l2": "per-step working set (170 MB fp16 weights + activations) exceeds the 126 MB L2; "
                              "no explicit flush"},
             "clocks": clocks,
@@ -628,9 +625,6 @@ def main():
     ap.add_argument("--no-tnn-plugin", action="store_true", help="skip the measurement through TNN + plug-in")
     ap.add_argument("--fold-layernorm", action="store_true",
                     help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
-    ap.add_argument("--layernorm-in-gemm", action="store_true",
-                    help="run each LayerNorm inside the launch of the GEMM that feeds it (5 launches per layer "
-                         "instead of 7; measured slower at this size)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
                                                             "a captured CUDA graph of one Forward")
     args = ap.parse_args()

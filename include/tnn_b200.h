@@ -129,20 +129,6 @@ typedef struct B200LinearDesc {
     const float* res_ln_beta;
     float        ln_eps;
     int32_t      reserved_;
-    /* ---- LayerNorm of the output rows inside the same launch (optional; NULL post_ln_out = off) --------------------
-     * y is written as usual (it is the exchange buffer: a row of y is produced by ceil(N / tile width) different CTA
-     * pairs); each pair then waits — counter per 256-row block in post_ln_sync, release/acquire, bounded — until the
-     * other tiles of its row block are in memory, and normalises its share of the block's rows:
-     *   post_ln_out[r, :] = (y[r, :] - mean) * rsqrt(var + ln_eps) * post_ln_gamma + post_ln_beta        (dtype)
-     * This removes the separate LayerNorm launch (~8 us at 8192 x 768) for ~2 us at the tail of the GEMM.
-     * Requirements: out_dtype == dtype; N % 8 == 0, N <= 1024; post_ln_ld % 8 == 0, >= N; no LayerNorm folding
-     * fields; post_ln_sync: ceil(M / 256) int32 of device memory, ALL ZERO on entry (cudaMemsetAsync on the same
-     * stream), left non-zero.  Always runs on CTA-pair tiles.  Same arithmetic as b200_add_layernorm_fwd. */
-    const float* post_ln_gamma;
-    const float* post_ln_beta;
-    void*        post_ln_out;
-    int64_t      post_ln_ld;
-    void*        post_ln_sync;
 } B200LinearDesc;
 B200_API int b200_linear_fwd(const B200LinearDesc* desc, b200_stream_t stream);
 
@@ -194,9 +180,12 @@ B200_API int b200_attention_fwd(const B200AttentionDesc* desc, b200_stream_t str
  * exits) — and then runs the same attention kernels.  It calls no cudaMalloc / cudaFree and no allocating routine,
  * on the device or on the host (its tensor maps live on the stack).
  *   - B > B200_STATIC_MAX_BATCH is refused with B200_ERR_STATIC_LIMIT; nothing is launched.
- *   - The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress, with that device
- *     current) and sets the kernels' shared-memory attribute; make that first call before starting any stream
- *     capture on that device.  Later calls only launch.
+ *   - The first call on a device is the warm-up: it looks up the scratch array's device address
+ *     (cudaGetSymbolAddress, with that device current) and sets the kernels' shared-memory attribute, under a host
+ *     mutex so that two threads may make it at once; the CUDA runtime may also load the kernels' module on that first
+ *     launch, which is the driver's business and outside this promise.  Make that call at start-up, before starting
+ *     any stream capture on that device.  Later calls only launch (the status-word address and the driver's
+ *     tensor-map encoder are looked up once per process behind a mutex / a function-local static; no memory is taken).
  *   - All calls on one GPU share the one scratch array.  Nothing in it needs clearing: each call overwrites the B
  *     entries it then reads, and entries beyond B are never read.  Two calls whose kernels can overlap on the GPU
  *     (different streams without an ordering between them) race on it: keep such calls on one stream, or order them.
@@ -292,44 +281,6 @@ typedef struct B200LayerNormDesc {
 B200_API int b200_add_layernorm_fwd(const B200LayerNormDesc* desc, b200_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------------------------
- * Several dependent operators of one encoder layer in ONE launch ("chain").  (No counterpart in the reference, whose
- * executor runs one layer acc after the other, source/tnn/core/default_network.cc:558-635.)
- *
- * At 64 x 128 tokens the GEMMs of a BERT-base layer last 15-35 us each, and every kernel boundary costs ~5 us in
- * which most SMs idle: the last tile's epilogue, the drain, the dependency hand-over, the first loads.  A chain is a
- * list of phases — B200_PHASE_LINEAR (a B200LinearDesc) or B200_PHASE_ADD_LAYERNORM (a B200LayerNormDesc) — executed
- * by one persistent kernel of CTA pairs.  Work items (256 x 192 GEMM tiles, 64-row LayerNorm items) are dealt to the
- * CTAs phase after phase in row-block order; an item starts as soon as the 256-row block(s) it reads have been
- * completed by the phase that writes them (a counter per phase and row block in `sync_words`, release/acquire), so the
- * tail of one phase overlaps the start of the next and nothing waits for a whole phase.
- *
- * Rules: every phase covers the same rows (linear.M == layernorm.rows for all phases); all tensors are `dtype`
- * (F16 or BF16, the same for all phases; no fp32 outputs); a phase may read, as x / residual, what an EARLIER phase of
- * the same chain writes as y (matched by pointer) or buffers that were complete before the call, and the data it
- * reads from an earlier phase must lie in the same 256-row block as the rows it produces (true for x, residual and
- * LayerNorm inputs of an encoder layer); no phase may overwrite a buffer that a phase which does not precede it in
- * this dependency order still reads.  Linear phases: no LayerNorm folding fields, block_n ignored (tiles are
- * 256 x 192).  LayerNorm phases: H % 8 == 0, H <= 1024, residual == NULL.  At most B200_CHAIN_MAX_PHASES phases, of
- * which at most B200_CHAIN_MAX_LINEAR linear ones.
- *
- * sync_words: device memory of b200_chain_sync_bytes(rows, count) bytes, ALL ZERO on entry (cudaMemsetAsync on the
- * same stream); the call leaves it non-zero.  Results equal those of the separate launches of the same descriptors
- * with block_n = 192 (same arithmetic, same order).
- */
-#define B200_CHAIN_MAX_PHASES    8
-#define B200_CHAIN_MAX_LINEAR    4
-#define B200_PHASE_LINEAR        0
-#define B200_PHASE_ADD_LAYERNORM 1
-typedef struct B200ChainPhase {
-    int32_t           kind;
-    int32_t           reserved_;
-    B200LinearDesc    linear;
-    B200LayerNormDesc layernorm;
-} B200ChainPhase;
-B200_API size_t b200_chain_sync_bytes(int64_t rows, int32_t phase_count);
-B200_API int b200_chain_fwd(const B200ChainPhase* phases, int32_t phase_count, void* sync_words, b200_stream_t stream);
-
-/* -------------------------------------------------------------------------------------------------------------------
  * One post-LN transformer-encoder layer (the fused form of the ~30 TNN layers of one BERT layer) and a whole encoder
  * stack, as a fixed sequence of the launchers above.  All buffers are the caller's.
  *   hidden  : `dtype` [tokens, H]   in/out (stack input, overwritten with the stack output)
@@ -337,8 +288,6 @@ B200_API int b200_chain_fwd(const B200ChainPhase* phases, int32_t phase_count, v
  *   workspace: b200_encoder_workspace_bytes(tokens, H, F, dtype) bytes, 256-byte aligned.
  * fold_layernorm = 0: seven launches per layer (QKV, attention, out-proj+residual, LayerNorm, FFN1+GELU,
  *   FFN2+residual, LayerNorm).  The fastest form measured at 64 x 128 tokens.
- * fold_layernorm = 2: five launches per layer: each LayerNorm runs inside the launch of the GEMM that produces its
- *   input (B200LinearDesc.post_ln_*).  Needs H <= 1024 (larger H runs the seven launches).  Bit-identical results.
  * fold_layernorm = 1: five launches per layer; both LayerNorms are folded into the neighbouring GEMMs (see
  *   B200LinearDesc) and only pre-LayerNorm activations are written.  The weights must then have been prepared with
  *   b200_fold_layernorm_weight: w_ffn1/ffn1_c1/ffn1_c2 from (W1, ln1 gamma/beta, b1) of the same layer, and for every
@@ -382,6 +331,10 @@ B200_API int         b200_device_status(void);
 /* Number of kernel launches issued by this library in this process (all devices, all threads). */
 B200_API uint64_t    b200_launch_count(void);
 B200_API const char* b200_version(void);
+/* Self-test of the tensor-map (TMA descriptor) cache the launchers share: `threads` host threads look maps up while
+ * the cache, limited to `capacity` entries for the test, keeps evicting; a stand-in replaces the driver's encoder, so
+ * no GPU or driver is needed.  Returns the number of maps that came back wrong (0 = pass) or B200_ERR_PARAM. */
+B200_API int         b200_selftest_tensor_map_cache(int threads, int maps_per_thread, int capacity);
 
 #ifdef __cplusplus
 }

@@ -30,6 +30,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
 
+def default_reference():
+    """The TNN checkout: $TNN_REFERENCE, else a directory named `reference` beside this repository."""
+    return os.environ.get("TNN_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def rglob(root, sub):
     return sorted(glob.glob(os.path.join(root, sub, "**", "*.cc"), recursive=True))
 
@@ -54,7 +59,7 @@ def collect(ref):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("TNN_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=default_reference())
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--profile", action="store_true", help="also define TNN_PROFILE (per-layer host timers)")
     ap.add_argument("--cxx", default="/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
@@ -109,7 +114,8 @@ def main():
     ninja_file = os.path.join(OUT, "build.ninja")
     with open(ninja_file, "w") as fh:
         fh.write("\n".join(lines) + "\n")
-    return subprocess.call(["ninja", "-f", ninja_file, "-j", str(args.jobs)])
+    # -C: ninja keeps its own state files (.ninja_log, .ninja_deps) in the directory it runs in
+    return subprocess.call(["ninja", "-C", OUT, "-f", ninja_file, "-j", str(args.jobs)])
 
 
 if __name__ == "__main__":

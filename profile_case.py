@@ -1,11 +1,11 @@
 """Run one kernel of the path a few times in isolation (for `ncu` captures and quick timing).
 
-    python -m tnn_b200.profile_case linear --M 8192 --N 2304 --K 768 [--epilogue gelu] [--block-n 256] [--iters 5]
-    python -m tnn_b200.profile_case attention --B 64 --S 128 --heads 12
-    python -m tnn_b200.profile_case layernorm --rows 8192 --H 768
-    python -m tnn_b200.profile_case encoder --B 64 --S 128 --layers 2
-    python -m tnn_b200.profile_case qa_head --rows 131072 --H 768
-    python -m tnn_b200.profile_case embedding --B 1024 --S 128 --H 768
+    python profile_case.py linear --M 8192 --N 2304 --K 768 [--epilogue gelu] [--block-n 256] [--iters 5]
+    python profile_case.py attention --B 64 --S 128 --heads 12
+    python profile_case.py layernorm --rows 8192 --H 768
+    python profile_case.py encoder --B 64 --S 128 --layers 2
+    python profile_case.py qa_head --rows 131072 --H 768
+    python profile_case.py embedding --B 1024 --S 128 --H 768
 
 Prints the mean CUDA-event time per launch.  Operands are seeded random device tensors; sizes default to the
 benchmark's config 2 shapes.
@@ -14,7 +14,7 @@ import argparse
 
 import torch
 
-from . import capi, ops
+from tnn_b200 import capi, ops
 
 
 def main():

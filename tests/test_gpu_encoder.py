@@ -10,14 +10,13 @@ from oracle import bert_oracle
 from oracle.make_golden import CASES, GOLDEN, golden_workload
 from tnn_b200 import capi, model_synth
 from tnn_b200.encoder import Encoder
-from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
+from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, tolerances, valid_rows
 
 pytestmark = pytest.mark.gpu
 
 
-def _run(wl, dtype, single_call=True, fold=True, layernorm_in_gemm=False):
+def _run(wl, dtype, single_call=True, fold=True):
     enc = Encoder.from_workload(wl, dtype, fold_layernorm=fold)
-    enc.layernorm_in_gemm = layernorm_in_gemm
     x = torch.from_numpy(wl.x).cuda()
     m = torch.from_numpy(wl.mask_add).cuda()
     y = enc.forward(x, m) if single_call else enc.forward_ops(x, m)
@@ -35,9 +34,9 @@ def test_against_reference_x86_fixture(cuda_device, name, dtype, fold):
     y = _run(wl, dtype, fold=fold)
     ref = g["x86"]
     # full tensor: padded query rows are computed like any other row, as the reference does
-    tol = MAX_ABS_TOL if dtype == torch.float16 else 4 * MAX_ABS_TOL   # bf16 carries 3 fewer mantissa bits
+    tol, cos_tol = tolerances(dtype)
     assert max_abs(y, ref) <= tol
-    assert cosine(y, ref) >= (COS_TOL if dtype == torch.float16 else 0.999)
+    assert cosine(y, ref) >= cos_tol
     assert max_abs(valid_rows(y, wl.lengths), valid_rows(ref, wl.lengths)) <= tol
 
 
@@ -49,23 +48,9 @@ def test_single_call_equals_layer_by_layer(cuda_device, fold):
     assert np.array_equal(a, b)
 
 
-def test_layernorm_in_gemm_launch_equals_separate_launches(cuda_device):
-    """b200_encoder_fwd with the LayerNorms inside the producing GEMM launches (5 launches per layer) against the
-    same stack with separate LayerNorm launches (7): the arithmetic is the same, so is every bit."""
-    for case in ("base_2layer_ragged", "large_1layer_s96"):
-        wl = golden_workload(**CASES[case])
-        a = _run(wl, torch.float16, fold=False)
-        b = _run(wl, torch.float16, fold=False, layernorm_in_gemm=True)
-        assert np.array_equal(a, b)
-    wl = model_synth.config_workload(2, batch=16, num_layers=2)
-    a = _run(wl, torch.float16, fold=False)
-    b = _run(wl, torch.float16, fold=False, layernorm_in_gemm=True)
-    assert np.array_equal(a, b)
-
-
 def test_config2_shape_subset_against_oracle(cuda_device):
-    """Config 2 geometry (12 layers, S=128, full length) on the first 4 sequences of the seeded batch."""
-    wl = model_synth.config_workload(2, batch=4)
+    """Config 2 geometry (12 layers, S=128, full length) on the first 8 sequences of the seeded batch."""
+    wl = model_synth.config_workload(2, batch=8)
     y = _run(wl, torch.float16)
     want = bert_oracle.encoder_forward(wl)
     assert max_abs(y, want) <= MAX_ABS_TOL
@@ -73,8 +58,8 @@ def test_config2_shape_subset_against_oracle(cuda_device):
 
 
 def test_config3_ragged_against_oracle(cuda_device):
-    """Config 3 geometry: S=256, lengths ~ U[16,256], 12 layers, first 4 sequences."""
-    wl = model_synth.config_workload(3, batch=4)
+    """Config 3 geometry: S=256, lengths ~ U[16,256], 12 layers, first 8 sequences."""
+    wl = model_synth.config_workload(3, batch=8)
     y = _run(wl, torch.float16)
     want = bert_oracle.encoder_forward(wl)
     assert max_abs(valid_rows(y, wl.lengths), valid_rows(want, wl.lengths)) <= MAX_ABS_TOL
@@ -91,18 +76,19 @@ def test_sequences_are_independent_at_full_batch(cuda_device):
     assert np.array_equal(y[:4], y4)
 
 
-def test_config4_geometry_bf16_and_f16_against_oracle(cuda_device):
-    """Config 4 geometry: BERT-large (H=1024, 16 heads, FFN 4096), S=384, lengths ~ U[128,384]; first 2 sequences of the
-    seeded batch and the first 4 of the 24 layers (sequences are independent; the oracle needs ~10 s per layer here)."""
-    wl = model_synth.config_workload(4, batch=2, num_layers=4)
+def test_config4_full_depth_f16_and_bf16_against_oracle(cuda_device):
+    """Config 4 at its full depth: BERT-large (H=1024, 16 heads, FFN 4096), all 24 layers, S=384, lengths ~ U[128,384];
+    the first 2 sequences of the seeded batch (sequences are independent; the oracle needs a few seconds per sequence).
+    fp16 meets the benchmark's bounds; bf16 meets the cosine bound and the stated max-abs deviation (util.py)."""
+    wl = model_synth.config_workload(4, batch=2)
+    assert len(wl.weights) == 24
     want = bert_oracle.encoder_forward(wl)
     vw = valid_rows(want, wl.lengths)
-    y = _run(wl, torch.float16, fold=False)
-    assert max_abs(valid_rows(y, wl.lengths), vw) <= MAX_ABS_TOL
-    assert cosine(valid_rows(y, wl.lengths), vw) >= COS_TOL
-    yb = _run(wl, torch.bfloat16, fold=False)
-    assert max_abs(valid_rows(yb, wl.lengths), vw) <= 4 * MAX_ABS_TOL
-    assert cosine(valid_rows(yb, wl.lengths), vw) >= 0.999
+    for dtype in (torch.float16, torch.bfloat16):
+        tol, cos_tol = tolerances(dtype)
+        y = _run(wl, dtype, fold=False)
+        assert max_abs(valid_rows(y, wl.lengths), vw) <= tol, dtype
+        assert cosine(valid_rows(y, wl.lengths), vw) >= cos_tol, dtype
 
 
 def test_config5_batch_shard_is_a_slice_of_the_full_batch(cuda_device):

@@ -251,38 +251,6 @@ def test_bad_arguments_on_gpu(cuda_device):
         ops.linear(x, w, block_n=96)
 
 
-# ------------------------------------------------------------------------------------------------ LayerNorm in the GEMM launch
-@pytest.mark.parametrize("M,N,K", [(8192, 768, 768), (8192, 768, 3072), (1000, 768, 256), (100, 1024, 512),
-                                   (700, 256, 128), (256, 64, 64)])
-@pytest.mark.parametrize("block_n", [0, 192, 256, 128])
-def test_linear_post_layernorm_equals_separate_launches(M, N, K, block_n):
-    """B200LinearDesc.post_ln_*: y and LayerNorm(y) from one launch are bit-identical to the two launches."""
-    dtype = torch.float16
-    g = torch.Generator(device="cuda").manual_seed(M + N + K)
-    x = torch.randn(M, K, device="cuda", generator=g).to(dtype)
-    r = torch.randn(M, N, device="cuda", generator=g).to(dtype)
-    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dtype)
-    b = torch.randn(N, device="cuda", generator=g) * 0.1
-    gamma = torch.randn(N, device="cuda", generator=g) * 0.2 + 1.0
-    beta = torch.randn(N, device="cuda", generator=g) * 0.1
-    bn_ref = block_n if (block_n != 0 or M <= 128) else 0
-    for residual, epi in [(r, ops.EPI_BIAS_RESIDUAL), (None, ops.EPI_BIAS)]:
-        sync = torch.zeros((M + 255) // 256, dtype=torch.int32, device="cuda")
-        out = torch.empty(M, N, device="cuda", dtype=dtype)
-        y = ops.linear(x, w, b, residual=residual, epilogue=epi, block_n=block_n, ln_eps=1e-12,
-                       post_ln=(gamma, beta, out, sync))
-        torch.cuda.synchronize()
-        assert capi.device_status() == capi.OK
-        if M > 128:
-            y_ref = ops.linear(x, w, b, residual=residual, epilogue=epi, block_n=bn_ref)
-            assert torch.equal(y, y_ref)
-        ln_ref = ops.add_layernorm(y, gamma, beta, 1e-12)
-        assert torch.equal(out, ln_ref)
-        # and against fp32 torch on the same rounded y
-        want = torch.nn.functional.layer_norm(y.float(), (N,), gamma, beta, 1e-12)
-        assert (out.float() - want).abs().max().item() < 2e-2
-
-
 @pytest.mark.parametrize("M,N,K", [(64, 768, 768), (8192, 768, 768), (300, 1024, 1024)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_linear_tanh_epilogue_against_oracle(M, N, K, dtype):

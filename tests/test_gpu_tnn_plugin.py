@@ -10,7 +10,7 @@ import pytest
 from oracle.make_golden import CASES, GOLDEN, POOLER_CASES, QA_CASES, golden_workload
 from tnn_b200 import model_synth as ms
 from tnn_b200 import tnn_runtime as rt
-from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, valid_rows
+from util import COS_TOL, MAX_ABS_TOL, cosine, max_abs, tolerances, valid_rows
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not rt.available(), reason="TNN host framework / plug-in missing")]
 
@@ -51,8 +51,9 @@ def test_bf16_precision_low(cuda_device):
     proto, model = _files(wl)
     y = _run(proto, model, wl, rt.DEVICE_CUDA, rt.PRECISION_LOW)
     ref = np.load(os.path.join(GOLDEN, "base_2layer_ragged.npz"))["x86"]
-    assert max_abs(y, ref) <= 4 * MAX_ABS_TOL
-    assert cosine(y, ref) >= 0.999
+    tol, cos_tol = tolerances("bfloat16")
+    assert max_abs(y, ref) <= tol
+    assert cosine(y, ref) >= cos_tol
 
 
 def test_plugin_path_equals_c_abi_path(cuda_device):

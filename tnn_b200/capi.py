@@ -32,9 +32,7 @@ class LinearDesc(_c.Structure):
                 ("dtype", _i32), ("out_dtype", _i32), ("epilogue", _i32), ("block_n", _i32),
                 ("out_stats", _vp), ("ln_in_stats", _vp), ("ln_c1", _vp), ("ln_c2", _vp),
                 ("res_ln_stats", _vp), ("res_ln_gamma", _vp), ("res_ln_beta", _vp),
-                ("ln_eps", _f32), ("reserved_", _i32),
-                ("post_ln_gamma", _vp), ("post_ln_beta", _vp), ("post_ln_out", _vp), ("post_ln_ld", _i64),
-                ("post_ln_sync", _vp)]
+                ("ln_eps", _f32), ("reserved_", _i32)]
 
 
 class AttentionDesc(_c.Structure):
@@ -66,14 +64,6 @@ class QAHeadDesc(_c.Structure):
                 ("N", _i32), ("x_dtype", _i32)]
 
 
-PHASE_LINEAR, PHASE_ADD_LAYERNORM = 0, 1
-CHAIN_MAX_PHASES, CHAIN_MAX_LINEAR = 8, 4
-
-
-class ChainPhase(_c.Structure):
-    _fields_ = [("kind", _i32), ("reserved_", _i32), ("linear", LinearDesc), ("layernorm", LayerNormDesc)]
-
-
 class EncoderLayerWeights(_c.Structure):
     _fields_ = [("w_qkv", _vp), ("b_qkv", _vp), ("w_o", _vp), ("b_o", _vp),
                 ("ln1_gamma", _vp), ("ln1_beta", _vp),
@@ -103,14 +93,13 @@ SYMBOLS = {
     "b200_embedding_layernorm_fwd": (_c.c_int, [_c.POINTER(EmbeddingDesc), _vp]),
     "b200_mask_from_input_mask": (_c.c_int, [_vp, _i64, _i64, _f32, _f32, _vp, _vp, _vp]),
     "b200_qa_head_fwd": (_c.c_int, [_c.POINTER(QAHeadDesc), _vp]),
-    "b200_chain_sync_bytes": (_c.c_size_t, [_i64, _i32]),
-    "b200_chain_fwd": (_c.c_int, [_c.POINTER(ChainPhase), _i32, _vp, _vp]),
     "b200_encoder_workspace_bytes": (_c.c_size_t, [_i64, _i64, _i64, _c.c_int]),
     "b200_encoder_fwd": (_c.c_int, [_c.POINTER(EncoderDesc), _vp]),
     "b200_status_string": (_c.c_char_p, [_c.c_int]),
     "b200_device_status": (_c.c_int, []),
     "b200_launch_count": (_c.c_uint64, []),
     "b200_version": (_c.c_char_p, []),
+    "b200_selftest_tensor_map_cache": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int]),
 }
 
 _lib = None

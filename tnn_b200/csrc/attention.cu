@@ -27,19 +27,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Cycle stamps (one SM's counter) of the first CTA's hand-offs for performance work: compiled in only with -DB200_TRACE.
-#ifdef B200_TRACE
-__device__ unsigned long long g_attn_trace[3][32][8];   // [role: wg0, wg1, mma][tile][event]
-#define ATTN_MARK(role, tile, ev)                                                                 \
-    do {                                                                                          \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) {               \
-            g_attn_trace[role][tile][ev] = static_cast<unsigned long long>(clock64());            \
-        }                                                                                         \
-    } while (0)
-#else
-#define ATTN_MARK(role, tile, ev)
-#endif
-
 constexpr int TQ = 128;   // queries per CTA
 constexpr int TK = 128;   // keys per tile
 constexpr int HD = 64;    // head dim
@@ -148,14 +135,6 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         if (tid == 0 && p.status) atomicOr(p.status, 4u);
         return;
     }
-    int kv_eff = p.S;
-    bool additive_only = (p.mask_add == nullptr);
-    if (p.kv_len != nullptr) {
-        const int kl = p.kv_len[b];
-        if (kl <= 0) additive_only = true;
-        else kv_eff = kl < p.S ? kl : p.S;
-    }
-    const int n_tiles = (kv_eff + TK - 1) / TK;
     const bool two = NWG == 2 && (p.S - q0) > TQ;   // the second query tile exists
 
     if (tid == 0) {
@@ -189,6 +168,16 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
     pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
+
+    // kv_len is written by a kernel earlier in the stream: it is read only here, behind the dependency wait.
+    int kv_eff = p.S;
+    bool additive_only = (p.mask_add == nullptr);
+    if (p.kv_len != nullptr) {
+        const int kl = p.kv_len[b];
+        if (kl <= 0) additive_only = true;
+        else kv_eff = kl < p.S ? kl : p.S;
+    }
+    const int n_tiles = (kv_eff + TK - 1) / TK;
 
     if (warp < 4) {
         setmaxnreg_dec<C::REGS_CONTROL>();   // the control warpgroup: producer, two UMMA issuers, an idle warp
@@ -268,17 +257,14 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 if (!mbar_wait(&s_free[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
                 if (!mbar_wait(&k_full[st_next], (static_cast<uint32_t>(j + 1) / PP_NST) & 1u, abort_flag)) return false;
                 tcgen05_fence_after();
-                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 2);   // scores taken, K of the next tile present
                 issue_s(wg_c, st_next);
                 if (last && lane == 0) umma_commit(&k_empty[st_next]);
-                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 3);   // next scores issued
                 return true;
             };
             auto step_pv = [&](auto wg_c, const int j, const bool last) -> bool {
                 constexpr int wg = decltype(wg_c)::value;
                 const int st = j % PP_NST;
                 if (!mbar_wait(&p_full[wg], static_cast<uint32_t>(j) & 1u, abort_flag)) return false;
-                if (lane == 0) ATTN_MARK(2, j, wg * 4 + 0);   // P of this warpgroup seen
                 if (!mbar_wait(&v_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) return false;
                 tcgen05_fence_after();
                 if (lane == 0) {
@@ -294,7 +280,6 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                                     k != 0 ? 1u : acc0);
                     umma_commit(&o_full[wg]);
                     if (last) umma_commit(&v_empty[st]);
-                    ATTN_MARK(2, j, wg * 4 + 1);   // PV issued
                 }
                 __syncwarp();
                 return true;
@@ -333,9 +318,7 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 const int st = j % PP_NST;
                 const uint32_t ph = static_cast<uint32_t>(j) & 1u;
                 if (!mbar_wait(&m_full[st], (static_cast<uint32_t>(j) / PP_NST) & 1u, abort_flag)) { ok = false; break; }
-                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 0);   // tile start
                 if (!mbar_wait(&s_full[wg], ph, abort_flag)) { ok = false; break; }
-                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 1);   // scores present
                 __syncwarp();
                 tcgen05_fence_after();
                 // The row's 128 scores move to registers in one go and the score columns are handed back at once:
@@ -385,11 +368,9 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 const float m_new = move ? tmax : m_run;
                 const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
                 const float alpha = move ? fast_exp2(m_run - m_use) : 1.f;
-                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 2);   // max known
                 // PV of the previous tile must be complete: it reads the P buffer written below, and it writes the
                 // accumulator a rescale would touch.
                 if (j > 0 && !mbar_wait(&o_full[wg], static_cast<uint32_t>(j - 1) & 1u, abort_flag)) { ok = false; break; }
-                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 3);   // previous PV complete
                 __syncwarp();
                 if (j > 0 && __any_sync(0xffffffffu, move)) {
                     tcgen05_fence_after();
@@ -439,7 +420,6 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
                 tmem_st_wait();               // P (and a rescaled O) have reached tensor memory
                 tcgen05_fence_before();
                 mbar_arrive(&p_full[wg]);
-                if ((warp & 3) == 2 && lane == 0) ATTN_MARK(wg, j, 4);   // P written
             }
             // the last PV
             if (ok && n_tiles > 0 && !mbar_wait(&o_full[wg], static_cast<uint32_t>(n_tiles - 1) & 1u, abort_flag)) ok = false;
@@ -747,14 +727,26 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
 }
 
+// Dynamic shared-memory limits of the four kernel instances, once per device (first launch on it).
+bool set_attention_attributes(int dev) {
+    static PerDeviceOnce once;
+    return once.ensure(dev, []() {
+        const bool ok =
+            cudaFuncSetAttribute(attention_single_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 S1_SMEM) == cudaSuccess &&
+            cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 S1_SMEM) == cudaSuccess &&
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) == cudaSuccess &&
+            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PPCfg<PP_NWG>::SMEM) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        return ok;
+    });
+}
+
 }  // namespace
 }  // namespace b200
-
-#ifdef B200_TRACE
-extern "C" __attribute__((visibility("default"))) int b200_debug_attn_trace(unsigned long long* host) {
-    return cudaMemcpyFromSymbol(host, b200::g_attn_trace, sizeof(b200::g_attn_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stream_) {
     using namespace b200;
@@ -777,10 +769,10 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
     const uint64_t sq[2] = {static_cast<uint64_t>(d->ldq) * 2, static_cast<uint64_t>(d->ldq) * 2 * d->S};
     const uint64_t sk[2] = {static_cast<uint64_t>(d->ldk) * 2, static_cast<uint64_t>(d->ldk) * 2 * d->S};
     const uint64_t sv[2] = {static_cast<uint64_t>(d->ldv) * 2, static_cast<uint64_t>(d->ldv) * 2 * d->S};
-    const CUtensorMap* tq = get_tensor_map(d->q, 3, dims, sq, box);
-    const CUtensorMap* tk = get_tensor_map(d->k, 3, dims, sk, box);
-    const CUtensorMap* tv = get_tensor_map(d->v, 3, dims, sv, box);
-    if (!tq || !tk || !tv) return B200_ERR_DRIVER;
+    CUtensorMap tq, tk, tv;
+    if (!get_tensor_map(&tq, d->q, 3, dims, sq, box) || !get_tensor_map(&tk, d->k, 3, dims, sk, box) ||
+        !get_tensor_map(&tv, d->v, 3, dims, sv, box))
+        return B200_ERR_DRIVER;
 
     AttnParams p;
     p.mask_add = d->mask_add;
@@ -799,17 +791,9 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
 
     if (d->S <= 128) {
         const uint64_t so[2] = {static_cast<uint64_t>(d->ldo) * 2, static_cast<uint64_t>(d->ldo) * 2 * d->S};
-        const CUtensorMap* to = get_tensor_map(d->out, 3, dims, so, box);
-        if (!to) return B200_ERR_DRIVER;
-        static bool attr1_set[64] = {false};
-        if (dev >= 0 && dev < 64 && !attr1_set[dev]) {
-            if (cudaFuncSetAttribute(attention_single_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     S1_SMEM) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     S1_SMEM) != cudaSuccess)
-                return B200_ERR_LAUNCH;
-            attr1_set[dev] = true;
-        }
+        CUtensorMap to;
+        if (!get_tensor_map(&to, d->out, 3, dims, so, box)) return B200_ERR_DRIVER;
+        if (!set_attention_attributes(dev)) return B200_ERR_LAUNCH;
         const long long items = static_cast<long long>(d->heads) * d->B;
         if (items > 0x7fffffff) return B200_ERR_UNSUPPORTED;
         int sms = 0;
@@ -818,31 +802,23 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         const cudaStream_t st = static_cast<cudaStream_t>(stream_);
         if (d->dtype == B200_F16)
             launch_kernel(attention_single_kernel<B200_F16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
-                          S1_SMEM, st, *tq, *tk, *tv, *to, p, static_cast<int>(items));
+                          S1_SMEM, st, tq, tk, tv, to, p, static_cast<int>(items));
         else
             launch_kernel(attention_single_kernel<B200_BF16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
-                          S1_SMEM, st, *tq, *tk, *tv, *to, p, static_cast<int>(items));
+                          S1_SMEM, st, tq, tk, tv, to, p, static_cast<int>(items));
         count_launch();
         return check_launch();
     }
 
-    static bool attr_set[64] = {false};
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess)
-            return B200_ERR_LAUNCH;
-        attr_set[dev] = true;
-    }
+    if (!set_attention_attributes(dev)) return B200_ERR_LAUNCH;
     dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
               static_cast<unsigned>(d->B));
     if (d->dtype == B200_F16)
         launch_kernel(attention_pingpong_kernel<B200_F16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
-                      static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
+                      static_cast<cudaStream_t>(stream_), tq, tk, tv, p);
     else
         launch_kernel(attention_pingpong_kernel<B200_BF16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
-                      static_cast<cudaStream_t>(stream_), *tq, *tk, *tv, p);
+                      static_cast<cudaStream_t>(stream_), tq, tk, tv, p);
     count_launch();
     return check_launch();
 }
@@ -855,8 +831,8 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
 static __device__ __align__(256) int g_static_kv_len[B200_STATIC_MAX_BATCH];
 
 namespace {
-int* g_static_kv_len_ptr[64] = {nullptr};   // per device, filled by the first call on that device
-bool g_static_attr_set[64] = {false};
+int* g_static_kv_len_ptr[b200::kMaxDevices] = {nullptr};   // per device, filled by the first call on that device
+b200::PerDeviceOnce g_static_once;                          // guards that first call against a second host thread
 }
 
 extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200_stream_t stream_) {
@@ -877,29 +853,19 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
     if (major != 10) return B200_ERR_NOT_SM100;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
-    // One-time set-up on this device (current device = the one the launches below go to).
-    if (g_static_kv_len_ptr[dev] == nullptr) {
-        int* ptr = nullptr;
-        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_kv_len) != cudaSuccess || ptr == nullptr) {
-            cudaGetLastError();
-            return B200_ERR_LAUNCH;
-        }
-        g_static_kv_len_ptr[dev] = ptr;
-    }
-    if (!g_static_attr_set[dev]) {
-        if (cudaFuncSetAttribute(attention_single_kernel<B200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 S1_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 S1_SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) != cudaSuccess) {
-            cudaGetLastError();
-            return B200_ERR_LAUNCH;
-        }
-        g_static_attr_set[dev] = true;
-    }
+    // One-time set-up on this device (current device = the one the launches below go to): the scratch array's device
+    // address and the kernels' shared-memory attribute.  Two host threads making their first call at once are
+    // serialised here; this takes a host mutex, no memory is allocated.
+    if (!g_static_once.ensure(dev, [dev]() {
+            int* ptr = nullptr;
+            if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_kv_len) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return false;
+            }
+            g_static_kv_len_ptr[dev] = ptr;
+            return set_attention_attributes(dev);
+        }))
+        return B200_ERR_LAUNCH;
     int* kv_len = g_static_kv_len_ptr[dev];
 
     // kv_len of this call's mask into the static scratch (every entry that is read below is written here first)

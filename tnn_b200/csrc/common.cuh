@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
 #include <utility>
 
 #include "../../include/tnn_b200.h"
@@ -62,14 +64,38 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // 2-D or 3-D tiled map over a 2-byte-element tensor whose innermost dimension is contiguous, 128- or 64-byte
 // swizzle, inner box = 64 or 32 elements.  dims/strides are innermost first; strides[i] is the byte stride of dim i+1.
 // Maps are cached per device by their full key; encoding takes about a microsecond and the same activations and
-// weights come back every Forward.  Returns nullptr if the driver entry point is missing or refuses the descriptor.
+// weights come back every Forward.  The 128-byte map is copied into `*out` under the cache's lock, so that no caller
+// ever holds a pointer into the cache (another thread may evict entries at any time).  Returns false if the driver
+// entry point is missing or refuses the descriptor.
 // swizzle_bytes: 128 (box inner extent 64 elements) or 64 (inner extent 32 elements).
-const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box, int swizzle_bytes = 128);
+bool get_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, int swizzle_bytes = 128);
 
 // The same encoding into caller-provided storage: no cache entry, no allocation of any kind.
 bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                        const uint32_t* box, int swizzle_bytes = 128);
+
+// One-time set-up per device (kernel attributes, symbol addresses, occupancy queries) that several host threads — one
+// per GPU, or several instances on one GPU — may reach at the same moment: double-checked under a mutex.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+    std::atomic<bool> done[kMaxDevices];
+    std::mutex mu;
+    PerDeviceOnce() {
+        for (auto& d : done) d.store(false, std::memory_order_relaxed);
+    }
+    // Runs `fn` (returning bool: success) once for `dev`; false if it failed (it is retried on the next call).
+    template <typename F>
+    bool ensure(int dev, F&& fn) {
+        if (dev < 0 || dev >= kMaxDevices) return false;
+        if (done[dev].load(std::memory_order_acquire)) return true;
+        std::lock_guard<std::mutex> lock(mu);
+        if (done[dev].load(std::memory_order_relaxed)) return true;
+        if (!fn()) return false;
+        done[dev].store(true, std::memory_order_release);
+        return true;
+    }
+};
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH; }
 

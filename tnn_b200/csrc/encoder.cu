@@ -8,14 +8,9 @@ namespace {
 
 inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
-// Layers whose in-launch LayerNorms get their own row-block counters; a deeper stack clears and reuses them.
-constexpr int kSyncLayers = 64;
-
 struct Workspace {
     char *qkv, *ctx, *tmp, *h1, *ffn;
     float *stats1, *stats2;   // row statistics of the two pre-LayerNorm activations (fold_layernorm == 1)
-    int* sync;                // [kSyncLayers][2][ceil(tokens / 256)] counters of the in-launch LayerNorms
-    size_t sync_bytes;
     size_t total;
 };
 
@@ -31,8 +26,6 @@ Workspace carve(char* base, int64_t tokens, int64_t H, int64_t F, int dtype) {
     const size_t stats_bytes = align256(static_cast<size_t>((H + 31) / 32) * tokens * 2 * sizeof(float));
     w.stats1 = reinterpret_cast<float*>(base + off); off += stats_bytes;
     w.stats2 = reinterpret_cast<float*>(base + off); off += stats_bytes;
-    w.sync_bytes = align256(static_cast<size_t>(kSyncLayers) * 2 * static_cast<size_t>((tokens + 255) / 256) * sizeof(int));
-    w.sync = reinterpret_cast<int*>(base + off); off += w.sync_bytes;
     w.total = off;
     return w;
 }
@@ -142,18 +135,10 @@ int b200_encoder_fwd(const B200EncoderDesc* d, b200_stream_t stream) {
         return B200_OK;
     }
 
-    // fold_layernorm == 0: the two LayerNorms as separate launches (seven launches per layer); == 2: inside the launch
-    // of the GEMM that produces their input (five).
-    const bool ln_in_launch = d->fold_layernorm == 2 && H <= 1024 && (H % 8) == 0;
-    const int64_t m_blocks = (tokens + 255) / 256;
+    // fold_layernorm == 0: the two LayerNorms as separate launches (seven launches per layer).
     for (int l = 0; l < d->num_layers; ++l) {
         const B200EncoderLayerWeights& lw = d->layers[l];
         int rc;
-        if (ln_in_launch && (l % kSyncLayers) == 0 &&
-            cudaMemsetAsync(w.sync, 0, w.sync_bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess)
-            return B200_ERR_LAUNCH;
-        int* sync1 = w.sync + static_cast<int64_t>(l % kSyncLayers) * 2 * m_blocks;
-        int* sync2 = sync1 + m_blocks;
 
         B200LinearDesc lin = {};
         lin.dtype = d->dtype;
@@ -184,18 +169,13 @@ int b200_encoder_fwd(const B200EncoderDesc* d, b200_stream_t stream) {
         lin.w_nk = lw.w_o; lin.ldw = H; lin.bias = lw.b_o;
         lin.y = w.tmp; lin.N = H; lin.ldy = H;
         lin.epilogue = B200_EPI_BIAS_RESIDUAL; lin.residual = d->hidden; lin.ldr = H;
-        if (ln_in_launch) {   // 4. LayerNorm 1 in the same launch
-            lin.post_ln_gamma = lw.ln1_gamma; lin.post_ln_beta = lw.ln1_beta;
-            lin.post_ln_out = w.h1; lin.post_ln_ld = H; lin.post_ln_sync = sync1;
-        }
         if ((rc = b200_linear_fwd(&lin, stream)) != B200_OK) return rc;
-        lin.post_ln_out = nullptr; lin.post_ln_gamma = lin.post_ln_beta = nullptr; lin.post_ln_sync = nullptr;
 
         B200LayerNormDesc ln = {};
         ln.x = w.tmp; ln.residual = nullptr; ln.gamma = lw.ln1_gamma; ln.beta = lw.ln1_beta; ln.y = w.h1;
         ln.rows = tokens; ln.H = H; ln.ldx = H; ln.ldr = 0; ln.ldy = H;
         ln.in_dtype = d->dtype; ln.out_dtype = d->dtype; ln.eps = d->ln_eps;
-        if (!ln_in_launch && (rc = b200_add_layernorm_fwd(&ln, stream)) != B200_OK) return rc;   // 4. LayerNorm 1
+        if ((rc = b200_add_layernorm_fwd(&ln, stream)) != B200_OK) return rc;   // 4. LayerNorm 1
 
         // 5. FFN up-projection + GELU
         lin.x = w.h1; lin.ldx = H; lin.K = H;
@@ -209,16 +189,11 @@ int b200_encoder_fwd(const B200EncoderDesc* d, b200_stream_t stream) {
         lin.w_nk = lw.w_ffn2; lin.ldw = F; lin.bias = lw.b_ffn2;
         lin.y = w.tmp; lin.N = H; lin.ldy = H;
         lin.epilogue = B200_EPI_BIAS_RESIDUAL; lin.residual = w.h1; lin.ldr = H;
-        if (ln_in_launch) {   // 7. LayerNorm 2 -> layer output, in the same launch
-            lin.post_ln_gamma = lw.ln2_gamma; lin.post_ln_beta = lw.ln2_beta;
-            lin.post_ln_out = d->hidden; lin.post_ln_ld = H; lin.post_ln_sync = sync2;
-        }
         if ((rc = b200_linear_fwd(&lin, stream)) != B200_OK) return rc;
-        lin.post_ln_out = nullptr; lin.post_ln_gamma = lin.post_ln_beta = nullptr; lin.post_ln_sync = nullptr;
 
         // 7. LayerNorm 2 -> layer output
         ln.x = w.tmp; ln.gamma = lw.ln2_gamma; ln.beta = lw.ln2_beta; ln.y = d->hidden;
-        if (!ln_in_launch && (rc = b200_add_layernorm_fwd(&ln, stream)) != B200_OK) return rc;
+        if ((rc = b200_add_layernorm_fwd(&ln, stream)) != B200_OK) return rc;
     }
     return B200_OK;
 }

@@ -170,17 +170,19 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 }
 
 int device_sm_count() {
-    static int sms[64] = {0};
+    static std::atomic<int> sms[kMaxDevices];   // 0 = not looked up yet; every thread would store the same value
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return 148;
-    if (sms[dev] == 0) {
+    if (dev < 0 || dev >= kMaxDevices) return 148;
+    int v = sms[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
         int n = 0, major = 0;
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-        sms[dev] = (major == 10) ? n : -1;
+        v = (major == 10) ? n : -1;
+        sms[dev].store(v, std::memory_order_relaxed);
     }
-    return sms[dev];
+    return v;
 }
 
 template <int BN, int STAGES, bool FOLD>
@@ -192,16 +194,14 @@ int launch_linear_t(const B200LinearDesc& d, cudaStream_t stream, int sm_count) 
     const uint64_t wd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.N)};
     const uint64_t ws[1] = {static_cast<uint64_t>(d.ldw) * 2};
     const uint32_t wb[2] = {BK, BN};
-    const CUtensorMap* tx = get_tensor_map(d.x, 2, xd, xs, xb);
-    const CUtensorMap* tw = get_tensor_map(d.w_nk, 2, wd, ws, wb);
-    if (!tx || !tw) return B200_ERR_DRIVER;
-    const CUtensorMap* ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
+    CUtensorMap tx, tw, ty;
+    if (!get_tensor_map(&tx, d.x, 2, xd, xs, xb) || !get_tensor_map(&tw, d.w_nk, 2, wd, ws, wb)) return B200_ERR_DRIVER;
+    ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
     if (d.out_dtype != B200_F32) {
         const uint64_t yd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
         const uint64_t ys[1] = {static_cast<uint64_t>(d.ldy) * 2};
         const uint32_t yb[2] = {32, 32};
-        ty = get_tensor_map(d.y, 2, yd, ys, yb, 64);
-        if (!ty) return B200_ERR_DRIVER;
+        if (!get_tensor_map(&ty, d.y, 2, yd, ys, yb, 64)) return B200_ERR_DRIVER;
     }
 
     LinearParams p;
@@ -232,17 +232,16 @@ int launch_linear_t(const B200LinearDesc& d, cudaStream_t stream, int sm_count) 
     p.k_slots = (p.K + 31) / 32;
     p.n_slots = (p.N + 31) / 32;
 
-    static bool attr_set[64] = {false};
+    static PerDeviceOnce attr_once;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(linear_kernel<BN, STAGES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 C::SMEM_BYTES) != cudaSuccess)
-            return B200_ERR_LAUNCH;
-        attr_set[dev] = true;
-    }
+    if (!attr_once.ensure(dev, []() {
+            return cudaFuncSetAttribute(linear_kernel<BN, STAGES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C::SMEM_BYTES) == cudaSuccess;
+        }))
+        return B200_ERR_LAUNCH;
     const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-    launch_kernel(linear_kernel<BN, STAGES, FOLD>, dim3(grid), dim3(kThreads), C::SMEM_BYTES, stream, *tx, *tw, *ty, p);
+    launch_kernel(linear_kernel<BN, STAGES, FOLD>, dim3(grid), dim3(kThreads), C::SMEM_BYTES, stream, tx, tw, ty, p);
     count_launch();
     return check_launch();
 }
@@ -260,10 +259,10 @@ struct TileChoice {
     bool pair;
     int bn;
 };
-TileChoice choose_tile(int64_t M, int64_t N, int sm_count, bool pair_only = false) {
+TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
     TileChoice best = {false, 128};
     double best_t = 1e300;
-    if (M > 128 || pair_only) {
+    if (M > 128) {
         const int bns[4] = {256, 192, 128, 64};
         const double cost[4] = {1.0, 1.03, 1.10, 1.40};
         for (int i = 0; i < 4; ++i) {
@@ -280,7 +279,7 @@ TileChoice choose_tile(int64_t M, int64_t N, int sm_count, bool pair_only = fals
     }
     const int bns1[3] = {256, 128, 64};
     const double cost1[3] = {1.35, 1.50, 1.90};
-    for (int i = 0; i < 3 && !pair_only; ++i) {
+    for (int i = 0; i < 3; ++i) {
         const int64_t tiles = ((M + BM - 1) / BM) * ((N + bns1[i] - 1) / bns1[i]);
         const int64_t waves = (tiles + sm_count - 1) / sm_count;
         const double t = static_cast<double>(waves) * (bns1[i] * cost1[i] + 16.0);
@@ -309,14 +308,6 @@ int validate_linear_desc(const B200LinearDesc* d) {
     if (d->ln_in_stats && (!d->ln_c1 || !d->ln_c2)) return B200_ERR_PARAM;
     if (d->res_ln_stats && (!d->res_ln_gamma || !d->res_ln_beta || d->epilogue != B200_EPI_BIAS_RESIDUAL))
         return B200_ERR_PARAM;
-    if (d->post_ln_out) {
-        if (!d->post_ln_gamma || !d->post_ln_beta || !d->post_ln_sync) return B200_ERR_PARAM;
-        if (d->out_dtype != d->dtype || d->N > 1024) return B200_ERR_UNSUPPORTED;
-        if ((d->post_ln_ld % 8) || d->post_ln_ld < d->N || !aligned16(d->post_ln_out)) return B200_ERR_PARAM;
-        if (!aligned16(d->post_ln_gamma) || !aligned16(d->post_ln_beta)) return B200_ERR_PARAM;
-        if (reinterpret_cast<uintptr_t>(d->post_ln_sync) & 3u) return B200_ERR_PARAM;
-        if (d->out_stats || d->ln_in_stats || d->res_ln_stats) return B200_ERR_UNSUPPORTED;
-    }
     return B200_OK;
 }
 
@@ -332,14 +323,11 @@ extern "C" int b200_linear_fwd(const B200LinearDesc* d, b200_stream_t stream_) {
     if (sms <= 0) return B200_ERR_NOT_SM100;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     TileChoice tc;
-    const bool post_ln = wants_post_ln(*d);
     if (d->block_n == 0) {
-        tc = choose_tile(d->M, d->N, sms, post_ln);
-        if (post_ln && !tc.pair) return B200_ERR_UNSUPPORTED;
+        tc = choose_tile(d->M, d->N, sms);
     } else if (d->block_n > 0) {
-        tc = {d->M > 128 || post_ln, d->block_n};
+        tc = {d->M > 128, d->block_n};
     } else {
-        if (post_ln) return B200_ERR_UNSUPPORTED;
         tc = {false, -d->block_n};
     }
     if (tc.pair) {

@@ -32,13 +32,6 @@ struct LinearParams {
     const float* res_ln_beta;
     float ln_eps;
     int k_slots, n_slots;   // ceil(K/32), ceil(N/32)
-    // LayerNorm of the output rows in the same launch (pair kernel, LN template flag): null ln_out = off
-    void* ln_out;
-    const float* ln_gamma;
-    const float* ln_beta;
-    long long ld_ln;
-    int* ln_sync;           // one counter per 256-row block
-    int ln_rows_per_tile;   // rows of a block normalised by the pair that owns tile n of it (multiple of 16)
 };
 
 
@@ -354,117 +347,6 @@ struct WarpEpilogue {
     }
 };
 
-// LayerNorm of `nrows` consecutive rows (from row0, rows >= M skipped) of a half-precision matrix by one warp, two rows
-// at a time so that their loads are in flight together.  The arithmetic and its order are those of
-// add_layernorm_rows_kernel (layernorm.cu): fp32 sum -> mean, fp32 sum of squared deviations -> 1/sqrt(var + eps).
-// x may have been written by other SMs during this launch, so it is read through L2 (ld.global.cg), never through the
-// non-coherent path.  NV = 16-byte groups per lane: H <= NV * 256, H % 8 == 0.
-template <int NV>
-__device__ __forceinline__ void layernorm_rows_warp(const void* x, long long ldx, void* y, long long ldy,
-                                                    const float* gamma, const float* beta, int H, float eps, int dtype,
-                                                    long long row0, int nrows, int M, int lane) {
-    const int groups = H >> 3;
-    const float inv_h = 1.0f / static_cast<float>(H);
-    const uint16_t* xin = reinterpret_cast<const uint16_t*>(x);
-    uint16_t* yout = reinterpret_cast<uint16_t*>(y);
-#pragma unroll 1
-    for (int b2 = 0; b2 < nrows; b2 += 2) {
-        uint4 raw[2][NV];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const long long row = row0 + b2 + r;
-#pragma unroll
-            for (int g = 0; g < NV; ++g) {
-                const int gi = g * 32 + lane;
-                if (b2 + r < nrows && row < M && gi < groups)
-                    raw[r][g] = __ldcg(reinterpret_cast<const uint4*>(xin + row * ldx + gi * 8));
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const long long row = row0 + b2 + r;
-            if (b2 + r >= nrows || row >= M) continue;   // uniform across the warp
-            float v[NV][8];
-            float sum = 0.f;
-#pragma unroll
-            for (int g = 0; g < NV; ++g) {
-                const int gi = g * 32 + lane;
-                if (gi < groups) {
-                    const uint32_t w[4] = {raw[r][g].x, raw[r][g].y, raw[r][g].z, raw[r][g].w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = unpack2(w[e], dtype);
-                        v[g][2 * e] = f.x;
-                        v[g][2 * e + 1] = f.y;
-                    }
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) sum += v[g][e];
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            const float mean = sum * inv_h;
-            float sq = 0.f;
-#pragma unroll
-            for (int g = 0; g < NV; ++g) {
-                const int gi = g * 32 + lane;
-                if (gi < groups) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float c = v[g][e] - mean;
-                        sq += c * c;
-                    }
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            const float rstd = 1.0f / sqrtf(sq * inv_h + eps);
-#pragma unroll
-            for (int g = 0; g < NV; ++g) {
-                const int gi = g * 32 + lane;
-                if (gi < groups) {
-                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + gi * 8));
-                    const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + gi * 8 + 4));
-                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + gi * 8));
-                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + gi * 8 + 4));
-                    const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                    const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                    float o[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[e] + bt[e];
-                    uint4 q;
-                    q.x = pack2(o[0], o[1], dtype);
-                    q.y = pack2(o[2], o[3], dtype);
-                    q.z = pack2(o[4], o[5], dtype);
-                    q.w = pack2(o[6], o[7], dtype);
-                    *reinterpret_cast<uint4*>(yout + row * ldy + gi * 8) = q;
-                }
-            }
-        }
-    }
-}
-
-// Row-block completion counters in global memory (release / acquire at gpu scope), used where CTAs of one launch
-// exchange rows: one warp adds 1 when its part of a row block is in memory; readers poll, bounded.
-__device__ __forceinline__ int load_acquire(const int* p) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void add_release(int* p) {
-    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p) : "memory");
-}
-constexpr uint32_t kDepPollLimit = 1u << 21;
-__device__ __forceinline__ bool wait_rows(const int* ctr, int target, volatile uint32_t* abort_flag) {
-    for (uint32_t i = 0; i < kDepPollLimit; ++i) {
-        if (load_acquire(ctr) >= target) return true;
-        if (i > 16) nanosleep(200);
-        if ((i & 63u) == 63u && *abort_flag) return false;
-    }
-    *abort_flag = 1u;
-    return false;
-}
-
 // CTA-pair kernel (linear_pair.cu).  BN in {64, 128, 192, 256}.
 template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count);
@@ -472,7 +354,6 @@ int device_sm_count();   // SMs of the current device, <= 0 if it is not an sm_1
 // Argument checks of b200_linear_fwd (pointers, alignment, leading dimensions, epilogue consistency).
 int validate_linear_desc(const B200LinearDesc* d);
 inline bool wants_fold(const B200LinearDesc& d) { return d.out_stats || d.ln_in_stats || d.res_ln_stats; }
-inline bool wants_post_ln(const B200LinearDesc& d) { return d.post_ln_out != nullptr; }
 // Number of CTA pairs of the pair kernel that can be co-resident on the current device (cached; 0 if unknown).
 int max_active_pairs(int bn);
 

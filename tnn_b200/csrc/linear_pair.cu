@@ -18,22 +18,7 @@ namespace lin {
 
 namespace {
 
-// Phase timestamps per CTA for performance work: compiled in only with -DB200_TRACE (never in the shipped library).
-#ifdef B200_TRACE
-__device__ unsigned long long g_trace[512][16];
-#define TRACE_MARK(i)                                                      \
-    do {                                                                   \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 512) {                 \
-            unsigned long long t_;                                         \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));         \
-            g_trace[blockIdx.x][i] = t_;                                   \
-        }                                                                  \
-    } while (0)
-#else
-#define TRACE_MARK(i)
-#endif
-
-template <int BN, bool RES, bool FOLD, bool LN>
+template <int BN, bool RES, bool FOLD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epi_warps<BN>(), 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_r,
@@ -59,7 +44,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const bool leader = rank == 0;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
-    if (warp == 0) TRACE_MARK(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -85,7 +69,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     cluster_sync_all();   // the peer's barriers are initialised and its TMEM allocated before anything is signalled
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (warp == 0) TRACE_MARK(1);
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         // The weights are constants: while the previous kernel of the stream drains, the grid brings them from HBM
@@ -97,7 +80,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tma_prefetch_l2_2d(&tm_w, (b % p.num_k_blocks) * BK, (b / p.num_k_blocks) * (BN / 2));
     }
     pdl_wait();   // x, the residual and the statistics come from earlier kernels; y may still be read by one
-    if (warp == 0) TRACE_MARK(2);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -139,7 +121,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     const uint32_t s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
-                    if (it == 0) TRACE_MARK(3);
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
                     const uint64_t a_desc = make_smem_desc_sw128(a_addr);
@@ -150,7 +131,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     umma_commit_pair(&empty[s]);
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
-                TRACE_MARK(4);   // last value: all UMMAs of the CTA pair issued
             }
         }
         __syncwarp();
@@ -185,10 +165,6 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             stage_vectors<FOLD>(p, vec_w, n_blk * BN + half * COLS, COLS, lane);
             if (!mbar_wait(&acc_full[buf], aph, abort_flag)) { ok = false; break; }
             __syncwarp();
-            if (ew == 0) {
-                if (tcount == 0) TRACE_MARK(5);   // first accumulator complete
-                TRACE_MARK(6);                    // last value: last accumulator complete
-            }
             tcgen05_fence_after();
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             if (!epi.template run<COLS>(vec_w, tacc, row, n_blk * BN, half * COLS)) { ok = false; break; }
@@ -198,33 +174,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 if (leader) mbar_arrive(&acc_empty[buf]);
                 else mbar_arrive_leader(&acc_empty[buf]);
             }
-            if (LN) {
-                // This warp's part of the tile is in memory -> count it; when all 16 warps of all tiles of the row
-                // block have counted, normalise this warp's rows of the block.  The tiles of one row block belong to
-                // different pairs (the launcher keeps #pairs >= tiles per block) and every pair counts before it
-                // waits, so the wait cannot be circular.
-                int ready = 0;
-                if (lane == 0) {
-                    tma_store_wait_all<0>();
-                    add_release(p.ln_sync + m_blk);
-                    ready = wait_rows(p.ln_sync + m_blk, p.num_n_tiles * 2 * EW, abort_flag) ? 1 : 0;
-                }
-                ready = __shfl_sync(0xffffffffu, ready, 0);
-                if (!ready) { ok = false; break; }
-                const int per_warp = p.ln_rows_per_tile / (2 * EW);
-                const int part0 = n_blk * p.ln_rows_per_tile;                       // first row of this tile's share
-                const int mine = part0 + (static_cast<int>(rank) * EW + ew) * per_warp;
-                int nrows = min(per_warp, 256 - mine);
-                if (nrows > 0)
-                    layernorm_rows_warp<4>(p.y, p.ldy, p.ln_out, p.ld_ln, p.ln_gamma, p.ln_beta, p.N, p.ln_eps, p.dtype,
-                                           static_cast<long long>(m_blk) * 256 + mine, nrows, p.M, lane);
-            }
         }
-        if (ew == 0) TRACE_MARK(7);               // last tile drained (stores issued)
         // this warp's tile stores have read their strips; the writes themselves are complete when the grid is
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
-        if (ew == 0) TRACE_MARK(8);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -236,18 +189,11 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 1u);
-    if (warp == 0) TRACE_MARK(9);
 }
 
 }  // namespace
 
-#ifdef B200_TRACE
-extern "C" __attribute__((visibility("default"))) int b200_debug_trace(unsigned long long* host) {
-    return cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif
-
-template <int BN, bool RES, bool FOLD, bool LN = false>
+template <int BN, bool RES, bool FOLD>
 int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     constexpr int EW = pair_epi_warps<BN>();
     using C = PairCfg<BN, RES, FOLD, EW>;
@@ -259,24 +205,21 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     const uint64_t wd[2] = {static_cast<uint64_t>(d.K), static_cast<uint64_t>(d.N)};
     const uint64_t ws[1] = {static_cast<uint64_t>(d.ldw) * 2};
     const uint32_t wb[2] = {BK, BN / 2};
-    const CUtensorMap* tx = get_tensor_map(d.x, 2, xd, xs, xb);
-    const CUtensorMap* tw = get_tensor_map(d.w_nk, 2, wd, ws, wb);
-    if (!tx || !tw) return B200_ERR_DRIVER;
-    const CUtensorMap* ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
+    CUtensorMap tx, tw, ty, tr;
+    if (!get_tensor_map(&tx, d.x, 2, xd, xs, xb) || !get_tensor_map(&tw, d.w_nk, 2, wd, ws, wb)) return B200_ERR_DRIVER;
+    ty = tx;   // placeholder when the output is fp32 (stored directly, map unused)
     if (d.out_dtype != B200_F32) {
         const uint64_t yd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
         const uint64_t ys[1] = {static_cast<uint64_t>(d.ldy) * 2};
         const uint32_t yb[2] = {32, 32};
-        ty = get_tensor_map(d.y, 2, yd, ys, yb, 64);
-        if (!ty) return B200_ERR_DRIVER;
+        if (!get_tensor_map(&ty, d.y, 2, yd, ys, yb, 64)) return B200_ERR_DRIVER;
     }
-    const CUtensorMap* tr = tx;   // placeholder without a residual
+    tr = tx;   // placeholder without a residual
     if (RES) {
         const uint64_t rd[2] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M)};
         const uint64_t rs[1] = {static_cast<uint64_t>(d.ldr) * 2};
         const uint32_t rb[2] = {32, 32};
-        tr = get_tensor_map(d.residual, 2, rd, rs, rb, 64);
-        if (!tr) return B200_ERR_DRIVER;
+        if (!get_tensor_map(&tr, d.residual, 2, rd, rs, rb, 64)) return B200_ERR_DRIVER;
     }
 
     LinearParams p;
@@ -306,29 +249,20 @@ int launch_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     p.ln_eps = d.ln_eps;
     p.k_slots = (p.K + 31) / 32;
     p.n_slots = (p.N + 31) / 32;
-    p.ln_out = d.post_ln_out;
-    p.ln_gamma = d.post_ln_gamma;
-    p.ln_beta = d.post_ln_beta;
-    p.ld_ln = d.post_ln_ld;
-    p.ln_sync = static_cast<int*>(d.post_ln_sync);
-    // 256 rows of a block shared out over its tiles, in units of one row per epilogue warp of the pair
-    p.ln_rows_per_tile = ((256 + p.num_n_tiles - 1) / p.num_n_tiles + 2 * EW - 1) / (2 * EW) * (2 * EW);
 
-    static bool attr_set[64] = {false};
+    static PerDeviceOnce attr_once;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(linear_pair_kernel<BN, RES, FOLD, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 C::SMEM_BYTES) != cudaSuccess)
-            return B200_ERR_LAUNCH;
-        attr_set[dev] = true;
-    }
+    if (!attr_once.ensure(dev, []() {
+            return cudaFuncSetAttribute(linear_pair_kernel<BN, RES, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C::SMEM_BYTES) == cudaSuccess;
+        }))
+        return B200_ERR_LAUNCH;
     int pairs = max_active_pairs(BN);   // (the RES variant uses no more shared memory per CTA than its stage count allows)
     if (pairs <= 0) pairs = sm_count / 2;
     if (p.num_tiles < pairs) pairs = p.num_tiles;
-    if (LN && pairs < p.num_n_tiles) return B200_ERR_UNSUPPORTED;   // the tiles of a row block need distinct owners
-    launch_kernel(linear_pair_kernel<BN, RES, FOLD, LN>, dim3(2 * pairs), dim3(C::THREADS), C::SMEM_BYTES, stream, *tx, *tw,
-                  *ty, *tr, p);
+    launch_kernel(linear_pair_kernel<BN, RES, FOLD>, dim3(2 * pairs), dim3(C::THREADS), C::SMEM_BYTES, stream, tx, tw,
+                  ty, tr, p);
     count_launch();
     return check_launch();
 }
@@ -339,7 +273,7 @@ int query_pairs(int sm_count) {
     // A persistent grid must not exceed what is co-resident: a pair that cannot be placed (GPCs with an odd number
     // of free SMs) would otherwise run as a second wave after the first has finished all the work.
     using C = PairCfg<BN, false, false, pair_epi_warps<BN>()>;
-    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(linear_pair_kernel<BN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess) {
         cudaGetLastError();
         return 0;
@@ -356,7 +290,7 @@ int query_pairs(int sm_count) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false, false, false>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<BN, false, false>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -365,19 +299,21 @@ int query_pairs(int sm_count) {
 }  // namespace
 
 int max_active_pairs(int bn) {
-    static int cache[64][4] = {};
+    static int cache[kMaxDevices][4] = {};
+    static PerDeviceOnce once[4];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return 0;
+    if (dev < 0 || dev >= kMaxDevices) return 0;
     const int idx = bn == 256 ? 0 : (bn == 192 ? 1 : (bn == 128 ? 2 : 3));
-    if (cache[dev][idx] == 0) {
+    once[idx].ensure(dev, [&]() {
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int n = bn == 256 ? query_pairs<256>(sms) : (bn == 192 ? query_pairs<192>(sms)
                                                   : (bn == 128 ? query_pairs<128>(sms) : query_pairs<64>(sms)));
         if (n > sms / 2) n = sms / 2;
         cache[dev][idx] = n > 0 ? n : -1;
-    }
+        return true;
+    });
     return cache[dev][idx] > 0 ? cache[dev][idx] : 0;
 }
 
@@ -385,11 +321,6 @@ template <int BN>
 int launch_linear_pair(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
     // The TMA residual path needs 16-byte aligned residual rows (checked by the caller) and a half-precision residual.
     const bool fold = wants_fold(d);
-    if (wants_post_ln(d)) {
-        if (fold) return B200_ERR_UNSUPPORTED;
-        if (d.epilogue == B200_EPI_BIAS_RESIDUAL) return launch_pair<BN, true, false, true>(d, stream, sm_count);
-        return launch_pair<BN, false, false, true>(d, stream, sm_count);
-    }
     if (d.epilogue == B200_EPI_BIAS_RESIDUAL)
         return fold ? launch_pair<BN, true, true>(d, stream, sm_count) : launch_pair<BN, true, false>(d, stream, sm_count);
     return fold ? launch_pair<BN, false, true>(d, stream, sm_count) : launch_pair<BN, false, false>(d, stream, sm_count);

@@ -5,7 +5,9 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 
@@ -24,7 +26,6 @@ bool pdl_enabled() {
     return on;
 }
 
-static constexpr int kMaxDevices = 64;
 static unsigned int* g_status_addr[kMaxDevices] = {nullptr};
 static std::mutex g_status_mutex;
 
@@ -47,7 +48,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Self-test hook (b200_selftest_tensor_map_cache): a stand-in encoder, so that the cache can be exercised on a machine
+// without a driver.  Null in normal operation.
+static std::atomic<EncodeTiledFn> g_encode_override{nullptr};
+
 static EncodeTiledFn resolve_encode() {
+    if (EncodeTiledFn o = g_encode_override.load(std::memory_order_acquire)) return o;
     static EncodeTiledFn fn = []() -> EncodeTiledFn {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
@@ -74,14 +80,18 @@ struct MapKeyHash {
     }
 };
 static std::mutex g_map_mutex;
-static std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
+static std::atomic<size_t> g_max_cached_maps{65536};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
-const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box, int swizzle_bytes) {
-    if (rank < 2 || rank > 3) return nullptr;
-    if (swizzle_bytes != 128 && swizzle_bytes != 64) return nullptr;
+bool get_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, int swizzle_bytes) {
+    if (!out || rank < 2 || rank > 3) return false;
+    if (swizzle_bytes != 128 && swizzle_bytes != 64) return false;
     int dev = 0;
-    cudaGetDevice(&dev);
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        dev = 0;
+    }
     MapKey key;
     std::memset(&key, 0, sizeof(key));
     key.v[0] = reinterpret_cast<uint64_t>(base);
@@ -94,35 +104,16 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
 
     std::lock_guard<std::mutex> lock(g_map_mutex);
     auto it = g_maps.find(key);
-    if (it != g_maps.end()) return it->second;
-
-    EncodeTiledFn encode = resolve_encode();
-    if (!encode) return nullptr;
-    // cudaMallocHost is not needed: the map is copied into the kernel's parameter space at launch.
-    CUtensorMap* map = new CUtensorMap;
-    cuuint64_t gdims[3] = {1, 1, 1};
-    cuuint64_t gstrides[2] = {0, 0};
-    cuuint32_t gbox[3] = {1, 1, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    for (int i = 0; i < rank; ++i) {
-        gdims[i] = dims[i];
-        gbox[i] = box[i];
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return true;
     }
-    for (int i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        delete map;
-        return nullptr;
-    }
-    if (g_maps.size() > 65536) {  // bound the cache: a caller that streams fresh pointers forever must not leak
-        for (auto& kv : g_maps) delete kv.second;
-        g_maps.clear();
-    }
-    g_maps.emplace(key, map);
-    return map;
+    if (!encode_tensor_map(out, base, rank, dims, strides_bytes, box, swizzle_bytes)) return false;
+    // Bound the cache: a caller that streams fresh pointers forever must not leak.  Entries are values, and callers
+    // hold copies, so dropping them all is safe whoever is launching at this moment.
+    if (g_maps.size() >= g_max_cached_maps.load(std::memory_order_relaxed)) g_maps.clear();
+    g_maps.emplace(key, *out);
+    return true;
 }
 
 // Encodes a tensor map into caller-provided storage (no cache, no allocation).  Same conventions as get_tensor_map.
@@ -176,6 +167,58 @@ int b200_device_status(void) {
         return (v & ~8u) != 0 ? B200_ERR_DEVICE_TIMEOUT : B200_ERR_INDEX;   // bit 3: index out of range
     }
     return B200_OK;
+}
+
+// Hammers the tensor-map cache from `threads` host threads with a stand-in encoder and a cache capacity of `capacity`
+// entries, so that evictions happen all the time while other threads are reading.  Every returned map is compared
+// with what the stand-in writes for its key.  Returns the number of wrong maps (0 = pass), negative on bad arguments.
+// Needs no GPU and no driver.
+int b200_selftest_tensor_map_cache(int threads, int maps_per_thread, int capacity) {
+    using namespace b200;
+    if (threads <= 0 || threads > 64 || maps_per_thread <= 0 || capacity <= 0) return B200_ERR_PARAM;
+    struct Stub {
+        static CUresult encode(CUtensorMap* map, CUtensorMapDataType, cuuint32_t rank, void* base, const cuuint64_t* dims,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) {
+            uint64_t* w = reinterpret_cast<uint64_t*>(map);
+            for (size_t i = 0; i < sizeof(CUtensorMap) / 8; ++i)
+                w[i] = reinterpret_cast<uint64_t>(base) * 0x9E3779B97F4A7C15ull + dims[1] * 31 + i + rank;
+            return CUDA_SUCCESS;
+        }
+    };
+    const size_t old_cap = g_max_cached_maps.exchange(static_cast<size_t>(capacity));
+    g_encode_override.store(&Stub::encode, std::memory_order_release);
+    std::atomic<int> bad{0};
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t) {
+        pool.emplace_back([&, t]() {
+            for (int round = 0; round < 4; ++round) {
+                for (int i = 0; i < maps_per_thread; ++i) {
+                    // half of the keys are shared between threads (hits and evictions race), half are private
+                    const uint64_t id = (i & 1) ? static_cast<uint64_t>(i) : (static_cast<uint64_t>(t) << 32) + i;
+                    void* base = reinterpret_cast<void*>((id + 1) << 8);
+                    const uint64_t dims[2] = {64, 128 + (id & 7)};
+                    const uint64_t strides[1] = {128};
+                    const uint32_t box[2] = {64, 128};
+                    CUtensorMap got, want;
+                    if (!get_tensor_map(&got, base, 2, dims, strides, box) ||
+                        Stub::encode(&want, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, dims, nullptr, nullptr, nullptr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+                        std::memcmp(&got, &want, sizeof(CUtensorMap)) != 0)
+                        bad.fetch_add(1);
+                }
+            }
+        });
+    }
+    for (auto& th : pool) th.join();
+    g_encode_override.store(nullptr, std::memory_order_release);
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        g_maps.clear();   // the stand-in's entries must not outlive the test
+    }
+    g_max_cached_maps.store(old_cap);
+    return bad.load();
 }
 
 uint64_t b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }

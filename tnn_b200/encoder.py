@@ -23,7 +23,6 @@ class Encoder:
         self._ws = None
         self._ws_key = None
         self.fold = False
-        self.layernorm_in_gemm = False    # True: each LayerNorm inside the launch of the GEMM that feeds it
 
     @classmethod
     def from_workload(cls, wl, dtype=torch.float16, device="cuda", fold_layernorm=True):
@@ -173,7 +172,7 @@ class Encoder:
         d.dtype = capi.dtype_code(self.dtype)
         d.ln_eps = float(self.cfg.ln_eps)
         d.mask_exclude_below = -5000.0
-        d.fold_layernorm = 1 if self.fold else (2 if self.layernorm_in_gemm else 0)
+        d.fold_layernorm = 1 if self.fold else 0
         rc = capi.lib().b200_encoder_fwd(ctypes.byref(d), capi.stream_ptr())
         capi.check(rc, "b200_encoder_fwd")
         return hidden

@@ -66,7 +66,7 @@ def convert(src, dtype, out=None):
 
 
 def _linear_desc(x, w_nk, bias, residual, epilogue, out_dtype, out, block_n, out_stats=None, ln_in=None, res_ln=None,
-                 ln_eps=1e-12, post_ln=None):
+                 ln_eps=1e-12):
     _require_cuda(x, w_nk, bias, residual, out)
     K = x.shape[-1]
     x2 = x.reshape(-1, K)
@@ -95,21 +95,13 @@ def _linear_desc(x, w_nk, bias, residual, epilogue, out_dtype, out, block_n, out
         d.ln_in_stats, d.ln_c1, d.ln_c2 = (t.data_ptr() for t in ln_in)
     if res_ln is not None:
         d.res_ln_stats, d.res_ln_gamma, d.res_ln_beta = (t.data_ptr() for t in res_ln)
-    if post_ln is not None:
-        # (gamma, beta, out, sync): LayerNorm of the output rows in the same launch; sync = zeroed int32 [ceil(M/256)]
-        g, b, o, sync = post_ln
-        o2 = o.reshape(-1, N)
-        assert o2.stride(1) == 1 and o.dtype == out.dtype and sync.dtype == torch.int32 and sync.numel() >= (M + 255) // 256
-        d.post_ln_gamma, d.post_ln_beta, d.post_ln_out, d.post_ln_ld = g.data_ptr(), b.data_ptr(), o2.data_ptr(), o2.stride(0)
-        d.post_ln_sync = sync.data_ptr()
     return d, out
 
 
 def linear(x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out_dtype=None, out=None, block_n=0,
-           out_stats=None, ln_in=None, res_ln=None, ln_eps=1e-12, post_ln=None):
+           out_stats=None, ln_in=None, res_ln=None, ln_eps=1e-12):
     """y[M,N] = epilogue(x[M,K] . w_nk[N,K]^T + bias (+ residual)); x may be `[..., K]`."""
-    d, out = _linear_desc(x, w_nk, bias, residual, epilogue, out_dtype, out, block_n, out_stats, ln_in, res_ln, ln_eps,
-                          post_ln)
+    d, out = _linear_desc(x, w_nk, bias, residual, epilogue, out_dtype, out, block_n, out_stats, ln_in, res_ln, ln_eps)
     rc = capi.lib().b200_linear_fwd(ctypes.byref(d), capi.stream_ptr())
     capi.check(rc, "b200_linear_fwd")
     return out
@@ -243,63 +235,3 @@ def qa_head(x, weight, bias=None, out=None):
     rc = capi.lib().b200_qa_head_fwd(ctypes.byref(d), capi.stream_ptr())
     capi.check(rc, "b200_qa_head_fwd")
     return out
-
-
-class Chain:
-    """Dependent GEMMs / LayerNorms of an encoder layer in one launch (b200_chain_fwd).
-
-        c = Chain()
-        t = c.linear(ctx, w_o, b_o, residual=h, epilogue=EPI_BIAS_RESIDUAL)
-        a = c.add_layernorm(t, g1, b1, eps)
-        f = c.linear(a, w1, bias1, epilogue=EPI_BIAS_GELU)
-        c.run()
-
-    The calls only record descriptors and allocate outputs; `run` clears the row-block counters and launches."""
-
-    def __init__(self):
-        self.phases = []
-        self._keep = []
-        self.rows = None
-
-    def _rows(self, n):
-        if self.rows is None:
-            self.rows = n
-        assert self.rows == n, "every phase of a chain covers the same rows"
-
-    def linear(self, x, w_nk, bias=None, residual=None, epilogue=EPI_BIAS, out=None):
-        d, out = _linear_desc(x, w_nk, bias, residual, epilogue, None, out, 0)
-        self._rows(d.M)
-        ph = capi.ChainPhase()
-        ph.kind = capi.PHASE_LINEAR
-        ph.linear = d
-        self.phases.append(ph)
-        self._keep += [x, w_nk, bias, residual, out]
-        return out
-
-    def add_layernorm(self, x, gamma, beta, eps, out=None):
-        d, out = _layernorm_desc(x, gamma, beta, eps, None, None, out)
-        self._rows(d.rows)
-        ph = capi.ChainPhase()
-        ph.kind = capi.PHASE_ADD_LAYERNORM
-        ph.layernorm = d
-        self.phases.append(ph)
-        self._keep += [x, gamma, beta, out]
-        return out
-
-    def sync_bytes(self):
-        return capi.lib().b200_chain_sync_bytes(self.rows, len(self.phases))
-
-    def run(self, sync=None):
-        n = len(self.phases)
-        words = (self.sync_bytes() + 3) // 4
-        dev = self._keep[0].device
-        if sync is None:
-            sync = torch.zeros((words,), dtype=torch.int32, device=dev)
-        else:
-            assert sync.dtype == torch.int32 and sync.numel() >= words and sync.is_contiguous()
-            sync.zero_()
-        arr = (capi.ChainPhase * n)(*self.phases)
-        rc = capi.lib().b200_chain_fwd(arr, n, sync.data_ptr(), capi.stream_ptr())
-        capi.check(rc, "b200_chain_fwd")
-        self._keep.append(sync)
-        return sync

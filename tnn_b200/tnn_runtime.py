@@ -13,8 +13,8 @@ from . import capi
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
-LIBTNN = os.environ.get("TNN_B200_LIBTNN", os.path.join(_ROOT, "oracle", "_ref", "libTNN.so"))
-SHIM = os.environ.get("TNN_B200_SHIM", os.path.join(_ROOT, "oracle", "_ref", "libtnn_capi.so"))
+LIBTNN = os.environ.get("TNN_B200_LIBTNN", os.path.join(_HERE, "host", "libTNN.so"))
+SHIM = os.environ.get("TNN_B200_SHIM", os.path.join(_HERE, "host", "libtnn_capi.so"))
 PLUGIN = os.path.join(_HERE, "lib", "libtnn_b200_plugin.so")
 
 DEVICE_NAIVE, DEVICE_X86, DEVICE_CUDA = 0, 1, 2
