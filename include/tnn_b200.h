@@ -328,12 +328,23 @@ B200_API const char* b200_status_string(int status);
 /* Reads and clears the current device's status word (synchronous, small).  0, B200_ERR_DEVICE_TIMEOUT or
  * B200_ERR_INDEX (a timeout takes precedence). */
 B200_API int         b200_device_status(void);
+/* The same without blocking the host: enqueues a copy of the current device's raw status word into *host_word (page-
+ * locked host memory, so that the copy is asynchronous) behind the work already in `stream`.  Once the stream has been
+ * synchronised, b200_decode_status_word(*host_word) gives the status; the device word is NOT cleared (a non-zero word
+ * is cleared by calling b200_device_status()). */
+B200_API int         b200_device_status_async(unsigned int* host_word, b200_stream_t stream);
+B200_API int         b200_decode_status_word(unsigned int word);
 /* Number of kernel launches issued by this library in this process (all devices, all threads). */
 B200_API uint64_t    b200_launch_count(void);
 B200_API const char* b200_version(void);
 /* Self-test of the tensor-map (TMA descriptor) cache the launchers share: `threads` host threads look maps up while
  * the cache, limited to `capacity` entries for the test, keeps evicting; a stand-in replaces the driver's encoder, so
  * no GPU or driver is needed.  Returns the number of maps that came back wrong (0 = pass) or B200_ERR_PARAM. */
+/* Self-test of the bounded-wait convention: launches one warp that waits on a barrier nobody arrives at, with a limit
+ * of 1024 polls (milliseconds at most); it gives up, sets the time-out bit of the status word and returns, so that
+ * after a synchronise b200_device_status() reports B200_ERR_DEVICE_TIMEOUT (and clears it) and the device carries on
+ * as before.  This is how every wait in the kernels ends when its partner never shows up; nothing traps or hangs. */
+B200_API int         b200_selftest_bounded_wait(b200_stream_t stream);
 B200_API int         b200_selftest_tensor_map_cache(int threads, int maps_per_thread, int capacity);
 
 #ifdef __cplusplus

@@ -24,13 +24,27 @@ def available():
 _lib = None
 
 
+def _loaded_libtnn():
+    """Path of a libTNN.so this process has already mapped, or None.  A process must hold ONE copy of the framework:
+    its registries (devices, layers, accs, passes) are static objects, and a second copy would own a second set."""
+    try:
+        with open("/proc/self/maps") as fh:
+            for line in fh:
+                path = line.rstrip("\n").rsplit(" ", 1)[-1]
+                if path.endswith("/libTNN.so"):
+                    return path
+    except OSError:
+        pass
+    return None
+
+
 def capi():
     global _lib
     if _lib is None:
         if not available():
             raise RuntimeError("reference build missing: run `python oracle/build_ref.py` where the reference "
                                "sources are present")
-        ctypes.CDLL(LIBTNN, mode=ctypes.RTLD_GLOBAL)
+        ctypes.CDLL(_loaded_libtnn() or LIBTNN, mode=ctypes.RTLD_GLOBAL)
         l = ctypes.CDLL(CAPI)
         l.tnnc_create.restype = ctypes.c_void_p
         l.tnnc_create.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,

@@ -301,3 +301,63 @@ def test_qa_head_rejects_bad_arguments():
         ops.qa_head(x, torch.zeros(768, 5, device="cuda"))          # more outputs than the kernel holds
     with pytest.raises(capi.B200Error):
         ops.qa_head(x[:, :762], torch.zeros(762, 2, device="cuda"))  # H not a multiple of 8
+
+
+# ------------------------------------------------------------------------------------------------ launch ordering
+def test_attention_reads_kv_len_behind_the_dependency_wait():
+    """A kernel launched with programmatic stream serialization may start before its predecessor has finished; it must
+    not read what the predecessor writes until its dependency wait.  b200_mask_from_input_mask writes mask and kv_len,
+    the long-sequence attention kernel (S = 256) launched right behind it on the same stream reads both.  Fifty rounds
+    with a new mask each, the same buffers every time (a stale kv_len from the previous round would change the
+    result), compared bit for bit with the same two launches separated by a device synchronise."""
+    dev = torch.device("cuda")
+    B, S, heads = 8, 256, 4
+    g = torch.Generator(device="cpu").manual_seed(5)
+    qkv = torch.randn(B, S, 3 * heads * 64, generator=g).to(dev).half()
+    mask_a, kv_a = torch.empty(B, S, device=dev), torch.empty(B, dtype=torch.int32, device=dev)
+    mask_b, kv_b = torch.empty(B, S, device=dev), torch.empty(B, dtype=torch.int32, device=dev)
+    out_a = torch.empty(B, S, heads * 64, dtype=torch.float16, device=dev)
+    out_b = torch.empty_like(out_a)
+    rng = np.random.default_rng(7)
+    for r in range(50):
+        lengths = rng.integers(1, S + 1, size=B)
+        im = torch.from_numpy((np.arange(S)[None, :] < lengths[:, None]).astype(np.int32)).to(dev)
+        torch.cuda.synchronize()
+        # back to back
+        ops.mask_from_input_mask(im, out_mask=mask_a, out_kv_len=kv_a)
+        ops.attention(qkv, heads, mask_a, kv_a, out=out_a)
+        torch.cuda.synchronize()
+        # synchronised
+        ops.mask_from_input_mask(im, out_mask=mask_b, out_kv_len=kv_b)
+        torch.cuda.synchronize()
+        ops.attention(qkv, heads, mask_b, kv_b, out=out_b)
+        torch.cuda.synchronize()
+        assert torch.equal(kv_a, kv_b)
+        assert torch.equal(out_a, out_b), r
+    assert capi.device_status() == capi.OK
+
+
+def test_bounded_wait_expires_cleanly_and_the_device_carries_on():
+    """The convention every device-side wait follows, shown on a kernel made for it: a warp waits on a barrier nobody
+    arrives at, gives up after its poll limit, flags the status word and returns.  The host sees
+    B200_ERR_DEVICE_TIMEOUT once, the word is clear again, and the next GEMM runs and is correct."""
+    lib = capi.lib()
+    assert capi.device_status() == capi.OK
+    assert lib.b200_selftest_bounded_wait(capi.stream_ptr()) == capi.OK
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.ERR_DEVICE_TIMEOUT
+    assert capi.device_status() == capi.OK
+    # the asynchronous read of the same word
+    word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    assert lib.b200_selftest_bounded_wait(capi.stream_ptr()) == capi.OK
+    assert lib.b200_device_status_async(word.data_ptr(), capi.stream_ptr()) == capi.OK
+    torch.cuda.synchronize()
+    assert lib.b200_decode_status_word(int(word[0])) == capi.ERR_DEVICE_TIMEOUT
+    assert capi.device_status() == capi.ERR_DEVICE_TIMEOUT   # the asynchronous read does not clear
+    assert capi.device_status() == capi.OK
+    x = torch.randn(512, 256, device="cuda").half()
+    w = (torch.randn(128, 256, device="cuda") * 0.05).half()
+    y = ops.linear(x, w)
+    torch.cuda.synchronize()
+    assert capi.device_status() == capi.OK
+    assert (y.float() - x.float() @ w.float().t()).abs().max().item() < 2e-2

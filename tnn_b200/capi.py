@@ -97,8 +97,11 @@ SYMBOLS = {
     "b200_encoder_fwd": (_c.c_int, [_c.POINTER(EncoderDesc), _vp]),
     "b200_status_string": (_c.c_char_p, [_c.c_int]),
     "b200_device_status": (_c.c_int, []),
+    "b200_device_status_async": (_c.c_int, [_vp, _vp]),
+    "b200_decode_status_word": (_c.c_int, [_c.c_uint]),
     "b200_launch_count": (_c.c_uint64, []),
     "b200_version": (_c.c_char_p, []),
+    "b200_selftest_bounded_wait": (_c.c_int, [_vp]),
     "b200_selftest_tensor_map_cache": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int]),
 }
 

@@ -10,10 +10,29 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 
 __device__ unsigned int g_device_status = 0;
+
+// Self-test of the bounded-wait convention (b200_selftest_bounded_wait): one warp waits on an mbarrier that nobody ever
+// arrives at, with a small poll limit, gives up, records it in the status word and returns normally.
+__global__ void bounded_wait_selftest_kernel(unsigned int* status, uint32_t poll_limit) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t gave_up;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        gave_up = 0;
+        mbar_fence_init();
+    }
+    __syncwarp();
+    bool arrived = false;
+    for (uint32_t i = 0; i < poll_limit && !arrived; ++i) arrived = mbar_try_wait(&bar, 0);
+    if (!arrived) gave_up = 1u;
+    __syncwarp();
+    if (threadIdx.x == 0 && gave_up != 0 && status != nullptr) atomicOr(status, 1u);
+}
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
@@ -164,9 +183,34 @@ int b200_device_status(void) {
     if (v != 0) {
         unsigned int zero = 0;
         cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice);
-        return (v & ~8u) != 0 ? B200_ERR_DEVICE_TIMEOUT : B200_ERR_INDEX;   // bit 3: index out of range
+        return b200_decode_status_word(v);
     }
     return B200_OK;
+}
+
+int b200_selftest_bounded_wait(b200_stream_t stream) {
+    unsigned int* p = b200::device_status_ptr();
+    if (!p) return B200_ERR_LAUNCH;
+    b200::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, 1024u);
+    b200::count_launch();
+    return b200::check_launch();
+}
+
+int b200_device_status_async(unsigned int* host_word, b200_stream_t stream) {
+    if (!host_word) return B200_ERR_PARAM;
+    unsigned int* p = b200::device_status_ptr();
+    if (!p) return B200_ERR_LAUNCH;
+    if (cudaMemcpyAsync(host_word, p, sizeof(unsigned int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) !=
+        cudaSuccess) {
+        cudaGetLastError();
+        return B200_ERR_LAUNCH;
+    }
+    return B200_OK;
+}
+
+int b200_decode_status_word(unsigned int word) {
+    if (word == 0) return B200_OK;
+    return (word & ~8u) != 0 ? B200_ERR_DEVICE_TIMEOUT : B200_ERR_INDEX;   // bit 3: index out of range
 }
 
 // Hammers the tensor-map cache from `threads` host threads with a stand-in encoder and a cache capacity of `capacity`

@@ -202,13 +202,15 @@ def embedding_layernorm(input_ids, segment_ids, word_emb, type_emb, pos_emb, gam
     return out
 
 
-def mask_from_input_mask(input_mask, masked_value=-10000.0, exclude_below=-5000.0):
-    """int32 0/1 `[B,S]` -> (additive fp32 mask `[B,S]`, int32 kv_len `[B]`)."""
-    _require_cuda(input_mask)
+def mask_from_input_mask(input_mask, masked_value=-10000.0, exclude_below=-5000.0, out_mask=None, out_kv_len=None):
+    """int32 0/1 `[B,S]` -> (additive fp32 mask `[B,S]`, int32 kv_len `[B]`), into the given buffers if any."""
+    _require_cuda(input_mask, out_mask, out_kv_len)
     B, S = input_mask.shape
     assert input_mask.dtype == torch.int32 and input_mask.is_contiguous()
-    mask_add = torch.empty((B, S), dtype=torch.float32, device=input_mask.device)
-    kv_len = torch.empty((B,), dtype=torch.int32, device=input_mask.device)
+    mask_add = out_mask if out_mask is not None else torch.empty((B, S), dtype=torch.float32, device=input_mask.device)
+    kv_len = out_kv_len if out_kv_len is not None else torch.empty((B,), dtype=torch.int32, device=input_mask.device)
+    assert mask_add.dtype == torch.float32 and mask_add.is_contiguous() and mask_add.numel() == B * S
+    assert kv_len.dtype == torch.int32 and kv_len.numel() == B
     rc = capi.lib().b200_mask_from_input_mask(input_mask.data_ptr(), B, S, masked_value, exclude_below,
                                               mask_add.data_ptr(), kv_len.data_ptr(), capi.stream_ptr())
     capi.check(rc, "b200_mask_from_input_mask")

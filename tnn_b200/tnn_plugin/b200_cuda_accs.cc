@@ -1,4 +1,4 @@
-// DEVICE_CUDA layer accs of the fused encoder graph: FusedLinear, FusedAttention and LayerNorm.  Each Forward is one
+// DEVICE_CUDA layer accs of the fused encoder graph: FusedLinear, FusedAttention and LayerNorm.  Each DoForward is one
 // launch through the kernel library's C ABI on the context's stream (plus a conversion launch where an fp32 blob
 // enters the half-precision region).  Registered in the device's acc registry like the reference's accs
 // (REGISTER_CUDA_ACC, source/tnn/device/cuda/acc/cuda_layer_acc.h:105-107).
@@ -112,7 +112,7 @@ Status B200CudaFusedLinearLayerAcc::AsCompute(Blob* src, void* staging, int64_t 
                         "b200_convert");
 }
 
-Status B200CudaFusedLinearLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaFusedLinearLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<FusedLinearLayerParam*>(param_);
     const int64_t rows = Rows(inputs[0]->GetBlobDesc().dims);
     B200LinearDesc d;
@@ -154,7 +154,7 @@ Status B200CudaFusedAttentionLayerAcc::Reshape(const std::vector<Blob*>& inputs,
     return TNN_OK;
 }
 
-Status B200CudaFusedAttentionLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaFusedAttentionLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<FusedAttentionLayerParam*>(param_);
     const DimsVector dims = inputs[0]->GetBlobDesc().dims;
     const int64_t B = dims[0], S = dims[1];
@@ -240,7 +240,7 @@ Status B200CudaFusedEmbeddingLayerAcc::Reshape(const std::vector<Blob*>& inputs,
     return TNN_OK;
 }
 
-Status B200CudaFusedEmbeddingLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaFusedEmbeddingLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<FusedEmbeddingLayerParam*>(param_);
     const DimsVector dims = inputs[0]->GetBlobDesc().dims;
     B200EmbeddingDesc d;
@@ -279,7 +279,7 @@ Status B200CudaFusedMaskLayerAcc::Reshape(const std::vector<Blob*>& inputs, cons
     return TNN_OK;
 }
 
-Status B200CudaFusedMaskLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaFusedMaskLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<FusedMaskLayerParam*>(param_);
     const DimsVector dims = inputs[0]->GetBlobDesc().dims;
     return B200ToStatus(b200_mask_from_input_mask(static_cast<const int32_t*>(DevicePtr(inputs[0])), dims[0], dims[1],
@@ -337,7 +337,7 @@ Status B200CudaFusedQAHeadLayerAcc::Reshape(const std::vector<Blob*>& inputs, co
     return EnsureBuffer(&logits_, &logits_cap_, static_cast<size_t>(M > 0 ? M : 1) * p->outputs * sizeof(float));
 }
 
-Status B200CudaFusedQAHeadLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaFusedQAHeadLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param_);
     const DimsVector dims = inputs[0]->GetBlobDesc().dims;
     B200QAHeadDesc d;
@@ -390,7 +390,7 @@ Status B200CudaSqueezeLayerAcc::Init(Context* context, LayerParam* param, LayerR
 Status B200CudaSqueezeLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     return TNN_OK;
 }
-Status B200CudaSqueezeLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaSqueezeLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     return CopyBlob(inputs[0], outputs[0], DevicePtr(inputs[0]), DevicePtr(outputs[0]), context_->GetStream());
 }
 B200_REGISTER_CUDA_ACC(Squeeze, LAYER_SQUEEZE)
@@ -404,7 +404,7 @@ Status B200CudaUnsqueezeLayerAcc::Init(Context* context, LayerParam* param, Laye
 Status B200CudaUnsqueezeLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     return TNN_OK;
 }
-Status B200CudaUnsqueezeLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaUnsqueezeLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     return CopyBlob(inputs[0], outputs[0], DevicePtr(inputs[0]), DevicePtr(outputs[0]), context_->GetStream());
 }
 B200_REGISTER_CUDA_ACC(Unsqueeze, LAYER_UNSQUEEZE)
@@ -432,7 +432,7 @@ Status B200CudaLayerNormLayerAcc::Reshape(const std::vector<Blob*>& inputs, cons
     return TNN_OK;
 }
 
-Status B200CudaLayerNormLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+Status B200CudaLayerNormLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
     auto* p = dynamic_cast<LayerNormLayerParam*>(param_);
     const DimsVector dims = inputs[0]->GetBlobDesc().dims;
     B200LayerNormDesc d;

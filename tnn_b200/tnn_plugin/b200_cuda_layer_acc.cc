@@ -45,7 +45,33 @@ Status B200CudaLayerAcc::ReloadConstantBlobs(const std::vector<Blob*>& inputs, b
 }
 
 Status B200CudaLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) { return TNN_OK; }
-Status B200CudaLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) { return TNN_OK; }
+Status B200CudaLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) { return TNN_OK; }
+
+Status B200CudaLayerAcc::Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
+    if (context_->Replaying()) return TNN_OK;   // the instance's graph stands for this layer's launches
+    context_->RecordCall(this, inputs, outputs);
+#if TNN_PROFILE
+    if (context_->profile_layer) {
+        auto pdata = std::make_shared<ProfilingData>();
+        UpdateProfilingData(pdata.get(), param_, inputs[0]->GetBlobDesc().dims, outputs[0]->GetBlobDesc().dims);
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, context_->GetStream());
+        Status st = DoForward(inputs, outputs);
+        cudaEventRecord(e1, context_->GetStream());
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        pdata->kernel_time = ms;
+        context_->AddProfilingData(pdata);
+        return st;
+    }
+#endif
+    return DoForward(inputs, outputs);
+}
 
 Status B200CudaLayerAcc::EnsureBuffer(void** ptr, size_t* capacity, size_t bytes) {
     if (bytes <= *capacity && *ptr) return TNN_OK;

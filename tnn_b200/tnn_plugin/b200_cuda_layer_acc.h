@@ -1,8 +1,14 @@
 // Base class of the plug-in's DEVICE_CUDA layer accs: the AbstractLayerAcc surface
 // (Init / Reshape / Forward over TNN Blobs, source/tnn/core/abstract_layer_acc.h:39-127) with the stream, the device
 // and the upload of constant input blobs, as the reference's CudaLayerAcc provides
-// (source/tnn/device/cuda/acc/cuda_layer_acc.{h,cc}).  Differences: device pointers honour BlobHandle.bytes_offset,
-// acc-private buffers are sized in Init/Reshape (never in Forward), errors come back as Status.
+// (source/tnn/device/cuda/acc/cuda_layer_acc.{h,cc}: Init :31-45, ReloadConstantBlobs :47-85, SupportDataFormat
+// :96-102 — the constant upload and the format list follow that file because AbstractLayerAcc's protected members
+// dictate them).  Differences: device pointers honour BlobHandle.bytes_offset, acc-private buffers are sized in
+// Init/Reshape (never in Forward), errors come back as Status, and Forward is a wrapper: the subclasses implement
+// DoForward, and Forward skips it while the context replays a captured CUDA graph of the whole instance
+// (b200_cuda_context.h).  Built with TNN_PROFILE, Forward brackets DoForward with CUDA events and feeds the layer's
+// device time to the context's profile, as the reference's CPU accs do with host timers
+// (source/tnn/device/x86/acc/x86_layer_acc.cc:55-73).
 #ifndef TNN_B200_CUDA_LAYER_ACC_H_
 #define TNN_B200_CUDA_LAYER_ACC_H_
 
@@ -22,7 +28,10 @@ public:
     virtual Status Init(Context* context, LayerParam* param, LayerResource* resource, const std::vector<Blob*>& inputs,
                         const std::vector<Blob*>& outputs);
     virtual Status Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);
-    virtual Status Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);
+    virtual Status Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) final;
+    // The layer's launches on the context's stream.  Also called by the context itself when a graph capture has to
+    // be re-run eagerly.
+    virtual Status DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);
     virtual Status ReloadConstantBlobs(const std::vector<Blob*>& inputs, bool only_reload_shape_differ_blob = false);
 
 protected:
@@ -50,7 +59,7 @@ private:
                             const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);                      \
         virtual ~B200Cuda##type_string##LayerAcc() {}                                                                  \
         virtual Status Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);                   \
-        virtual Status Forward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);                   \
+        virtual Status DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs);                 \
                                                                                                                        \
     private:
 

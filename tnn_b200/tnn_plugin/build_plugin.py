@@ -46,7 +46,7 @@ def main():
     if not os.path.exists(host_lib) or os.path.getmtime(host_lib) < os.path.getmtime(a.libtnn):
         shutil.copy2(a.libtnn, host_lib)
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-    common = [cxx, "-std=gnu++11", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-include", "cstdint",
+    common = [cxx, "-std=gnu++11", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-fopenmp", "-include", "cstdint",
               "-I%s/include" % ref, "-I%s/source" % ref]
     subprocess.check_call(common + [os.path.join(HERE, "tnn_capi.cc"), "-o", os.path.join(HOST, "libtnn_capi.so"),
                                     "-L" + HOST, "-lTNN", "-ldl", "-Wl,-rpath,$ORIGIN"])
@@ -59,7 +59,7 @@ def main():
     out = os.path.join(libdir, "libtnn_b200_plugin.so")
     cmd = (common + ["-I%s/include" % cuda, "-I%s/include" % ROOT, "-I%s/third_party/xbyak" % ref] + srcs +
            ["-o", out, "-L" + libdir, "-ltnn_b200", "-L" + HOST, "-lTNN",
-            "-L%s/lib64" % cuda, "-lcudart_static", "-ldl", "-lrt", "-lpthread",
+            "-L%s/lib64" % cuda, "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-fopenmp",
             "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../host"])
     subprocess.check_call(cmd)
     return 0

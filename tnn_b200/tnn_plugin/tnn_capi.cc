@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <map>
 #include <memory>
 #include <sstream>
 #include <string>
@@ -28,6 +29,10 @@ struct Handle {
     std::shared_ptr<Instance> inst;
     DeviceType device;
     std::string last_error;
+    // The caller-driven conversion path (BlobConverter on an input / output blob, as TNNTest drives it,
+    // test/test.cc:99-152): converters and Mats are created once per blob and reused.
+    std::map<std::string, std::shared_ptr<BlobConverter>> converters;
+    std::map<std::string, std::shared_ptr<Mat>> mats;
 };
 
 bool read_file(const char* path, std::string* out) {
@@ -49,6 +54,17 @@ int64_t count(const DimsVector& d) {
     int64_t n = 1;
     for (int x : d) n *= x;
     return n;
+}
+
+// `kind` of the C interface -> MatType: 0 = NCHW_FLOAT, 1 = RESERVED_FP16_TEST, 2 = RESERVED_BFP16_TEST, 3 = NC_INT32.
+bool mat_type_of(int kind, MatType* mt) {
+    switch (kind) {
+        case 0: *mt = NCHW_FLOAT; return true;
+        case 1: *mt = RESERVED_FP16_TEST; return true;
+        case 2: *mt = RESERVED_BFP16_TEST; return true;
+        case 3: *mt = NC_INT32; return true;
+        default: return false;
+    }
 }
 
 }  // namespace
@@ -184,16 +200,6 @@ TNNC_API int64_t tnnc_get_output_half(void* handle, const char* name, uint16_t* 
 // 3 = NC_INT32.  The pointer is device memory of the instance's GPU; the converter's branch for
 // image.GetDeviceType() == DEVICE_CUDA (reference: source/tnn/device/cuda/cuda_blob_converter.cc:140-149) copies or
 // converts device to device on the instance's stream.
-static bool mat_type_of(int kind, MatType* mt) {
-    switch (kind) {
-        case 0: *mt = NCHW_FLOAT; return true;
-        case 1: *mt = RESERVED_FP16_TEST; return true;
-        case 2: *mt = RESERVED_BFP16_TEST; return true;
-        case 3: *mt = NC_INT32; return true;
-        default: return false;
-    }
-}
-
 TNNC_API int tnnc_set_input_device(void* handle, const char* name, void* device_ptr, int64_t n, int kind) {
     Handle* h = static_cast<Handle*>(handle);
     MatType mt;
@@ -230,6 +236,145 @@ TNNC_API int64_t tnnc_get_output_device(void* handle, const char* name, int kind
     if (st != TNN_OK || !mat) { h->last_error = st.description(); return -3; }
     *device_ptr = mat->GetData();
     return n;
+}
+
+
+
+// ---- the reference benchmark's own loop, piece by piece (test/test.cc:125-152): BlobConverter::ConvertFromMatAsync on
+// the input blobs, Instance::ForwardAsync, BlobConverter::ConvertToMat on the output blobs, all on the instance's
+// command queue.  `kind`: 0 = NCHW_FLOAT, 1 = RESERVED_FP16_TEST, 2 = RESERVED_BFP16_TEST, 3 = NC_INT32.  `host` is the
+// caller's buffer (pageable or page-locked); it is wrapped in a Mat, never copied by the shim.
+static Status io_objects(Handle* h, const char* name, bool input, void* host, int64_t n, int kind,
+                         std::shared_ptr<BlobConverter>* conv, std::shared_ptr<Mat>* mat) {
+    MatType mt;
+    if (!mat_type_of(kind, &mt)) return Status(TNNERR_PARAM_ERR, "bad Mat kind");
+    BlobMap blobs;
+    Status st = input ? h->inst->GetAllInputBlobs(blobs) : h->inst->GetAllOutputBlobs(blobs);
+    if (st != TNN_OK) return st;
+    auto it = (name && name[0]) ? blobs.find(name) : blobs.begin();
+    if (it == blobs.end()) return Status(TNNERR_PARAM_ERR, std::string("no blob named ") + (name ? name : ""));
+    const DimsVector dims = it->second->GetBlobDesc().dims;
+    if (count(dims) != n) return Status(TNNERR_PARAM_ERR, "element count mismatch");
+    const std::string key = std::string(input ? "i:" : "o:") + it->first;
+    auto c = h->converters.find(key);
+    if (c == h->converters.end()) c = h->converters.emplace(key, std::make_shared<BlobConverter>(it->second)).first;
+    *conv = c->second;
+    auto m = h->mats.find(key);
+    if (m == h->mats.end() || m->second->GetData() != host || m->second->GetMatType() != mt ||
+        !DimsVectorUtils::Equal(m->second->GetDims(), dims)) {
+        h->mats[key] = std::make_shared<Mat>(DEVICE_NAIVE, mt, dims, host);
+        m = h->mats.find(key);
+    }
+    *mat = m->second;
+    return TNN_OK;
+}
+
+TNNC_API int tnnc_from_mat_async(void* handle, const char* name, void* host, int64_t n, int kind) {
+    Handle* h = static_cast<Handle*>(handle);
+    std::shared_ptr<BlobConverter> conv;
+    std::shared_ptr<Mat> mat;
+    Status st = io_objects(h, name, true, host, n, kind, &conv, &mat);
+    void* q = nullptr;
+    if (st == TNN_OK) st = h->inst->GetCommandQueue(&q);
+    if (st == TNN_OK) st = conv->ConvertFromMatAsync(*mat, MatConvertParam(), q);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st ? (int)st : -1; }
+    return 0;
+}
+
+TNNC_API int tnnc_to_mat(void* handle, const char* name, void* host, int64_t n, int kind, int blocking) {
+    Handle* h = static_cast<Handle*>(handle);
+    std::shared_ptr<BlobConverter> conv;
+    std::shared_ptr<Mat> mat;
+    Status st = io_objects(h, name, false, host, n, kind, &conv, &mat);
+    void* q = nullptr;
+    if (st == TNN_OK) st = h->inst->GetCommandQueue(&q);
+    if (st == TNN_OK) st = blocking ? conv->ConvertToMat(*mat, MatConvertParam(), q)
+                                    : conv->ConvertToMatAsync(*mat, MatConvertParam(), q);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st ? (int)st : -1; }
+    return 0;
+}
+
+TNNC_API int tnnc_forward_async(void* handle) {
+    Handle* h = static_cast<Handle*>(handle);
+    Status st = h->inst->ForwardAsync(nullptr);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st; }
+    return 0;
+}
+
+TNNC_API void* tnnc_command_queue(void* handle) {
+    Handle* h = static_cast<Handle*>(handle);
+    void* q = nullptr;
+    return h->inst->GetCommandQueue(&q) == TNN_OK ? q : nullptr;
+}
+
+// The whole loop, natively, over `n_handles` instances taken round-robin (1 = exactly the reference benchmark's loop;
+// 2 = the usual serving arrangement, two instances of one model on one GPU, so that one instance's copies run while
+// the other computes).  Per step: every input of the instance whose turn it is goes ConvertFromMatAsync, then
+// ForwardAsync; the instance that was issued n_handles - 1 steps earlier is drained with a blocking ConvertToMat of
+// every output.  inputs / outputs: n_handles x n_in (n_out) records, instance-major.  Runs `warmup` untimed steps, then
+// `steps` timed ones (drained to the last); returns the wall time of the timed steps in milliseconds, negative on error.
+struct TnncIo {
+    const char* name;
+    void* host;
+    int64_t n;
+    int32_t kind;
+    int32_t reserved_;
+};
+
+TNNC_API double tnnc_run_pipeline(void** handles, int n_handles, const TnncIo* inputs, int n_in, const TnncIo* outputs,
+                                  int n_out, int warmup, int steps) {
+    if (!handles || n_handles <= 0 || n_in <= 0 || n_out <= 0 || steps <= 0) return -1.0;
+    std::vector<Handle*> hs(n_handles);
+    for (int k = 0; k < n_handles; ++k) hs[k] = static_cast<Handle*>(handles[k]);
+    struct Bound { std::shared_ptr<BlobConverter> conv; std::shared_ptr<Mat> mat; };
+    std::vector<std::vector<Bound>> in(n_handles), out(n_handles);
+    std::vector<void*> queue(n_handles, nullptr);
+    for (int k = 0; k < n_handles; ++k) {
+        if (hs[k]->inst->GetCommandQueue(&queue[k]) != TNN_OK) return -2.0;
+        for (int i = 0; i < n_in; ++i) {
+            const TnncIo& io = inputs[k * n_in + i];
+            Bound b;
+            Status st = io_objects(hs[k], io.name, true, io.host, io.n, io.kind, &b.conv, &b.mat);
+            if (st != TNN_OK) { hs[k]->last_error = st.description(); return -3.0; }
+            in[k].push_back(b);
+        }
+        for (int i = 0; i < n_out; ++i) {
+            const TnncIo& io = outputs[k * n_out + i];
+            Bound b;
+            Status st = io_objects(hs[k], io.name, false, io.host, io.n, io.kind, &b.conv, &b.mat);
+            if (st != TNN_OK) { hs[k]->last_error = st.description(); return -3.0; }
+            out[k].push_back(b);
+        }
+    }
+    MatConvertParam param;
+    auto issue = [&](int k) -> bool {
+        for (auto& b : in[k])
+            if (b.conv->ConvertFromMatAsync(*b.mat, param, queue[k]) != TNN_OK) return false;
+        Status st = hs[k]->inst->ForwardAsync(nullptr);
+        if (st != TNN_OK) { hs[k]->last_error = st.description(); return false; }
+        return true;
+    };
+    auto drain = [&](int k) -> bool {
+        for (auto& b : out[k]) {
+            Status st = b.conv->ConvertToMat(*b.mat, param, queue[k]);
+            if (st != TNN_OK) { hs[k]->last_error = st.description(); return false; }
+        }
+        return true;
+    };
+    auto run = [&](int count) -> bool {
+        for (int s = 0; s < count; ++s) {
+            if (!issue(s % n_handles)) return false;
+            if (s >= n_handles - 1 && !drain((s - (n_handles - 1)) % n_handles)) return false;
+        }
+        for (int s = count > n_handles - 1 ? count - (n_handles - 1) : 0; s < count; ++s)
+            if (!drain(s % n_handles)) return false;
+        return true;
+    };
+    if (warmup > 0 && !run(warmup)) return -4.0;
+    auto t0 = std::chrono::steady_clock::now();
+    if (!run(steps)) return -5.0;
+    auto t1 = std::chrono::steady_clock::now();
+    return std::chrono::duration<double, std::milli>(t1 - t0).count();
 }
 
 TNNC_API int tnnc_forward(void* handle) {

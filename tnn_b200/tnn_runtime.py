@@ -22,6 +22,29 @@ PRECISION_AUTO, PRECISION_NORMAL, PRECISION_HIGH, PRECISION_LOW = -1, 0, 1, 2
 
 _state = {}
 
+MAT_F32, MAT_F16, MAT_BF16, MAT_I32 = 0, 1, 2, 3
+_KIND_OF = {np.dtype(np.float32): MAT_F32, np.dtype(np.float16): MAT_F16, np.dtype(np.int32): MAT_I32}
+
+
+class TnncIo(ctypes.Structure):
+    """One input or output of tnnc_run_pipeline: blob name, host buffer, element count, Mat kind."""
+    _fields_ = [("name", ctypes.c_char_p), ("host", ctypes.c_void_p), ("n", ctypes.c_int64), ("kind", ctypes.c_int32),
+                ("reserved_", ctypes.c_int32)]
+
+
+def _loaded_libtnn():
+    """Path of a libTNN.so this process has already mapped, or None.  A process must hold ONE copy of the framework:
+    its registries (devices, layers, accs, passes) are static objects, and a second copy would own a second set."""
+    try:
+        with open("/proc/self/maps") as fh:
+            for line in fh:
+                path = line.rstrip("\n").rsplit(" ", 1)[-1]
+                if path.endswith("/libTNN.so"):
+                    return path
+    except OSError:
+        pass
+    return None
+
 
 def available():
     return all(os.path.exists(p) for p in (LIBTNN, SHIM, PLUGIN, capi.LIB_PATH))
@@ -33,7 +56,7 @@ def load():
         for p in (LIBTNN, capi.LIB_PATH, PLUGIN, SHIM):
             if not os.path.exists(p):
                 raise RuntimeError("missing %s (build with tnn_b200/tnn_plugin/build_plugin.py)" % p)
-        ctypes.CDLL(LIBTNN, mode=ctypes.RTLD_GLOBAL)
+        ctypes.CDLL(_loaded_libtnn() or LIBTNN, mode=ctypes.RTLD_GLOBAL)
         ctypes.CDLL(capi.LIB_PATH, mode=ctypes.RTLD_GLOBAL)
         plugin = ctypes.CDLL(PLUGIN, mode=ctypes.RTLD_GLOBAL)
         shim = ctypes.CDLL(SHIM)
@@ -58,6 +81,23 @@ def load():
         shim.tnnc_get_output.restype = ctypes.c_int64
         shim.tnnc_get_output.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64,
                                          ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        shim.tnnc_from_mat_async.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+        shim.tnnc_to_mat.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                     ctypes.c_int]
+        shim.tnnc_forward_async.argtypes = [ctypes.c_void_p]
+        shim.tnnc_command_queue.restype = ctypes.c_void_p
+        shim.tnnc_command_queue.argtypes = [ctypes.c_void_p]
+        shim.tnnc_run_pipeline.restype = ctypes.c_double
+        shim.tnnc_run_pipeline.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(TnncIo),
+                                           ctypes.c_int, ctypes.POINTER(TnncIo), ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        plugin.tnnb200_arena_stats.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint64)]
+        plugin.tnnb200_release_cached_memory.restype = ctypes.c_uint64
+        plugin.tnnb200_release_cached_memory.argtypes = [ctypes.c_int]
+        plugin.tnnb200_inject_allocation_failure.argtypes = [ctypes.c_int, ctypes.c_int]
+        plugin.tnnb200_graph_counters.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint64)]
+        plugin.tnnb200_host_alloc.restype = ctypes.c_void_p
+        plugin.tnnb200_host_alloc.argtypes = [ctypes.c_size_t]
+        plugin.tnnb200_host_free.argtypes = [ctypes.c_void_p]
         plugin.tnnb200_fuse_and_pack.restype = ctypes.c_int
         plugin.tnnb200_fuse_and_pack.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
                                                  ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p]
@@ -91,6 +131,88 @@ def fuse_and_pack(proto_path, model_path, out_proto_path, out_model_path, precis
     if n < 0:
         raise RuntimeError("tnnb200_fuse_and_pack failed: %d" % n)
     return n
+
+
+ARENA_KEYS = ("driver_allocations", "driver_frees", "bytes_reserved", "bytes_in_use", "live_blocks", "requests",
+              "pinned_allocations", "pinned_bytes_reserved")
+
+
+def arena_stats(device_id=0):
+    """Counters of the plug-in's device-memory arena on one GPU (tnnb200_arena_stats) as a dict."""
+    _, plugin = load()
+    out = (ctypes.c_uint64 * 8)()
+    plugin.tnnb200_arena_stats(device_id, out)
+    return dict(zip(ARENA_KEYS, (int(v) for v in out)))
+
+
+def release_cached_memory(device_id=-1):
+    _, plugin = load()
+    return int(plugin.tnnb200_release_cached_memory(device_id))
+
+
+def inject_allocation_failure(skip, count):
+    """Host-side fault injection: after `skip` more successful device allocations of the plug-in, the next `count`
+    report out-of-memory (count = 0 switches it off)."""
+    _, plugin = load()
+    plugin.tnnb200_inject_allocation_failure(int(skip), int(count))
+
+
+class PinnedArray:
+    """A numpy array over page-locked host memory from the plug-in (tnnb200_host_alloc): Mats that wrap it are copied
+    by DMA directly, without a staging copy on the host."""
+
+    def __init__(self, shape, dtype):
+        _, self._plugin = load()
+        self.nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        self.ptr = self._plugin.tnnb200_host_alloc(max(self.nbytes, 1))
+        if not self.ptr:
+            raise MemoryError("tnnb200_host_alloc(%d) failed" % self.nbytes)
+        buf = (ctypes.c_char * self.nbytes).from_address(self.ptr)
+        self.array = np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+    def free(self):
+        if getattr(self, "ptr", None):
+            self.array = None
+            self._plugin.tnnb200_host_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def run_pipeline(instances, inputs, outputs, warmup, steps):
+    """The reference benchmark's loop (ConvertFromMatAsync of every input -> ForwardAsync -> blocking ConvertToMat of
+    every output, test/test.cc:125-152) run natively over `instances` taken round-robin (tnnc_run_pipeline).
+    inputs / outputs: per instance a list of (blob name, numpy array); the arrays are the host buffers themselves
+    (pageable numpy memory or PinnedArray.array).  Returns the wall time of the `steps` timed steps in seconds."""
+    shim, _ = load()
+    n = len(instances)
+    assert len(inputs) == n and len(outputs) == n
+    n_in, n_out = len(inputs[0]), len(outputs[0])
+    keep = []
+
+    def records(per_inst, width):
+        arr = (TnncIo * (n * width))()
+        for k, ios in enumerate(per_inst):
+            assert len(ios) == width
+            for i, (name, a) in enumerate(ios):
+                assert a.flags["C_CONTIGUOUS"]
+                nm = name.encode()
+                keep.append(nm)
+                r = arr[k * width + i]
+                r.name, r.host, r.n, r.kind = nm, a.ctypes.data, a.size, _KIND_OF[a.dtype]
+        return arr
+
+    ins, outs = records(inputs, n_in), records(outputs, n_out)
+    hs = (ctypes.c_void_p * n)(*[inst.h for inst in instances])
+    ms = shim.tnnc_run_pipeline(hs, n, ins, n_in, outs, n_out, int(warmup), int(steps))
+    if ms < 0:
+        raise RuntimeError("tnnc_run_pipeline failed (%g): %s" % (
+            ms, "; ".join(shim.tnnc_last_error(i.h).decode() for i in instances)))
+    return ms / 1e3
 
 
 class Instance:
@@ -163,6 +285,34 @@ class Instance:
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
+
+    # ---- the caller-driven conversion path (BlobConverter + ForwardAsync, as the reference's benchmark uses them)
+    def from_mat_async(self, name, arr):
+        """ConvertFromMatAsync of a host array (float32 / float16 / int32; the array itself is the Mat's memory)."""
+        assert arr.flags["C_CONTIGUOUS"]
+        self._check(self.shim.tnnc_from_mat_async(self.h, name.encode(), arr.ctypes.data, arr.size, _KIND_OF[arr.dtype]),
+                    "ConvertFromMatAsync(%s)" % name)
+
+    def forward_async(self):
+        self._check(self.shim.tnnc_forward_async(self.h), "ForwardAsync")
+
+    def to_mat(self, name, arr, blocking=True):
+        """ConvertToMat (blocking) or ConvertToMatAsync into a host array; with blocking=False the array is complete
+        once the instance's command queue has been synchronised (a later blocking conversion does that)."""
+        assert arr.flags["C_CONTIGUOUS"] and arr.flags["WRITEABLE"]
+        self._check(self.shim.tnnc_to_mat(self.h, name.encode(), arr.ctypes.data, arr.size, _KIND_OF[arr.dtype],
+                                          1 if blocking else 0), "ConvertToMat(%s)" % name)
+
+    def command_queue(self):
+        return self.shim.tnnc_command_queue(self.h)
+
+    def graph_counters(self):
+        """{eager, captures, launches, failures} of the plug-in's CUDA-graph replay for this instance."""
+        _, plugin = load()
+        out = (ctypes.c_uint64 * 4)()
+        if plugin.tnnb200_graph_counters(ctypes.c_void_p(self.command_queue()), out) != 0:
+            raise RuntimeError("instance is not served by the tnn_b200 plug-in")
+        return dict(zip(("eager", "captures", "launches", "failures"), (int(v) for v in out)))
 
     def time_forward(self, warmup, iters):
         ms = self.shim.tnnc_time_forward(self.h, warmup, iters)
