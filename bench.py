@@ -3,15 +3,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One step = one Forward of the fused 12-layer encoder over one batch (fp32 activations in, fp16 fused region, fp32 out).
-Per GPU the batch is the benchmark's config 2 (64 sequences x 128 tokens); with N GPUs every rank runs its own batch
-(independent replicas, no collective on the data path), so `value` = N * 64 * K / max-over-ranks(device time).
+Workload: the benchmark's config 5 — a 12-layer BERT-base encoder over 1024 sequences x 128 tokens per step in total,
+split evenly over the N GPUs (1024 / N sequences per GPU; strong scaling; one process per GPU, batch-sharded
+replicas, no collective on the data path).  One step = one Forward of the fused encoder over a rank's batch through
+TNN's own Instance API on DEVICE_CUDA served by the tnn_b200 plug-in (fp32 activations in, fp16 fused region,
+fp32 out).
 
 Keys of the JSON line beyond the base contract:
+  value        inputs resident in the instance's blobs: K x Instance::ForwardAsync, CUDA events on the instance's
+               stream, the K-step block repeated until >= --min-seconds are measured, max over ranks
+  e2e          host to host through TNN's API: BlobConverter::ConvertFromMatAsync of the inputs (fp32 Mats in page-locked
+               memory) -> ForwardAsync -> ConvertToMat of the fp32 output every step, two instances per GPU in turn
+  e2e_pageable the same loop, one instance, pageable Mats;  e2e_half_io: half-precision Mats (half the bytes)
   roofline     the projection/FFN GEMM kernel (dominant): algorithmic FLOPs of its launches / their CUDA-event time
   cpu_baseline the reference's own DEVICE_X86 implementation timed on this host on a bounded sample (rank 0, N = 1)
-  e2e          the same metric with HOST buffers: pinned fp32 input -> H2D -> Forward -> D2H of the fp32 output per step
-  e2e_half_io  the same with half-precision host buffers (half the bytes, no conversions): informational
+  parity       the timed workload's first Forward against the CPU oracle (first 2 sequences)
 `--impl reference` times the reference's CPU implementation of the same path with all host cores.
 """
 import argparse
@@ -28,45 +34,8 @@ if ROOT not in sys.path:
 
 METRIC = "bert_base_seq128_sequences_per_s"
 UNIT = "sequences/s"
-BATCH_PER_GPU = 64
+TOTAL_BATCH = 1024      # config 5: 1024 sequences per step in total, split evenly over the GPUs
 SEQ = 128
-
-
-def tnn_plugin_seq_per_s(wl, warmup=5, iters=30):
-    """The same workload through the drop-in path: the unmodified reference framework (oracle/_ref/libTNN.so) with the
-    tnn_b200 plug-in serving DEVICE_CUDA — Instance::Forward over the fused graph, fp32 blobs at both ends.  Returns a
-    dict (Forward-only and host-to-host figures) or None when the reference build is not present."""
-    try:
-        from tnn_b200 import model_synth, tnn_runtime
-        if not tnn_runtime.available():
-            return None
-        import shutil
-        import tempfile
-        d = tempfile.mkdtemp(prefix="tnnb200_bench_")
-        try:
-            proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
-            model_synth.write_tnn_model(wl, proto, model)
-            inst = tnn_runtime.Instance(proto, model, device=tnn_runtime.DEVICE_CUDA)
-            inst.set_input("x", wl.x)
-            inst.set_input("mask", wl.mask_add)
-            ms = inst.time_forward(warmup, iters)               # Instance::Forward incl. its stream synchronise
-            n = min(iters, 10)
-            t0 = time.perf_counter()
-            for _ in range(n):
-                inst.set_input("x", wl.x)                       # host Mat -> device blob
-                inst.forward()
-                inst.get_output()                               # device blob -> host Mat
-            host_ms = (time.perf_counter() - t0) / n * 1e3
-            inst.close()
-        finally:
-            shutil.rmtree(d, ignore_errors=True)
-        B = wl.x.shape[0]
-        return {"forward_value": B / ms * 1e3, "forward_ms": ms, "host_to_host_value": B / host_ms * 1e3,
-                "host_to_host_ms": host_ms, "unit": UNIT,
-                "note": "TNN Instance::Forward on DEVICE_CUDA served by the plug-in (fused graph, eager launches, "
-                        "blocking Forward); host_to_host adds SetInputMat/GetOutputMat with pageable fp32 host Mats"}
-    except Exception as e:   # the drop-in measurement is supplementary: never fail the bench line over it
-        return {"error": str(e)[:300]}
 
 
 def measured_peaks():
@@ -198,10 +167,11 @@ def run_reference_arm(args):
     value, kind, desc = cpu_reference_seq_per_s(2, instances, layers=12, warmup=1, iters=steps)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": 1, "ms_per_step": 1e3 * instances * 2 / value, "higher_is_better": True, "scaling": "weak",
+        "warmup": 1, "ms_per_step": 1e3 * instances * 2 / value, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BERT-base 12-layer encoder, S=128, fp32, reference DEVICE_X86 on host cores; "
-                               "each step = %d instances x 2 sequences" % instances},
+        "config": {"workload": "config 5: BERT-base 12-layer encoder, S=128, fp32, reference DEVICE_X86 on the host "
+                               "cores; each step = a bounded sample of the 1024-sequence batch: %d instances x 2 "
+                               "sequences" % instances},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": instances, "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
@@ -219,11 +189,36 @@ def reduce_max_over_ranks(t, world):
 
 
 # ------------------------------------------------------------------------------------------------ our arm
+class PluginReplica:
+    """One or two TNN instances of the encoder on one GPU, DEVICE_CUDA served by the plug-in: the drop-in path an
+    unchanged TNN application takes.  Two instances are the serving arrangement: while one computes, the other's
+    input is on its way to the device and its previous output on its way back."""
+
+    def __init__(self, wl, device_id, instances, input_dtype=None):
+        import shutil
+        import tempfile
+        from tnn_b200 import model_synth, tnn_runtime
+        self.rt = tnn_runtime
+        self.dir = tempfile.mkdtemp(prefix="tnnb200_bench_")
+        try:
+            proto, model = os.path.join(self.dir, "m.tnnproto"), os.path.join(self.dir, "m.tnnmodel")
+            model_synth.write_tnn_model(wl, proto, model, input_dtype=input_dtype)
+            self.insts = [tnn_runtime.Instance(proto, model, device=tnn_runtime.DEVICE_CUDA, device_id=device_id)
+                          for _ in range(instances)]
+        finally:
+            shutil.rmtree(self.dir, ignore_errors=True)   # the files are read at Init; nothing refers to them later
+
+    def close(self):
+        for i in self.insts:
+            i.close()
+        self.insts = []
+
+
 def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from tnn_b200 import capi, model_synth, ops
+    from tnn_b200 import capi, model_synth, ops, tnn_runtime
     from tnn_b200.encoder import Encoder
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -237,6 +232,9 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()  # fail loudly here if the CUDA library is missing
+    if not tnn_runtime.available():
+        raise SystemExit("bench.py needs the TNN host framework and the plug-in (tnn_b200/host, tnn_b200/lib): "
+                         "the benchmark runs through TNN's own Instance API")
 
     # ---- the benchmark's standalone attention sweep (16 heads x d64, batch 16, S = 512/1024/2048, all-ones mask).
     # A kernel timed alone, so it runs first, before the long loops bring the GPU to its power cap (the measured
@@ -264,30 +262,148 @@ def run_ours(args):
                                     "frac_of_tensor_peak": round(fl_ / ms_ / 1e9 / peaks["tflops"], 4)})
             del qkv_, out_
 
-    B = args.batch
+    # ---- the workload: config 5 — BERT-base, 1024 sequences x 128 tokens in total, split evenly over the GPUs
+    total = args.total_batch
+    if total % world:
+        raise SystemExit("--total-batch must be a multiple of the number of GPUs")
+    B = total // world
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
-    enc = Encoder.from_workload(wl, torch.float16, dev, fold_layernorm=args.fold_layernorm)
-    x_dev = torch.from_numpy(wl.x).to(dev)
-    mask_dev = torch.from_numpy(wl.mask_add.reshape(B, SEQ)).to(dev).contiguous()
-    kv_len = ops.mask_to_kv_len(mask_dev)
-    hidden = torch.empty((B, SEQ, cfg.hidden), dtype=torch.float16, device=dev)
-    out_dev = torch.empty((B, SEQ, cfg.hidden), dtype=torch.float32, device=dev)
-
-    def step_resident():
-        ops.convert(x_dev, torch.float16, out=hidden)
-        enc.forward_hidden(hidden, mask_dev, kv_len)
-        ops.convert(hidden, torch.float32, out=out_dev)
+    H, F, L = cfg.hidden, cfg.ffn, len(wl.weights)
+    tokens = B * SEQ
+    mask4 = np.ascontiguousarray(wl.mask_add.reshape(B, 1, 1, SEQ))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    replica = PluginReplica(wl, local, instances=2)
+    insts = replica.insts
+    streams = [torch.cuda.ExternalStream(i.command_queue(), device=dev) for i in insts]
+
+    # ---- one-step parity check of the timed workload (first 2 sequences against the CPU oracle), which is also the
+    # layer-by-layer warm-up Forward of every instance
+    n0 = capi.launch_count()
+    insts[0].set_input("x", wl.x)
+    insts[0].set_input("mask", mask4)
+    insts[0].forward()
+    launches_per_step = capi.launch_count() - n0          # kernels of one Forward (conversions of the two Mats included)
+    y_first = insts[0].get_output()
+    parity = None
+    if rank == 0:
+        from oracle import bert_oracle
+        sub = model_synth.Workload(wl.cfg, wl.weights, wl.x[:2], wl.lengths[:2], wl.mask_add[:2], wl.meta)
+        want = bert_oracle.encoder_forward(sub)
+        err = float(np.abs(y_first[:2] - want).max())
+        parity = {"max_abs_vs_oracle_first_2_sequences": err, "bound": 2e-2, "ok": bool(err <= 2e-2)}
+        if not parity["ok"]:
+            raise SystemExit("parity check of the timed workload failed: %g" % err)
+    for inst in insts[1:]:
+        inst.set_input("x", wl.x)
+        inst.set_input("mask", mask4)
+        inst.forward()
+    for _ in range(max(3, args.warmup)):                   # graph capture happens on the first of these
+        for inst in insts:
+            inst.forward()
+    graph_state = insts[0].graph_counters()
+    barrier()
+
+    # ---- timed region: inputs resident in the instance's blobs, `steps` x ForwardAsync, CUDA events on the
+    # instance's own stream; the block is repeated until at least `--min-seconds` of device time have been measured
+    sampler = ClockSampler(local)
+    sampler.start()
+    block_ms = []
+    st0 = streams[0]
+    while True:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(st0)
+        for _ in range(args.steps):
+            insts[0].forward_async()
+        e1.record(st0)
+        barrier()
+        block_ms.append(e0.elapsed_time(e1))
+        stop = torch.tensor([1.0 if sum(block_ms) >= args.min_seconds * 1e3 or len(block_ms) >= 64 else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(stop, op=dist.ReduceOp.MIN)    # every rank runs the same number of blocks
+        if float(stop[0]) > 0:
+            break
+    blocks = len(block_ms)
+    ms_total = sum(block_ms)
+    clocks = sampler.stop()
+    if capi.device_status() != capi.OK:
+        raise SystemExit("device status word set: a bounded wait ran out")
+
+    # ---- e2e: the same metric host to host through TNN's API — per step ConvertFromMatAsync of the inputs (fp32 Mats
+    # in page-locked host memory), ForwardAsync, ConvertToMat of the fp32 output; two instances in turn
+    def pinned(a):
+        p = tnn_runtime.PinnedArray(a.shape, a.dtype)
+        p.array[...] = a
+        return p
+
+    def e2e_run(replica_insts, x_arr, out_dtype, pin, steps):
+        keep, ins, outs = [], [], []
+        for _ in replica_insts:
+            if pin:
+                px, pm, po = pinned(x_arr), pinned(mask4), pinned(np.zeros((B, SEQ, H), out_dtype))
+                keep += [px, pm, po]
+                ins.append([("x", px.array), ("mask", pm.array)])
+                outs.append([("", po.array)])
+            else:
+                ins.append([("x", np.array(x_arr, copy=True)), ("mask", np.array(mask4, copy=True))])
+                outs.append([("", np.zeros((B, SEQ, H), out_dtype))])
+        barrier()
+        secs = tnn_runtime.run_pipeline(replica_insts, ins, outs, warmup=min(4, steps), steps=steps)
+        barrier()
+        ok = bool(np.array_equal(outs[0][0][1].astype(np.float32), y_first.astype(out_dtype).astype(np.float32))) \
+            if out_dtype == np.float32 else None
+        h2d = x_arr.nbytes + mask4.nbytes
+        d2h = outs[0][0][1].nbytes
+        for p in keep:
+            p.free()
+        return secs, h2d, d2h, ok
+
+    e2e_steps = max(args.steps, int(np.ceil(args.min_seconds * 1e3 / (ms_total / (blocks * args.steps)))))
+    e2e_s, h2d, d2h, e2e_same = e2e_run(insts, wl.x, np.float32, True, e2e_steps)
+    pageable_steps = max(4, min(e2e_steps, args.steps))
+    pageable_s, _, _, _ = e2e_run(insts[:1], wl.x, np.float32, False, pageable_steps)
+    replica.close()
+
+    # the same with half-precision Mats (the model declares a half input; RESERVED_FP16_TEST Mats): half the bytes
+    half_s = None
+    if not args.no_half_io:
+        rep16 = PluginReplica(wl, local, instances=2, input_dtype="half")
+        x16 = wl.x.astype(np.float16)
+        for inst in rep16.insts:
+            inst.set_input_half("x", x16)
+            inst.set_input("mask", mask4)
+            inst.forward()
+            inst.forward()
+        half_s, h2d16, d2h16, _ = e2e_run(rep16.insts, x16, np.float16, True, e2e_steps)
+        rep16.close()
+
+    # ---- roofline of the dominant kernel (the GEMM): the step's GEMM launches alone, in their order, with every
+    # layer's own weights (170 MB per pass, more than L2) and the step's activation buffers, through the C ABI, replayed
+    # as a CUDA graph and timed with one event pair; plus an instrumented pass with an event pair around every launch
+    enc = Encoder.from_workload(wl, torch.float16, dev, fold_layernorm=False)
+    shapes = {"qkv": (tokens, 3 * H, H), "out_proj": (tokens, H, H), "ffn1": (tokens, F, H), "ffn2": (tokens, H, F)}
+    qkv_b = torch.empty(tokens, 3 * H, device=dev, dtype=torch.float16)
+    ctx_b = torch.randn(tokens, H, device=dev).to(torch.float16)
+    t_b = torch.empty(tokens, H, device=dev, dtype=torch.float16)
+    f_b = torch.empty(tokens, F, device=dev, dtype=torch.float16)
+    h_b = torch.randn(tokens, H, device=dev).to(torch.float16)
+    mask_dev = torch.zeros(B, SEQ, device=dev)
+    kv_len = ops.mask_to_kv_len(mask_dev)
+
+    def gemm_only_step():
+        for Lw in enc.layers:
+            ops.linear(h_b, Lw["w_qkv"], Lw["b_qkv"], out=qkv_b)
+            ops.linear(ctx_b, Lw["w_o"], Lw["b_o"], residual=h_b, epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b)
+            ops.linear(h_b, Lw["w_ffn1"], Lw["b_ffn1"], epilogue=ops.EPI_BIAS_GELU, out=f_b)
+            ops.linear(f_b, Lw["w_ffn2"], Lw["b_ffn2"], residual=h_b, epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b)
+
     def capture(fn):
-        """One Forward as a CUDA graph (the launch sequence is fixed: same buffers, same kernels every step)."""
-        if args.no_graph:
-            return None
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -298,121 +414,27 @@ def run_ours(args):
             torch.cuda.synchronize()
             return None
 
-    for _ in range(3):
-        step_resident()
+    for _ in range(2):
+        gemm_only_step()
     torch.cuda.synchronize()
-    n0 = capi.launch_count()
-    step_resident()
-    launches_per_step = capi.launch_count() - n0
-    graph = capture(step_resident)
-    run_step = graph.replay if graph is not None else step_resident
-    for _ in range(max(3, args.warmup)):
-        run_step()
-    barrier()
-
-    # ---- timed region: device-resident inputs
-    sampler = ClockSampler(local)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = launches_per_step * args.steps      # kernels of this library executed in the timed region
-    clocks = sampler.stop()
-    if capi.device_status() != capi.OK:
-        raise SystemExit("device status word set: a bounded wait ran out")
-
-    # ---- e2e: host buffers, copies inside the timed region (double-buffered so copies overlap the previous step)
-    x_host = torch.from_numpy(wl.x).pin_memory()
-    out_host = [torch.empty((B, SEQ, cfg.hidden), dtype=torch.float32).pin_memory() for _ in range(2)]
-    x_in = [torch.empty_like(x_dev) for _ in range(2)]
-    o_out = [torch.empty_like(out_dev) for _ in range(2)]
-    hid = [torch.empty_like(hidden) for _ in range(2)]
-    s_copy_in, s_copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    s_main = torch.cuda.current_stream(dev)
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_done = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]
-
-    def compute_on(b):
-        ops.convert(x_in[b], torch.float16, out=hid[b])
-        enc.forward_hidden(hid[b], mask_dev, kv_len)
-        ops.convert(hid[b], torch.float32, out=o_out[b])
-
-    e2e_graphs = [capture(lambda b=b: compute_on(b)) for b in range(2)]
-
-    def e2e_loop(n):
-        for i in range(n):
-            b = i & 1
-            with torch.cuda.stream(s_copy_in):
-                s_copy_in.wait_event(ev_free[b])           # the compute that last read x_in[b] is done
-                x_in[b].copy_(x_host, non_blocking=True)
-                ev_in[b].record(s_copy_in)
-            s_main.wait_event(ev_in[b])
-            s_main.wait_event(ev_out[b])                    # o_out[b] has been drained to the host
-            if e2e_graphs[b] is not None:
-                e2e_graphs[b].replay()
-            else:
-                compute_on(b)
-            ev_free[b].record(s_main)
-            ev_done[b].record(s_main)
-            with torch.cuda.stream(s_copy_out):
-                s_copy_out.wait_event(ev_done[b])
-                out_host[b].copy_(o_out[b], non_blocking=True)
-                ev_out[b].record(s_copy_out)
-
-    e2e_loop(4)
-    barrier()
-    t0 = time.perf_counter()
-    e2e_loop(args.steps)
+    gemm_graph = capture(gemm_only_step)
+    run_gemms = gemm_graph.replay if gemm_graph is not None else gemm_only_step
+    for _ in range(2):
+        run_gemms()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, min(args.steps, 20))
+    g0.record()
+    for _ in range(reps):
+        run_gemms()
+    g1.record()
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    barrier()
-    h2d = x_host.numel() * 4
-    d2h = out_host[0].numel() * 4
+    gemm_launches_per_pass = 4 * L
+    gemm_pass_ms = g0.elapsed_time(g1) / reps
+    flops_per_pass = sum(2.0 * m * n * kk for (m, n, kk) in shapes.values()) * L
+    achieved = flops_per_pass / gemm_pass_ms / 1e9
 
-    # ---- the same with half-precision host buffers (RESERVED_FP16_TEST Mats in the plug-in): half the bytes over PCIe,
-    # no conversion launches; the copies go straight into / out of the encoder's hidden-state buffer
-    x_host16 = torch.from_numpy(wl.x.astype(np.float16)).pin_memory()
-    out_host16 = [torch.empty((B, SEQ, cfg.hidden), dtype=torch.float16).pin_memory() for _ in range(2)]
-    half_graphs = [capture(lambda b=b: enc.forward_hidden(hid[b], mask_dev, kv_len)) for b in range(2)]
-
-    def half_loop(n):
-        for i in range(n):
-            b = i & 1
-            with torch.cuda.stream(s_copy_in):
-                s_copy_in.wait_event(ev_out[b])            # hid[b]'s previous result has been drained to the host
-                hid[b].view(B, SEQ, cfg.hidden).copy_(x_host16, non_blocking=True)
-                ev_in[b].record(s_copy_in)
-            s_main.wait_event(ev_in[b])
-            if half_graphs[b] is not None:
-                half_graphs[b].replay()
-            else:
-                enc.forward_hidden(hid[b], mask_dev, kv_len)
-            ev_done[b].record(s_main)
-            with torch.cuda.stream(s_copy_out):
-                s_copy_out.wait_event(ev_done[b])
-                out_host16[b].copy_(hid[b].view(B, SEQ, cfg.hidden), non_blocking=True)
-                ev_out[b].record(s_copy_out)
-
-    torch.cuda.synchronize()
-    half_loop(4)
-    barrier()
-    t0 = time.perf_counter()
-    half_loop(args.steps)
-    torch.cuda.synchronize()
-    e2e_half_s = time.perf_counter() - t0
-    barrier()
-
-    # ---- roofline of the dominant kernel (the GEMM): an instrumented pass with an event pair around every launch
-    tokens = B * SEQ
-    H, F = cfg.hidden, cfg.ffn
-    shapes = {"qkv": (tokens, 3 * H, H), "out_proj": (tokens, H, H), "ffn1": (tokens, F, H), "ffn2": (tokens, H, F)}
+    # per-kernel times: one event pair per launch, the stream held by a spin kernel while the host enqueues, so that
+    # every pair spans exactly one kernel on the device (plus 3-6 us of event handling)
     ev_pairs = {k: [] for k in list(shapes) + ["attention", "layernorm"]}
 
     def timed(name, fn):
@@ -423,127 +445,93 @@ def run_ours(args):
         ev_pairs[name].append((a, b2))
         return r
 
-    def instrumented_step():
-        h = ops.convert(x_dev, torch.float16, out=hidden)
-        for L in enc.layers:
-            qkv = timed("qkv", lambda: ops.linear(h, L["w_qkv"], L["b_qkv"]))
-            ctx = timed("attention", lambda: ops.attention(qkv, cfg.heads, mask_dev, kv_len))
-            t = timed("out_proj", lambda: ops.linear(ctx, L["w_o"], L["b_o"], residual=h,
-                                                     epilogue=ops.EPI_BIAS_RESIDUAL))
-            a = timed("layernorm", lambda: ops.add_layernorm(t, L["ln1_g"], L["ln1_b"], cfg.ln_eps))
-            f1 = timed("ffn1", lambda: ops.linear(a, L["w_ffn1"], L["b_ffn1"], epilogue=ops.EPI_BIAS_GELU))
-            t2 = timed("ffn2", lambda: ops.linear(f1, L["w_ffn2"], L["b_ffn2"], residual=a,
-                                                  epilogue=ops.EPI_BIAS_RESIDUAL))
-            h = timed("layernorm", lambda: ops.add_layernorm(t2, L["ln2_g"], L["ln2_b"], cfg.ln_eps))
+    def instrumented_layers(n_layers):
+        for Lw in enc.layers[:n_layers]:
+            timed("qkv", lambda: ops.linear(h_b, Lw["w_qkv"], Lw["b_qkv"], out=qkv_b))
+            timed("attention", lambda: ops.attention(qkv_b.view(B, SEQ, 3 * H), cfg.heads, mask_dev, kv_len,
+                                                     out=ctx_b.view(B, SEQ, H)))
+            timed("out_proj", lambda: ops.linear(ctx_b, Lw["w_o"], Lw["b_o"], residual=h_b,
+                                                 epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b))
+            timed("layernorm", lambda: ops.add_layernorm(t_b, Lw["ln1_g"], Lw["ln1_b"], cfg.ln_eps, out=ctx_b))
+            timed("ffn1", lambda: ops.linear(ctx_b, Lw["w_ffn1"], Lw["b_ffn1"], epilogue=ops.EPI_BIAS_GELU, out=f_b))
+            timed("ffn2", lambda: ops.linear(f_b, Lw["w_ffn2"], Lw["b_ffn2"], residual=ctx_b,
+                                             epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b))
+            timed("layernorm", lambda: ops.add_layernorm(t_b, Lw["ln2_g"], Lw["ln2_b"], cfg.ln_eps, out=ctx_b))
 
-    # The host needs ~20 us per launch-plus-two-events, the kernels 10-35 us: issued naively, the event pairs would time
-    # the host.  Each instrumented step is therefore queued behind a spin kernel that holds the stream for a few
-    # milliseconds, so that all its launches and events are already in the queue when the GPU reaches them and every
-    # event pair spans exactly one kernel on the device (launch gap included).
-    def hold_stream():
-        torch.cuda._sleep(int(12e6))          # ~6 ms of GPU clock cycles
-
-    for _ in range(2):
-        instrumented_step()
+    instrumented_layers(2)
     torch.cuda.synchronize()
     for k in ev_pairs:
         ev_pairs[k].clear()
-    for _ in range(min(args.steps, 20)):
-        hold_stream()
-        instrumented_step()
+    for _ in range(3):
+        torch.cuda._sleep(int(12e6))          # ~6 ms of GPU clock cycles: holds the stream while the host enqueues
+        instrumented_layers(L)
         torch.cuda.synchronize()
     kernel_ms = {k: [a.elapsed_time(b2) for a, b2 in v] for k, v in ev_pairs.items()}
-    gemm_flops = gemm_ms = 0.0
     per_shape = {}
+    gemm_flops = gemm_ms = 0.0
     for k, (m, n, kk) in shapes.items():
         fl = 2.0 * m * n * kk
         tms = statistics.mean(kernel_ms[k])
         per_shape[k] = {"M": m, "N": n, "K": kk, "ms": round(tms, 4), "tflops": round(fl / tms / 1e9, 1)}
         gemm_flops += fl * len(kernel_ms[k])
         gemm_ms += sum(kernel_ms[k])
-    peaks = measured_peaks()
     achieved_bracketed = gemm_flops / gemm_ms / 1e9
-    n_gemm = sum(len(kernel_ms[k]) for k in shapes)
-
-    # The roofline figure itself: the step's GEMM launches alone, in their order, with every layer's own weights (170 MB
-    # per pass, more than L2) and the step's activation buffers, replayed as a CUDA graph and timed with one event
-    # pair.  (An event pair around every single launch adds 3-6 us of event handling to each 15-40 us kernel and
-    # switches off the overlap of consecutive launches; those bracketed figures are kept in `per_shape`.)
-    qkv_b = torch.empty(tokens, 3 * H, device=dev, dtype=torch.float16)
-    ctx_b = torch.randn(tokens, H, device=dev).to(torch.float16)
-    t_b = torch.empty(tokens, H, device=dev, dtype=torch.float16)
-    f_b = torch.empty(tokens, F, device=dev, dtype=torch.float16)
-    h_b = torch.randn(tokens, H, device=dev).to(torch.float16)
-
-    def gemm_only_step():
-        for L in enc.layers:
-            ops.linear(h_b, L["w_qkv"], L["b_qkv"], out=qkv_b)
-            ops.linear(ctx_b, L["w_o"], L["b_o"], residual=h_b, epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b)
-            ops.linear(h_b, L["w_ffn1"], L["b_ffn1"], epilogue=ops.EPI_BIAS_GELU, out=f_b)
-            ops.linear(f_b, L["w_ffn2"], L["b_ffn2"], residual=h_b, epilogue=ops.EPI_BIAS_RESIDUAL, out=t_b)
-
-    for _ in range(3):
-        gemm_only_step()
-    torch.cuda.synchronize()
-    gemm_graph = capture(gemm_only_step)
-    run_gemms = gemm_graph.replay if gemm_graph is not None else gemm_only_step
-    for _ in range(3):
-        run_gemms()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = min(args.steps, 50)
-    g0.record()
-    for _ in range(reps):
-        run_gemms()
-    g1.record()
-    torch.cuda.synchronize()
-    gemm_launches_per_pass = 4 * len(enc.layers)
-    gemm_pass_ms = g0.elapsed_time(g1) / reps
-    flops_per_pass = sum(2.0 * m * n * kk for (m, n, kk) in shapes.values()) * len(enc.layers)
-    achieved = flops_per_pass / gemm_pass_ms / 1e9
     attn_ms = statistics.mean(kernel_ms["attention"])
     attn_flops = 4.0 * SEQ * SEQ * 64 * cfg.heads * B
+    ln_ms = statistics.mean(kernel_ms["layernorm"])
 
-    # ---- reduce over ranks
-    ms_t = torch.tensor([ms_total, e2e_s * 1e3, e2e_half_s * 1e3], dtype=torch.float64, device=dev)
+    # ---- reduce over ranks (the job's time is the slowest rank's)
+    ms_t = torch.tensor([ms_total, e2e_s * 1e3, pageable_s * 1e3, (half_s or 0.0) * 1e3], dtype=torch.float64, device=dev)
     ms_t = reduce_max_over_ranks(ms_t, world)
-    ms_total_max, e2e_ms_max = float(ms_t[0]), float(ms_t[1])
-    seqs = world * B * args.steps
-    value = seqs / (ms_total_max / 1e3)
-    e2e_value = seqs / (e2e_ms_max / 1e3)
-    e2e_half_value = seqs / (float(ms_t[2]) / 1e3)
+    ms_total_max = float(ms_t[0])
+    timed_steps = blocks * args.steps
+    value = world * B * timed_steps / (ms_total_max / 1e3)
+    e2e_value = world * B * e2e_steps / (float(ms_t[1]) / 1e3)
+    pageable_value = world * B * pageable_steps / (float(ms_t[2]) / 1e3)
+    half_value = (world * B * e2e_steps / (float(ms_t[3]) / 1e3)) if half_s else None
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         v, kind, desc = cpu_reference_seq_per_s(8, 1, layers=12, warmup=1, iters=2)
         cpu_baseline = {"value": v, "unit": UNIT, "cores": 1, "kind": kind, "sample": desc}
 
-    tnn_plugin = None
-    if rank == 0 and world == 1 and not args.no_tnn_plugin:
-        tnn_plugin = tnn_plugin_seq_per_s(wl)
-
     if rank == 0:
-        flops_per_seq = model_synth.layer_flops(SEQ, H, F) * len(enc.layers)
+        flops_per_seq = model_synth.layer_flops(SEQ, H, F) * L
+        limiter = None
+        if e2e_value < 0.9 * value:
+            limiter = ("host <-> device copies: %.0f MB in + %.0f MB out per step per GPU over the host's DMA path, "
+                       "shared by %d GPU(s)" % (h2d / 1e6, d2h / 1e6, world))
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms_total_max / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "config 2: BERT-base 12-layer encoder, batch %d x seq %d per GPU, fp16 weights, "
-                                   "all sequences full length, fp32 activations in/out" % (B, SEQ),
-                       "batch_per_gpu": B, "seq_len": SEQ, "layers": len(enc.layers),
-                       "parallelism": "independent replicas, batch-sharded, no collective",
-                       "launch": "CUDA graph of one Forward" if graph is not None else "eager launches",
-                       "layernorm": "folded into the GEMM epilogues" if enc.fold else "separate kernels",
+            "warmup": max(3, args.warmup), "ms_per_step": ms_total_max / timed_steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "config 5: BERT-base 12-layer encoder, %d sequences x %d tokens in total split over "
+                                   "%d GPU(s) (%d per GPU per step), fp16 weights, all sequences full length, fp32 "
+                                   "activations in/out" % (total, SEQ, world, B),
+                       "total_batch": total, "batch_per_gpu": B, "seq_len": SEQ, "layers": L,
+                       "parallelism": "batch-sharded replicas (one TNN instance pair per GPU), no collective",
+                       "path": "TNN Instance::ForwardAsync on DEVICE_CUDA served by the tnn_b200 plug-in; CUDA-graph "
+                               "replay inside the plug-in: " + json.dumps(graph_state),
+                       "timed_steps": timed_steps, "blocks_of_steps": blocks,
                        "l2": "per-step working set (170 MB fp16 weights + activations) exceeds the 126 MB L2; "
                              "no explicit flush"},
             "clocks": clocks,
+            "parity": parity,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "pinned fp32 host buffers, copies double-buffered on side streams, wall clock"
+                    "steps": e2e_steps, "output_equals_blocking_forward": e2e_same, "limiter": limiter,
+                    "note": "through TNN's API with the plug-in: per step BlobConverter::ConvertFromMatAsync of x and the "
+                            "mask (fp32 Mats over page-locked host memory) -> Instance::ForwardAsync -> blocking "
+                            "BlobConverter::ConvertToMat of the fp32 output (the reference benchmark's loop, "
+                            "test/test.cc:125-152), two instances per GPU in turn; wall clock"
                             + ("" if numa is None else "; rank bound to the %d CPUs local to its GPU" % numa)},
-            "e2e_half_io": {"value": e2e_half_value, "unit": UNIT, "h2d_bytes_per_step": h2d // 2,
-                            "d2h_bytes_per_step": d2h // 2,
-                            "note": "the same with pinned fp16 host buffers (half-precision Mats): half the bytes, no "
-                                    "conversion launches; informational, the fp32 line above is the e2e number"},
-            "gpu_launches": launches,
+            "e2e_pageable": {"value": pageable_value, "unit": UNIT, "steps": pageable_steps,
+                             "note": "the same loop with ONE instance and pageable fp32 host Mats (what an unchanged "
+                                     "single-instance caller does): the converter stages through page-locked memory"},
+            "e2e_half_io": None if half_value is None else {
+                "value": half_value, "unit": UNIT, "h2d_bytes_per_step": h2d16, "d2h_bytes_per_step": d2h16,
+                "note": "the e2e loop with half-precision Mats (model input declared half): half the bytes, no "
+                        "conversion launches"},
+            "gpu_launches": launches_per_step * timed_steps,
             "roofline": {"bound": "tensor", "kernel": "linear_pair_kernel (projection/FFN GEMM, tcgen05 cta_group::2)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "peak_source": "of " + peaks["source"] + " (burst)",
@@ -560,21 +548,19 @@ def run_ours(args):
                          "per_shape_note": "one event pair around every single launch (stream held while the host "
                                            "enqueues): includes 3-6 us of event handling per launch",
                          "achieved_event_bracketed": achieved_bracketed,
-                         "traffic": ncu_traffic_per_launch(B, per_shape),
+                         "traffic": ncu_traffic_per_launch(tokens, per_shape),
                          "traffic_note": "DRAM read+write bytes per launch from one ncu capture per GEMM shape "
-                                         "(profiles/linear_pair_kernel_config2_shapes.md), averaged over the shapes "
-                                         "captured; equals the operand bytes, outputs stay in L2"},
+                                         "(profiles/), averaged over the shapes captured"},
             "attention_sweep": attention_sweep,
             "attention_sweep_note": "each point: 10 launches between one CUDA-event pair, timed before the long loops "
                                     "(burst clocks, as the measured tensor peak was)",
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
                                  "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
-            "layernorm_kernel": {"ms": statistics.mean(kernel_ms["layernorm"]),
-                                 "gbs": tokens * H * 2 * 2 / statistics.mean(kernel_ms["layernorm"]) / 1e6},
+            "layernorm_kernel": {"ms": ln_ms, "gbs": tokens * H * 2 * 2 / ln_ms / 1e6,
+                                 "frac_of_hbm_peak": tokens * H * 2 * 2 / ln_ms / 1e6 / peaks["hbm_gbs"]},
             "model_tflops": value * flops_per_seq / 1e12,
             "model_frac_of_tensor_peak": value * flops_per_seq / 1e12 / peaks["tflops"] / world,
             "cpu_baseline": cpu_baseline,
-            "tnn_plugin": tnn_plugin,
         }
         print(json.dumps(line))
     if world > 1:
@@ -583,14 +569,17 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of linear_pair_kernel, from ncu captures of the GEMM shapes
-# of the default workload (batch 64 x seq 128: M = 8192).  The figures belong to that M only.
-NCU_DRAM_BYTES_M8192 = {"qkv": 16.16e6 + 0.54e6, "ffn1": 17.35e6 + 2.26e6, "ffn2": 67.69e6 + 4.36e6}
+# (profiles/linear_pair_kernel_*.md), keyed by the row count M the capture ran at.  The figures belong to that M only.
+NCU_DRAM_BYTES = {
+    8192: {"qkv": 16.16e6 + 0.54e6, "ffn1": 17.35e6 + 2.26e6, "ffn2": 67.69e6 + 4.36e6},
+}
 
 
-def ncu_traffic_per_launch(batch, per_shape):
-    if batch != BATCH_PER_GPU:
+def ncu_traffic_per_launch(tokens, per_shape):
+    table = NCU_DRAM_BYTES.get(tokens)
+    if not table:
         return None
-    vals = [NCU_DRAM_BYTES_M8192[k] for k in per_shape if k in NCU_DRAM_BYTES_M8192]
+    vals = [table[k] for k in per_shape if k in table]
     return sum(vals) / len(vals) if vals else None
 
 
@@ -616,17 +605,16 @@ def _bind_to_gpu_cpus(index):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="sequences per GPU per step")
+    ap.add_argument("--total-batch", type=int, default=TOTAL_BATCH,
+                    help="sequences per step over all GPUs (config 5: 1024, split evenly)")
+    ap.add_argument("--min-seconds", type=float, default=2.0,
+                    help="the block of --steps timed steps is repeated until this much device time has been measured")
+    ap.add_argument("--no-half-io", action="store_true", help="skip the half-precision-Mat end-to-end figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-attention-sweep", action="store_true")
-    ap.add_argument("--no-tnn-plugin", action="store_true", help="skip the measurement through TNN + plug-in")
-    ap.add_argument("--fold-layernorm", action="store_true",
-                    help="fold both LayerNorms of a layer into the neighbouring GEMM epilogues (5 launches per layer)")
-    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
-                                                            "a captured CUDA graph of one Forward")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -22,6 +22,13 @@ extern "C" {
  * precision: TNN's Precision enum.  Returns the layer count or a negative error.  Needs no GPU. */
 TNNB200_API int tnnb200_test_fuse(const char* proto, size_t proto_len, const char* model, size_t model_len, int precision,
                                   char* out, size_t out_cap);
+/* The same the way Instance::Init runs it for DEVICE_CUDA (source/tnn/core/instance.cc:86-124): if the pass refuses the
+ * graph and fold_constants != 0, the reference's constant folder evaluates the graph's shape arithmetic on DEVICE_NAIVE
+ * and the pass runs again.  Layers the folder has evaluated are left out of the listing.  err receives the text of
+ * the last refusal (e.g. the layers without a CUDA implementation). */
+TNNB200_API int tnnb200_test_fuse_ex(const char* proto, size_t proto_len, const char* model, size_t model_len,
+                                     int precision, int fold_constants, char* out, size_t out_cap, char* err,
+                                     size_t err_cap);
 /* Runs the pass and saves the optimised model with the reference's ModelPacker
  * (source/tnn/interpreter/tnn/model_packer.cc:70-248).  Returns the layer count or a negative error.  Needs no GPU. */
 TNNB200_API int tnnb200_fuse_and_pack(const char* proto, size_t proto_len, const char* model, size_t model_len,

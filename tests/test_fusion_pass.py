@@ -102,6 +102,54 @@ def test_export_style_graph_fuses_like_the_resource_style():
     assert rt.fuse_report(proto2, model2) == lines
 
 
+def test_shape_subgraph_export_fuses_after_constant_folding():
+    """Reshape layers whose target shape is computed in the graph (Shape -> Gather -> Concat -> two-input Reshape).  On
+    its own the pass cannot see through them and must leave the WHOLE graph alone (a half-fused graph would break the
+    constant folder's run on the CPU device that TNN starts next), saying which layers stand in the way; once the
+    reference's constant folder has evaluated the shape arithmetic, the pass fuses the graph to the same seven layers
+    per encoder layer, and the folded layers are gone from what is instantiated."""
+    wl = ms.make_workload(ms.BERT_BASE, 2, 32, seed=2, num_layers=2)
+    d = tempfile.mkdtemp(prefix="fuse_shapes_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, style="export_shapes")
+    with pytest.raises(rt.FuseRefused) as e:
+        rt.fuse_report(proto, model)
+    msg = str(e.value)
+    assert "no CUDA implementation" in msg and "Shape 'l0_q_r_shape'" in msg and "left unfused" in msg
+    lines = rt.fuse_report(proto, model, fold_constants=True)
+    assert [ln.split()[0] for ln in lines] == ["FusedLinear", "FusedAttention", "FusedLinear", "LayerNorm",
+                                               "FusedLinear", "FusedLinear", "LayerNorm"] * 2
+    ref_lines = None
+    proto0, model0 = os.path.join(d, "r.tnnproto"), os.path.join(d, "r.tnnmodel")
+    ms.write_tnn_model(wl, proto0, model0, style="export")
+    ref_lines = rt.fuse_report(proto0, model0)
+    assert [ln.split()[0] for ln in ref_lines] == [ln.split()[0] for ln in lines]
+
+
+def test_graph_with_a_layer_the_device_cannot_run_is_refused_whole():
+    """An encoder followed by a layer without a CUDA implementation (Sigmoid): nothing is fused — not even the parts
+    the pass knows — and the refusal names the layer, with and without constant folding.  Instance::Init then fails
+    with this text instead of stumbling over fused layers on the CPU device."""
+    wl = ms.make_workload(ms.EncoderConfig(1, 256, 4, 1024), 2, 16, seed=7)
+    d = tempfile.mkdtemp(prefix="fuse_refuse_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    out = ms.write_tnn_model(wl, proto, model)
+    text = open(proto).read().split("\n")
+    # append Sigmoid(out) -> sig and make it the graph's output
+    n_layers = int(text[4].strip('", '))
+    text[4] = '" %d ,"' % (n_layers + 1)
+    text[3] = '"sig ,"'
+    text[2] = text[2].replace(' ,"', ' sig ,"')
+    while text and not text[-1].strip():
+        text.pop()
+    text.append('"Sigmoid sig 1 1 %s sig ,"' % out)
+    open(proto, "w").write("\n".join(text) + "\n")
+    for fold in (False, True):
+        with pytest.raises(rt.FuseRefused) as e:
+            rt.fuse_report(proto, model, fold_constants=fold)
+        assert "Sigmoid 'sig'" in str(e.value) and "no CPU fallback" in str(e.value)
+
+
 def test_qa_head_fuses_to_one_layer_with_two_named_outputs():
     """MatMul [H, 2] -> Add -> SplitV becomes one FusedQAHead; the two Squeeze layers behind it keep the graph's
     output names; the fused model survives the ModelPacker round trip."""

@@ -162,6 +162,44 @@ def test_export_style_graph_matches_x86_fixture(cuda_device):
     assert max_abs(y.reshape(ref.shape), ref) <= MAX_ABS_TOL
 
 
+def test_shape_subgraph_export_runs_through_instance_init(cuda_device):
+    """Target shapes computed in the graph (Shape -> Gather -> Concat -> two-input Reshape).  Instance::Init's own
+    sequence for DEVICE_CUDA — a first attempt the pass refuses as a whole, the constant folder on the CPU device, a
+    second attempt in which the pass fuses the folded graph — ends in the same fused layers and the same bits as the
+    resource-style graph."""
+    name = "base_2layer_ragged"
+    wl = golden_workload(**CASES[name])
+    d = tempfile.mkdtemp(prefix="plug_shapes_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, style="export_shapes")
+    y = _run(proto, model, wl, rt.DEVICE_CUDA)
+    proto0, model0 = _files(wl)
+    assert np.array_equal(y, _run(proto0, model0, wl, rt.DEVICE_CUDA))
+    ref = np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]
+    assert max_abs(y.reshape(ref.shape), ref) <= MAX_ABS_TOL
+
+
+def test_unsupported_layer_fails_with_the_pass_explanation(cuda_device):
+    """A graph the device cannot run whole (an encoder followed by Sigmoid): instance creation fails, and the message
+    is the pass's — which layer has no CUDA implementation — not a complaint about fused layers on the CPU device."""
+    wl = ms.make_workload(ms.EncoderConfig(1, 256, 4, 1024), 2, 16, seed=7)
+    d = tempfile.mkdtemp(prefix="plug_refuse_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    out = ms.write_tnn_model(wl, proto, model)
+    text = open(proto).read().split("\n")
+    n_layers = int(text[4].strip('", '))
+    text[4] = '" %d ,"' % (n_layers + 1)
+    text[3] = '"sig ,"'
+    text[2] = text[2].replace(' ,"', ' sig ,"')
+    while text and not text[-1].strip():
+        text.pop()
+    text.append('"Sigmoid sig 1 1 %s sig ,"' % out)
+    open(proto, "w").write("\n".join(text) + "\n")
+    with pytest.raises(RuntimeError) as e:
+        rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    assert "Sigmoid 'sig'" in str(e.value) and "no CUDA implementation" in str(e.value)
+
+
 def test_qa_head_matches_x86_fixture(cuda_device):
     """Encoder layer + span-extraction head: one FusedQAHead, outputs `unstack:0` / `unstack:1` as the demo reads them."""
     name = "base_1layer_qa"

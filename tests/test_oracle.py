@@ -89,6 +89,30 @@ def test_export_style_graph_gives_the_fixture_on_the_reference():
     assert max_abs(y, np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]) < 2e-5
 
 
+def test_shape_subgraph_export_gives_the_fixture_on_the_reference():
+    """The export form whose head-split / head-merge Reshape layers take their target shape from a Shape -> Gather ->
+    Concat subgraph in the graph: the reference folds the subgraph at Init and runs to the same committed fixture."""
+    import tempfile
+    from oracle import tnn_ref
+    if not tnn_ref.available():
+        pytest.skip("the reference build is not here")
+    name = "base_2layer_ragged"
+    wl = golden_workload(**CASES[name])
+    d = tempfile.mkdtemp(prefix="export_shapes_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    model_synth.write_tnn_model(wl, proto, model, style="export_shapes")
+    text = open(proto).read()
+    assert "Shape " in text and "Gather " in text and "Concat " in text and "Reshape l0_q_r 2 1" in text
+    for device in (tnn_ref.DEVICE_X86, tnn_ref.DEVICE_NAIVE):
+        inst = tnn_ref.TnnInstance(proto, model, device=device)
+        inst.set_input("x", wl.x)
+        inst.set_input("mask", wl.mask_add)
+        inst.forward()
+        y = inst.get_output().reshape(wl.x.shape)
+        inst.close()
+        assert max_abs(y, np.load(os.path.join(GOLDEN, name + ".npz"))["x86"]) < 2e-5
+
+
 def test_gather_out_of_range_is_an_error():
     with pytest.raises(IndexError):
         bert_oracle.gather_rows(np.zeros((4, 2), np.float32), np.array([0, 4]))

@@ -139,9 +139,14 @@ def _pstr(s):
 
 
 def _raw(a):
-    a = np.ascontiguousarray(a, dtype=np.float32)
+    """A RawBuffer record: fp32 (data type 0) unless the array is int32 (data type 3, include/tnn/core/common.h:31-49)."""
+    a = np.asarray(a)
+    if a.dtype == np.int32:
+        a, code = np.ascontiguousarray(a), 3
+    else:
+        a, code = np.ascontiguousarray(a, dtype=np.float32), 0
     dims = a.shape
-    return (struct.pack("<Iii", MAGIC_RAW, 0, a.nbytes) + struct.pack("<i", len(dims)) +
+    return (struct.pack("<Iii", MAGIC_RAW, code, a.nbytes) + struct.pack("<i", len(dims)) +
             b"".join(struct.pack("<i", d) for d in dims) + a.tobytes())
 
 
@@ -150,7 +155,11 @@ def _encoder_graph(wl, input_name, mask_name, style="resource"):
     `style` "resource": weights and biases are layer resources and the scale is Mul(1/sqrt(d)), the form the TNN
     converters write after constant folding; "export": weights and biases are entries of the constant map consumed as
     second inputs (MatMul weight_position -1; every second bias written as Add(bias, x)) and the scale is
-    Div(sqrt(d)), the form of a plain converter export."""
+    Div(sqrt(d)), the form of a plain converter export; "export_shapes": the export form whose head-split and
+    head-merge Reshape layers take their target shape as a second input computed in the graph — Shape(x) ->
+    Gather(index 0), Gather(index 1) -> Concat with the constant head count and head size — as exporters write a
+    reshape whose batch and sequence dimensions are dynamic (source/tnn/layer/reshape_layer.cc:72-91 fills the
+    Reshape's shape from that input once the constant folder has evaluated it)."""
     cfg = wl.cfg
     B, S, H = wl.x.shape
     NH, D, F = cfg.heads, cfg.head_dim, cfg.ffn
@@ -164,8 +173,33 @@ def _encoder_graph(wl, input_name, mask_name, style="resource"):
 
     n_linear = [0]
 
+    def gather_resource(name, index):
+        # GatherLayerResource: no data, indices = int32 [1] (gather_layer_interpreter.cc:29-43)
+        res.append(struct.pack("<i", _TYPE_ID["Gather"]) + _pstr("Gather") + _pstr(name) + struct.pack("<i", 0) +
+                   struct.pack("<i", 1) + _raw(np.array([index], np.int32)))
+
+    def reshape(name, x, tail, static_params):
+        """Reshape of [B, S, ...] to [B, S] + tail: static parameters, or (export_shapes) a shape computed in the graph."""
+        if style != "export_shapes":
+            layer("Reshape", name, [x], [name], static_params)
+            return name
+        layer("Shape", name + "_shape", [x], [name + "_shape"])
+        parts = []
+        for i in (0, 1):
+            g = "%s_dim%d" % (name, i)
+            layer("Gather", g, [name + "_shape"], [g], "0 0 1")
+            gather_resource(g, i)
+            parts.append(g)
+        for j, v in enumerate(tail):
+            c = "%s_c%d" % (name, j)
+            consts[c] = np.array([v], np.int32)
+            parts.append(c)
+        layer("Concat", name + "_target", parts, [name + "_target"], "0")
+        layer("Reshape", name, [x, name + "_target"], [name], "0 0 0 0")
+        return name
+
     def linear(name, x, w, b):
-        if style == "export":
+        if style in ("export", "export_shapes"):
             n_linear[0] += 1
             consts[name + "_w"] = w
             consts[name + "_bias"] = b.reshape(-1)
@@ -191,10 +225,10 @@ def _encoder_graph(wl, input_name, mask_name, style="resource"):
         for n, w, b, perm in (("q", lw.wq, lw.bq, "0 2 1 3"), ("k", lw.wk, lw.bk, "0 2 3 1"),
                               ("v", lw.wv, lw.bv, "0 2 1 3")):
             o = linear(p + n, x, w, b)
-            layer("Reshape", p + n + "_r", [o], [p + n + "_r"], "0 4 4 0 0 %d %d 0" % (NH, D))
+            reshape(p + n + "_r", o, (NH, D), "0 4 4 0 0 %d %d 0" % (NH, D))
             layer("Permute", p + n + "_p", [p + n + "_r"], [p + n + "_p"], "4 " + perm)
         layer("MatMul", p + "qk", [p + "q_p", p + "k_p"], [p + "qk"], "-1")
-        if style == "export":
+        if style in ("export", "export_shapes"):
             layer("Div", p + "qk_s", [p + "qk"], [p + "qk_s"], "1")
             resource("Div", p + "qk_s", np.array([np.sqrt(D)], np.float32))
         else:
@@ -204,7 +238,7 @@ def _encoder_graph(wl, input_name, mask_name, style="resource"):
         layer("Softmax", p + "sm", [p + "qk_m"], [p + "sm"], "3")
         layer("MatMul", p + "ctx", [p + "sm", p + "v_p"], [p + "ctx"], "-1")
         layer("Permute", p + "ctx_p", [p + "ctx"], [p + "ctx_p"], "4 0 2 1 3")
-        layer("Reshape", p + "ctx_r", [p + "ctx_p"], [p + "ctx_r"], "0 3 3 0 0 %d 0" % H)
+        reshape(p + "ctx_r", p + "ctx_p", (H,), "0 3 3 0 0 %d 0" % H)
         o = linear(p + "o", p + "ctx_r", lw.wo, lw.bo)
         layer("Add", p + "res1", [o, x], [p + "res1"], "-1")
         a = lnorm(p + "ln1", p + "res1", lw.ln1_g, lw.ln1_b)

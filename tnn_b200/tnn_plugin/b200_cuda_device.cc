@@ -355,6 +355,8 @@ Status B200CudaDevice::RegisterLayerAccCreator(LayerType type, LayerAccCreator* 
     return TNN_OK;
 }
 
+bool B200CudaDevice::HasLayerAcc(LayerType type) { return GetLayerCreatorMap().count(type) > 0; }
+
 std::map<LayerType, std::shared_ptr<LayerAccCreator>>& B200CudaDevice::GetLayerCreatorMap() {
     static std::map<LayerType, std::shared_ptr<LayerAccCreator>> m;
     return m;

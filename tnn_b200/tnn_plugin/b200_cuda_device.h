@@ -55,6 +55,7 @@ public:
     virtual NetworkType ConvertAutoNetworkType();
 
     static Status RegisterLayerAccCreator(LayerType type, LayerAccCreator* creator);
+    static bool HasLayerAcc(LayerType type);
 
     // Page-locked host memory for the blob converters' staging (cached like device memory: a released block is kept
     // and handed to the next request it fits).

@@ -25,9 +25,12 @@
 #include <cmath>
 #include <map>
 #include <memory>
+#include <set>
 #include <string>
+#include <tuple>
 #include <vector>
 
+#include "b200_cuda_device.h"
 #include "b200_plugin_common.h"
 #include "tnn/interpreter/layer_param.h"
 #include "tnn/interpreter/layer_resource.h"
@@ -48,6 +51,10 @@ public:
     virtual Status Optimize(NetStructure* structure, NetResource* resource);
 
 private:
+    // The rewriting itself, on working copies (see Optimize).  `keep_reshape`: two-input Reshape layers to leave in
+    // their two-input form; `survivors`: Reshape layers that were given a static shape and were not fused afterwards.
+    Status Fuse(NetStructure* structure, NetResource* resource, int dtype, const std::set<std::string>& keep_reshape,
+                std::vector<std::string>* survivors);
     Precision precision_ = PRECISION_AUTO;
 };
 
@@ -103,13 +110,19 @@ bool PermuteIs(const std::shared_ptr<Node>& n, const std::vector<int>& want) {
     return p && p->orders == want;
 }
 
-// Reshape [B,S,H] -> [B,S,heads,head_dim]: shape {0,0,heads,head_dim}
-bool SplitHeads(const std::shared_ptr<Node>& n, int* heads, int* head_dim) {
+// Reshape [B,S,H] -> [B,S,heads,head_dim]: shape {., ., heads, head_dim}, one of the two possibly written as -1
+// ("whatever is left": exporters do, and the reference's CPU Reshape rewrites its parameter that way when the constant
+// folder has run, source/tnn/device/cpu/acc/cpu_reshape_layer_acc.cc:56-89); `width` = heads * head_dim.
+bool SplitHeads(const std::shared_ptr<Node>& n, int width, int* heads, int* head_dim) {
     if (!n || n->info->inputs.size() != 1) return false;
     auto p = std::dynamic_pointer_cast<ReshapeLayerParam>(n->info->param);
-    if (!p || p->shape.size() != 4 || p->shape[2] <= 0 || p->shape[3] <= 0) return false;
-    *heads    = p->shape[2];
-    *head_dim = p->shape[3];
+    if (!p || p->shape.size() != 4 || p->axis != 0) return false;
+    int h = p->shape[2], d = p->shape[3];
+    if (h == -1 && d > 0 && width % d == 0) h = width / d;
+    if (d == -1 && h > 0 && width % h == 0) d = width / h;
+    if (h <= 0 || d <= 0) return false;
+    *heads    = h;
+    *head_dim = d;
     return true;
 }
 
@@ -155,7 +168,8 @@ Status AddFusedLinear(const std::shared_ptr<Graph>& g, const std::vector<std::st
 // Shared objects are never modified: every new resource is a new object whose RawBuffer shares the constant's storage
 // (or, for the reciprocal, owns four new bytes); the resource map is shared by the instances of a model, and a second
 // instance's pass finds the entries of the first and replaces them with equal ones.
-void Canonicalize(NetStructure* structure, NetResource* resource) {
+void Canonicalize(NetStructure* structure, NetResource* resource, const std::set<std::string>& keep_reshape,
+                  std::vector<std::string>* static_reshapes) {
     auto constant = [&](const std::string& name) -> std::shared_ptr<RawBuffer> {
         auto it = resource->constant_map.find(name);
         if (it == resource->constant_map.end() || !it->second || it->second->GetDataType() != DATA_TYPE_FLOAT) return nullptr;
@@ -215,6 +229,58 @@ void Canonicalize(NetStructure* structure, NetResource* resource) {
             l->type     = LAYER_MUL;
             l->type_str = "Mul";
             p->type     = "Mul";
+        }
+    }
+    // Reshape(x, target) with the target shape an int32 constant — either a plain constant of the model or the result
+    // of a Shape -> Gather -> Concat subgraph that the constant folder has evaluated (its value then sits in the
+    // constant map under the blob's name) — becomes the one-input Reshape with that shape as its parameter, which is
+    // what the reference's own Reshape layer does with such an input at Init
+    // (ReshapeLayer::FillLayerParamWithConstantResource, source/tnn/layer/reshape_layer.cc:72-91).  Meant for the
+    // Reshape layers that disappear in the attention pattern; the caller repeats the pass without this step for any
+    // that does not (`keep_reshape`).
+    bool any_reshape = false;
+    for (auto& l : structure->layers) {
+        if (l->type != LAYER_RESHAPE || l->inputs.size() != 2 || keep_reshape.count(l->name)) continue;
+        auto it = resource->constant_map.find(l->inputs[1]);
+        if (it == resource->constant_map.end() || !it->second || it->second->GetDataType() != DATA_TYPE_INT32) continue;
+        auto p = std::dynamic_pointer_cast<ReshapeLayerParam>(l->param);
+        const int n = it->second->GetDataCount();
+        if (!p || n < 1 || n > 6) continue;
+        const int* dims = it->second->force_to<int*>();
+        p->shape.assign(dims, dims + n);
+        p->axis     = 0;
+        p->num_axes = n;
+        absorbed.push_back(l->inputs[1]);
+        l->inputs.pop_back();
+        static_reshapes->push_back(l->name);
+        any_reshape = true;
+    }
+    // Constant layers whose outputs nothing reads any more (the shape arithmetic behind such a Reshape) leave the
+    // structure together with their folded values.
+    for (bool again = any_reshape; again;) {
+        again = false;
+        for (size_t i = 0; i < structure->layers.size(); ++i) {
+            auto l = structure->layers[i];
+            if (!resource->constant_layers.count(l->name)) continue;
+            bool used = false;
+            for (auto& o : l->outputs) {
+                used = used || structure->outputs.count(o) > 0;
+                for (auto& m : structure->layers)
+                    for (auto& in : m->inputs) used = used || in == o;
+            }
+            if (used) continue;
+            for (auto& o : l->outputs) {
+                resource->constant_map.erase(o);
+                resource->constant_blob_flags.erase(o);
+                structure->blobs.erase(o);
+            }
+            for (auto& in : l->inputs) absorbed.push_back(in);
+            resource->constant_layers.erase(l->name);
+            resource->shape_differ_layers.erase(l->name);
+            resource->resource_map.erase(l->name);
+            structure->layers.erase(structure->layers.begin() + i);
+            again = true;
+            break;
         }
     }
     // A constant nothing reads any more leaves this instance's constant map (the map is the instance's own copy; its
@@ -278,6 +344,14 @@ const char* kAttentionUnmasked = R"(
 
 }  // namespace
 
+// All or nothing.  Instance::Init for DEVICE_CUDA tries the network twice (source/tnn/core/instance.cc:86-124): if the
+// first DefaultNetwork::Init fails, the constant folder runs the graph's shape arithmetic on DEVICE_NAIVE — over the very
+// NetStructure this pass has been given — and the network is initialised again.  A graph left half fused by a first
+// attempt that then fails (fused layers have no CPU implementation) would break that retry.  So the pass works on
+// copies and commits them only if every layer of the result can run: it has a DEVICE_CUDA acc, or the constant folder
+// has evaluated it (constant layers are not instantiated, source/tnn/core/default_network.cc:255-259).  Otherwise the
+// graph is left exactly as it was and the Status names the layers that stand in the way; on the first attempt TNN
+// discards it and retries with the constants folded, on the second it is what the caller sees.
 Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResource* resource) {
     if (!structure || !resource) return Status(TNNERR_NET_ERR, "Error: empty NetStructure or NetResource");
     if (precision_ == PRECISION_HIGH)
@@ -292,7 +366,47 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
             l->type == LAYER_B200_FUSED_QA_HEAD)
             return TNN_OK;
 
-    Canonicalize(structure, resource);
+    // A two-input Reshape whose target shape is a folded constant is given that shape as a parameter so that the
+    // attention pattern can see through it; one that does not end up inside a fused attention must keep its two-input
+    // form (its shape follows the inputs when the instance is reshaped), so the attempt is repeated without touching it.
+    std::shared_ptr<NetStructure> work_structure;
+    NetResource work_resource;
+    std::set<std::string> keep_reshape;
+    for (int attempt = 0; attempt < 3; ++attempt) {
+        work_structure = structure->Copy();   // layer infos and their params are copied
+        if (!work_structure) return Status(TNNERR_OUTOFMEMORY, "tnn_b200: cannot copy the NetStructure");
+        work_resource = *resource;            // maps of shared objects; the pass replaces entries, never edits them
+        std::vector<std::string> survivors;
+        RETURN_ON_NEQ(Fuse(work_structure.get(), &work_resource, dtype, keep_reshape, &survivors), TNN_OK);
+        if (survivors.empty()) break;
+        if (attempt == 2) return Status(TNNERR_NET_ERR, "tnn_b200: the fusion pass did not settle");
+        keep_reshape.insert(survivors.begin(), survivors.end());
+    }
+
+    std::string missing;
+    int n_missing = 0;
+    for (auto& l : work_structure->layers) {
+        if (work_resource.constant_layers.count(l->name)) continue;
+        if (B200CudaDevice::HasLayerAcc(l->type)) continue;
+        if (++n_missing <= 8) missing += (missing.empty() ? "" : ", ") + l->type_str + " '" + l->name + "'";
+    }
+    if (n_missing > 0) {
+        if (n_missing > 8) missing += ", ... (" + std::to_string(n_missing) + " in all)";
+        return Status(TNNERR_LAYER_ERR,
+                      "tnn_b200: DEVICE_CUDA cannot run this graph: no CUDA implementation for " + missing +
+                          " (after fusing the encoder subgraphs; layers the constant folder evaluates are exempt). "
+                          "The graph was left unfused; there is no CPU fallback.");
+    }
+    *structure = *work_structure;
+    *resource  = work_resource;
+    return TNN_OK;
+}
+
+Status NetOptimizerB200FuseAttention::Fuse(NetStructure* structure, NetResource* resource, int dtype,
+                                           const std::set<std::string>& keep_reshape,
+                                           std::vector<std::string>* survivors) {
+    std::vector<std::string> static_reshapes;
+    Canonicalize(structure, resource, keep_reshape, &static_reshapes);
 
     std::shared_ptr<Graph> graph = std::make_shared<Graph>();
     Status status = graph->fromInterpreted(structure, resource);
@@ -437,8 +551,8 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
                 return nullptr;
             if (q.K != k.K || q.K != v.K || q.N != k.N || q.N != v.N) return nullptr;
             int heads = 0, head_dim = 0, h2 = 0, d2 = 0, h3 = 0, d3 = 0;
-            if (!SplitHeads(node("q_r"), &heads, &head_dim) || !SplitHeads(node("k_r"), &h2, &d2) ||
-                !SplitHeads(node("v_r"), &h3, &d3))
+            if (!SplitHeads(node("q_r"), q.N, &heads, &head_dim) || !SplitHeads(node("k_r"), q.N, &h2, &d2) ||
+                !SplitHeads(node("v_r"), q.N, &h3, &d3))
                 return nullptr;
             if (heads != h2 || heads != h3 || head_dim != d2 || head_dim != d3 || heads * head_dim != q.N) return nullptr;
             if (!PermuteIs(node("q_p"), {0, 2, 1, 3}) || !PermuteIs(node("k_p"), {0, 2, 3, 1}) ||
@@ -452,7 +566,7 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
             if (!sm || (sm->axis != 3 && sm->axis != -1)) return nullptr;
             // merged heads: Reshape back to [B, S, H]
             auto ctx_r = std::dynamic_pointer_cast<ReshapeLayerParam>(node("ctx_r")->info->param);
-            if (!ctx_r || ctx_r->shape.size() != 3 || ctx_r->shape[2] != q.N) return nullptr;
+            if (!ctx_r || ctx_r->shape.size() != 3 || (ctx_r->shape[2] != q.N && ctx_r->shape[2] != -1)) return nullptr;
             // scale: Mul by a one-element constant held as the layer's resource
             auto mul = node("qk_s");
             auto mul_param = std::dynamic_pointer_cast<MultidirBroadcastLayerParam>(mul->info->param);
@@ -647,6 +761,9 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
         };
         RETURN_ON_FAIL(graph->rewrite(pattern, gen));
     }
+    for (const auto& name : static_reshapes)
+        for (auto& l : structure->layers)
+            if (l->name == name) survivors->push_back(name);
     return TNN_OK;
 }
 
@@ -657,17 +774,21 @@ Status NetOptimizerB200FuseAttention::Optimize(NetStructure* structure, NetResou
 // Host-only hook for tests: run the pass on a model and describe the resulting layer list
 // ("<type> <name> <inputs> -> <outputs>" per line).  Needs no GPU.
 #include "tnn/interpreter/abstract_model_interpreter.h"
+#include <cstdio>
+
+#include "tnn/core/const_folder.h"
 #include "tnn/interpreter/default_model_interpreter.h"
 
-extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const char* proto, size_t proto_len,
-                                                                         const char* model, size_t model_len,
-                                                                         int precision, char* out, size_t out_cap) {
+// What Instance::Init does around the pass for DEVICE_CUDA (source/tnn/core/instance.cc:86-124), without a device: the
+// pass on the interpreted model; if it refuses and `fold_constants` is set, the reference's constant folder on
+// DEVICE_NAIVE over the same structure, then the pass again.  `err` receives the last refusal's text.
+static int RunPassLikeInstanceInit(TNN_NS::DefaultModelInterpreter* interp, int precision, int fold_constants, char* err,
+                                   size_t err_cap) {
     using namespace TNN_NS;
-    auto* interp = dynamic_cast<DefaultModelInterpreter*>(CreateModelInterpreter(MODEL_TYPE_TNN));
-    if (!interp) return -1;
-    std::unique_ptr<DefaultModelInterpreter> guard(interp);
-    std::vector<std::string> params = {std::string(proto, proto_len), std::string(model, model_len)};
-    if (interp->Interpret(params) != TNN_OK) return -2;
+    auto note = [&](const std::string& m) {
+        if (err && err_cap > 0) std::snprintf(err, err_cap, "%s", m.c_str());
+    };
+    note("");
     optimizer::NetOptimizerB200FuseAttention pass;
     NetworkConfig cfg;
     cfg.device_type  = DEVICE_CUDA;
@@ -675,11 +796,44 @@ extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const ch
     cfg.precision    = static_cast<Precision>(precision);
     if (!pass.IsSupported(cfg)) return -3;
     Status st = pass.Optimize(interp->GetNetStructure(), interp->GetNetResource());
-    if (st != TNN_OK) return -4;
+    if (st != TNN_OK && fold_constants) {
+        note(st.description());
+        auto folder = std::make_shared<ConstFolder>();
+        ModelConfig mc;
+        mc.model_type = MODEL_TYPE_TNN;
+        NetworkConfig fc = cfg;
+        InputShapesMap none;
+        Status fs = folder->Init(fc, mc, interp, none, none);
+        if (fs != TNN_OK) {
+            note("constant folder: " + fs.description());
+            return -7;
+        }
+        st = pass.Optimize(interp->GetNetStructure(), interp->GetNetResource());
+    }
+    if (st != TNN_OK) {
+        note(st.description());
+        return -4;
+    }
     // run it again: must be a no-op
     if (pass.Optimize(interp->GetNetStructure(), interp->GetNetResource()) != TNN_OK) return -5;
+    return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse_ex(const char* proto, size_t proto_len,
+                                                                            const char* model, size_t model_len,
+                                                                            int precision, int fold_constants, char* out,
+                                                                            size_t out_cap, char* err, size_t err_cap) {
+    using namespace TNN_NS;
+    auto* interp = dynamic_cast<DefaultModelInterpreter*>(CreateModelInterpreter(MODEL_TYPE_TNN));
+    if (!interp) return -1;
+    std::unique_ptr<DefaultModelInterpreter> guard(interp);
+    std::vector<std::string> params = {std::string(proto, proto_len), std::string(model, model_len)};
+    if (interp->Interpret(params) != TNN_OK) return -2;
+    const int rc = RunPassLikeInstanceInit(interp, precision, fold_constants, err, err_cap);
+    if (rc != 0) return rc;
     std::string text;
     for (auto& l : interp->GetNetStructure()->layers) {
+        if (interp->GetNetResource()->constant_layers.count(l->name)) continue;   // folded: never instantiated
         text += l->type_str + " " + l->name;
         for (auto& i : l->inputs) text += " " + i;
         text += " ->";
@@ -689,6 +843,12 @@ extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const ch
     if (text.size() + 1 > out_cap) return -6;
     std::memcpy(out, text.c_str(), text.size() + 1);
     return static_cast<int>(interp->GetNetStructure()->layers.size());
+}
+
+extern "C" __attribute__((visibility("default"))) int tnnb200_test_fuse(const char* proto, size_t proto_len,
+                                                                         const char* model, size_t model_len,
+                                                                         int precision, char* out, size_t out_cap) {
+    return tnnb200_test_fuse_ex(proto, proto_len, model, model_len, precision, 0, out, out_cap, nullptr, 0);
 }
 
 // Host-only: run the pass on a model and save the optimised model with the reference's ModelPacker.  The saved pair

@@ -101,6 +101,10 @@ def load():
         plugin.tnnb200_fuse_and_pack.restype = ctypes.c_int
         plugin.tnnb200_fuse_and_pack.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
                                                  ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p]
+        plugin.tnnb200_test_fuse_ex.restype = ctypes.c_int
+        plugin.tnnb200_test_fuse_ex.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
+                                                ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t,
+                                                ctypes.c_char_p, ctypes.c_size_t]
         plugin.tnnb200_test_fuse.restype = ctypes.c_int
         plugin.tnnb200_test_fuse.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t,
                                              ctypes.c_int, ctypes.c_char_p, ctypes.c_size_t]
@@ -108,15 +112,25 @@ def load():
     return _state["shim"], _state["plugin"]
 
 
-def fuse_report(proto_path, model_path, precision=PRECISION_AUTO):
-    """Run only the graph pass on a model (no GPU needed); returns the fused layer list as text lines."""
+class FuseRefused(RuntimeError):
+    """The graph pass left the model unfused; `.args[0]` is its explanation."""
+
+
+def fuse_report(proto_path, model_path, precision=PRECISION_AUTO, fold_constants=False):
+    """Run only the graph pass on a model (no GPU needed); returns the fused layer list as text lines.
+    fold_constants: if the pass refuses the graph, run the reference's constant folder on it (as Instance::Init does for
+    DEVICE_CUDA) and try again.  Raises FuseRefused with the pass's explanation if the graph stays unfused."""
     _, plugin = load()
     proto = open(proto_path, "rb").read()
     model = open(model_path, "rb").read()
     buf = ctypes.create_string_buffer(1 << 22)
-    n = plugin.tnnb200_test_fuse(proto, len(proto), model, len(model), precision, buf, len(buf))
+    err = ctypes.create_string_buffer(4096)
+    n = plugin.tnnb200_test_fuse_ex(proto, len(proto), model, len(model), precision, 1 if fold_constants else 0,
+                                    buf, len(buf), err, len(err))
+    if n == -4:
+        raise FuseRefused(err.value.decode())
     if n < 0:
-        raise RuntimeError("tnnb200_test_fuse failed: %d" % n)
+        raise RuntimeError("tnnb200_test_fuse_ex failed: %d %s" % (n, err.value.decode()))
     return buf.value.decode().strip().split("\n")
 
 
