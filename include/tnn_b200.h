@@ -255,6 +255,10 @@ typedef struct B200QAHeadDesc {
     int64_t ldx, ld_out;
     int32_t N;
     int32_t x_dtype;
+    /* Optional: one destination per output.  If out_n[0] is not NULL, output n of token t goes to out_n[n][t] for every
+     * n < N (all N pointers must be set; `out` and `ld_out` are then ignored), so that a caller whose outputs are
+     * separate buffers — the two output blobs of the TNN graph — needs no copy behind the kernel. */
+    float* out_n[4];
 } B200QAHeadDesc;
 B200_API int b200_qa_head_fwd(const B200QAHeadDesc* desc, b200_stream_t stream);
 

@@ -361,3 +361,4 @@ def test_bounded_wait_expires_cleanly_and_the_device_carries_on():
     torch.cuda.synchronize()
     assert capi.device_status() == capi.OK
     assert (y.float() - x.float() @ w.float().t()).abs().max().item() < 2e-2
+

@@ -61,7 +61,7 @@ class EmbeddingDesc(_c.Structure):
 class QAHeadDesc(_c.Structure):
     _fields_ = [("x", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp),
                 ("M", _i64), ("H", _i64), ("ldx", _i64), ("ld_out", _i64),
-                ("N", _i32), ("x_dtype", _i32)]
+                ("N", _i32), ("x_dtype", _i32), ("out_n", _vp * 4)]
 
 
 class EncoderLayerWeights(_c.Structure):

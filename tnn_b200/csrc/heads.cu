@@ -15,7 +15,7 @@ constexpr int kHeadMaxN = 4;
 // features in separate planes, so that the 32 lanes of a warp read consecutive float4 (no bank conflicts; the plain
 // transposed layout read with a 32-byte lane stride, two-way conflicts, and ncu showed the shared-memory pipe 85 %
 // busy at 38 % of DRAM throughput); one read serves both rows.  fp32 accumulation in feature order within a lane,
-// lanes combined by a butterfly.  Output n of token t goes to out[n * ld_out + t].
+// lanes combined by a butterfly.  Output n of token t goes to out[n * ld_out + t], or to out_n[n][t].
 template <int N, int NV>
 __global__ void __launch_bounds__(256) qa_head_kernel(B200QAHeadDesc d) {
     extern __shared__ __align__(16) float w_s[];
@@ -28,8 +28,12 @@ __global__ void __launch_bounds__(256) qa_head_kernel(B200QAHeadDesc d) {
     }
     __syncthreads();
     float bias[N];
+    float* dst[N];   // output n of token t goes to dst[n][t]
 #pragma unroll
-    for (int n = 0; n < N; ++n) bias[n] = d.bias ? d.bias[n] : 0.f;
+    for (int n = 0; n < N; ++n) {
+        bias[n] = d.bias ? d.bias[n] : 0.f;
+        dst[n] = d.out_n[0] != nullptr ? d.out_n[n] : d.out + n * d.ld_out;
+    }
     const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const long long nwarps = static_cast<long long>(gridDim.x) * 8;
     pdl_launch_dependents();
@@ -90,8 +94,8 @@ __global__ void __launch_bounds__(256) qa_head_kernel(B200QAHeadDesc d) {
         if (lane == 0) {
 #pragma unroll
             for (int n = 0; n < N; ++n) {
-                d.out[n * d.ld_out + t0] = acc[0][n] + bias[n];
-                if (two) d.out[n * d.ld_out + t1] = acc[1][n] + bias[n];
+                dst[n][t0] = acc[0][n] + bias[n];
+                if (two) dst[n][t1] = acc[1][n] + bias[n];
             }
         }
     }
@@ -120,9 +124,15 @@ extern "C" int b200_qa_head_fwd(const B200QAHeadDesc* d, b200_stream_t stream_) 
     using namespace b200;
     if (!d || d->M < 0 || d->H <= 0 || d->N <= 0) return B200_ERR_PARAM;
     if (d->M == 0 && d->N <= kHeadMaxN && (d->H % 8) == 0) return B200_OK;   // nothing to do: pointers may be null
-    if (!d->x || !d->weight || !d->out) return B200_ERR_PARAM;
+    if (!d->x || !d->weight) return B200_ERR_PARAM;
+    if (d->out_n[0] != nullptr) {
+        for (int n = 0; n < d->N && n < kHeadMaxN; ++n)
+            if (d->out_n[n] == nullptr) return B200_ERR_PARAM;
+    } else if (!d->out || d->ld_out < d->M) {
+        return B200_ERR_PARAM;
+    }
     if (!is_half_dtype(d->x_dtype)) return B200_ERR_PARAM;
-    if ((d->H % 8) || (d->ldx % 8) || d->ldx < d->H || d->ld_out < d->M) return B200_ERR_PARAM;
+    if ((d->H % 8) || (d->ldx % 8) || d->ldx < d->H) return B200_ERR_PARAM;
     if (!aligned16(d->x)) return B200_ERR_PARAM;
     if (d->N > kHeadMaxN || d->H * d->N * 4 > 48 * 1024 || d->H > 4096) return B200_ERR_UNSUPPORTED;
     int dev = 0, major = 0;

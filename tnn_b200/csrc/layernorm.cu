@@ -40,6 +40,7 @@ __device__ __forceinline__ void store8(void* base, long long elem_off, int dtype
     }
 }
 
+
 // ---------------------------------------------------------------- (residual +) LayerNorm
 // One warp per row; a lane holds NV groups of 8 consecutive elements (group g of the lane = elements
 // (g*32 + lane)*8 ..), so every load/store instruction of the warp covers 512 (or 1024 for fp32) contiguous bytes.
@@ -173,43 +174,58 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4))
     pdl_wait();
     if (row < d.rows) fetch(row);
     __syncthreads();
+    // The arithmetic runs on pairs (packed fp32: one issue slot per two adds / multiplies / fmas).  Under the power cap
+    // of a long run the SM clock drops by 40 % while HBM keeps its rate, and this kernel, which is bound by HBM at full
+    // clock, becomes bound by its instruction stream: halving the stream is what keeps it on the memory roof.
     for (; row < d.rows; row += nwarps) {
-        float v[NV][8];
-        float sum = 0.f;
+        uint64_t v[NV][4];   // the lane's elements as pairs (2e, 2e+1)
+        uint64_t sum2 = 0ull;
 #pragma unroll
         for (int g = 0; g < NV; ++g) {
             const int gi = g * 32 + lane;
             if (gi < groups) {
-                decode(raw[g], v[g]);
+                float f[8];
+                decode(raw[g], f);
                 if (RESID && d.residual) {
                     float r[8];
                     decode(rres[g], r);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[g][e] += r[e];
+                    for (int e = 0; e < 8; ++e) f[e] += r[e];
                 }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) sum += v[g][e];
+                for (int e = 0; e < 4; ++e) {
+                    v[g][e] = pack_f32x2(f[2 * e], f[2 * e + 1]);
+                    sum2 = add_f32x2(sum2, v[g][e]);
+                }
             }
         }
         if (row + nwarps < d.rows) fetch(row + nwarps);   // next row's loads fly during the reductions below
+        float s_lo, s_hi;
+        unpack_f32x2(sum2, s_lo, s_hi);
+        float sum = s_lo + s_hi;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         const float mean = sum * inv_h;
-        float sq = 0.f;
+        const uint64_t nmean2 = pack_f32x2(-mean, -mean);
+        uint64_t sq2 = 0ull;
 #pragma unroll
         for (int g = 0; g < NV; ++g) {
             const int gi = g * 32 + lane;
             if (gi < groups) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float c = v[g][e] - mean;
-                    sq += c * c;
+                for (int e = 0; e < 4; ++e) {
+                    v[g][e] = add_f32x2(v[g][e], nmean2);        // deviations from the mean, kept for the output
+                    sq2 = fma_f32x2(v[g][e], v[g][e], sq2);
                 }
             }
         }
+        float q_lo, q_hi;
+        unpack_f32x2(sq2, q_lo, q_hi);
+        float sq = q_lo + q_hi;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         const float rstd = 1.0f / sqrtf(sq * inv_h + d.eps);
+        const uint64_t rstd2 = pack_f32x2(rstd, rstd);
 #pragma unroll
         for (int g = 0; g < NV; ++g) {
             const int gi = g * 32 + lane;
@@ -218,11 +234,14 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4))
                 const float4 g1 = *reinterpret_cast<const float4*>(gb + gi * 8 + 4);
                 const float4 b0 = *reinterpret_cast<const float4*>(gb + H + gi * 8);
                 const float4 b1 = *reinterpret_cast<const float4*>(gb + H + gi * 8 + 4);
-                const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const uint64_t gm[4] = {pack_f32x2(g0.x, g0.y), pack_f32x2(g0.z, g0.w), pack_f32x2(g1.x, g1.y),
+                                        pack_f32x2(g1.z, g1.w)};
+                const uint64_t bt[4] = {pack_f32x2(b0.x, b0.y), pack_f32x2(b0.z, b0.w), pack_f32x2(b1.x, b1.y),
+                                        pack_f32x2(b1.z, b1.w)};
                 float o[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = (v[g][e] - mean) * rstd * gm[e] + bt[e];
+                for (int e = 0; e < 4; ++e)
+                    unpack_f32x2(fma_f32x2(mul_f32x2(v[g][e], rstd2), gm[e], bt[e]), o[2 * e], o[2 * e + 1]);
                 store8(d.y, row * d.ldy + gi * 8, d.out_dtype, o);
             }
         }

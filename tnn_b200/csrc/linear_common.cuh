@@ -51,6 +51,25 @@ __device__ __forceinline__ float gelu_erf(float x) {
     return fmaf(h, t, h);
 }
 
+// Two values at once on the packed fp32 pipe (one issue slot per pair for every multiply / add / fma): the same
+// operations with the same roundings as gelu_erf, so the results are identical bit for bit.  The epilogue of the
+// 768-deep GEMMs is issue-bound (it has to finish within the next tile's mainloop), which is what this halves.
+__device__ __forceinline__ void gelu_erf_x2(float& a, float& b) {
+    const uint64_t x = pack_f32x2(a, b);
+    float qa, qb;
+    unpack_f32x2(mul_f32x2(x, x), qa, qb);
+    const uint64_t x2 = pack_f32x2(fminf(qa, 36.0f), fminf(qb, 36.0f));
+    const uint64_t poly = fma_f32x2(x2, fma_f32x2(x2, pack_f32x2(-3.51516788e-4f, -3.51516788e-4f),
+                                                  pack_f32x2(3.70056460e-2f, 3.70056460e-2f)),
+                                    pack_f32x2(7.97507884e-1f, 7.97507884e-1f));
+    float ta, tb;
+    unpack_f32x2(mul_f32x2(x, poly), ta, tb);
+    asm("tanh.approx.f32 %0, %1;" : "=f"(ta) : "f"(ta));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(tb) : "f"(tb));
+    const uint64_t h = mul_f32x2(x, pack_f32x2(0.5f, 0.5f));
+    unpack_f32x2(fma_f32x2(h, pack_f32x2(ta, tb), h), a, b);
+}
+
 // Stage one warp's per-column vectors (COLS floats each, starting at column n_first) in its private shared-memory
 // strips: strip 0 = bias (or c2 when the input LayerNorm is folded), 1 = c1, 2 = gamma, 3 = beta of a folded residual
 // LayerNorm.  Columns at or beyond N read as 0, so that they contribute nothing anywhere.
@@ -268,15 +287,15 @@ struct WarpEpilogue {
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 b = *reinterpret_cast<const float4*>(vec_w + c * 32 + g * 4);
-                    v[g * 4 + 0] += b.x;
-                    v[g * 4 + 1] += b.y;
-                    v[g * 4 + 2] += b.z;
-                    v[g * 4 + 3] += b.w;
+                    unpack_f32x2(add_f32x2(pack_f32x2(v[g * 4 + 0], v[g * 4 + 1]), pack_f32x2(b.x, b.y)), v[g * 4 + 0],
+                                 v[g * 4 + 1]);
+                    unpack_f32x2(add_f32x2(pack_f32x2(v[g * 4 + 2], v[g * 4 + 3]), pack_f32x2(b.z, b.w)), v[g * 4 + 2],
+                                 v[g * 4 + 3]);
                 }
             }
             if (p.epilogue == B200_EPI_BIAS_GELU) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                for (int j = 0; j < 32; j += 2) gelu_erf_x2(v[j], v[j + 1]);
             } else if (p.epilogue == B200_EPI_BIAS_TANH) {
                 // hardware tanh: relative error <= 2^-11, below the half-precision rounding of the result
 #pragma unroll

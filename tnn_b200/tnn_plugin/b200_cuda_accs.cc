@@ -107,9 +107,18 @@ Status B200CudaFusedLinearLayerAcc::AsCompute(Blob* src, void* staging, int64_t 
         return TNN_OK;
     }
     if (sdt < 0 || !staging) return Status(TNNERR_PARAM_ERR, "FusedLinear: unsupported input data type");
+    // another layer of this Forward may already have converted this blob (the graph input is both the first
+    // projection's operand and the first residual)
+    if (const void* done = context_->FindConverted(DevicePtr(src), p->compute_dtype, count)) {
+        *out = done;
+        return TNN_OK;
+    }
     *out = staging;
-    return B200ToStatus(b200_convert(DevicePtr(src), sdt, staging, p->compute_dtype, count, context_->GetStream()),
-                        "b200_convert");
+    RETURN_ON_NEQ(B200ToStatus(b200_convert(DevicePtr(src), sdt, staging, p->compute_dtype, count, context_->GetStream()),
+                               "b200_convert"),
+                  TNN_OK);
+    context_->NoteConverted(DevicePtr(src), p->compute_dtype, count, staging);
+    return TNN_OK;
 }
 
 Status B200CudaFusedLinearLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
@@ -293,8 +302,6 @@ B200_REGISTER_CUDA_ACC(FusedMask, LAYER_B200_FUSED_MASK)
 B200_DECLARE_CUDA_ACC(FusedQAHead)
     float* weight_ = nullptr;    // fp32 [H, outputs]
     float* bias_   = nullptr;    // fp32 [outputs]
-    void* logits_  = nullptr;    // fp32 [outputs, M]: the kernel's output, copied into the output blobs
-    size_t logits_cap_ = 0;
 };
 
 Status B200CudaFusedQAHeadLayerAcc::Init(Context* context, LayerParam* param, LayerResource* resource,
@@ -332,9 +339,7 @@ Status B200CudaFusedQAHeadLayerAcc::Init(Context* context, LayerParam* param, La
 }
 
 Status B200CudaFusedQAHeadLayerAcc::Reshape(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
-    auto* p = dynamic_cast<FusedQAHeadLayerParam*>(param_);
-    const int64_t M = Rows(inputs[0]->GetBlobDesc().dims);
-    return EnsureBuffer(&logits_, &logits_cap_, static_cast<size_t>(M > 0 ? M : 1) * p->outputs * sizeof(float));
+    return TNN_OK;
 }
 
 Status B200CudaFusedQAHeadLayerAcc::DoForward(const std::vector<Blob*>& inputs, const std::vector<Blob*>& outputs) {
@@ -345,22 +350,15 @@ Status B200CudaFusedQAHeadLayerAcc::DoForward(const std::vector<Blob*>& inputs, 
     d.x = DevicePtr(inputs[0]);
     d.weight = weight_;
     d.bias = bias_;
-    d.out = static_cast<float*>(logits_);
     d.M = Rows(dims);
     d.H = p->hidden;
     d.ldx = d.H;
-    d.ld_out = d.M;
     d.N = p->outputs;
     d.x_dtype = B200DataType(inputs[0]->GetBlobDesc().data_type);
-    RETURN_ON_NEQ(B200ToStatus(b200_qa_head_fwd(&d, context_->GetStream()), "b200_qa_head_fwd"), TNN_OK);
-    for (int n = 0; n < p->outputs; ++n) {
-        if (cudaMemcpyAsync(DevicePtr(outputs[n]), static_cast<float*>(logits_) + n * d.M, static_cast<size_t>(d.M) * sizeof(float),
-                            cudaMemcpyDeviceToDevice, context_->GetStream()) != cudaSuccess) {
-            cudaGetLastError();
-            return Status(TNNERR_CUDA_MEMCPY_ERROR, "FusedQAHead: output copy failed");
-        }
-    }
-    return TNN_OK;
+    // every output straight into its own blob (the graph's "unstack"): no copy behind the kernel
+    if (p->outputs > 4) return Status(TNNERR_PARAM_ERR, "FusedQAHead: at most 4 outputs");
+    for (int n = 0; n < p->outputs; ++n) d.out_n[n] = static_cast<float*>(DevicePtr(outputs[n]));
+    return B200ToStatus(b200_qa_head_fwd(&d, context_->GetStream()), "b200_qa_head_fwd");
 }
 B200_REGISTER_CUDA_ACC(FusedQAHead, LAYER_B200_FUSED_QA_HEAD)
 

@@ -154,7 +154,9 @@ void B200CudaContext::RecordCall(B200CudaLayerAcc* acc, const std::vector<Blob*>
 }
 
 Status B200CudaContext::RunCallsEagerly() {
-    // `calls_` holds what the executor asked for during this Forward, in order.
+    // `calls_` holds what the executor asked for during this Forward, in order.  What the accs cached for this Forward
+    // (kv_len, converted inputs) was recorded into the failed capture, never executed: a new id voids those caches.
+    ++forward_id_;
     std::vector<Call> todo;
     todo.swap(calls_);
     for (Call& c : todo) RETURN_ON_NEQ(c.acc->DoForward(c.inputs, c.outputs), TNN_OK);
@@ -285,6 +287,17 @@ Status B200CudaContext::Synchronize() {
     Status st = CheckStatusAfterSync();
     if (st != TNN_OK) sticky_error_ = st;
     return st;
+}
+
+const void* B200CudaContext::FindConverted(const void* src, int dtype, int64_t count) const {
+    for (const Converted& c : converted_)
+        if (c.forward_id == forward_id_ && c.src == src && c.dtype == dtype && c.count == count && c.dst) return c.dst;
+    return nullptr;
+}
+
+void B200CudaContext::NoteConverted(const void* src, int dtype, int64_t count, const void* dst) {
+    converted_[converted_next_] = Converted{src, dst, count, dtype, forward_id_};
+    converted_next_             = (converted_next_ + 1) % 4;
 }
 
 Status B200CudaContext::ReserveWorkspace(size_t bytes) {

@@ -65,6 +65,11 @@ public:
     static const int kKvLenCapacity = 65536;
     const int* GetKvLen(const float* mask, int batch, int seq, float exclude_below, Status* status);
 
+    // Half-precision copies of fp32 blobs made during the current Forward (the graph input feeds the first layer's
+    // projection and, as the residual, its output projection): the second layer that needs one reuses the first's.
+    const void* FindConverted(const void* src, int dtype, int64_t count) const;
+    void NoteConverted(const void* src, int dtype, int64_t count, const void* dst);
+
     // ---- graph replay, driven by B200CudaLayerAcc::Forward
     // True while a captured graph stands in for the accs' launches: the acc returns without launching.
     bool Replaying() const { return mode_ == kReplay; }
@@ -100,6 +105,16 @@ private:
     const float* kv_mask_   = nullptr;   // mask the cached kv_len belongs to (valid for the current Forward only)
     int kv_batch_ = 0, kv_seq_ = 0;
     unsigned long long forward_id_ = 0, kv_forward_id_ = ~0ull;
+
+    struct Converted {
+        const void* src;
+        const void* dst;
+        int64_t count;
+        int dtype;
+        unsigned long long forward_id;
+    };
+    Converted converted_[4] = {};
+    int converted_next_ = 0;
 
     unsigned int* host_status_ = nullptr;   // pinned; receives the device status word at the end of every Forward
     Status sticky_error_       = TNN_OK;    // reported by the next OnInstanceForwardBegin (Forward drops Synchronize's)
