@@ -102,8 +102,8 @@ def main():
         work = a.B * a.S * a.H * 2 * 4 * 1e3   # bytes per token: three table rows in, one row out
         unit = "GB/s"
     else:
-        from . import model_synth
-        from .encoder import Encoder
+        from tnn_b200 import model_synth
+        from tnn_b200.encoder import Encoder
         wl = model_synth.make_workload(model_synth.BERT_BASE, a.B, a.S, seed=0, num_layers=a.layers)
         enc = Encoder.from_workload(wl, dt, dev)
         hidden = torch.from_numpy(wl.x).to(dev).to(dt)

@@ -160,8 +160,10 @@ def test_steady_state_takes_no_memory_from_the_driver(cuda_device):
 
 
 def test_injected_allocation_failure_is_reported_and_leaks_nothing(cuda_device):
-    """Host-side fault injection: an allocation that fails during CreateInst comes back as an error status (instance
-    creation raises, nothing aborts), the blocks taken before the failure are returned, and the next creation works."""
+    """Host-side fault injection: allocations that fail during CreateInst come back as an error status (instance
+    creation raises, nothing aborts), the blocks taken before the failure are returned, and the next creation works.
+    Instance::Init tries a DEVICE_CUDA network twice (source/tnn/core/instance.cc:86-124), so the injection stays on
+    until both attempts have failed: the first one `skip` allocations into its Init, the second at its first."""
     wl = golden_workload(**CASES["c1_attention_block"])
     proto, model = _files(wl)
     warm = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
@@ -169,10 +171,12 @@ def test_injected_allocation_failure_is_reported_and_leaks_nothing(cuda_device):
     warm.close()
     before = rt.arena_stats(0)
     for skip in (0, 2, 7):            # the first allocation (context set-up), an early one, one in the middle of Init
-        rt.inject_allocation_failure(skip, 1)
-        with pytest.raises(RuntimeError):
-            rt.Instance(proto, model, device=rt.DEVICE_CUDA)
-        rt.inject_allocation_failure(0, 0)
+        rt.inject_allocation_failure(skip, 1 << 30)
+        try:
+            with pytest.raises(RuntimeError):
+                rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+        finally:
+            rt.inject_allocation_failure(0, 0)
         after = rt.arena_stats(0)
         assert after["live_blocks"] == before["live_blocks"], (skip, before, after)
         assert after["bytes_in_use"] == before["bytes_in_use"]

@@ -17,6 +17,11 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+// 1: the next item's Q and K are loaded as soon as the scores are complete; 0: after PV (kept for A/B measurements)
+#ifndef B200_ATTN_EARLY_QK
+#define B200_ATTN_EARLY_QK 1
+#endif
+
 namespace b200 {
 namespace {
 
@@ -470,11 +475,12 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 //     scores that are dead by then;
 //   * only ceil(kv_len / 32) 32-key chunks are computed: QK^T runs with N = 32*chunks, the softmax reads that many
 //     chunks, PV runs 2*chunks k-steps — padded tails of short sequences cost nothing;
-//   * operand tiles are handed to the next item as early as they die: Q and K when the scores are complete (the next
-//     item's Q and K then travel during this item's softmax, PV and output), V when PV is complete.  At large batches
-//     the kernel is bound by HBM (Q, K, V in, O out: 1 KB per query row and head), so what counts is how many of
-//     these loads are in flight per SM at any time;
-//   * the output leaves straight from registers: a thread owns a query row, i.e. 128 contiguous bytes per head.
+//   * operand tiles are handed to the next item as they die: Q and K when the scores are complete (the next item's Q
+//     and K then travel during this item's softmax, PV and output: 1.2 % of a BERT-base step at 1024 sequences against
+//     issuing them after PV), V when the output tile, which is staged (swizzled) in the V tile and leaves through one
+//     TMA store clipped at row S, has been read by that store.  (Storing the output straight from registers — a thread
+//     owns a query row, 128 contiguous bytes per head — frees V earlier but measured 35 % slower: 32 rows per store
+//     instruction are 32 half-written sectors.)
 constexpr int S1_OFF_MASK = 3 * TILE_BYTES;
 constexpr int S1_OFF_BAR = S1_OFF_MASK + TK * 4;
 constexpr int S1_SMEM = S1_OFF_BAR + 64;
@@ -484,7 +490,8 @@ constexpr int S1_CTAS_PER_SM = 4;
 template <int DT>
 __global__ void __launch_bounds__(kAttnThreads, S1_CTAS_PER_SM)
 attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_v, const AttnParams p, const int num_items) {
+                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                        const AttnParams p, const int num_items) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S1_OFF_BAR);
     uint64_t* bar_qk = bars + 0;
@@ -512,6 +519,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         prefetch_tmap(&tm_q);
         prefetch_tmap(&tm_k);
         prefetch_tmap(&tm_v);
+        prefetch_tmap(&tm_o);
     }
     if (warp == 0) {
         tmem_alloc(tmem_slot, S1_TMEM_COLS);
@@ -587,10 +595,12 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
         }
         if (!mbar_wait(bar_s, ph, abort_flag)) { ok = false; break; }
+        const int next = item + gridDim.x;
+#if B200_ATTN_EARLY_QK
         // The scores are complete, so Q and K are dead: the next item's Q and K start travelling now and have the
         // whole softmax, PV and output of this item to arrive.
-        const int next = item + gridDim.x;
         if (tid == 0 && next < num_items) load_qk(next);
+#endif
         __syncwarp();
         tcgen05_fence_after();
         float l_sum = 0.f;
@@ -678,36 +688,50 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             }
         }
         if (!mbar_wait(bar_o, ph, abort_flag)) { ok = false; break; }
-        // PV is complete, so V is dead too: the next item's V follows its Q and K
-        if (tid == 0 && next < num_items) load_v(next);
+#if !B200_ATTN_EARLY_QK
+        // Q, K, V are dead now: the next item's Q and K start travelling while this item's output is written
+        if (tid == 0 && next < num_items) load_qk(next);
+#endif
         __syncwarp();
         tcgen05_fence_after();
         {
             const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(b) * p.S + tid) * p.ldo + head * HD;
+            uint8_t* orow = smem + OFF_V + tid * 128;   // output tile staged in the V tile
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
                 tmem_ld_wait(r);
-                if (tid < p.S) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 qv;
-                        qv.x = pack2t<DT>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-                        qv.y = pack2t<DT>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-                        qv.z = pack2t<DT>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-                        qv.w = pack2t<DT>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = qv;
-                    }
+                for (int g = 0; g < 4; ++g) {
+                    uint4 qv;
+                    qv.x = pack2t<DT>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+                    qv.y = pack2t<DT>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+                    qv.z = pack2t<DT>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+                    qv.w = pack2t<DT>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+                    const int chunk = (c * 4 + g) ^ (tid & 7);
+                    *reinterpret_cast<uint4*>(orow + chunk * 16) = qv;
                 }
             }
+            fence_async_proxy_shared();
         }
         tcgen05_fence_before();
-        __syncthreads();   // orders this item's TMEM reads before the next item's UMMAs
+        __syncthreads();   // also orders this item's TMEM reads before the next item's UMMAs
+        if (tid == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&tm_o)), "r"(smem_u32(smem + OFF_V)), "r"(head * HD), "r"(0),
+                           "r"(b)
+                         : "memory");
+            tma_store_commit();
+            if (next < num_items) {
+                tma_store_wait_read<0>();   // the store has read the staged tile: V may be overwritten
+                load_v(next);
+            }
+        }
     }
-    if (tid == 0 && !ok) {
-        for (int i = 0; i < 64; ++i) nanosleep(10000);   // let copies in flight land
+    if (tid == 0) {
+        if (ok) tma_store_wait_read<0>();
+        else for (int i = 0; i < 64; ++i) nanosleep(10000);   // let copies in flight land
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -781,6 +805,9 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
     p.status = device_status_ptr();
 
     if (d->S <= 128) {
+        const uint64_t so[2] = {static_cast<uint64_t>(d->ldo) * 2, static_cast<uint64_t>(d->ldo) * 2 * d->S};
+        CUtensorMap to;
+        if (!get_tensor_map(&to, d->out, 3, dims, so, box)) return B200_ERR_DRIVER;
         if (!set_attention_attributes(dev)) return B200_ERR_LAUNCH;
         const long long items = static_cast<long long>(d->heads) * d->B;
         if (items > 0x7fffffff) return B200_ERR_UNSUPPORTED;
@@ -790,10 +817,10 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
         const cudaStream_t st = static_cast<cudaStream_t>(stream_);
         if (d->dtype == B200_F16)
             launch_kernel(attention_single_kernel<B200_F16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
-                          S1_SMEM, st, tq, tk, tv, p, static_cast<int>(items));
+                          S1_SMEM, st, tq, tk, tv, to, p, static_cast<int>(items));
         else
             launch_kernel(attention_single_kernel<B200_BF16>, dim3(static_cast<unsigned>(grid1)), dim3(kAttnThreads),
-                          S1_SMEM, st, tq, tk, tv, p, static_cast<int>(items));
+                          S1_SMEM, st, tq, tk, tv, to, p, static_cast<int>(items));
         count_launch();
         return check_launch();
     }
@@ -866,9 +893,10 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
     const uint64_t sq[2] = {static_cast<uint64_t>(d->ldq) * 2, static_cast<uint64_t>(d->ldq) * 2 * d->S};
     const uint64_t sk[2] = {static_cast<uint64_t>(d->ldk) * 2, static_cast<uint64_t>(d->ldk) * 2 * d->S};
     const uint64_t sv[2] = {static_cast<uint64_t>(d->ldv) * 2, static_cast<uint64_t>(d->ldv) * 2 * d->S};
-    CUtensorMap tq, tk, tv;
+    const uint64_t so[2] = {static_cast<uint64_t>(d->ldo) * 2, static_cast<uint64_t>(d->ldo) * 2 * d->S};
+    CUtensorMap tq, tk, tv, to;
     if (!encode_tensor_map(&tq, d->q, 3, dims, sq, box) || !encode_tensor_map(&tk, d->k, 3, dims, sk, box) ||
-        !encode_tensor_map(&tv, d->v, 3, dims, sv, box))
+        !encode_tensor_map(&tv, d->v, 3, dims, sv, box) || !encode_tensor_map(&to, d->out, 3, dims, so, box))
         return B200_ERR_DRIVER;
 
     AttnParams p;
@@ -893,10 +921,10 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
         const long long grid1 = items < 1ll * S1_CTAS_PER_SM * sms ? items : 1ll * S1_CTAS_PER_SM * sms;
         if (d->dtype == B200_F16)
             attention_single_kernel<B200_F16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
-                tq, tk, tv, p, static_cast<int>(items));
+                tq, tk, tv, to, p, static_cast<int>(items));
         else
             attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
-                tq, tk, tv, p, static_cast<int>(items));
+                tq, tk, tv, to, p, static_cast<int>(items));
     } else {
         dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
                   static_cast<unsigned>(d->B));
