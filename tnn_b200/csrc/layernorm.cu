@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(B200LayerNormDesc d)
 // speed is the number of resident warps.
 template <int NV, bool F32IN, bool RESID>
 __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4)) add_layernorm_rows_kernel(B200LayerNormDesc d) {
-    extern __shared__ float gb[];   // gamma[H] | beta[H]
+    extern __shared__ float gb[];   // gamma | beta, NV * 256 floats each, in the lane-major layout described below
     const int lane = threadIdx.x & 31;
     const int H = static_cast<int>(d.H);
     const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -167,9 +167,15 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4))
     long long row = warp0;
     // gamma/beta are constants: they are staged while the producer of x may still be running
     pdl_launch_dependents();
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-        *reinterpret_cast<float4*>(gb + i) = __ldg(reinterpret_cast<const float4*>(d.gamma + i));
-        *reinterpret_cast<float4*>(gb + H + i) = __ldg(reinterpret_cast<const float4*>(d.beta + i));
+    // Layout: the two float4 halves of a lane's group of 8 live in separate planes, [g][half][lane], so that the 32 lanes
+    // of a warp read 32 consecutive float4 (4 wavefronts per load, the minimum; in feature order the lanes would sit
+    // 32 bytes apart, every load would take 8 wavefronts, and the kernel was bound by exactly that: 94 % of the
+    // L1 / shared-memory pipe at 44 % of HBM in the profile).
+    for (int j = threadIdx.x; j < H / 4; j += blockDim.x) {
+        const int gi = j >> 1, half = j & 1;
+        const int dst = (((gi >> 5) * 2 + half) * 32 + (gi & 31)) * 4;
+        *reinterpret_cast<float4*>(gb + dst) = __ldg(reinterpret_cast<const float4*>(d.gamma) + j);
+        *reinterpret_cast<float4*>(gb + NV * 256 + dst) = __ldg(reinterpret_cast<const float4*>(d.beta) + j);
     }
     pdl_wait();
     if (row < d.rows) fetch(row);
@@ -230,10 +236,9 @@ __global__ void __launch_bounds__(256, (NV >= 4 || F32IN) ? 2 : (RESID ? 3 : 4))
         for (int g = 0; g < NV; ++g) {
             const int gi = g * 32 + lane;
             if (gi < groups) {
-                const float4 g0 = *reinterpret_cast<const float4*>(gb + gi * 8);
-                const float4 g1 = *reinterpret_cast<const float4*>(gb + gi * 8 + 4);
-                const float4 b0 = *reinterpret_cast<const float4*>(gb + H + gi * 8);
-                const float4 b1 = *reinterpret_cast<const float4*>(gb + H + gi * 8 + 4);
+                const float4* gp = reinterpret_cast<const float4*>(gb) + g * 64 + lane;
+                const float4* bp = reinterpret_cast<const float4*>(gb + NV * 256) + g * 64 + lane;
+                const float4 g0 = gp[0], g1 = gp[32], b0 = bp[0], b1 = bp[32];
                 const uint64_t gm[4] = {pack_f32x2(g0.x, g0.y), pack_f32x2(g0.z, g0.w), pack_f32x2(g1.x, g1.y),
                                         pack_f32x2(g1.z, g1.w)};
                 const uint64_t bt[4] = {pack_f32x2(b0.x, b0.y), pack_f32x2(b0.z, b0.w), pack_f32x2(b1.x, b1.y),
@@ -382,7 +387,8 @@ int b200_add_layernorm_fwd(const B200LayerNormDesc* d, b200_stream_t stream_) {
         long long blocks = (d->rows + 7) / 8;
         if (blocks > 148ll * per_sm) blocks = 148ll * per_sm;
         const unsigned g2 = static_cast<unsigned>(blocks);
-        const size_t sm = static_cast<size_t>(d->H) * 2 * sizeof(float);
+        const int nv_t = nv <= 1 ? 1 : (nv <= 3 ? 3 : 4);                      // the template instance's groups per lane
+        const size_t sm = static_cast<size_t>(nv_t) * 256 * 2 * sizeof(float);   // gamma and beta planes
         if (nv <= 1) {
             if (f32) launch_rows<1, true>(d->residual != nullptr, g2, sm, stream, *d);
             else launch_rows<1, false>(d->residual != nullptr, g2, sm, stream, *d);

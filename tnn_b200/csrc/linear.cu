@@ -253,8 +253,12 @@ int launch_linear(const B200LinearDesc& d, cudaStream_t stream, int sm_count) {
 }
 
 // Tile choice.  Estimated time ~ waves * (columns per tile * cost per column + fixed per-tile cost), in units of
-// "accumulator columns per SM".  Pair tiles (256 x BN on two SMs) keep the tensor pipe busier than single-CTA tiles
-// (128 x BN) because they need half the w traffic per SM; narrow tiles pay more shared-memory reads per flop.
+// "accumulator columns per SM".  What bounds a k-block is the slower of the tensor pipe (2 clocks per accumulator
+// column for a 256-row pair tile) and the SM's read port from L2 (64 bytes per clock: every SM of a pair fetches 128
+// rows of x and BN/2 rows of w per k-block, (128 + BN/2) * 128 bytes): 512 | 512 clocks for BN = 256, 384 | 448 for 192,
+// 256 | 384 for 128, 128 | 320 for 64 — the profile of the 256-wide tile shows 11.3 TB/s from L2 to the SMs, 80 % of
+// 148 ports, at 89 % tensor-pipe activity.  Hence the cost per column rises as tiles narrow.  Single-CTA tiles
+// (128 x BN) fetch BN rows of w per SM and k-block.
 struct TileChoice {
     bool pair;
     int bn;
@@ -264,7 +268,7 @@ TileChoice choose_tile(int64_t M, int64_t N, int sm_count) {
     double best_t = 1e300;
     if (M > 128) {
         const int bns[4] = {256, 192, 128, 64};
-        const double cost[4] = {1.0, 1.03, 1.10, 1.40};
+        const double cost[4] = {1.0, 1.17, 1.50, 2.50};
         for (int i = 0; i < 4; ++i) {
             int pairs = max_active_pairs(bns[i]);
             if (pairs <= 0) continue;

@@ -123,18 +123,21 @@ __device__ __forceinline__ void row_stats(const float* stats, int slots, long lo
 // are stored directly.  (Rotating more strips per warp was tried: the wait for the TMA engine to have read a strip is
 // not on the critical path, while the extra shared memory costs a pipeline stage.)
 //
-// With RES the residual tile comes in the same way: a TMA load of the 32 x 32 chunk into the strip one chunk ahead,
-// read back swizzled, added, and the strip is then reused for the output of that chunk.
+// With RES the residual tile comes in the same way: a TMA load of the 32 x 32 chunk into a strip one chunk ahead,
+// read back swizzled, added, and the strip is then reused for the output of that chunk.  Three strips rotate: the strip
+// that receives the residual of chunk c + 1 last held the output of chunk c - 2, whose store was issued a whole chunk
+// ago and has read its source by now (with two strips it was the store issued an instant earlier, and every chunk of
+// the short-K residual GEMMs, whose epilogue is co-critical, waited for the store engine).
 //
 // FOLD compiles the LayerNorm-folding paths in (row statistics in/out, folded input / residual LayerNorm); without
 // it the kernel carries neither their registers nor their shared-memory strips.
 constexpr int kStageBytesPerWarp = 32 * 64;
-template <bool RES> constexpr int strips_per_warp() { return RES ? 2 : 1; }
+template <bool RES> constexpr int strips_per_warp() { return RES ? 3 : 1; }
 template <bool FOLD> constexpr int vec_strips() { return FOLD ? 4 : 1; }   // bias|c2, c1, gamma, beta
 
 template <int CHUNKS, bool RES, bool FOLD>
 struct WarpEpilogue {
-    static constexpr int NSTRIPS = RES ? 2 : 1;
+    static constexpr int NSTRIPS = RES ? 3 : 1;
     const LinearParams& p;
     const CUtensorMap* tm_y;
     const CUtensorMap* tm_r;
@@ -187,10 +190,10 @@ struct WarpEpilogue {
         return c < CHUNKS && n_first + c * 32 < p.N && row0 < p.M;
     }
     // lane 0: start the residual load of the chunk that will be processed as number `seq`.  Its strip last held the
-    // output of chunk seq-2, the most recent store of this warp.
+    // output of chunk seq - 3; at most the latest store (chunk seq - 2 or later) may still be reading its strip.
     __device__ __forceinline__ void issue_residual(uint32_t seq, int n0, int row0) {
         if (lane == 0) {
-            tma_store_wait_read<0>();
+            tma_store_wait_read<1>();
             const uint32_t si = seq % NSTRIPS;
             mbar_expect_tx(rbars + si, kStageBytesPerWarp);
             tma_load_2d(strips + si * kStageBytesPerWarp, tm_r, rbars + si, n0, row0);

@@ -34,8 +34,8 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
-    uint64_t* res_bars = acc_empty + 2;                       // 2 per epilogue warp (RES only)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + 2 * EW);
+    uint64_t* res_bars = acc_empty + 2;                       // 3 per epilogue warp (RES only)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bars + 3 * EW);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -54,7 +54,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], 2 * EW);   // leader's copy: epilogue warps of both CTAs
         }
-        for (int b = 0; b < 2 * EW; ++b) mbar_init(&res_bars[b], 1);
+        for (int b = 0; b < 3 * EW; ++b) mbar_init(&res_bars[b], 1);
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tmap(&tm_x);
@@ -144,7 +144,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         float* vec_w = reinterpret_cast<float*>(smem + C::BIAS_OFFSET) + ew * vec_strips<FOLD>() * COLS;
         WarpEpilogue<CHUNKS, RES, FOLD> epi{p, &tm_y, &tm_r,
                                             smem + C::OUT_OFFSET + ew * kStageBytesPerWarp * strips_per_warp<RES>(),
-                                            res_bars + 2 * ew, abort_flag, lane, 0u};
+                                            res_bars + 3 * ew, abort_flag, lane, 0u};
         uint32_t tcount = 0;
         bool ok = true;
         const long long row_in_tile = static_cast<long long>(rank) * 128 + quarter * 32 + lane;
