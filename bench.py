@@ -13,7 +13,7 @@ Keys of the JSON line beyond the base contract:
   value        inputs resident in the instance's blobs: K x Instance::ForwardAsync, CUDA events on the instance's
                stream, the K-step block repeated until >= --min-seconds are measured, max over ranks
   e2e          host to host through TNN's API: BlobConverter::ConvertFromMatAsync of the inputs (fp32 Mats in page-locked
-               memory) -> ForwardAsync -> ConvertToMat of the fp32 output every step, two instances per GPU in turn
+               memory) -> ForwardAsync -> ConvertToMat of the fp32 output every step, three instances per GPU in turn
   e2e_pageable the same loop, one instance, pageable Mats;  e2e_half_io: half-precision Mats (half the bytes)
   roofline     the projection/FFN GEMM kernel (dominant): algorithmic FLOPs of its launches / their CUDA-event time
   cpu_baseline the reference's own DEVICE_X86 implementation timed on this host on a bounded sample (rank 0, N = 1)
@@ -190,9 +190,9 @@ def reduce_max_over_ranks(t, world):
 
 # ------------------------------------------------------------------------------------------------ our arm
 class PluginReplica:
-    """One or two TNN instances of the encoder on one GPU, DEVICE_CUDA served by the plug-in: the drop-in path an
-    unchanged TNN application takes.  Two instances are the serving arrangement: while one computes, the other's
-    input is on its way to the device and its previous output on its way back."""
+    """A few TNN instances of the encoder on one GPU, DEVICE_CUDA served by the plug-in: the drop-in path an unchanged
+    TNN application takes.  Several instances are the serving arrangement: while one computes, another's input is on
+    its way to the device and a third's output on its way back."""
 
     def __init__(self, wl, device_id, instances, input_dtype=None):
         import shutil
@@ -267,6 +267,35 @@ def run_ours(args):
     if total % world:
         raise SystemExit("--total-batch must be a multiple of the number of GPUs")
     B = total // world
+
+    # The step's two memory-bound kernels timed alone at this GPU's share of the batch, also before the long loops:
+    # the measured copy bandwidth they are compared with is a burst figure, and inside a power-capped step the SM
+    # clock is 30-40 % lower (the figures from inside the step are `attention_kernel` and `layernorm_kernel`).
+    alone = {}
+    if rank == 0 and not args.no_attention_sweep:
+        rows_ = B * SEQ
+        x_ = torch.randn(rows_, 768, device=dev).to(torch.float16)
+        y_ = torch.empty_like(x_)
+        g_, b_ = torch.ones(768, device=dev), torch.zeros(768, device=dev)
+        qkv_ = torch.randn(B, SEQ, 3 * 768, device=dev).to(torch.float16)
+        msk_ = torch.zeros(B, SEQ, device=dev)
+        kvl_ = ops.mask_to_kv_len(msk_)
+        for name_, fn_, bytes_ in (
+                ("layernorm", lambda: ops.add_layernorm(x_, g_, b_, 1e-12, out=y_), rows_ * 768 * 2 * 2),
+                ("attention", lambda: ops.attention(qkv_, 12, msk_, kvl_, out=y_.view(B, SEQ, 768)), rows_ * 768 * 2 * 4)):
+            for _ in range(3):
+                fn_()
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(10):
+                fn_()
+            a1.record()
+            torch.cuda.synchronize()
+            ms_ = a0.elapsed_time(a1) / 10
+            alone[name_] = {"ms": round(ms_, 4), "gbs": round(bytes_ / ms_ / 1e6, 1),
+                            "frac_of_hbm_peak": round(bytes_ / ms_ / 1e6 / peaks["hbm_gbs"], 4)}
+        del x_, y_, qkv_
     wl = model_synth.make_workload(model_synth.BERT_BASE, B, SEQ, seed=0 + rank)
     cfg = wl.cfg
     H, F, L = cfg.hidden, cfg.ffn, len(wl.weights)
@@ -278,7 +307,9 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    replica = PluginReplica(wl, local, instances=2)
+    # Three instances: one instance's chain per step is H2D -> Forward -> D2H; with 403 MB each way the two copies
+    # together can take longer than a Forward, and the third instance keeps the GPU fed meanwhile.
+    replica = PluginReplica(wl, local, instances=args.pipeline_instances)
     insts = replica.insts
     streams = [torch.cuda.ExternalStream(i.command_queue(), device=dev) for i in insts]
 
@@ -336,7 +367,7 @@ def run_ours(args):
         raise SystemExit("device status word set: a bounded wait ran out")
 
     # ---- e2e: the same metric host to host through TNN's API — per step ConvertFromMatAsync of the inputs (fp32 Mats
-    # in page-locked host memory), ForwardAsync, ConvertToMat of the fp32 output; two instances in turn
+    # in page-locked host memory), ForwardAsync, ConvertToMat of the fp32 output; the instances in turn
     def pinned(a):
         p = tnn_runtime.PinnedArray(a.shape, a.dtype)
         p.array[...] = a
@@ -373,7 +404,7 @@ def run_ours(args):
     # the same with half-precision Mats (the model declares a half input; RESERVED_FP16_TEST Mats): half the bytes
     half_s = None
     if not args.no_half_io:
-        rep16 = PluginReplica(wl, local, instances=2, input_dtype="half")
+        rep16 = PluginReplica(wl, local, instances=args.pipeline_instances, input_dtype="half")
         x16 = wl.x.astype(np.float16)
         for inst in rep16.insts:
             inst.set_input_half("x", x16)
@@ -507,7 +538,7 @@ def run_ours(args):
                       "note": "through TNN's API with the plug-in: per step BlobConverter::ConvertFromMatAsync of x and "
                               "the mask (Mats over page-locked host memory) -> Instance::ForwardAsync -> blocking "
                               "BlobConverter::ConvertToMat of the output (the reference benchmark's loop, "
-                              "test/test.cc:125-152), two instances per GPU in turn; wall clock"
+                              "test/test.cc:125-152), %d instances per GPU in turn; wall clock" % args.pipeline_instances
                               + ("" if numa is None else "; rank bound to the %d CPUs local to its GPU" % numa)}
         half_route = None if half_value is None else {
             "value": half_value, "unit": UNIT, "h2d_bytes_per_step": h2d16, "d2h_bytes_per_step": d2h16,
@@ -530,7 +561,7 @@ def run_ours(args):
                                    "%d GPU(s) (%d per GPU per step), fp16 weights, all sequences full length, fp32 "
                                    "activations in/out" % (total, SEQ, world, B),
                        "total_batch": total, "batch_per_gpu": B, "seq_len": SEQ, "layers": L,
-                       "parallelism": "batch-sharded replicas (one TNN instance pair per GPU), no collective",
+                       "parallelism": "batch-sharded replicas (%d TNN instances per GPU), no collective" % args.pipeline_instances,
                        "path": "TNN Instance::ForwardAsync on DEVICE_CUDA served by the tnn_b200 plug-in; CUDA-graph "
                                "replay inside the plug-in: " + json.dumps(graph_state),
                        "timed_steps": timed_steps, "blocks_of_steps": blocks,
@@ -562,15 +593,25 @@ def run_ours(args):
                                            "enqueues): includes 3-6 us of event handling per launch",
                          "achieved_event_bracketed": achieved_bracketed,
                          "traffic": ncu_traffic_per_launch(tokens, per_shape),
-                         "traffic_note": "DRAM read+write bytes per launch from one ncu capture per GEMM shape "
-                                         "(profiles/), averaged over the shapes captured"},
+                         "traffic_note": "DRAM read+write bytes per launch, averaged over the four GEMM shapes: from the "
+                                         "ncu captures at 32 768 rows (profiles/linear_pair_kernel_config5_shapes_"
+                                         "m32768.md) scaled by rows / 32768 (activations grow with the rows, the "
+                                         "weights are 1-5 MB); below the algorithmic bytes because part of every "
+                                         "output is still in L2 when its kernel ends"},
             "attention_sweep": attention_sweep,
             "attention_sweep_note": "each point: 10 launches between one CUDA-event pair, timed before the long loops "
                                     "(burst clocks, as the measured tensor peak was)",
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
-                                 "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"]},
+                                 "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"],
+                                 "gbs": tokens * H * 2 * 4 / attn_ms / 1e6,
+                                 "frac_of_hbm_peak": tokens * H * 2 * 4 / attn_ms / 1e6 / peaks["hbm_gbs"],
+                                 "bound": "hbm at S = 128: 64 flop per compulsory byte (QKV in, context out) against "
+                                          "a ridge of 256"},
             "layernorm_kernel": {"ms": ln_ms, "gbs": tokens * H * 2 * 2 / ln_ms / 1e6,
                                  "frac_of_hbm_peak": tokens * H * 2 * 2 / ln_ms / 1e6 / peaks["hbm_gbs"]},
+            "memory_bound_kernels_alone": alone,
+            "memory_bound_kernels_alone_note": "10 launches between one CUDA-event pair before the long loops (burst "
+                                               "clocks): compulsory bytes / time against the measured copy bandwidth",
             "model_tflops": value * flops_per_seq / 1e12,
             "model_frac_of_tensor_peak": value * flops_per_seq / 1e12 / peaks["tflops"] / world,
             "cpu_baseline": cpu_baseline,
@@ -582,17 +623,25 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of linear_pair_kernel, from ncu captures of the GEMM shapes
-# (profiles/linear_pair_kernel_*.md), keyed by the row count M the capture ran at.  The figures belong to that M only.
+# (profiles/linear_pair_kernel_*.md), keyed by the row count M the capture ran at.  ncu's size rule keeps captures small,
+# so the config-5 shares (131 072 ... 16 384 rows per GPU) are represented by the 32 768-row capture scaled by the row
+# count: x, the residual and y grow with M, the weights (1-5 MB) do not.
 NCU_DRAM_BYTES = {
     8192: {"qkv": 16.16e6 + 0.54e6, "ffn1": 17.35e6 + 2.26e6, "ffn2": 67.69e6 + 4.36e6},
+    32768: {"qkv": 53.91e6 + 99.29e6, "ffn1": 55.09e6 + 148.87e6, "ffn2": 257.54e6 + 39.24e6,
+            "out_proj": 101.89e6 + 24.31e6},
 }
 
 
 def ncu_traffic_per_launch(tokens, per_shape):
-    table = NCU_DRAM_BYTES.get(tokens)
-    if not table:
+    """Average DRAM bytes per GEMM launch of the step (the four shapes launch equally often)."""
+    if tokens in NCU_DRAM_BYTES:
+        table, scale = NCU_DRAM_BYTES[tokens], 1.0
+    elif tokens >= 16384:
+        table, scale = NCU_DRAM_BYTES[32768], tokens / 32768.0
+    else:
         return None
-    vals = [table[k] for k in per_shape if k in table]
+    vals = [table[k] * scale for k in per_shape if k in table]
     return sum(vals) / len(vals) if vals else None
 
 
@@ -628,6 +677,8 @@ def main():
     ap.add_argument("--no-half-io", action="store_true", help="skip the half-precision-Mat end-to-end figure")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-attention-sweep", action="store_true")
+    ap.add_argument("--pipeline-instances", type=int, default=3,
+                    help="TNN instances per GPU that the end-to-end loop alternates between")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -109,7 +109,7 @@ def test_back_to_back_pipelined_forwards_return_each_inputs_own_result(cuda_devi
         p.free()
 
 
-@pytest.mark.parametrize("n_inst", [1, 2])
+@pytest.mark.parametrize("n_inst", [1, 2, 3])
 def test_native_pipeline_loop_over_instances(cuda_device, n_inst):
     """tnnc_run_pipeline (the reference benchmark's loop, over one instance or two taken in turn): after the loop every
     instance's output buffer holds the result of the input it was given."""
