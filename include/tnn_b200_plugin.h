@@ -44,6 +44,11 @@ TNNB200_API uint64_t tnnb200_release_cached_memory(int device_id);
 /* Test hook: after `skip` more successful device allocations of the plug-in, the next `count` fail with
  * TNNERR_OUTOFMEMORY (host-side fault injection; count = 0 switches it off). */
 TNNB200_API void tnnb200_inject_allocation_failure(int skip, int count);
+/* Host-only self-test of the arena's sub-allocation logic (best fit over slabs, merging of freed ranges, the
+ * one-allocation-per-block mode with pooled = 0): `steps` seeded random requests and releases against a fake backing
+ * store, invariants checked after each.  No CUDA call is made.  Returns 0, or the step at which an invariant broke
+ * (message in `err`). */
+TNNB200_API int tnnb200_selftest_range_arena(unsigned seed, int steps, int pooled, char* err, int err_cap);
 
 /* CUDA-graph replay counters of the instance that owns `command_queue` (Instance::GetCommandQueue): out[0] Forwards
  * launched layer by layer, [1] captures, [2] graph launches, [3] failed captures / launches (re-run layer by layer).

@@ -4,11 +4,14 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <string>
 #include <unordered_map>
 #include <vector>
 
 #include "b200_cuda_context.h"
+#include "b200_range_arena.h"
 #include "tnn/utils/blob_memory_size_utils.h"
 #include "tnn/utils/data_type_utils.h"
 #include "tnn/utils/dims_utils.h"
@@ -25,40 +28,8 @@ constexpr size_t kAlign = 256;
 inline size_t RoundUp(size_t n, size_t a) { return (n + a - 1) / a * a; }
 
 // ---------------------------------------------------------------------------------------------------- device arena
-// One slab = one cudaMalloc.  Free ranges are kept by offset so that neighbours merge in O(log n).
-struct Slab {
-    char* base;
-    size_t size;
-    size_t in_use;
-    std::map<size_t, size_t> free_ranges;   // offset -> length
-};
-
-struct Live {
-    int device;
-    Slab* slab;
-    size_t length;
-};
-
-struct Arena {
-    std::mutex mu;
-    std::vector<Slab*> slabs[kMaxGpus];
-    std::unordered_map<void*, Live> live;
-    B200ArenaStats stats[kMaxGpus];
-    // pinned host blocks that were released and wait for the next request they fit
-    std::vector<std::pair<void*, size_t>> pinned_free;
-    std::unordered_map<void*, size_t> pinned_live;
-    uint64_t pinned_allocations = 0;
-    uint64_t pinned_bytes       = 0;
-    Arena() {
-        for (auto& s : stats) s = B200ArenaStats();
-    }
-};
-
-Arena& TheArena() {
-    static Arena* a = new Arena();   // never destroyed: blocks may be freed from static destructors of the host
-    return *a;
-}
-
+// One RangeArena per GPU (the sub-allocation logic, b200_range_arena.h) over cudaMalloc'ed slabs, plus a cache of pinned
+// host blocks.
 size_t SlabBytes() {
     static const size_t v = []() -> size_t {
         const char* e = std::getenv("TNN_B200_ARENA_SLAB_MB");
@@ -78,30 +49,40 @@ bool ArenaEnabled() {
     return on;
 }
 
-void* TakeFrom(Slab* s, std::map<size_t, size_t>::iterator it, size_t bytes) {
-    const size_t off = it->first, len = it->second;
-    s->free_ranges.erase(it);
-    if (len > bytes) s->free_ranges[off + bytes] = len - bytes;
-    s->in_use += bytes;
-    return s->base + off;
+struct Arena {
+    std::mutex mu;
+    tnn_b200::RangeArena* ranges[kMaxGpus];
+    B200ArenaStats stats[kMaxGpus];
+    // pinned host blocks that were released and wait for the next request they fit
+    std::vector<std::pair<void*, size_t>> pinned_free;
+    std::unordered_map<void*, size_t> pinned_live;
+    uint64_t pinned_allocations = 0;
+    uint64_t pinned_bytes       = 0;
+    Arena() {
+        for (auto& s : stats) s = B200ArenaStats();
+        for (auto& r : ranges) r = nullptr;
+    }
+    tnn_b200::RangeArena& Ranges(int dev) {
+        if (!ranges[dev]) ranges[dev] = new tnn_b200::RangeArena(SlabBytes(), kAlign, ArenaEnabled());
+        return *ranges[dev];
+    }
+};
+
+Arena& TheArena() {
+    static Arena* a = new Arena();   // never destroyed: blocks may be freed from static destructors of the host
+    return *a;
 }
 
-void GiveBack(Slab* s, size_t off, size_t len) {
-    s->in_use -= len;
-    auto next = s->free_ranges.lower_bound(off);
-    if (next != s->free_ranges.end() && off + len == next->first) {
-        len += next->second;
-        next = s->free_ranges.erase(next);
+void* CudaSlabAlloc(size_t bytes) {
+    void* base = nullptr;
+    if (cudaMalloc(&base, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
     }
-    if (next != s->free_ranges.begin()) {
-        auto prev = std::prev(next);
-        if (prev->first + prev->second == off) {
-            prev->second += len;
-            return;
-        }
-    }
-    s->free_ranges[off] = len;
+    return base;
 }
+
+void CudaSlabFree(void* base) { cudaFree(base); }   // the pointer identifies its GPU: no device switch needed
 
 }  // namespace
 
@@ -157,49 +138,19 @@ Status B200CudaDevice::Allocate(void** handle, size_t bytes) {
     }
     // 256-byte granularity: more than the TMA descriptors need (16), and vector loads of a trailing partial group
     // stay inside the block.
-    const size_t rounded = RoundUp(bytes ? bytes : 1, kAlign);
     Arena& a = TheArena();
     std::lock_guard<std::mutex> lock(a.mu);
     B200ArenaStats& st = a.stats[dev];
     ++st.requests;
-
-    Slab* best_slab = nullptr;
-    std::map<size_t, size_t>::iterator best_it;
-    if (ArenaEnabled()) {
-        size_t best_len = ~static_cast<size_t>(0);
-        for (Slab* s : a.slabs[dev]) {
-            for (auto it = s->free_ranges.begin(); it != s->free_ranges.end(); ++it) {
-                if (it->second >= rounded && it->second < best_len) {
-                    best_len  = it->second;
-                    best_slab = s;
-                    best_it   = it;
-                }
-            }
-        }
-    }
-    if (!best_slab) {
-        const size_t slab_bytes = ArenaEnabled() ? (rounded > SlabBytes() / 2 ? rounded : SlabBytes()) : rounded;
-        void* base = nullptr;
-        if (cudaMalloc(&base, slab_bytes) != cudaSuccess || base == nullptr) {
-            cudaGetLastError();
-            return Status(TNNERR_OUTOFMEMORY, "cuda alloc failed");
-        }
+    const tnn_b200::RangeArena::TakeResult r = a.Ranges(dev).Take(bytes, CudaSlabAlloc);
+    if (!r.ptr) return Status(TNNERR_OUTOFMEMORY, "cuda alloc failed");
+    if (r.new_slab) {
         ++st.driver_allocations;
-        st.bytes_reserved += slab_bytes;
-        Slab* s = new Slab();
-        s->base   = static_cast<char*>(base);
-        s->size   = slab_bytes;
-        s->in_use = 0;
-        s->free_ranges[0] = slab_bytes;
-        a.slabs[dev].push_back(s);
-        best_slab = s;
-        best_it   = s->free_ranges.begin();
+        st.bytes_reserved += r.new_slab;
     }
-    void* p = TakeFrom(best_slab, best_it, rounded);
-    a.live[p] = Live{dev, best_slab, rounded};
-    st.bytes_in_use += rounded;
+    st.bytes_in_use += r.length;
     ++st.live_blocks;
-    *handle = p;
+    *handle = r.ptr;
     return TNN_OK;
 }
 
@@ -207,28 +158,19 @@ Status B200CudaDevice::Free(void* handle) {
     if (!handle) return TNN_OK;
     Arena& a = TheArena();
     std::lock_guard<std::mutex> lock(a.mu);
-    auto it = a.live.find(handle);
-    if (it == a.live.end()) return Status(TNNERR_COMMON_ERROR, "cuda free: block does not belong to this device");
-    const Live l = it->second;
-    a.live.erase(it);
-    B200ArenaStats& st = a.stats[l.device];
-    st.bytes_in_use -= l.length;
-    --st.live_blocks;
-    GiveBack(l.slab, static_cast<size_t>(static_cast<char*>(handle) - l.slab->base), l.length);
-    if (!ArenaEnabled() && l.slab->in_use == 0) {
-        auto& v = a.slabs[l.device];
-        for (size_t i = 0; i < v.size(); ++i) {
-            if (v[i] == l.slab) {
-                v.erase(v.begin() + i);
-                break;
-            }
+    for (int dev = 0; dev < kMaxGpus; ++dev) {
+        if (!a.ranges[dev] || !a.ranges[dev]->Owns(handle)) continue;
+        const tnn_b200::RangeArena::GiveResult r = a.ranges[dev]->Give(handle, CudaSlabFree);
+        B200ArenaStats& st = a.stats[dev];
+        st.bytes_in_use -= r.length;
+        --st.live_blocks;
+        if (r.freed_slab) {
+            ++st.driver_frees;
+            st.bytes_reserved -= r.freed_slab;
         }
-        cudaFree(l.slab->base);
-        ++st.driver_frees;
-        st.bytes_reserved -= l.slab->size;
-        delete l.slab;
+        return TNN_OK;
     }
-    return TNN_OK;
+    return Status(TNNERR_COMMON_ERROR, "cuda free: block does not belong to this device");
 }
 
 uint64_t B200CudaDevice::ReleaseCachedMemory(int device_id) {
@@ -236,20 +178,12 @@ uint64_t B200CudaDevice::ReleaseCachedMemory(int device_id) {
     std::lock_guard<std::mutex> lock(a.mu);
     uint64_t released = 0;
     for (int dev = 0; dev < kMaxGpus; ++dev) {
-        if (device_id >= 0 && dev != device_id) continue;
-        auto& v = a.slabs[dev];
-        for (size_t i = 0; i < v.size();) {
-            if (v[i]->in_use == 0) {
-                cudaFree(v[i]->base);   // the pointer identifies its GPU: no device switch needed
-                ++a.stats[dev].driver_frees;
-                a.stats[dev].bytes_reserved -= v[i]->size;
-                released += v[i]->size;
-                delete v[i];
-                v.erase(v.begin() + i);
-            } else {
-                ++i;
-            }
-        }
+        if ((device_id >= 0 && dev != device_id) || !a.ranges[dev]) continue;
+        size_t slabs      = 0;
+        const size_t freed = a.ranges[dev]->ReleaseEmpty(CudaSlabFree, &slabs);
+        a.stats[dev].driver_frees += slabs;
+        a.stats[dev].bytes_reserved -= freed;
+        released += freed;
     }
     for (auto& b : a.pinned_free) {
         cudaFreeHost(b.first);
@@ -259,6 +193,86 @@ uint64_t B200CudaDevice::ReleaseCachedMemory(int device_id) {
     a.pinned_free.clear();
     cudaGetLastError();
     return released;
+}
+
+// Host-only exercise of the sub-allocation logic: a seeded random sequence of requests and releases against a fake
+// backing store (address ranges that are never touched), with the structural invariants checked after every step.
+// Returns 0, or the number of the step at which an invariant broke (message in `why`).
+int B200CudaDevice::SelfTestRangeArena(unsigned seed, int steps, int pooled, std::string* why) {
+    struct Backing {
+        uintptr_t next = 1u << 20;
+        std::map<uintptr_t, size_t> slabs;
+        size_t allocated = 0, freed = 0;
+    } backing;
+    auto alloc = [&](size_t bytes) -> void* {
+        const uintptr_t base = backing.next;
+        backing.next += (bytes + 4095) / 4096 * 4096 + 4096;   // a hole between slabs: blocks must not merge across them
+        backing.slabs[base] = bytes;
+        ++backing.allocated;
+        return reinterpret_cast<void*>(base);
+    };
+    auto release = [&](void* p) {
+        backing.slabs.erase(reinterpret_cast<uintptr_t>(p));
+        ++backing.freed;
+    };
+    const size_t slab = 1u << 20, align = 256;
+    tnn_b200::RangeArena arena(slab, align, pooled != 0);
+    std::vector<std::pair<void*, size_t>> held;
+    uint64_t state = seed * 2654435761u + 12345u;
+    auto rnd = [&]() -> uint32_t {
+        state = state * 6364136223846793005ull + 1442695040888963407ull;
+        return static_cast<uint32_t>(state >> 33);
+    };
+    auto fail = [&](int step, const std::string& msg) {
+        if (why) *why = msg;
+        return step;
+    };
+    for (int step = 1; step <= steps; ++step) {
+        const bool take = held.empty() || (rnd() % 100) < (held.size() < 200 ? 60u : 35u);
+        if (take) {
+            const uint32_t kind = rnd() % 10;
+            const size_t bytes = kind == 0 ? 0 : kind < 6 ? 1 + rnd() % 5000 : kind < 9 ? 1 + rnd() % 300000
+                                                                                          : slab / 2 + rnd() % (2 * slab);
+            const auto r = arena.Take(bytes, alloc);
+            if (!r.ptr) return fail(step, "Take failed although the backing store never refuses");
+            if (r.length < bytes || r.length % align || r.length >= bytes + align + (bytes ? 0 : 1))
+                return fail(step, "wrong rounded length");
+            // the block lies inside one slab of the backing store
+            const uintptr_t p = reinterpret_cast<uintptr_t>(r.ptr);
+            auto it = backing.slabs.upper_bound(p);
+            if (it == backing.slabs.begin()) return fail(step, "block below every slab");
+            --it;
+            if (p + r.length > it->first + it->second) return fail(step, "block reaches past its slab");
+            for (const auto& h : held) {
+                const uintptr_t q = reinterpret_cast<uintptr_t>(h.first);
+                if (p < q + h.second && q < p + r.length) return fail(step, "two live blocks overlap");
+            }
+            held.push_back(std::make_pair(r.ptr, r.length));
+        } else {
+            const size_t i = rnd() % held.size();
+            const auto r = arena.Give(held[i].first, release);
+            if (!r.found || r.length != held[i].second) return fail(step, "Give did not recognise a live block");
+            if (arena.Give(held[i].first, release).found) return fail(step, "a block could be given back twice");
+            held.erase(held.begin() + i);
+        }
+        const std::string bad = arena.CheckInvariants();
+        if (!bad.empty()) return fail(step, bad);
+        if (arena.live_blocks() != held.size()) return fail(step, "live block count");
+        size_t bytes_held = 0;
+        for (const auto& h : held) bytes_held += h.second;
+        if (arena.bytes_in_use() != bytes_held) return fail(step, "bytes in use");
+        if (!pooled && arena.slab_count() != held.size()) return fail(step, "unpooled: one slab per block");
+    }
+    for (const auto& h : held)
+        if (!arena.Give(h.first, release).found) return fail(steps + 1, "final release");
+    const std::string bad = arena.CheckInvariants();
+    if (!bad.empty()) return fail(steps + 1, bad);
+    if (arena.bytes_in_use() != 0 || arena.live_blocks() != 0) return fail(steps + 1, "not empty after releasing all");
+    const size_t reserved = arena.bytes_reserved();
+    if (arena.ReleaseEmpty(release) != reserved || arena.slab_count() != 0 || !backing.slabs.empty() ||
+        backing.allocated != backing.freed)
+        return fail(steps + 2, "slabs left behind after ReleaseEmpty");
+    return 0;
 }
 
 B200ArenaStats B200CudaDevice::Stats(int device_id) {

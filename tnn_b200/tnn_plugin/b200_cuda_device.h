@@ -19,6 +19,7 @@
 
 #include <cstdint>
 #include <map>
+#include <string>
 #include <memory>
 
 #include "tnn/core/abstract_device.h"
@@ -70,6 +71,11 @@ public:
     // Test hook: after `skip` more successful device allocations, the next `count` fail with TNNERR_OUTOFMEMORY
     // (host-side fault injection; no GPU fault is provoked).  count = 0 switches it off.
     static void InjectAllocationFailure(int skip, int count);
+
+    // Host-only self-test of the arena's sub-allocation logic (no CUDA call): `steps` seeded random requests and
+    // releases against a fake backing store with the structural invariants checked after each; pooled = 0 tests the
+    // one-allocation-per-block mode.  Returns 0, or the step at which an invariant broke (message in `why`).
+    static int SelfTestRangeArena(unsigned seed, int steps, int pooled, std::string* why);
 
 private:
     static std::map<LayerType, std::shared_ptr<LayerAccCreator>>& GetLayerCreatorMap();

@@ -94,6 +94,9 @@ def load():
         plugin.tnnb200_release_cached_memory.restype = ctypes.c_uint64
         plugin.tnnb200_release_cached_memory.argtypes = [ctypes.c_int]
         plugin.tnnb200_inject_allocation_failure.argtypes = [ctypes.c_int, ctypes.c_int]
+        plugin.tnnb200_selftest_range_arena.restype = ctypes.c_int
+        plugin.tnnb200_selftest_range_arena.argtypes = [ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_char_p,
+                                                        ctypes.c_int]
         plugin.tnnb200_graph_counters.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint64)]
         plugin.tnnb200_host_alloc.restype = ctypes.c_void_p
         plugin.tnnb200_host_alloc.argtypes = [ctypes.c_size_t]
@@ -169,6 +172,14 @@ def inject_allocation_failure(skip, count):
     report out-of-memory (count = 0 switches it off)."""
     _, plugin = load()
     plugin.tnnb200_inject_allocation_failure(int(skip), int(count))
+
+
+def selftest_range_arena(seed, steps, pooled=True):
+    """Runs the arena's host-only self-test (no CUDA call); returns (failing step or 0, message)."""
+    _, plugin = load()
+    err = ctypes.create_string_buffer(256)
+    rc = plugin.tnnb200_selftest_range_arena(int(seed), int(steps), 1 if pooled else 0, err, len(err))
+    return int(rc), err.value.decode()
 
 
 class PinnedArray:
