@@ -298,3 +298,44 @@ def test_saved_fused_model_runs_identically(cuda_device):
     a = _run(proto, model, wl, rt.DEVICE_CUDA)
     b = _run(proto2, model2, wl, rt.DEVICE_CUDA)
     assert np.array_equal(a, b)
+
+
+def test_instance_reshape_within_the_created_shapes(cuda_device):
+    """Instance::Reshape (source/tnn/core/instance.cc:143-152, default_network.cc:456-500): smaller batch and sequence
+    length, then back to the created shape, on the same instances.  DEVICE_CUDA must follow DEVICE_X86 at every shape
+    (the replayed graph of the previous shape must not be used), take nothing from the driver on the way, and return
+    to the first result bit for bit."""
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    proto, model = _files(wl)
+    B, S, H = wl.x.shape
+    cuda = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    x86 = rt.Instance(proto, model, device=rt.DEVICE_X86, precision=rt.PRECISION_HIGH)
+
+    def run(inst, x, mask):
+        inst.set_input("x", x)
+        inst.set_input("mask", mask)
+        inst.forward()
+        inst.forward()          # the second Forward of a shape is the captured one, the third a replay
+        inst.forward()
+        return inst.get_output()
+
+    first = run(cuda, wl.x, wl.mask_add)
+    before = rt.arena_stats(0)
+    captures = cuda.graph_counters()["captures"]
+    for b, s in ((1, 96), (B, 64), (1, 1), (B, S - 8), (B, S)):
+        x = np.ascontiguousarray(wl.x[:b, :s])
+        mask = np.ascontiguousarray(wl.mask_add[:b, :, :, :s])
+        for inst in (cuda, x86):
+            inst.reshape({"x": [b, s, H], "mask": [b, 1, 1, s]})
+        y, ref = run(cuda, x, mask), run(x86, x, mask)
+        assert y.shape == ref.shape == (b, s, H)
+        lengths = np.minimum(wl.lengths[:b], s)
+        assert max_abs(valid_rows(y, lengths), valid_rows(ref, lengths)) <= MAX_ABS_TOL, (b, s)
+        assert cosine(y, ref) >= COS_TOL, (b, s)
+    assert np.array_equal(y, first)
+    after = rt.arena_stats(0)
+    assert after["driver_allocations"] == before["driver_allocations"]
+    counters = cuda.graph_counters()
+    assert counters["captures"] > captures and counters["failures"] == 0
+    cuda.close()
+    x86.close()

@@ -377,6 +377,22 @@ TNNC_API double tnnc_run_pipeline(void** handles, int n_handles, const TnncIo* i
     return std::chrono::duration<double, std::milli>(t1 - t0).count();
 }
 
+// Instance::Reshape: new dims for `n_inputs` named input blobs at once (dims_flat holds them back to back, nds[i] dims
+// each).  The shapes must stay within those the instance was created with (TNN sizes blob memory at Init).
+TNNC_API int tnnc_reshape(void* handle, int n_inputs, const char* const* names, const int* dims_flat, const int* nds) {
+    Handle* h = static_cast<Handle*>(handle);
+    if (!names || !dims_flat || !nds || n_inputs <= 0) { h->last_error = "bad arguments"; return -1; }
+    InputShapesMap shapes;
+    const int* p = dims_flat;
+    for (int i = 0; i < n_inputs; ++i) {
+        shapes[names[i]] = DimsVector(p, p + nds[i]);
+        p += nds[i];
+    }
+    Status st = h->inst->Reshape(shapes);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st ? (int)st : -1; }
+    return 0;
+}
+
 TNNC_API int tnnc_forward(void* handle) {
     Handle* h = static_cast<Handle*>(handle);
     Status st = h->inst->Forward();

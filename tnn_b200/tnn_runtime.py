@@ -76,6 +76,8 @@ def load():
                                                 ctypes.POINTER(ctypes.c_void_p)]
         shim.tnnc_get_output_device.restype = ctypes.c_int64
         shim.tnnc_forward.argtypes = [ctypes.c_void_p]
+        shim.tnnc_reshape.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                      ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         shim.tnnc_time_forward.restype = ctypes.c_double
         shim.tnnc_time_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
         shim.tnnc_get_output.restype = ctypes.c_int64
@@ -310,6 +312,14 @@ class Instance:
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
+
+    def reshape(self, shapes):
+        """Instance::Reshape with `{input name: dims}`; the shapes must stay within those of the model file."""
+        names = (ctypes.c_char_p * len(shapes))(*[k.encode() for k in shapes])
+        flat = [int(d) for v in shapes.values() for d in v]
+        dims = (ctypes.c_int * len(flat))(*flat)
+        nds = (ctypes.c_int * len(shapes))(*[len(v) for v in shapes.values()])
+        self._check(self.shim.tnnc_reshape(self.h, len(shapes), names, dims, nds), "Reshape")
 
     # ---- the caller-driven conversion path (BlobConverter + ForwardAsync, as the reference's benchmark uses them)
     def from_mat_async(self, name, arr):
