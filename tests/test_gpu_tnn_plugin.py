@@ -339,3 +339,53 @@ def test_instance_reshape_within_the_created_shapes(cuda_device):
     assert counters["captures"] > captures and counters["failures"] == 0
     cuda.close()
     x86.close()
+
+
+def test_share_memory_modes_and_shared_command_queue(cuda_device):
+    """NetworkConfig.share_memory_mode and Instance::ShareCommandQueue on DEVICE_CUDA (include/tnn/core/common.h:117-125,
+    source/tnn/core/blob_manager.cc:230-262,314-330, source/tnn/device/cuda/cuda_context.cc ShareCommandQueue): blob
+    memory provided by the caller (handles = base + bytes_offset), blob memory shared by the instances of one thread,
+    and two instances on one command queue all give the result of a default instance, bit for bit."""
+    import torch
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    proto, model = _files(wl)
+    x2 = np.ascontiguousarray(wl.x * np.float32(0.5))
+
+    def run(inst, x):
+        inst.set_input("x", x)
+        inst.set_input("mask", wl.mask_add)
+        inst.forward()
+        inst.forward()
+        return inst.get_output()
+
+    plain = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    want1, want2 = run(plain, wl.x), run(plain, x2)
+    assert not np.array_equal(want1, want2)
+
+    ext = rt.Instance(proto, model, device=rt.DEVICE_CUDA, share_memory_mode=rt.SHARE_MEMORY_FROM_EXTERNAL)
+    size = ext.forward_memory_size()
+    assert size > wl.x.nbytes
+    block = torch.full((size + 512,), 0x5A, dtype=torch.uint8, device=cuda_device)
+    ext.set_forward_memory(block.data_ptr())
+    assert np.array_equal(run(ext, wl.x), want1)
+    assert np.array_equal(run(ext, x2), want2)
+    torch.cuda.synchronize()
+    assert bool((block[size:] == 0x5A).all())          # nothing was written behind the block
+    ext.close()
+
+    a = rt.Instance(proto, model, device=rt.DEVICE_CUDA, share_memory_mode=rt.SHARE_MEMORY_ONE_THREAD)
+    b = rt.Instance(proto, model, device=rt.DEVICE_CUDA, share_memory_mode=rt.SHARE_MEMORY_ONE_THREAD)
+    for _ in range(2):                                  # the instances take turns on the shared blob memory
+        assert np.array_equal(run(a, wl.x), want1)
+        assert np.array_equal(run(b, x2), want2)
+    a.close()
+    b.close()
+
+    c = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
+    c.share_command_queue(plain)
+    assert c.command_queue() == plain.command_queue()
+    for _ in range(2):
+        assert np.array_equal(run(c, x2), want2)
+        assert np.array_equal(run(plain, wl.x), want1)
+    c.close()
+    plain.close()

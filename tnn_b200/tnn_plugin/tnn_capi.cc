@@ -75,8 +75,11 @@ extern "C" {
 
 // device: 0 = DEVICE_NAIVE, 1 = DEVICE_X86, 2 = DEVICE_CUDA.  precision: -1 auto, 0 normal, 1 high, 2 low.
 // Returns an opaque handle or NULL (message in err).
-TNNC_API void* tnnc_create(const char* proto_path, const char* model_path, int device, int device_id, int precision,
-                           int cpu_threads, char* err, int errlen) {
+// share_memory_mode: 0 = every instance allocates its blob memory, 1 = instances created by one thread share it
+// (SHARE_MEMORY_MODE_SHARE_ONE_THREAD), 2 = the caller provides it (SHARE_MEMORY_MODE_SET_FROM_EXTERNAL: ask
+// tnnc_forward_memory_size, then tnnc_set_forward_memory before the first Forward).
+TNNC_API void* tnnc_create_ex(const char* proto_path, const char* model_path, int device, int device_id, int precision,
+                              int cpu_threads, int share_memory_mode, char* err, int errlen) {
     std::unique_ptr<Handle> h(new Handle);
     ModelConfig mc;
     mc.model_type = MODEL_TYPE_TNN;
@@ -96,6 +99,7 @@ TNNC_API void* tnnc_create(const char* proto_path, const char* model_path, int d
     nc.device_id = device_id;
     nc.network_type = NETWORK_TYPE_DEFAULT;
     nc.precision = static_cast<Precision>(precision);
+    nc.share_memory_mode = static_cast<ShareMemoryMode>(share_memory_mode);
     h->device = nc.device_type;
     h->inst = h->net.CreateInst(nc, st);
     if (st != TNN_OK || !h->inst) {
@@ -106,7 +110,37 @@ TNNC_API void* tnnc_create(const char* proto_path, const char* model_path, int d
     return h.release();
 }
 
+TNNC_API void* tnnc_create(const char* proto_path, const char* model_path, int device, int device_id, int precision,
+                           int cpu_threads, char* err, int errlen) {
+    return tnnc_create_ex(proto_path, model_path, device, device_id, precision, cpu_threads, 0, err, errlen);
+}
+
 TNNC_API void tnnc_destroy(void* handle) { delete static_cast<Handle*>(handle); }
+
+// Instance::GetForwardMemorySize / SetForwardMemory (include/tnn/core/instance.h): bytes of blob memory the instance
+// needs, and the caller's block of that size on the instance's device.
+TNNC_API int64_t tnnc_forward_memory_size(void* handle) {
+    Handle* h = static_cast<Handle*>(handle);
+    int bytes = 0;   // the reference's interface counts in int: blob memory above 2 GiB cannot be set from outside
+    Status st = h->inst->GetForwardMemorySize(bytes);
+    if (st != TNN_OK) { h->last_error = st.description(); return -1; }
+    return static_cast<int64_t>(bytes);
+}
+
+TNNC_API int tnnc_set_forward_memory(void* handle, void* memory) {
+    Handle* h = static_cast<Handle*>(handle);
+    Status st = h->inst->SetForwardMemory(memory);
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st ? (int)st : -1; }
+    return 0;
+}
+
+// Instance::ShareCommandQueue: `handle` enqueues on `other`'s command queue from now on.
+TNNC_API int tnnc_share_command_queue(void* handle, void* other) {
+    Handle* h = static_cast<Handle*>(handle);
+    Status st = h->inst->ShareCommandQueue(static_cast<Handle*>(other)->inst.get());
+    if (st != TNN_OK) { h->last_error = st.description(); return (int)st ? (int)st : -1; }
+    return 0;
+}
 
 TNNC_API const char* tnnc_last_error(void* handle) { return static_cast<Handle*>(handle)->last_error.c_str(); }
 

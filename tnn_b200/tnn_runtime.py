@@ -63,6 +63,13 @@ def load():
         shim.tnnc_create.restype = ctypes.c_void_p
         shim.tnnc_create.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                      ctypes.c_int, ctypes.c_char_p, ctypes.c_int]
+        shim.tnnc_create_ex.restype = ctypes.c_void_p
+        shim.tnnc_create_ex.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                        ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_int]
+        shim.tnnc_forward_memory_size.restype = ctypes.c_int64
+        shim.tnnc_forward_memory_size.argtypes = [ctypes.c_void_p]
+        shim.tnnc_set_forward_memory.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        shim.tnnc_share_command_queue.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         shim.tnnc_destroy.argtypes = [ctypes.c_void_p]
         shim.tnnc_last_error.restype = ctypes.c_char_p
         shim.tnnc_last_error.argtypes = [ctypes.c_void_p]
@@ -242,14 +249,18 @@ def run_pipeline(instances, inputs, outputs, warmup, steps):
     return ms / 1e3
 
 
+SHARE_MEMORY_DEFAULT, SHARE_MEMORY_ONE_THREAD, SHARE_MEMORY_FROM_EXTERNAL = 0, 1, 2
+
+
 class Instance:
     """TNN::Init + CreateInst on a device; set_input / forward / get_output move fp32 host arrays."""
 
-    def __init__(self, proto_path, model_path, device=DEVICE_CUDA, device_id=0, precision=PRECISION_AUTO, threads=1):
+    def __init__(self, proto_path, model_path, device=DEVICE_CUDA, device_id=0, precision=PRECISION_AUTO, threads=1,
+                 share_memory_mode=SHARE_MEMORY_DEFAULT):
         self.shim, _ = load()
         err = ctypes.create_string_buffer(1024)
-        self.h = self.shim.tnnc_create(proto_path.encode(), model_path.encode(), device, device_id, precision,
-                                       threads, err, 1024)
+        self.h = self.shim.tnnc_create_ex(proto_path.encode(), model_path.encode(), device, device_id, precision,
+                                          threads, share_memory_mode, err, 1024)
         if not self.h:
             raise RuntimeError("TNN instance creation failed: %s" % err.value.decode())
 
@@ -312,6 +323,21 @@ class Instance:
 
     def forward(self):
         self._check(self.shim.tnnc_forward(self.h), "Forward")
+
+    def forward_memory_size(self):
+        """Instance::GetForwardMemorySize: bytes of blob memory the instance needs."""
+        n = self.shim.tnnc_forward_memory_size(self.h)
+        if n < 0:
+            raise RuntimeError("GetForwardMemorySize: %s" % self.shim.tnnc_last_error(self.h).decode())
+        return int(n)
+
+    def set_forward_memory(self, device_pointer):
+        """Instance::SetForwardMemory (share_memory_mode SET_FROM_EXTERNAL): the caller's block on the device."""
+        self._check(self.shim.tnnc_set_forward_memory(self.h, ctypes.c_void_p(device_pointer)), "SetForwardMemory")
+
+    def share_command_queue(self, other):
+        """Instance::ShareCommandQueue: this instance enqueues on `other`'s command queue from now on."""
+        self._check(self.shim.tnnc_share_command_queue(self.h, other.h), "ShareCommandQueue")
 
     def reshape(self, shapes):
         """Instance::Reshape with `{input name: dims}`; the shapes must stay within those of the model file."""
