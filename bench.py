@@ -340,8 +340,10 @@ def run_ours(args):
     graph_state = insts[0].graph_counters()
     barrier()
 
-    # ---- timed region: inputs resident in the instance's blobs, `steps` x ForwardAsync, CUDA events on the
-    # instance's own stream; the block is repeated until at least `--min-seconds` of device time have been measured
+    # ---- timed region: inputs resident in the instances' blobs, `steps` x ForwardAsync over the instances in turn (the
+    # serving arrangement: one instance's wave tails are filled by the next one's kernels), CUDA events on the first
+    # instance's stream, which waits for the others at the end of the block; the block is repeated until at least
+    # `--min-seconds` of device time have been measured
     sampler = ClockSampler(local)
     sampler.start()
     block_ms = []
@@ -350,8 +352,12 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(st0)
-        for _ in range(args.steps):
-            insts[0].forward_async()
+        for k in range(args.steps):
+            insts[k % len(insts)].forward_async()
+        for st in streams[1:]:                              # the block ends when every instance's stream has drained
+            done = torch.cuda.Event()
+            done.record(st)
+            st0.wait_event(done)
         e1.record(st0)
         barrier()
         block_ms.append(e0.elapsed_time(e1))
@@ -563,8 +569,8 @@ def run_ours(args):
                                    "activations in/out" % (total, SEQ, world, B),
                        "total_batch": total, "batch_per_gpu": B, "seq_len": SEQ, "layers": L,
                        "parallelism": "batch-sharded replicas (%d TNN instances per GPU), no collective" % args.pipeline_instances,
-                       "path": "TNN Instance::ForwardAsync on DEVICE_CUDA served by the tnn_b200 plug-in; CUDA-graph "
-                               "replay inside the plug-in: " + json.dumps(graph_state),
+                       "path": "TNN Instance::ForwardAsync on DEVICE_CUDA served by the tnn_b200 plug-in, the GPU's "
+                               "instances in turn; CUDA-graph replay inside the plug-in: " + json.dumps(graph_state),
                        "timed_steps": timed_steps, "blocks_of_steps": blocks,
                        "l2": "per-step working set (170 MB fp16 weights + activations) exceeds the 126 MB L2; "
                              "no explicit flush"},
