@@ -1,7 +1,10 @@
 // Fused multi-head attention for sm_100a, head_dim 64:  out = softmax(scale * Q K^T + mask) V, flash-style: no score
 // matrix ever leaves the SM.  Two kernels share the building blocks below:
 //   attention_single_kernel   S <= 128: persistent CTAs (four per SM), one (sequence, head) item at a time;
-//   attention_pingpong_kernel S  > 128: two 128-query tiles per CTA in ping-pong over a ring of 128-key tiles.
+//   attention_pingpong_kernel S  > 128: two 128-query tiles per CTA in ping-pong over a ring of 128-key tiles, one item
+//                             (256 queries of one head of one sequence) per CTA: used for S > 1024;
+//   attention_pingpong_persistent_kernel: the same with one CTA per SM walking a list of items without draining
+//                             anything in between: used for 128 < S <= 1024.
 //
 //   TMA   : Q, K, V tiles [128 x 64] straight out of the token-major QKV activation (the head split of the unfused
 //           graph's Reshape+Permute is just the TMA column coordinate h*64) into 128-byte-swizzled shared memory.
@@ -53,6 +56,8 @@ struct AttnParams {
     float mask_below;
     uint32_t idesc_qk, idesc_pv;
     unsigned int* status;
+    int n_qb;            // long-sequence kernel: query blocks (NWG x 128 queries) per sequence
+    long long n_items;   // long-sequence kernel: n_qb * heads * B
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -84,16 +89,20 @@ struct AttnParams {
 #ifndef PP_NWG
 #define PP_NWG 2
 #endif
-template <int NWG>
+template <int NWG, int QSETS>
 struct PPCfg {
     static constexpr int THREADS = 128 + 128 * NWG;               // control warpgroup + softmax warpgroups
     // registers per thread after the control warpgroup has handed most of its share to the softmax warpgroups
     static constexpr int REGS_CONTROL = 72;
     static constexpr int REGS_SOFTMAX = NWG == 1 ? 184 : 216;
     static constexpr int CTAS_PER_SM = NWG == 1 ? 2 : 1;
+    // setmaxnreg moves registers inside the pool the CTA was launched with (threads x the launch-time count, which
+    // the compiler caps at 65536 / threads-per-SM rounded down to 8): the raised count of the softmax warpgroups must
+    // fit into what the control warpgroup gives up, or setmaxnreg.inc waits forever.
+    static constexpr int REGS_LAUNCH = (65536 / (THREADS * (NWG == 1 ? 2 : 1))) / 8 * 8;
     static constexpr int NST = NWG == 1 ? 2 : 4;                  // K/V/mask ring depth (key tiles in flight)
-    static constexpr int OFF_Q = 0;                               // NWG x 16 KB
-    static constexpr int OFF_K = NWG * TILE_BYTES;
+    static constexpr int OFF_Q = 0;                               // two query sets of NWG x 16 KB (this item, the next)
+    static constexpr int OFF_K = QSETS * NWG * TILE_BYTES;
     static constexpr int OFF_V = OFF_K + NST * TILE_BYTES;
     static constexpr int OFF_MASK = OFF_V + NST * TILE_BYTES;     // NST x 128 floats
     static constexpr int OFF_BAR = OFF_MASK + NST * TK * 4;
@@ -102,13 +111,17 @@ struct PPCfg {
     static constexpr int COL_O = 128 * NWG;                       // + 64 * wg
     static constexpr int COL_P = 192 * NWG;                       // + 64 * wg
 };
+static_assert(128 * PPCfg<1, 1>::REGS_CONTROL + 128 * PPCfg<1, 1>::REGS_SOFTMAX <= PPCfg<1, 1>::THREADS * PPCfg<1, 1>::REGS_LAUNCH,
+              "setmaxnreg: the softmax warpgroup's registers must come out of the CTA's own pool");
+static_assert(128 * PPCfg<2, 1>::REGS_CONTROL + 256 * PPCfg<2, 1>::REGS_SOFTMAX <= PPCfg<2, 1>::THREADS * PPCfg<2, 1>::REGS_LAUNCH,
+              "setmaxnreg: the softmax warpgroups' registers must come out of the CTA's own pool");
 constexpr float kLazyLog2 = 8.0f;   // the running maximum moves only when a tile exceeds it by more than 2^8
 
 template <int DT, int NWG>
-__global__ void __launch_bounds__(PPCfg<NWG>::THREADS, PPCfg<NWG>::CTAS_PER_SM)
+__global__ void __launch_bounds__(PPCfg<NWG, 1>::THREADS, PPCfg<NWG, 1>::CTAS_PER_SM)
 attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
-    using C = PPCfg<NWG>;
+    using C = PPCfg<NWG, 1>;
     constexpr int PP_NST = C::NST;
     constexpr int PP_OFF_Q = C::OFF_Q, PP_OFF_K = C::OFF_K, PP_OFF_V = C::OFF_V, PP_OFF_MASK = C::OFF_MASK;
     constexpr int PP_OFF_BAR = C::OFF_BAR, PP_TMEM_COLS = C::TMEM_COLS;
@@ -465,6 +478,457 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
 }
 
+// The same kernel as a persistent one, for items of up to 8 key tiles (S <= 1024), where what happens between two items
+// weighs most: one CTA per resident slot, items dealt round-robin.
+template <int DT, int NWG>
+__global__ void __launch_bounds__(PPCfg<NWG, 2>::THREADS, PPCfg<NWG, 2>::CTAS_PER_SM)
+attention_pingpong_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    using C = PPCfg<NWG, 2>;
+    constexpr int PP_NST = C::NST;
+    constexpr int PP_OFF_Q = C::OFF_Q, PP_OFF_K = C::OFF_K, PP_OFF_V = C::OFF_V, PP_OFF_MASK = C::OFF_MASK;
+    constexpr int PP_OFF_BAR = C::OFF_BAR, PP_TMEM_COLS = C::TMEM_COLS;
+    constexpr int Q_SET_BYTES = NWG * TILE_BYTES;   // the query tiles of one item
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PP_OFF_BAR);
+    uint64_t* q_full = bars + 0;                  // [2] the two query sets
+    uint64_t* q_empty = bars + 2;                 // [2] every QK^T that reads the set has completed
+    uint64_t* k_full = bars + 4;                  // [PP_NST]
+    uint64_t* v_full = k_full + PP_NST;           // [PP_NST]
+    uint64_t* k_empty = v_full + PP_NST;          // [PP_NST]
+    uint64_t* v_empty = k_empty + PP_NST;         // [PP_NST]
+    uint64_t* m_full = v_empty + PP_NST;          // [PP_NST] mask of the stage written (32 arrivals)
+    uint64_t* s_full = m_full + PP_NST;           // [2] per warpgroup
+    uint64_t* p_full = s_full + 2;                // [2] (128 arrivals)
+    uint64_t* o_full = p_full + 2;                // [2]
+    uint64_t* s_free = o_full + 2;                // [2] the warpgroup holds its scores in registers (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* mask_s = reinterpret_cast<float*>(smem + PP_OFF_MASK);
+    volatile uint32_t* plain_s = tmem_slot + 2;   // [PP_NST] per stage: every key valid, mask 0
+    volatile uint32_t* wg0_tiles = tmem_slot + 2 + PP_NST;   // key tiles warpgroup 0 has written its weights for
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (tid == 0 && p.status) atomicOr(p.status, 4u);
+        return;
+    }
+
+    if (tid == 0) {
+        *wg0_tiles = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&q_full[i], 1);
+            mbar_init(&q_empty[i], NWG);           // one commit per UMMA-issuing warp
+        }
+        for (int i = 0; i < PP_NST; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], NWG);           // one commit per UMMA-issuing warp
+            mbar_init(&v_empty[i], NWG);
+            mbar_init(&m_full[i], 32);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&o_full[i], 1);
+            mbar_init(&s_free[i], 128);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tm_q);
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, PP_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();   // qkv and kv_len come from earlier kernels; the output may still be read by one
+
+    // Persistent CTAs: items (a block of NWG x 128 queries of one head of one sequence) are dealt round-robin, and every
+    // role walks the same list.  Nothing is drained between items: the K/V ring, the score / weight / output columns
+    // and all barriers carry on (phases follow running counters), the next item's queries land in the other of two
+    // query sets while this item is still at work, and its first QK^T is issued during this item's last softmax.
+    // `t0` = number of key tiles of all earlier items of this CTA (ring stage and phase of the item's first tile).
+    struct Item {
+        int b, head, q0, n_tiles;
+        bool two;         // the second query tile exists
+        bool additive_only;
+    };
+    auto load_item = [&](int id) -> Item {
+        Item it;
+        const int qb = id % p.n_qb;
+        const int rest = id / p.n_qb;
+        it.head = rest % p.heads;
+        it.b = rest / p.heads;
+        it.q0 = qb * NWG * TQ;
+        it.two = NWG == 2 && (p.S - it.q0) > TQ;
+        // kv_len is written by a kernel earlier in the stream: it is read only here, behind the dependency wait.
+        int kv_eff = p.S;
+        it.additive_only = (p.mask_add == nullptr);
+        if (p.kv_len != nullptr) {
+            const int kl = p.kv_len[it.b];
+            if (kl <= 0) it.additive_only = true;
+            else kv_eff = kl < p.S ? kl : p.S;
+        }
+        it.n_tiles = (kv_eff + TK - 1) / TK;
+        return it;
+    };
+    const int n_items = static_cast<int>(p.n_items);
+    const int id0 = static_cast<int>(blockIdx.x), id_step = static_cast<int>(gridDim.x);
+
+    if (warp < 4) {
+        setmaxnreg_dec<C::REGS_CONTROL>();   // the control warpgroup: producer, two UMMA issuers, an idle warp
+        if (warp == 0) {
+            // ------------------------------------------------------------ producer
+            bool ok = true;
+            uint32_t t0 = 0;   // key tiles of the CTA's earlier items
+            int k = 0;         // items of the CTA so far
+            for (int id = id0; ok && id < n_items; id += id_step, ++k) {
+                const Item it = load_item(id);
+                const int set = k & 1;
+                // the set's previous item (two items back) must have finished its last QK^T
+                if (!mbar_wait(&q_empty[set], ((static_cast<uint32_t>(k) >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                if (lane == 0) {
+                    uint8_t* qs = smem + PP_OFF_Q + set * Q_SET_BYTES;
+                    mbar_expect_tx(&q_full[set], (it.two ? 2 : 1) * TILE_BYTES);
+                    tma_load_3d(qs, &tm_q, &q_full[set], it.head * HD, it.q0, it.b);
+                    if (it.two) tma_load_3d(qs + TILE_BYTES, &tm_q, &q_full[set], it.head * HD, it.q0 + TQ, it.b);
+                }
+                for (int j = 0; ok && j < it.n_tiles; ++j) {
+                    const uint32_t t = t0 + static_cast<uint32_t>(j);
+                    const int st = static_cast<int>(t % PP_NST);
+                    const uint32_t ph = (t / PP_NST) & 1u;
+                    if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    if (lane == 0) {
+                        mbar_expect_tx(&k_full[st], TILE_BYTES);
+                        tma_load_3d(smem + PP_OFF_K + st * TILE_BYTES, &tm_k, &k_full[st], it.head * HD, j * TK, it.b);
+                    }
+                    // v_empty also says that both warpgroups are done with this stage's mask
+                    if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    if (lane == 0) {
+                        mbar_expect_tx(&v_full[st], TILE_BYTES);
+                        tma_load_3d(smem + PP_OFF_V + st * TILE_BYTES, &tm_v, &v_full[st], it.head * HD, j * TK, it.b);
+                    }
+                    bool zero = true;
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = j * TK + lane * 4 + i;
+                        float m = -INFINITY;
+                        if (key < p.S) {
+                            const float a = p.mask_add ? p.mask_add[static_cast<long long>(it.b) * p.S + key] : 0.f;
+                            if (it.additive_only || a > p.mask_below) m = a * 1.4426950408889634f;
+                        }
+                        mask_s[st * TK + lane * 4 + i] = m;
+                        zero = zero && m == 0.f;
+                    }
+                    // a "plain" tile (all 128 keys valid, additive mask 0) lets the softmax skip the mask altogether
+                    const bool plain_tile = __all_sync(0xffffffffu, zero) && p.scale_log2 > 0.f;
+                    if (lane == 0) plain_s[st] = plain_tile ? 1u : 0u;
+                    mbar_arrive(&m_full[st]);
+                }
+                t0 += static_cast<uint32_t>(it.n_tiles);
+            }
+            if (!ok && lane == 0) {
+                for (int i = 0; i < 64; ++i) nanosleep(10000);
+            }
+            __syncwarp();
+        } else if (warp == 1 || (NWG == 2 && warp == 2)) {
+            // ------------------------------------------------------------ UMMA issuers (one warp per warpgroup)
+            // The whole warp runs this role's control flow (all waits, all address arithmetic: warp-uniform, every
+            // descriptor an immediate offset from one built once); lane 0 alone executes the tcgen05.mma and
+            // tcgen05.commit instructions, so that each commit covers the UMMAs before it.  Both warps walk every
+            // item: where an item has no second query tile, warp 2 issues nothing but still waits for the stage's
+            // loads and commits, so that every "empty" barrier gets its NWG arrivals once per use and in step.
+            const int wg = warp - 1;
+            const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+            const uint64_t dq0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_Q));   // descriptor addresses: 16-byte units
+            const uint64_t dk0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_K));   // + stage * (TILE_BYTES >> 4)
+            const uint64_t dv0 = make_smem_desc_sw128(smem_u32(smem + PP_OFF_V));
+            uint32_t u_s = 0, u_pv = 0;   // score tiles / PV products this warp has issued
+            // S_w = Q_w K^T of tile j of `it`: as soon as the warpgroup holds its previous scores in registers.
+            // `k` = items of the CTA before this one (query set and its phase), `t0` = key tiles before it, `n` = its key
+            // tiles, `two` = it has a second query tile.
+            auto issue_s = [&](const int k, const uint32_t t0, const int n, const bool two_, const int j) -> bool {
+                const uint32_t t = t0 + static_cast<uint32_t>(j);
+                const int st = static_cast<int>(t % PP_NST);
+                const int set = k & 1;
+                const bool active = wg == 0 || two_;
+                if (j == 0 && !mbar_wait(&q_full[set], (static_cast<uint32_t>(k) >> 1) & 1u, abort_flag)) return false;
+                if (active && u_s > 0 && !mbar_wait(&s_free[wg], (u_s - 1u) & 1u, abort_flag)) return false;
+                if (!mbar_wait(&k_full[st], (t / PP_NST) & 1u, abort_flag)) return false;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    if (active) {
+                        const uint64_t a_desc = dq0 + static_cast<uint64_t>((set * NWG + wg) * (TILE_BYTES >> 4));
+                        const uint64_t b_desc = dk0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                        const uint32_t d_tmem = tmem_base + wg * 128;
+    #pragma unroll
+                        for (int kk = 0; kk < HD / 16; ++kk)
+                            umma_f16_ss(d_tmem, a_desc + 2u * kk, b_desc + 2u * kk, idesc_qk, kk != 0 ? 1u : 0u);
+                        umma_commit(&s_full[wg]);
+                    }
+                    umma_commit(&k_empty[st]);
+                    if (j == n - 1) umma_commit(&q_empty[set]);
+                }
+                __syncwarp();
+                if (active) ++u_s;
+                return true;
+            };
+            // O_w (+)= P_w V of tile j: when the warpgroup has written P_w.
+            auto issue_pv = [&](const uint32_t t0, const bool two_, const int j) -> bool {
+                const uint32_t t = t0 + static_cast<uint32_t>(j);
+                const int st = static_cast<int>(t % PP_NST);
+                const bool active = wg == 0 || two_;
+                if (active && !mbar_wait(&p_full[wg], u_pv & 1u, abort_flag)) return false;
+                if (!mbar_wait(&v_full[st], (t / PP_NST) & 1u, abort_flag)) return false;
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    if (active) {
+                        const uint64_t b_desc = dv0 + static_cast<uint64_t>(st * (TILE_BYTES >> 4));
+                        const uint32_t d_tmem = tmem_base + C::COL_O + wg * 64;
+                        const uint32_t a_tmem = tmem_base + C::COL_P + wg * 64;
+                        const uint32_t acc0 = j != 0 ? 1u : 0u;
+                        // O_w accumulates in TMEM over the item's key tiles (the softmax rescales it in place when it
+                        // must); P_w is read from TMEM (8 columns per 16 keys), V from shared memory (2 KB per 16 keys)
+    #pragma unroll
+                        for (int kk = 0; kk < TK / 16; ++kk)
+                            umma_f16_ts(d_tmem, a_tmem + kk * 8, b_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                                        kk != 0 ? 1u : acc0);
+                        umma_commit(&o_full[wg]);
+                    }
+                    umma_commit(&v_empty[st]);
+                }
+                __syncwarp();
+                if (active) ++u_pv;
+                return true;
+            };
+            bool ok = true;
+            int id = id0, k = 0;
+            uint32_t t0 = 0;
+            int n = 0;
+            bool two_ = false;
+            if (id < n_items) {
+                const Item it = load_item(id);
+                n = it.n_tiles;
+                two_ = it.two;
+                ok = __all_sync(0xffffffffu, issue_s(k, t0, n, two_, 0));
+            }
+            while (ok && id < n_items) {
+                const int id_n = id + id_step;
+                int n_n = 0;
+                bool two_n = false;
+                if (id_n < n_items) {
+                    const Item it = load_item(id_n);
+                    n_n = it.n_tiles;
+                    two_n = it.two;
+                }
+                for (int j = 0; ok && j < n; ++j) {
+                    // the scores of the following tile (of this item, or the first of the next) before this tile's PV
+                    if (j + 1 < n) ok = issue_s(k, t0, n, two_, j + 1);
+                    else if (id_n < n_items) ok = issue_s(k + 1, t0 + static_cast<uint32_t>(n), n_n, two_n, 0);
+                    if (ok) ok = issue_pv(t0, two_, j);
+                    ok = __all_sync(0xffffffffu, ok);
+                }
+                t0 += static_cast<uint32_t>(n);
+                id = id_n;
+                ++k;
+                n = n_n;
+                two_ = two_n;
+            }
+            __syncwarp();
+        }
+    } else {
+        setmaxnreg_inc<C::REGS_SOFTMAX>();
+        // ------------------------------------------------------------ softmax warpgroups
+        const int wg = (warp - 4) >> 2;   // warps 4..7 -> 0, 8..11 -> 1
+        const int r_in_tile = ((warp & 3) << 5) + lane;          // TMEM lane = query row of the tile
+        const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t t_s = tmem_base + lane_field + wg * 128;
+        const uint32_t t_o = tmem_base + lane_field + C::COL_O + wg * 64;
+        const uint32_t t_p = tmem_base + lane_field + C::COL_P + wg * 64;
+        uint32_t u = 0;   // key tiles this warpgroup has been through (phase of its score / weight / output barriers)
+        uint32_t t = 0;   // key tiles of the CTA so far (ring stage and phase)
+        bool ok = true;
+        // (only the id is carried through an item: the row of scores needs the registers; the output's coordinates are
+        // decoded again when the item is done)
+        for (int id = id0; ok && id < n_items; id += id_step) {
+            int n_tiles;
+            {
+                const Item it = load_item(id);
+                n_tiles = it.n_tiles;
+                if (!(wg == 0 || it.two)) {
+                    t += static_cast<uint32_t>(n_tiles);
+                    continue;
+                }
+            }
+            float m_run = -INFINITY, l_run = 0.f;
+            for (int j = 0; j < n_tiles; ++j, ++u, ++t) {
+                const int st = static_cast<int>(t % PP_NST);
+                const uint32_t ph = u & 1u;
+                if (!mbar_wait(&m_full[st], (t / PP_NST) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&s_full[wg], ph, abort_flag)) { ok = false; break; }
+                __syncwarp();
+                tcgen05_fence_after();
+                // The row's 128 scores move to registers in one go and the score columns are handed back at once:
+                // the next tile's QK^T runs while this tile's softmax is still at work.
+                uint32_t s[TK];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_wait(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+                tcgen05_fence_before();
+                mbar_arrive(&s_free[wg]);
+                const float* mrow = mask_s + st * TK;
+                const bool plain_tile = plain_s[st] != 0u;   // warp-uniform (CTA-uniform)
+                float tmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains (latency)
+                if (plain_tile) {
+#pragma unroll
+                    for (int g = 0; g < TK / 8; ++g) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            tmx[c] = fmax3(tmx[c], __uint_as_float(s[g * 8 + c * 2]), __uint_as_float(s[g * 8 + c * 2 + 1]));
+                    }
+                } else {
+                    // s <- score * scale + mask (log2 units; -inf drops the key): the exp pass only subtracts the maximum
+                    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+#pragma unroll
+                    for (int g = 0; g < TK / 4; ++g) {
+                        const float4 mk = *reinterpret_cast<const float4*>(mrow + g * 4);
+                        float v0, v1, v2, v3;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[g * 4 + 0]), __uint_as_float(s[g * 4 + 1])), sc2,
+                                               pack_f32x2(mk.x, mk.y)), v0, v1);
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[g * 4 + 2]), __uint_as_float(s[g * 4 + 3])), sc2,
+                                               pack_f32x2(mk.z, mk.w)), v2, v3);
+                        s[g * 4 + 0] = __float_as_uint(v0);
+                        s[g * 4 + 1] = __float_as_uint(v1);
+                        s[g * 4 + 2] = __float_as_uint(v2);
+                        s[g * 4 + 3] = __float_as_uint(v3);
+                        tmx[g & 1] = fmax3(tmx[g & 1], v0, v1);
+                        tmx[2 + (g & 1)] = fmax3(tmx[2 + (g & 1)], v2, v3);
+                    }
+                }
+                float tmax = fmaxf(fmaxf(tmx[0], tmx[1]), fmaxf(tmx[2], tmx[3]));
+                if (plain_tile) tmax *= p.scale_log2;   // = max of the scaled scores: the scale is positive
+                // Lazy reference maximum: it only moves when the tile's maximum exceeds it by more than 2^kLazyLog2
+                // (weights stay <= 2^kLazyLog2, exact in half precision and harmless in the fp32 sums), so most tiles
+                // leave the output accumulator in TMEM untouched.
+                const bool move = tmax > m_run + kLazyLog2;
+                const float m_new = move ? tmax : m_run;
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = move ? fast_exp2(m_run - m_use) : 1.f;
+                // PV of the item's previous tile must be complete: it reads the P buffer written below, and it writes
+                // the accumulator a rescale would touch.  (For an item's first tile the previous item's last PV was
+                // awaited before its output was read.)
+                if (j > 0 && !mbar_wait(&o_full[wg], (u - 1u) & 1u, abort_flag)) { ok = false; break; }
+                __syncwarp();
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int cc = 0; cc < HD / 32; ++cc) {
+                        uint32_t ro[32];
+                        tmem_ld_32x32b_x32(t_o + cc * 32, ro);
+                        tmem_ld_wait(ro);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * alpha);
+                        tmem_st_32x32b_x32(t_o + cc * 32, ro);
+                    }
+                }
+                // Phase offset.  A scheduler's exp unit is saturated only while both of its softmax warps are in their exp
+                // pass (8.9 cycles per score per scheduler), runs at ~70 % with one (11.6) and idles with none; started
+                // together the two warpgroups stay in lockstep: both in the exp pass, then both out of it.  So warpgroup
+                // 1 begins an item's first exp pass only when warpgroup 0 has finished its own (warpgroup 0 takes part in
+                // every item, so its tile count is the CTA's, `t`); for the next tiles one's exp pass covers the other's
+                // loads, maximum and hand-offs.  (The offset decays over ~6 tiles; renewing it every tile, every second or
+                // every fourth tile, or holding it with a mutual rule, all measured slower than letting it decay within
+                // an item; set only once per CTA the persistent kernel ran 10-13 % slower on long sequences.)
+                // (A parity wait can only name the phase in progress or the one before it, and warpgroup 0 may be further
+                // ahead than that: its own count of finished tiles is looked at first, the wait is tried a bounded number
+                // of times, and nothing depends on its outcome but the timing.)
+                if (NWG == 2 && wg == 1 && j == 0) {
+                    for (int spin = 0; spin < 64 && *wg0_tiles <= t; ++spin)
+                        if (mbar_try_wait(&p_full[0], t & 1u)) break;
+                }
+                // exp pass: P goes to tensor memory as the A operand of the PV UMMA, two consecutive keys per 32-bit
+                // column, 32 keys at a time into columns [16c, 16c + 16) of the warpgroup's P region
+                const uint64_t mul2 = plain_tile ? pack_f32x2(p.scale_log2, p.scale_log2) : pack_f32x2(1.f, 1.f);
+                const uint64_t neg2 = pack_f32x2(-m_use, -m_use);
+                uint64_t ps2[2] = {0ull, 0ull};   // 2 x 2 partial sums
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int i = c * 32 + e * 2;
+                        float x0, x1;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), mul2, neg2), x0, x1);
+                        x0 = fast_exp2(x0);
+                        x1 = fast_exp2(x1);
+                        ps2[e & 1] = add_f32x2(ps2[e & 1], pack_f32x2(x0, x1));
+                        pk[e] = pack2t<DT>(x0, x1);
+                    }
+                    tmem_st_32x32b_x16(t_p + c * 16, pk);
+                }
+                float a0, a1, a2, a3;
+                unpack_f32x2(ps2[0], a0, a1);
+                unpack_f32x2(ps2[1], a2, a3);
+                l_run = l_run * alpha + ((a0 + a1) + (a2 + a3));
+                m_run = m_new;
+                tmem_st_wait();               // P (and a rescaled O) have reached tensor memory
+                tcgen05_fence_before();
+                if (NWG == 2 && wg == 0 && r_in_tile == 0) *wg0_tiles = t + 1u;   // before this thread's arrival: see above
+                mbar_arrive(&p_full[wg]);
+            }
+            if (!ok) break;
+            // the item's last PV, then its output: normalised and stored from registers.  The accumulator columns are
+            // free for the next item as soon as they are in registers; its first PV is issued only after this
+            // warpgroup's next p_full arrivals, which follow these loads in program order.
+            if (n_tiles > 0 && !mbar_wait(&o_full[wg], (u - 1u) & 1u, abort_flag)) { ok = false; break; }
+            __syncwarp();
+            tcgen05_fence_after();
+            const Item it = load_item(id);
+            const int q = it.q0 + wg * TQ + r_in_tile;
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            uint16_t* dst =
+                reinterpret_cast<uint16_t*>(p.out) + (static_cast<long long>(it.b) * p.S + q) * p.ldo + it.head * HD;
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_o + c * 32, r);
+                tmem_ld_wait(r);
+                if (q < p.S) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 qv;
+                        qv.x = pack2t<DT>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+                        qv.y = pack2t<DT>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+                        qv.z = pack2t<DT>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+                        qv.w = pack2t<DT>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = qv;
+                    }
+                }
+            }
+            tcgen05_fence_before();
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, PP_TMEM_COLS);
+    }
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Sequences of at most 128 tokens (the benchmark's S = 128): one key tile per (sequence, head), so no running
 // rescale.  An item is tiny (4.2 MFLOP on 48 KB of operands) and its steps depend on each other (loads -> QK^T ->
@@ -742,7 +1206,7 @@ attention_single_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, 2u);
 }
 
-// Dynamic shared-memory limits of the four kernel instances, once per device (first launch on it).
+// Dynamic shared-memory limits of the kernel instances, once per device (first launch on it).
 bool set_attention_attributes(int dev) {
     static PerDeviceOnce once;
     return once.ensure(dev, []() {
@@ -752,12 +1216,61 @@ bool set_attention_attributes(int dev) {
             cudaFuncSetAttribute(attention_single_kernel<B200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  S1_SMEM) == cudaSuccess &&
             cudaFuncSetAttribute(attention_pingpong_kernel<B200_F16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) == cudaSuccess &&
+                                 PPCfg<PP_NWG, 1>::SMEM) == cudaSuccess &&
             cudaFuncSetAttribute(attention_pingpong_kernel<B200_BF16, PP_NWG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PPCfg<PP_NWG>::SMEM) == cudaSuccess;
+                                 PPCfg<PP_NWG, 1>::SMEM) == cudaSuccess &&
+            cudaFuncSetAttribute(attention_pingpong_persistent_kernel<B200_F16, PP_NWG>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PPCfg<PP_NWG, 2>::SMEM) == cudaSuccess &&
+            cudaFuncSetAttribute(attention_pingpong_persistent_kernel<B200_BF16, PP_NWG>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PPCfg<PP_NWG, 2>::SMEM) == cudaSuccess;
         if (!ok) cudaGetLastError();
         return ok;
     });
+}
+
+// Launch of the long-sequence attention (S > 128).  Items of up to 8 key tiles (S <= 1024) go to the persistent kernel:
+// one CTA per resident slot, nothing drained between items (6-14 % faster at S = 256 ... 1024).  Longer items run one
+// per CTA: there the persistent form measured 5-8 % slower (S = 2048, 4096), with a fixed deal of items to CTAs as
+// well as with one item per CTA.  `with_attributes` = launch with the programmatic-dependent-launch attribute.
+int launch_pingpong(AttnParams& p, int dtype, long long S, int heads, long long B, int dev, cudaStream_t stream,
+                    const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, bool with_attributes) {
+    const int n_qb = static_cast<int>((S + PP_NWG * TQ - 1) / (PP_NWG * TQ));
+    p.n_qb = n_qb;
+    p.n_items = static_cast<long long>(n_qb) * heads * B;
+    if (S <= 8 * TK) {
+        if (p.n_items > 0x7fff0000ll) return B200_ERR_UNSUPPORTED;   // item ids are 32-bit in the kernel
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long slots = static_cast<long long>(sms > 0 ? sms : 1) * PPCfg<PP_NWG, 2>::CTAS_PER_SM;
+        const dim3 grid(static_cast<unsigned>(p.n_items < slots ? p.n_items : slots));
+        const dim3 block(PPCfg<PP_NWG, 2>::THREADS);
+        constexpr size_t smem = PPCfg<PP_NWG, 2>::SMEM;
+        if (with_attributes) {
+            if (dtype == B200_F16)
+                launch_kernel(attention_pingpong_persistent_kernel<B200_F16, PP_NWG>, grid, block, smem, stream, tq, tk, tv, p);
+            else
+                launch_kernel(attention_pingpong_persistent_kernel<B200_BF16, PP_NWG>, grid, block, smem, stream, tq, tk, tv, p);
+        } else if (dtype == B200_F16) {
+            attention_pingpong_persistent_kernel<B200_F16, PP_NWG><<<grid, block, smem, stream>>>(tq, tk, tv, p);
+        } else {
+            attention_pingpong_persistent_kernel<B200_BF16, PP_NWG><<<grid, block, smem, stream>>>(tq, tk, tv, p);
+        }
+        return B200_OK;
+    }
+    const dim3 grid(static_cast<unsigned>(n_qb), static_cast<unsigned>(heads), static_cast<unsigned>(B));
+    const dim3 block(PPCfg<PP_NWG, 1>::THREADS);
+    constexpr size_t smem = PPCfg<PP_NWG, 1>::SMEM;
+    if (with_attributes) {
+        if (dtype == B200_F16)
+            launch_kernel(attention_pingpong_kernel<B200_F16, PP_NWG>, grid, block, smem, stream, tq, tk, tv, p);
+        else
+            launch_kernel(attention_pingpong_kernel<B200_BF16, PP_NWG>, grid, block, smem, stream, tq, tk, tv, p);
+    } else if (dtype == B200_F16) {
+        attention_pingpong_kernel<B200_F16, PP_NWG><<<grid, block, smem, stream>>>(tq, tk, tv, p);
+    } else {
+        attention_pingpong_kernel<B200_BF16, PP_NWG><<<grid, block, smem, stream>>>(tq, tk, tv, p);
+    }
+    return B200_OK;
 }
 
 }  // namespace
@@ -826,14 +1339,8 @@ extern "C" int b200_attention_fwd(const B200AttentionDesc* d, b200_stream_t stre
     }
 
     if (!set_attention_attributes(dev)) return B200_ERR_LAUNCH;
-    dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
-              static_cast<unsigned>(d->B));
-    if (d->dtype == B200_F16)
-        launch_kernel(attention_pingpong_kernel<B200_F16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
-                      static_cast<cudaStream_t>(stream_), tq, tk, tv, p);
-    else
-        launch_kernel(attention_pingpong_kernel<B200_BF16, PP_NWG>, grid, dim3(PPCfg<PP_NWG>::THREADS), PPCfg<PP_NWG>::SMEM,
-                      static_cast<cudaStream_t>(stream_), tq, tk, tv, p);
+    const int rc = launch_pingpong(p, d->dtype, d->S, d->heads, d->B, dev, static_cast<cudaStream_t>(stream_), tq, tk, tv, true);
+    if (rc != B200_OK) return rc;
     count_launch();
     return check_launch();
 }
@@ -926,12 +1433,8 @@ extern "C" int b200_attention_masked_fwd_static(const B200AttentionDesc* d, b200
             attention_single_kernel<B200_BF16><<<static_cast<unsigned>(grid1), kAttnThreads, S1_SMEM, stream>>>(
                 tq, tk, tv, to, p, static_cast<int>(items));
     } else {
-        dim3 grid(static_cast<unsigned>((d->S + PP_NWG * TQ - 1) / (PP_NWG * TQ)), static_cast<unsigned>(d->heads),
-                  static_cast<unsigned>(d->B));
-        if (d->dtype == B200_F16)
-            attention_pingpong_kernel<B200_F16, PP_NWG><<<grid, PPCfg<PP_NWG>::THREADS, PPCfg<PP_NWG>::SMEM, stream>>>(tq, tk, tv, p);
-        else
-            attention_pingpong_kernel<B200_BF16, PP_NWG><<<grid, PPCfg<PP_NWG>::THREADS, PPCfg<PP_NWG>::SMEM, stream>>>(tq, tk, tv, p);
+        const int rc = launch_pingpong(p, d->dtype, d->S, d->heads, d->B, dev, stream, tq, tk, tv, false);
+        if (rc != B200_OK) return rc;
     }
     count_launch();
     return check_launch();
