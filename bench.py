@@ -247,16 +247,20 @@ def run_ours(args):
             msk_ = torch.zeros(16, S_, device=dev)
             kvl_ = ops.mask_to_kv_len(msk_)
             out_ = torch.empty(16, S_, 16 * 64, device=dev, dtype=torch.float16)
+            for _ in range(10):                             # also brings the clocks up from idle
+                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+            torch.cuda.synchronize()
+            best_ = None
             for _ in range(3):
-                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
-            torch.cuda.synchronize()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(10):
-                ops.attention(qkv_, 16, msk_, kvl_, out=out_)
-            a1.record()
-            torch.cuda.synchronize()
-            ms_ = a0.elapsed_time(a1) / 10
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(10):
+                    ops.attention(qkv_, 16, msk_, kvl_, out=out_)
+                a1.record()
+                torch.cuda.synchronize()
+                t_ = a0.elapsed_time(a1) / 10
+                best_ = t_ if best_ is None or t_ < best_ else best_
+            ms_ = best_
             fl_ = 4.0 * S_ * S_ * 64 * 16 * 16
             attention_sweep.append({"S": S_, "ms": round(ms_, 4), "tflops": round(fl_ / ms_ / 1e9, 1),
                                     "frac_of_tensor_peak": round(fl_ / ms_ / 1e9 / peaks["tflops"], 4)})
@@ -606,7 +610,7 @@ def run_ours(args):
                                          "weights are 1-5 MB); below the algorithmic bytes because part of every "
                                          "output is still in L2 when its kernel ends"},
             "attention_sweep": attention_sweep,
-            "attention_sweep_note": "each point: 10 launches between one CUDA-event pair, timed before the long loops "
+            "attention_sweep_note": "each point: 10 launches between one CUDA-event pair, best of 3, timed before the long loops "
                                     "(burst clocks, as the measured tensor peak was)",
             "attention_kernel": {"ms": attn_ms, "tflops": attn_flops / attn_ms / 1e9,
                                  "frac_of_tensor_peak": attn_flops / attn_ms / 1e9 / peaks["tflops"],

@@ -196,6 +196,8 @@ def _attention_case(cuda_device, dt, B, S, heads, lengths, seed=0, holes=False):
 @pytest.mark.parametrize("B,S,heads,lengths", [
     (2, 128, 12, [128, 128]), (3, 128, 2, [1, 17, 100]), (2, 96, 4, [96, 5]), (2, 200, 3, [200, 131]),
     (2, 256, 2, [16, 256]), (1, 384, 16, [300]), (1, 1, 1, [1]), (2, 512, 2, [512, 129]), (1, 130, 1, [130]),
+    # the persistent long-sequence kernel's last length and the one-item kernel's first
+    (3, 1024, 2, [1024, 700, 130]), (2, 1152, 1, [1152, 600]),
 ])
 def test_attention(cuda_device, dt, B, S, heads, lengths):
     got, want, *_ = _attention_case(cuda_device, dt, B, S, heads, lengths, seed=S + B)
@@ -203,6 +205,21 @@ def test_attention(cuda_device, dt, B, S, heads, lengths):
     for b, n in enumerate(lengths):
         # every query row, padded ones included, is computed like the reference computes it
         assert max_abs(got[b], want[b]) < tol
+    assert cosine(got, want) > 0.9995
+
+
+@pytest.mark.parametrize("S", [384, 200, 640])
+def test_attention_many_items_per_persistent_cta(cuda_device, S):
+    """More items than resident CTAs, ragged lengths: every CTA of the persistent long-sequence kernel walks several
+    items with different numbers of key tiles; at S = 384 and 640 every second item has one query tile only (the second
+    UMMA-issuing warp and the second softmax warpgroup sit those out), at S = 200 the second tile is partly empty."""
+    B, heads = 50, 4
+    rng = np.random.default_rng(S)
+    lengths = [int(x) for x in rng.integers(1, S + 1, B)]
+    lengths[0], lengths[1] = S, 1
+    got, want, *_ = _attention_case(cuda_device, "f16", B, S, heads, lengths, seed=S)
+    for b in range(B):
+        assert max_abs(got[b], want[b]) < 6e-3, (b, lengths[b])
     assert cosine(got, want) > 0.9995
 
 
