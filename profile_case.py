@@ -4,6 +4,7 @@
     python profile_case.py attention --B 64 --S 128 --heads 12
     python profile_case.py layernorm --rows 8192 --H 768
     python profile_case.py encoder --B 64 --S 128 --layers 2
+    python profile_case.py encoder --config 4 --iters 10          # BERT-large, 64 x 384, ragged, 24 layers
     python profile_case.py qa_head --rows 131072 --H 768
     python profile_case.py embedding --B 1024 --S 128 --H 768
 
@@ -34,6 +35,8 @@ def main():
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--H", type=int, default=768)
     ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--fold", action="store_true", help="encoder: the five-launch layer with both LayerNorms folded")
+    ap.add_argument("--config", type=int, default=0, help="encoder: run benchmark configuration 2..5 as specified")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
@@ -104,8 +107,14 @@ def main():
     else:
         from tnn_b200 import model_synth
         from tnn_b200.encoder import Encoder
-        wl = model_synth.make_workload(model_synth.BERT_BASE, a.B, a.S, seed=0, num_layers=a.layers)
-        enc = Encoder.from_workload(wl, dt, dev)
+        if a.config:
+            # one of the benchmark's five configurations at its own batch, lengths and depth (3 and 4 are ragged:
+            # the figure printed is on effective FLOPs, padding earns nothing)
+            wl = model_synth.config_workload(a.config)
+            a.B, a.S = wl.x.shape[0], wl.x.shape[1]
+        else:
+            wl = model_synth.make_workload(model_synth.BERT_BASE, a.B, a.S, seed=0, num_layers=a.layers)
+        enc = Encoder.from_workload(wl, dt, dev, fold_layernorm=a.fold)
         hidden = torch.from_numpy(wl.x).to(dev).to(dt)
         mask = torch.from_numpy(wl.mask_add.reshape(a.B, a.S)).to(dev)
         kv = ops.mask_to_kv_len(mask)
@@ -142,6 +151,9 @@ def main():
     ms = e0.elapsed_time(e1) / a.iters
     print("%s: %.4f ms per call, %.1f %s, device status %d" % (a.kernel, ms, work / ms / 1e9, unit,
                                                               capi.device_status()))
+    if a.kernel == "encoder":
+        print("encoder: %d sequences x %d tokens, %d layers: %.1f sequences/s" % (a.B, a.S, len(wl.weights),
+                                                                                 a.B / ms * 1e3))
 
 
 if __name__ == "__main__":

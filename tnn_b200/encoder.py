@@ -25,9 +25,10 @@ class Encoder:
         self.fold = False
 
     @classmethod
-    def from_workload(cls, wl, dtype=torch.float16, device="cuda", fold_layernorm=True):
+    def from_workload(cls, wl, dtype=torch.float16, device="cuda", fold_layernorm=False):
         """`fold_layernorm`: prepare the weights for the five-launch form of a layer (both LayerNorms folded into
-        the neighbouring GEMMs); only full encoder layers can be folded."""
+        the neighbouring GEMMs); only full encoder layers can be folded.  Off by default: at BERT's K = 768 the
+        seven-launch layer with its own LayerNorm kernel is the faster one, and it is what the TNN plug-in runs."""
         enc = cls(wl.cfg, dtype, torch.device(device))
         enc.fold = bool(fold_layernorm) and wl.cfg.with_ffn
         H, F = wl.cfg.hidden, wl.cfg.ffn
