@@ -479,7 +479,11 @@ attention_pingpong_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 }
 
 // The same kernel as a persistent one, for items of up to 8 key tiles (S <= 1024), where what happens between two items
-// weighs most: one CTA per resident slot, items dealt round-robin.
+// weighs most: one CTA per resident slot, items dealt round-robin.  The tile loop is written out a second time instead
+// of being shared with the kernel above: the throughput of both depends on the phase relation the two softmax
+// warpgroups fall into, and that relation reacted to every restructuring that was measured (this form run with one
+// item per CTA is 5-8 % slower than the kernel above on items of 16 and 32 tiles; with the UMMA-issuing warps
+// specialised at compile time it is 8-16 % slower than as written here), so each form keeps the code it was tuned with.
 template <int DT, int NWG>
 __global__ void __launch_bounds__(PPCfg<NWG, 2>::THREADS, PPCfg<NWG, 2>::CTAS_PER_SM)
 attention_pingpong_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
