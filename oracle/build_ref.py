@@ -18,7 +18,7 @@ project is not run; this script restates its source selection and flags for the 
 * `-include cstdint -include algorithm`: gcc 13 no longer pulls these in transitively
   (source/tnn/utils/data_type_utils.cc:61 uses uint64_t, source/tnn/core/profile.cc:146 uses std::sort).
 
-Usage:  python oracle/build_ref.py [--reference /path/to/TNN] [--jobs N] [--profile]
+Usage:  python oracle/build_ref.py [--reference /path/to/TNN] [--jobs N] [--profile --out oracle/_ref_profile]
 """
 import argparse
 import glob
@@ -62,8 +62,13 @@ def main():
     ap.add_argument("--reference", default=default_reference())
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--profile", action="store_true", help="also define TNN_PROFILE (per-layer host timers)")
+    ap.add_argument("--out", default=None, help="output directory (default oracle/_ref; a TNN_PROFILE build changes "
+                                                 "class layouts and needs a directory of its own, e.g. oracle/_ref_profile)")
     ap.add_argument("--cxx", default="/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     args = ap.parse_args()
+    global OUT
+    if args.out:
+        OUT = os.path.abspath(args.out)
     ref = os.path.abspath(args.reference)
     if not os.path.isdir(os.path.join(ref, "source", "tnn")):
         print("reference sources not found at %s; nothing built" % ref)

@@ -427,6 +427,34 @@ TNNC_API int tnnc_reshape(void* handle, int n_inputs, const char* const* names, 
     return 0;
 }
 
+// Instance::StartProfile / FinishProfile (include/tnn/core/instance.h:103-109), which exist only in a TNN_PROFILE
+// build of the host framework.  tnnc_finish_profile copies the per-layer table into `buf` and returns its length;
+// both return -1 in a build without the switch.
+TNNC_API int tnnc_start_profile(void* handle) {
+#if TNN_PROFILE
+    static_cast<Handle*>(handle)->inst->StartProfile();
+    return 0;
+#else
+    (void)handle;
+    return -1;
+#endif
+}
+
+TNNC_API int64_t tnnc_finish_profile(void* handle, char* buf, int64_t cap) {
+#if TNN_PROFILE
+    const std::string s = static_cast<Handle*>(handle)->inst->FinishProfile(false);
+    if (buf && cap > 0) {
+        const size_t n = s.size() < static_cast<size_t>(cap - 1) ? s.size() : static_cast<size_t>(cap - 1);
+        std::memcpy(buf, s.data(), n);
+        buf[n] = 0;
+    }
+    return static_cast<int64_t>(s.size());
+#else
+    (void)handle; (void)buf; (void)cap;
+    return -1;
+#endif
+}
+
 TNNC_API int tnnc_forward(void* handle) {
     Handle* h = static_cast<Handle*>(handle);
     Status st = h->inst->Forward();

@@ -13,9 +13,12 @@ from . import capi
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
-LIBTNN = os.environ.get("TNN_B200_LIBTNN", os.path.join(_HERE, "host", "libTNN.so"))
-SHIM = os.environ.get("TNN_B200_SHIM", os.path.join(_HERE, "host", "libtnn_capi.so"))
-PLUGIN = os.path.join(_HERE, "lib", "libtnn_b200_plugin.so")
+# TNN_B200_PROFILE_BUILD=1 selects the TNN_PROFILE build of host framework, shim and plug-in (build_plugin.py --profile):
+# the switch changes the layout of TNN's classes, so the three must come from the same build and a process uses one.
+_SUFFIX = "_profile" if os.environ.get("TNN_B200_PROFILE_BUILD", "0") not in ("", "0") else ""
+LIBTNN = os.environ.get("TNN_B200_LIBTNN", os.path.join(_HERE, "host" + _SUFFIX, "libTNN.so"))
+SHIM = os.environ.get("TNN_B200_SHIM", os.path.join(_HERE, "host" + _SUFFIX, "libtnn_capi.so"))
+PLUGIN = os.path.join(_HERE, "lib" + _SUFFIX, "libtnn_b200_plugin.so")
 
 DEVICE_NAIVE, DEVICE_X86, DEVICE_CUDA = 0, 1, 2
 PRECISION_AUTO, PRECISION_NORMAL, PRECISION_HIGH, PRECISION_LOW = -1, 0, 1, 2
@@ -83,6 +86,9 @@ def load():
                                                 ctypes.POINTER(ctypes.c_void_p)]
         shim.tnnc_get_output_device.restype = ctypes.c_int64
         shim.tnnc_forward.argtypes = [ctypes.c_void_p]
+        shim.tnnc_start_profile.argtypes = [ctypes.c_void_p]
+        shim.tnnc_finish_profile.restype = ctypes.c_int64
+        shim.tnnc_finish_profile.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int64]
         shim.tnnc_reshape.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
                                       ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         shim.tnnc_time_forward.restype = ctypes.c_double
@@ -338,6 +344,19 @@ class Instance:
     def share_command_queue(self, other):
         """Instance::ShareCommandQueue: this instance enqueues on `other`'s command queue from now on."""
         self._check(self.shim.tnnc_share_command_queue(self.h, other.h), "ShareCommandQueue")
+
+    def start_profile(self):
+        """Instance::StartProfile (TNN_PROFILE builds only): per-layer timing of the Forwards that follow."""
+        if self.shim.tnnc_start_profile(self.h) != 0:
+            raise RuntimeError("not a TNN_PROFILE build of the host framework")
+
+    def finish_profile(self):
+        """Instance::FinishProfile: the per-layer table as text."""
+        buf = ctypes.create_string_buffer(1 << 20)
+        n = self.shim.tnnc_finish_profile(self.h, buf, len(buf))
+        if n < 0:
+            raise RuntimeError("not a TNN_PROFILE build of the host framework")
+        return buf.value.decode(errors="replace")
 
     def reshape(self, shapes):
         """Instance::Reshape with `{input name: dims}`; the shapes must stay within those of the model file."""
