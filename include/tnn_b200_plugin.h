@@ -50,6 +50,16 @@ TNNB200_API void tnnb200_inject_allocation_failure(int skip, int count);
  * (message in `err`). */
 TNNB200_API int tnnb200_selftest_range_arena(unsigned seed, int steps, int pooled, char* err, int err_cap);
 
+/* The blob converter's host-side conversion (TNN_B200_HOST_CONVERT=1: fp32 host Mats of half-precision blobs are
+ * converted on the host cores so that half the bytes cross the bus): src[n] fp32 -> half_out[n] (half_dtype 0 = fp16,
+ * 1 = bfloat16 as in tnn_b200.h; round to nearest even, like the device's conversion kernel) and, if back_out is
+ * given, back to fp32.  force_scalar = 1 uses the portable scalar code instead of F16C.  No CUDA call is made.
+ * Returns 1 if the vector path was used, 0 if the scalar one, negative on bad arguments. */
+TNNB200_API int tnnb200_host_convert(const float* src, uint64_t n, int half_dtype, int force_scalar,
+                                     uint16_t* half_out, float* back_out);
+/* How many Mat <-> blob conversions of this process took the host-side route so far. */
+TNNB200_API uint64_t tnnb200_host_conversions(void);
+
 /* CUDA-graph replay counters of the instance that owns `command_queue` (Instance::GetCommandQueue): out[0] Forwards
  * launched layer by layer, [1] captures, [2] graph launches, [3] failed captures / launches (re-run layer by layer).
  * Returns 0, or -1 if the queue belongs to no live instance of the plug-in. */

@@ -183,3 +183,44 @@ def test_injected_allocation_failure_is_reported_and_leaks_nothing(cuda_device):
     ok = rt.Instance(proto, model, device=rt.DEVICE_CUDA)
     assert np.array_equal(_blocking(ok, wl.x, wl.mask_add), want)
     ok.close()
+
+
+@pytest.mark.parametrize("input_dtype,precision", [("half", rt.PRECISION_AUTO), ("bf16", rt.PRECISION_LOW)])
+def test_host_side_half_conversion_changes_no_bit(cuda_device, monkeypatch, input_dtype, precision):
+    """TNN_B200_HOST_CONVERT=1: fp32 host Mats of half-precision blobs (a model whose activation input is declared half
+    or bfloat16) are converted on the host cores, so that half the bytes cross the bus.  Same bits as the device-side
+    conversion, through the blocking calls and through the pipelined loop, with pageable and page-locked Mats."""
+    wl = golden_workload(**CASES["base_2layer_ragged"])
+    d = tempfile.mkdtemp(prefix="plug_hostconv_")
+    proto, model = os.path.join(d, "m.tnnproto"), os.path.join(d, "m.tnnmodel")
+    ms.write_tnn_model(wl, proto, model, input_dtype=input_dtype)
+    insts = [rt.Instance(proto, model, device=rt.DEVICE_CUDA, precision=precision) for _ in range(2)]
+    monkeypatch.delenv("TNN_B200_HOST_CONVERT", raising=False)
+    want = _blocking(insts[0], wl.x, wl.mask_add)
+    n0 = rt.host_conversions()
+    monkeypatch.setenv("TNN_B200_HOST_CONVERT", "1")
+    assert np.array_equal(_blocking(insts[0], wl.x, wl.mask_add), want)
+    assert rt.host_conversions() == n0 + 2        # the activation in, the result out; the fp32 mask blob is a plain copy
+    keep = []
+    for pin in (False, True):
+        ins, outs = [], []
+        for _ in insts:
+            if pin:
+                px, pm, po = (rt.PinnedArray(a.shape, np.float32) for a in (wl.x, wl.mask_add, want))
+                px.array[...] = wl.x
+                pm.array[...] = wl.mask_add
+                po.array[...] = 0
+                keep += [px, pm, po]
+                ins.append([("x", px.array), ("mask", pm.array)])
+                outs.append([("", po.array)])
+            else:
+                ins.append([("x", np.array(wl.x, copy=True)), ("mask", np.array(wl.mask_add, copy=True))])
+                outs.append([("", np.zeros_like(want))])
+        assert rt.run_pipeline(insts, ins, outs, warmup=2, steps=5) > 0
+        for o in outs:
+            assert np.array_equal(o[0][1], want), pin
+    assert rt.host_conversions() == n0 + 2 + 2 * 2 * (2 + 5)   # two rounds of 7 steps, in and out
+    for p in keep:
+        p.free()
+    for i in insts:
+        i.close()

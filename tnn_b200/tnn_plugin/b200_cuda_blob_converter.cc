@@ -20,8 +20,13 @@
 #include <cuda_runtime.h>
 #include <omp.h>
 
+#include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
+#if defined(__x86_64__)
+#include <immintrin.h>
+#endif
 
 #include "b200_cuda_context.h"
 #include "b200_cuda_device.h"
@@ -37,12 +42,19 @@ namespace {
 
 constexpr size_t kChunkBytes = 8u << 20;
 
+// Worker threads for the host-side copies and conversions: up to 8 of the cores this process may run on.  (Not
+// omp_get_max_threads(): launchers such as torchrun export OMP_NUM_THREADS=1, which is about the framework's own
+// loops, and a num_threads clause takes precedence over it.)
+int HostThreads() {
+    int n = omp_get_num_procs();
+    return n > 8 ? 8 : (n < 1 ? 1 : n);
+}
+
 // memcpy with a few threads: one thread moves ~10 GB/s, a PCIe 5 x16 link 50+.
 void ParallelCopy(void* dst, const void* src, size_t bytes) {
     const size_t piece = 1u << 20;
     const long pieces  = static_cast<long>((bytes + piece - 1) / piece);
-    int threads        = omp_get_max_threads();
-    if (threads > 8) threads = 8;
+    const int threads  = HostThreads();
     if (pieces < 4 || threads < 2) {
         std::memcpy(dst, src, bytes);
         return;
@@ -53,6 +65,122 @@ void ParallelCopy(void* dst, const void* src, size_t bytes) {
         const size_t n   = off + piece <= bytes ? piece : bytes - off;
         std::memcpy(static_cast<char*>(dst) + off, static_cast<const char*>(src) + off, n);
     }
+}
+
+// ---- fp32 <-> half precision on the host cores (round to nearest even, as the device's conversion kernel does)
+inline uint16_t FloatToHalfBits(float f) {
+    uint32_t x;
+    std::memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    x &= 0x7fffffffu;
+    if (x >= 0x7f800000u) return static_cast<uint16_t>(sign | (x > 0x7f800000u ? 0x7e00u : 0x7c00u));   // NaN / inf
+    if (x >= 0x477ff000u) return static_cast<uint16_t>(sign | 0x7c00u);                                  // rounds to inf
+    if (x < 0x33000001u) return static_cast<uint16_t>(sign);                                            // rounds to zero
+    if (x < 0x38800000u) {                                                                               // subnormal half
+        const int shift   = 126 - static_cast<int>(x >> 23);          // 14 ... 24
+        const uint32_t m  = (x & 0x7fffffu) | 0x800000u;
+        const uint32_t q  = m >> shift, rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+        return static_cast<uint16_t>(sign | (q + ((rem > half || (rem == half && (q & 1u))) ? 1u : 0u)));
+    }
+    const uint32_t r = x + 0xfffu + ((x >> 13) & 1u);                  // normal: round the 13 dropped bits to even
+    return static_cast<uint16_t>(sign | ((r - 0x38000000u) >> 13));
+}
+inline float HalfBitsToFloat(uint16_t h) {
+    const uint32_t sign = (static_cast<uint32_t>(h) & 0x8000u) << 16;
+    uint32_t e = (h >> 10) & 0x1fu, m = h & 0x3ffu, x;
+    if (e == 0) {
+        if (m == 0) {
+            x = sign;
+        } else {
+            int s = 0;
+            while (!(m & 0x400u)) { m <<= 1; ++s; }
+            x = sign | (static_cast<uint32_t>(113 - s) << 23) | ((m & 0x3ffu) << 13);
+        }
+    } else if (e == 31) {
+        x = sign | 0x7f800000u | (m << 13);
+    } else {
+        x = sign | ((e + 112u) << 23) | (m << 13);
+    }
+    float f;
+    std::memcpy(&f, &x, 4);
+    return f;
+}
+inline uint16_t FloatToBf16Bits(float f) {
+    uint32_t x;
+    std::memcpy(&x, &f, 4);
+    if ((x & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((x >> 16) | 0x40u);   // NaN stays NaN
+    return static_cast<uint16_t>((x + 0x7fffu + ((x >> 16) & 1u)) >> 16);
+}
+
+#if defined(__x86_64__)
+__attribute__((target("avx2,f16c"))) void FloatToHalfRun(uint16_t* dst, const float* src, size_t n) {
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8)
+        _mm_storeu_si128(reinterpret_cast<__m128i*>(dst + i),
+                         _mm256_cvtps_ph(_mm256_loadu_ps(src + i), _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC));
+    for (; i < n; ++i) dst[i] = FloatToHalfBits(src[i]);
+}
+__attribute__((target("avx2,f16c"))) void HalfToFloatRun(float* dst, const uint16_t* src, size_t n) {
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8)
+        _mm256_storeu_ps(dst + i, _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(src + i))));
+    for (; i < n; ++i) dst[i] = HalfBitsToFloat(src[i]);
+}
+bool HaveF16C() {
+    static const bool have = __builtin_cpu_supports("f16c") && __builtin_cpu_supports("avx2");
+    return have;
+}
+#else
+bool HaveF16C() { return false; }
+void FloatToHalfRun(uint16_t*, const float*, size_t) {}
+void HalfToFloatRun(float*, const uint16_t*, size_t) {}
+#endif
+
+// `half_dtype`: B200_F16 or B200_BF16.  A few threads each take whole pieces.
+void ParallelToHalf(uint16_t* dst, const float* src, size_t n, int half_dtype) {
+    const size_t piece = 1u << 18;
+    const long pieces  = static_cast<long>((n + piece - 1) / piece);
+    const int threads  = pieces < 4 ? 1 : HostThreads();
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long i = 0; i < pieces; ++i) {
+        const size_t off = static_cast<size_t>(i) * piece;
+        const size_t m   = off + piece <= n ? piece : n - off;
+        if (half_dtype == B200_F16) {
+            if (HaveF16C()) FloatToHalfRun(dst + off, src + off, m);
+            else for (size_t k = 0; k < m; ++k) dst[off + k] = FloatToHalfBits(src[off + k]);
+        } else {
+            for (size_t k = 0; k < m; ++k) dst[off + k] = FloatToBf16Bits(src[off + k]);
+        }
+    }
+}
+void ParallelToFloat(float* dst, const uint16_t* src, size_t n, int half_dtype) {
+    const size_t piece = 1u << 18;
+    const long pieces  = static_cast<long>((n + piece - 1) / piece);
+    const int threads  = pieces < 4 ? 1 : HostThreads();
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long i = 0; i < pieces; ++i) {
+        const size_t off = static_cast<size_t>(i) * piece;
+        const size_t m   = off + piece <= n ? piece : n - off;
+        if (half_dtype == B200_F16) {
+            if (HaveF16C()) HalfToFloatRun(dst + off, src + off, m);
+            else for (size_t k = 0; k < m; ++k) dst[off + k] = HalfBitsToFloat(src[off + k]);
+        } else {
+            for (size_t k = 0; k < m; ++k) {
+                const uint32_t x = static_cast<uint32_t>(src[off + k]) << 16;
+                std::memcpy(dst + off + k, &x, 4);
+            }
+        }
+    }
+}
+
+// TNN_B200_HOST_CONVERT=1: fp32 host Mats of half-precision blobs are converted on the host cores, so that only half
+// the bytes cross the bus (several GPUs share the host's DMA path; with one GPU the plain copy is as fast and costs
+// no host time).  Read at every conversion.
+std::atomic<uint64_t> g_host_conversions{0};   // conversions that took the host-side route (for tests)
+
+bool HostConvertWanted() {
+    const char* e = std::getenv("TNN_B200_HOST_CONVERT");
+    return e != nullptr && e[0] != 0 && e[0] != '0';
 }
 
 bool IsPageLocked(const void* p) {
@@ -141,6 +269,27 @@ private:
         }
         const size_t bytes      = static_cast<size_t>(count) * mes;
         const bool need_convert = mdt != bdt;
+
+        // fp32 host Mat <-> half-precision blob, converted on the host cores (opt-in): half the bytes on the bus, no
+        // device staging, no conversion launch.  ConvertToMatAsync keeps the device route (its tail runs in a stream
+        // callback, which must stay off thread teams).
+        if (!mat_on_device && need_convert && mdt == B200_F32 && (bdt == B200_F16 || bdt == B200_BF16) &&
+            (!to_mat || blocking) && HostConvertWanted()) {
+            RETURN_ON_NEQ(to_mat ? ToHostAsFloat(static_cast<float*>(image.GetData()), blob_ptr, count, bdt, stream)
+                                 : FromHostAsHalf(blob_ptr, static_cast<const float*>(image.GetData()), count, bdt, stream),
+                          TNN_OK);
+            if (blocking) {
+                if (cudaStreamSynchronize(stream) != cudaSuccess) {
+                    cudaGetLastError();
+                    return Status(TNNERR_CUDA_SYNC_ERROR, "stream sync failed");
+                }
+                if (to_mat) {
+                    if (B200CudaContext* ctx = B200CudaContext::FromCommandQueue(command_queue))
+                        RETURN_ON_NEQ(ctx->CheckStatusAfterSync(), TNN_OK);
+                }
+            }
+            return TNN_OK;
+        }
 
         // The Mat-typed image of the data on the device: the blob itself, or the staging buffer next to it.
         char* dev_side = blob_ptr;
@@ -242,6 +391,59 @@ private:
         return TNN_OK;
     }
 
+    // fp32 host Mat -> half-precision blob: chunks are converted into the page-locked staging buffer by the host cores
+    // and copied from there, one chunk's conversion running while the previous chunk is on the bus.
+    Status FromHostAsHalf(char* blob_ptr, const float* src, int64_t count, int half_dtype, cudaStream_t stream) {
+        const size_t n = static_cast<size_t>(count);
+        ++g_host_conversions;
+        RETURN_ON_NEQ(EnsurePinned(n * 2), TNN_OK);
+        WaitStageFree();
+        const size_t chunk = kChunkBytes / 4;   // elements
+        uint16_t* stage    = static_cast<uint16_t*>(pinned_);
+        for (size_t off = 0; off < n; off += chunk) {
+            const size_t m = off + chunk <= n ? chunk : n - off;
+            ParallelToHalf(stage + off, src + off, m, half_dtype);
+            RETURN_ON_NEQ(Copy(blob_ptr + off * 2, stage + off, m * 2, cudaMemcpyHostToDevice, stream), TNN_OK);
+        }
+        return MarkStageBusy(stream);
+    }
+
+    // half-precision blob -> fp32 host Mat (blocking): every chunk is converted out of the staging buffer as soon as it
+    // has landed there.
+    Status ToHostAsFloat(float* dst, const char* blob_ptr, int64_t count, int half_dtype, cudaStream_t stream) {
+        const size_t n = static_cast<size_t>(count);
+        ++g_host_conversions;
+        RETURN_ON_NEQ(EnsurePinned(n * 2), TNN_OK);
+        WaitStageFree();
+        const size_t chunk  = kChunkBytes / 4;   // elements
+        const size_t chunks = (n + chunk - 1) / chunk;
+        while (chunk_done_.size() < chunks) {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                return Status(TNNERR_CUDA_SYNC_ERROR, "cudaEventCreate failed");
+            }
+            chunk_done_.push_back(e);
+        }
+        uint16_t* stage = static_cast<uint16_t*>(pinned_);
+        for (size_t c = 0; c < chunks; ++c) {
+            const size_t off = c * chunk;
+            const size_t m   = off + chunk <= n ? chunk : n - off;
+            RETURN_ON_NEQ(Copy(stage + off, blob_ptr + off * 2, m * 2, cudaMemcpyDeviceToHost, stream), TNN_OK);
+            cudaEventRecord(chunk_done_[c], stream);
+        }
+        for (size_t c = 0; c < chunks; ++c) {
+            const size_t off = c * chunk;
+            const size_t m   = off + chunk <= n ? chunk : n - off;
+            if (cudaEventSynchronize(chunk_done_[c]) != cudaSuccess) {
+                cudaGetLastError();
+                return Status(TNNERR_CUDA_SYNC_ERROR, "event sync failed");
+            }
+            ParallelToFloat(dst + off, stage + off, m, half_dtype);
+        }
+        return TNN_OK;
+    }
+
     Status EnsurePinned(size_t bytes) {
         if (bytes <= pinned_bytes_ && pinned_) return TNN_OK;
         WaitStageFree();
@@ -305,6 +507,40 @@ private:
     std::vector<cudaEvent_t> chunk_done_;
     HostCopyJob job_{nullptr, nullptr, 0};
 };
+
+}  // namespace TNN_NS
+
+// The converter's host-side fp32 <-> half conversion, callable without a GPU (declared in include/tnn_b200_plugin.h).
+extern "C" __attribute__((visibility("default"))) int tnnb200_host_convert(const float* src, uint64_t n, int half_dtype,
+                                                                            int force_scalar, uint16_t* half_out,
+                                                                            float* back_out) {
+    using namespace TNN_NS;
+    if (!src || !half_out || (half_dtype != B200_F16 && half_dtype != B200_BF16)) return -1;
+    if (force_scalar) {
+        for (uint64_t i = 0; i < n; ++i)
+            half_out[i] = half_dtype == B200_F16 ? FloatToHalfBits(src[i]) : FloatToBf16Bits(src[i]);
+        if (back_out) {
+            for (uint64_t i = 0; i < n; ++i) {
+                if (half_dtype == B200_F16) {
+                    back_out[i] = HalfBitsToFloat(half_out[i]);
+                } else {
+                    const uint32_t x = static_cast<uint32_t>(half_out[i]) << 16;
+                    std::memcpy(back_out + i, &x, 4);
+                }
+            }
+        }
+        return 0;
+    }
+    ParallelToHalf(half_out, src, static_cast<size_t>(n), half_dtype);
+    if (back_out) ParallelToFloat(back_out, half_out, static_cast<size_t>(n), half_dtype);
+    return HaveF16C() ? 1 : 0;
+}
+
+extern "C" __attribute__((visibility("default"))) uint64_t tnnb200_host_conversions() {
+    return TNN_NS::g_host_conversions.load();
+}
+
+namespace TNN_NS {
 
 DECLARE_BLOB_CONVERTER_CREATER(B200Cuda);
 REGISTER_BLOB_CONVERTER(B200Cuda, DEVICE_CUDA);

@@ -112,6 +112,10 @@ def load():
         plugin.tnnb200_selftest_range_arena.restype = ctypes.c_int
         plugin.tnnb200_selftest_range_arena.argtypes = [ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_char_p,
                                                         ctypes.c_int]
+        plugin.tnnb200_host_conversions.restype = ctypes.c_uint64
+        plugin.tnnb200_host_convert.restype = ctypes.c_int
+        plugin.tnnb200_host_convert.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
+                                                ctypes.c_void_p, ctypes.c_void_p]
         plugin.tnnb200_graph_counters.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint64)]
         plugin.tnnb200_host_alloc.restype = ctypes.c_void_p
         plugin.tnnb200_host_alloc.argtypes = [ctypes.c_size_t]
@@ -195,6 +199,26 @@ def selftest_range_arena(seed, steps, pooled=True):
     err = ctypes.create_string_buffer(256)
     rc = plugin.tnnb200_selftest_range_arena(int(seed), int(steps), 1 if pooled else 0, err, len(err))
     return int(rc), err.value.decode()
+
+
+def host_conversions():
+    """Mat <-> blob conversions of this process that took the converter's host-side route."""
+    _, plugin = load()
+    return int(plugin.tnnb200_host_conversions())
+
+
+def host_convert(src, bf16=False, force_scalar=False):
+    """The blob converter's host-side fp32 -> half conversion and back: (uint16 bit patterns, fp32 round trip, vector
+    path used)."""
+    _, plugin = load()
+    a = np.ascontiguousarray(src, dtype=np.float32).ravel()
+    half = np.empty(a.shape, np.uint16)
+    back = np.empty(a.shape, np.float32)
+    rc = plugin.tnnb200_host_convert(a.ctypes.data, a.size, 1 if bf16 else 0, 1 if force_scalar else 0,
+                                     half.ctypes.data, back.ctypes.data)
+    if rc < 0:
+        raise RuntimeError("tnnb200_host_convert failed")
+    return half, back, bool(rc)
 
 
 class PinnedArray:
