@@ -437,7 +437,6 @@ def run_ours(args):
 
     e2e_steps = max(args.steps, int(np.ceil(args.min_seconds * 1e3 / (ms_total / (blocks * args.steps)))))
     e2e_s, h2d, d2h, e2e_same = e2e_run(insts, wl.x, np.float32, True, e2e_steps)
-    hostconv_s, hostconv_same = None, None
     pageable_steps = max(4, min(e2e_steps, args.steps))
     pageable_s, _, _, _ = e2e_run(insts[:1], wl.x, np.float32, False, pageable_steps)
     replica.close()
@@ -453,15 +452,6 @@ def run_ours(args):
             inst.forward()
             inst.forward()
         half_s, h2d16, d2h16, _ = e2e_run(rep16.insts, x16, np.float16, True, e2e_steps)
-        # Several GPUs share the host's DMA path, and fp32 Mats are twice the bytes: the same instances fed fp32 Mats
-        # with the converter's host-side conversion switched on (TNN_B200_HOST_CONVERT=1: the host cores turn fp32 into
-        # half precision and back, half the bytes cross the bus).
-        if world > 1:
-            os.environ["TNN_B200_HOST_CONVERT"] = "1"
-            try:
-                hostconv_s, _, _, hostconv_same = e2e_run(rep16.insts, wl.x, np.float32, True, e2e_steps)
-            finally:
-                os.environ.pop("TNN_B200_HOST_CONVERT", None)
         rep16.close()
 
     # ---- roofline of the dominant kernel (the GEMM): the step's GEMM launches alone, in their order, with every
@@ -562,8 +552,7 @@ def run_ours(args):
     ln_ms = statistics.mean(kernel_ms["layernorm"])
 
     # ---- reduce over ranks (the job's time is the slowest rank's)
-    ms_t = torch.tensor([ms_total, e2e_s * 1e3, pageable_s * 1e3, (half_s or 0.0) * 1e3, (hostconv_s or 0.0) * 1e3],
-                        dtype=torch.float64, device=dev)
+    ms_t = torch.tensor([ms_total, e2e_s * 1e3, pageable_s * 1e3, (half_s or 0.0) * 1e3], dtype=torch.float64, device=dev)
     ms_t = reduce_max_over_ranks(ms_t, world)
     ms_total_max = float(ms_t[0])
     timed_steps = blocks * args.steps
@@ -571,7 +560,6 @@ def run_ours(args):
     e2e_value = world * B * e2e_steps / (float(ms_t[1]) / 1e3)
     pageable_value = world * B * pageable_steps / (float(ms_t[2]) / 1e3)
     half_value = (world * B * e2e_steps / (float(ms_t[3]) / 1e3)) if half_s else None
-    hostconv_value = (world * B * e2e_steps / (float(ms_t[4]) / 1e3)) if hostconv_s else None
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -625,11 +613,6 @@ def run_ours(args):
             "e2e": e2e_line,
             e2e_other[0]: e2e_other[1],
             "e2e_limiter": limiter,
-            "e2e_fp32_host_convert": None if hostconv_value is None else {
-                "value": hostconv_value, "unit": UNIT, "steps": e2e_steps, "output_equals_blocking_forward": hostconv_same,
-                "note": "fp32 Mats in and out of the model whose input is declared half, with TNN_B200_HOST_CONVERT=1: the "
-                        "plug-in's converter turns fp32 into half precision on the host cores (and back), so that half "
-                        "the bytes cross the bus"},
             "e2e_pageable": {"value": pageable_value, "unit": UNIT, "steps": pageable_steps,
                              "note": "the same loop with ONE instance and pageable fp32 host Mats (what an unchanged "
                                      "single-instance caller does): the converter stages through page-locked memory"},
